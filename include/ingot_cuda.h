@@ -1,0 +1,239 @@
+/*
+ * ingot_cuda.h — C ABI of libingot_cuda.so, the sm_100a (B200) implementation
+ * of ingot's decode hot path: block-quantised weights (GGUF Q4_0, Q8_0, Q4_K,
+ * Q6_K, plus F32/F16/BF16), fused dequantise-and-dot GEMV, gate/up + GLU,
+ * expert-routed GEMV, top-k routing, expert combine, and the dequant-GEMM.
+ *
+ * The boundary it replaces is the reference's Rust `Gpu` type ("the only
+ * unsafe boundary", src/metal.rs:1) together with the operator layer in
+ * src/metal_generic.rs and the data model in src/gguf.rs / src/weights.rs.
+ * Each entry point cites the reference function it stands in for.  All
+ * pointers are plain host or device addresses; there are no C++ or framework
+ * types in any signature.
+ *
+ * Conventions (identical to the reference's kernel parameter block `p[]`,
+ * kernels/generic.metal:294-297, src/metal_generic.rs:195-202):
+ *   cols    K, the contiguous dimension of a weight row (Tensor.dims[0])
+ *   rows    N, output rows of one matrix (Tensor.dims[1])
+ *   stride  bytes of one weight row = cols / block * block_bytes
+ *   kind    GGML type id: 0 F32, 1 F16, 2 Q4_0, 8 Q8_0, 12 Q4_K, 14 Q6_K, 30 BF16
+ *   expert  index into experts stacked as [expert][rows][stride]
+ *   x       activations [tokens][cols]; y outputs [tokens][rows], float32
+ *   x_kind  type of x: 0 (float32, what the reference uses) or 30 (bfloat16)
+ * Operators take DEVICE pointers and are asynchronous on the handle's stream;
+ * the *_host conveniences take HOST pointers and block.
+ *
+ * Threading: a handle is owned by one host thread, like the reference's
+ * !Send/!Sync `Gpu` (src/metal.rs:193-208).
+ *
+ * Errors: every call returns an ingot_status.  A device failure is sticky:
+ * later calls on the handle return INGOT_DEVICE ("requires reload"), matching
+ * src/metal.rs:663-671,1349-1353.
+ */
+#ifndef INGOT_CUDA_H
+#define INGOT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define INGOT_API __attribute__((visibility("default")))
+#else
+#define INGOT_API
+#endif
+
+typedef int32_t ingot_status;
+enum {
+    INGOT_OK = 0,
+    INGOT_INVALID = 1,      /* io::ErrorKind::InvalidData: shape/layout/bounds (src/lib.rs:39-41) */
+    INGOT_UNSUPPORTED = 2,  /* "no kernel for this type": Ok(None)/false in src/metal_generic.rs */
+    INGOT_DEVICE = 3,       /* io::Error::other: CUDA failure; sticky */
+    INGOT_EOF = 4,          /* io::ErrorKind::UnexpectedEof (src/gguf.rs:359-362) */
+    INGOT_INTERRUPTED = 5,  /* io::ErrorKind::Interrupted (src/generic.rs:52-54) */
+    INGOT_TIMEOUT = 6       /* a bounded device-side wait ran out */
+};
+
+enum {
+    INGOT_KIND_F32 = 0, INGOT_KIND_F16 = 1, INGOT_KIND_Q4_0 = 2, INGOT_KIND_Q8_0 = 8,
+    INGOT_KIND_Q4_K = 12, INGOT_KIND_Q6_K = 14, INGOT_KIND_BF16 = 30
+};
+
+typedef struct ingot_gpu ingot_gpu;      /* opaque; the reference's `Gpu` */
+typedef struct ingot_graph ingot_graph;  /* opaque; a recorded `Command` */
+
+/* ---- data model --------------------------------------------------------- */
+
+/* geometry(kind) -> (block elements, block bytes): src/gguf.rs:470-491.
+ * INGOT_UNSUPPORTED for a type outside this path. */
+INGOT_API ingot_status ingot_geometry(uint32_t kind, uint32_t *block, uint32_t *bytes);
+
+/* Row stride and total bytes of a tensor of `cols` x `rows` x `count`
+ * (stride/bytes derivation in src/gguf.rs:152-161); INGOT_INVALID when cols is
+ * not a whole number of blocks or a product overflows. */
+INGOT_API ingot_status ingot_tensor_layout(uint32_t kind, uint64_t cols, uint64_t rows, uint64_t count,
+                                           uint64_t *stride, uint64_t *bytes);
+
+/* ---- handle ------------------------------------------------------------- */
+
+/* Gpu::new (src/metal.rs:238-533): binds CUDA device `device`, creates the
+ * stream and the device status word.  INGOT_DEVICE when the device is not an
+ * sm_100 part or CUDA fails. */
+INGOT_API ingot_status ingot_gpu_create(int32_t device, ingot_gpu **out);
+INGOT_API void ingot_gpu_destroy(ingot_gpu *gpu);
+
+/* Text of the last error on this handle (never NULL). */
+INGOT_API const char *ingot_last_error(const ingot_gpu *gpu);
+
+/* Runs later operators on a caller-owned cudaStream_t (NULL restores the
+ * handle's own stream).  The Command <-> stream correspondence:
+ * src/metal.rs:659-673. */
+INGOT_API ingot_status ingot_gpu_set_stream(ingot_gpu *gpu, void *cuda_stream);
+
+/* Options: INGOT_OPT_PDL (default 1) launches kernels with programmatic
+ * dependent launch so a kernel's weight prefetch overlaps its predecessor's
+ * tail; INGOT_OPT_FORCE_PLAIN (default 0) routes every GEMV through the plain
+ * one-warp-per-row kernel (a test hook). */
+enum { INGOT_OPT_PDL = 1, INGOT_OPT_FORCE_PLAIN = 2 };
+INGOT_API ingot_status ingot_gpu_set_option(ingot_gpu *gpu, int32_t option, int32_t value);
+
+/* Command::wait / Gpu::complete (src/metal.rs:1224-1235): blocks until the
+ * stream drains, then reports CUDA errors and the device status word
+ * (INGOT_TIMEOUT, INGOT_INVALID for an out-of-range expert id or a non-finite
+ * router logit). */
+INGOT_API ingot_status ingot_synchronize(ingot_gpu *gpu);
+
+/* ---- buffers (Gpu::bytes / floats / zeros / output / read_f32:
+ *      src/metal.rs:1251-1333, 649-658) ---------------------------------- */
+
+INGOT_API ingot_status ingot_buffer_alloc(ingot_gpu *gpu, size_t bytes, void **device_ptr);
+INGOT_API ingot_status ingot_buffer_free(ingot_gpu *gpu, void *device_ptr);
+/* host -> device, asynchronous on the handle's stream when `host` is pinned */
+INGOT_API ingot_status ingot_buffer_upload(ingot_gpu *gpu, void *device_ptr, const void *host, size_t bytes);
+/* device -> host; returns after the copy has completed */
+INGOT_API ingot_status ingot_buffer_read(ingot_gpu *gpu, void *host, const void *device_ptr, size_t bytes);
+INGOT_API ingot_status ingot_buffer_zero(ingot_gpu *gpu, void *device_ptr, size_t bytes);
+/* Page-locked host memory for uploads/readbacks. */
+INGOT_API ingot_status ingot_host_alloc(ingot_gpu *gpu, size_t bytes, void **host_ptr);
+INGOT_API ingot_status ingot_host_free(ingot_gpu *gpu, void *host_ptr);
+
+/* Gpu::load_weight (src/metal.rs:546-582) for a discrete GPU: validates the
+ * tensor layout (kind, cols, rows, count, stride) against `bytes`, allocates
+ * HBM and copies the GGUF bytes unchanged.  Replaces the no-copy mmap. */
+INGOT_API ingot_status ingot_weight_upload(ingot_gpu *gpu, const void *host, uint32_t kind, uint64_t cols,
+                                           uint64_t rows, uint64_t count, size_t bytes, void **device_ptr);
+
+/* ---- operators on device buffers ---------------------------------------- */
+
+/* read_rows (kernels/qwen.metal:35): y[r][j] = weight_at(row r, j) for
+ * `rows` rows (all stacked experts); bit-exact. */
+INGOT_API ingot_status ingot_dequant_rows(ingot_gpu *gpu, const void *w, uint32_t cols, uint64_t rows,
+                                          uint32_t stride, uint32_t kind, float *y);
+
+/* Gpu::matmul (src/metal.rs:877-1107) / Gpu::generic_project
+ * (src/metal_generic.rs:175-228) / Gpu::matvec (src/metal.rs:846-875):
+ * y[t][r] = sum_j W[expert][r][j] x[t][j] for `count` tokens.  count <= 4 runs
+ * the fp32 GEMV; larger counts run in groups of four until the tensor-core
+ * GEMM (ingot_gemm) is asked for explicitly. */
+INGOT_API ingot_status ingot_matmul(ingot_gpu *gpu, const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
+                                    uint32_t kind, uint32_t expert, const void *x, uint32_t x_kind,
+                                    uint32_t count, float *y);
+
+/* Gpu::generic_gate_up (src/metal_generic.rs:231-261): y[t][r] =
+ * glu(gate x, up x); gelu != 0 selects tanh-GeLU, else SiLU. */
+INGOT_API ingot_status ingot_gate_up(ingot_gpu *gpu, const void *gate, const void *up, uint32_t cols,
+                                     uint32_t rows, uint32_t stride, uint32_t kind, const void *x,
+                                     uint32_t x_kind, uint32_t count, uint32_t gelu, float *y);
+
+/* Gpu::generic_routed (src/metal_generic.rs:298-329) and the generic-format
+ * project_routed_batch (kernels/qwen.metal:93-112): for each pair p,
+ * y[p] = W[ids[p]] x[per_pair ? p : p / top].  `experts` bounds ids. */
+INGOT_API ingot_status ingot_routed(ingot_gpu *gpu, const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
+                                    uint32_t kind, uint32_t experts, const void *x, uint32_t x_kind,
+                                    const uint32_t *ids, uint32_t per_pair, uint32_t top, uint32_t pairs,
+                                    float *y);
+
+/* Gpu::generic_routed_gate_up (src/metal_generic.rs:264-296):
+ * y[p] = silu(gate[ids[p]] x[p / top]) * (up[ids[p]] x[p / top]). */
+INGOT_API ingot_status ingot_routed_gate_up(ingot_gpu *gpu, const void *gate, const void *up, uint32_t cols,
+                                            uint32_t rows, uint32_t stride, uint32_t kind, uint32_t experts,
+                                            const void *x, uint32_t x_kind, const uint32_t *ids, uint32_t top,
+                                            uint32_t pairs, float *y);
+
+/* route_topk (kernels/generic.metal:479-494; CPU route(): src/lib.rs:43-60):
+ * ids[t][k], weights[t][k] for k < top; ties go to the lowest expert id.
+ * experts <= 512.  top == 0 or top > experts is INGOT_INVALID; a non-finite
+ * logit is reported by ingot_synchronize as INGOT_INVALID. */
+INGOT_API ingot_status ingot_route_topk(ingot_gpu *gpu, const float *logits, uint32_t experts, uint32_t top,
+                                        uint32_t tokens, uint32_t *ids, float *weights);
+
+/* moe_sum (kernels/generic.metal:17): y[t][j] = sum_e routed[t*top+e][j] *
+ * weights[t*top+e], in route order.  width % 4 == 0. */
+INGOT_API ingot_status ingot_moe_sum(ingot_gpu *gpu, const float *routed, const float *weights, uint32_t width,
+                                     uint32_t top, uint32_t tokens, float *y);
+
+/* Gpu::activation (src/metal.rs:1172-1197; swiglu kernels/moe.metal:405-410,
+ * gelu_mul kernels/generic_arch.metal:7-10). */
+INGOT_API ingot_status ingot_activation(ingot_gpu *gpu, const float *gate, const float *up, uint64_t n,
+                                        uint32_t gelu, float *y);
+
+/* Gpu::merge (src/metal.rs:1199-1223; combine kernels/moe.metal:412-422):
+ * y[j] = sum_e routed[e][j] * weights[e] + shared[j] * sigmoid(shared_logit[0]). */
+INGOT_API ingot_status ingot_merge(ingot_gpu *gpu, const float *routed, const float *shared,
+                                   const float *weights, const float *shared_logit, uint32_t width,
+                                   uint32_t top, float *y);
+
+/* Gpu::add_rms (src/metal_generic.rs; kernel kernels/generic.metal:390-404):
+ * per row s = a + b (when add), y = s * rsqrt(mean(s^2) + eps) * w.  `w`, `s`,
+ * `y`, `y_bf16` may be NULL; y_bf16 receives y rounded to bfloat16. */
+INGOT_API ingot_status ingot_add_rms(ingot_gpu *gpu, const float *a, const float *b, const float *w, float *s,
+                                     float *y, void *y_bf16, uint32_t width, uint32_t rows, float eps,
+                                     uint32_t add);
+
+/* expert_layout + expert_pairs (kernels/prefill.metal:7-35): stable
+ * expert-major grouping of `pairs` ids.  layout [experts][2] = (count, first),
+ * tiles [tile_capacity][4] = (expert, first, n <= 32, mode), packed[pos] =
+ * pair index, inverse[pair] = pos. */
+INGOT_API ingot_status ingot_expert_layout(ingot_gpu *gpu, const uint32_t *ids, uint32_t pairs,
+                                           uint32_t experts, uint32_t tile_capacity, uint32_t *layout,
+                                           uint32_t *tiles, uint32_t *packed, uint32_t *inverse);
+
+/* combine_packed without the shared expert (kernels/prefill.metal:39). */
+INGOT_API ingot_status ingot_combine_packed(ingot_gpu *gpu, const float *routed, const float *weights,
+                                            const uint32_t *inverse, uint32_t width, uint32_t top,
+                                            uint32_t tokens, float *y);
+
+/* float32 -> bfloat16 (round to nearest even) for activations. */
+INGOT_API ingot_status ingot_convert_bf16(ingot_gpu *gpu, const float *x, uint64_t n, void *y_bf16);
+
+/* ---- command recording (Command: src/metal.rs:659-673; a whole decode step
+ *      is one command buffer, src/generic.rs:701-704) ---------------------- */
+
+/* Starts recording the operators issued on this handle into a CUDA graph. */
+INGOT_API ingot_status ingot_command_begin(ingot_gpu *gpu);
+/* Ends recording; the graph can be replayed any number of times. */
+INGOT_API ingot_status ingot_command_end(ingot_gpu *gpu, ingot_graph **out);
+INGOT_API ingot_status ingot_command_submit(ingot_gpu *gpu, ingot_graph *graph);
+INGOT_API void ingot_command_destroy(ingot_graph *graph);
+
+/* ---- host-vector conveniences (the reference's public parity hooks) ------ */
+
+/* Gpu::dequant(&Matrix) (src/metal.rs:1581-1601) with validate_matrix
+ * (src/metal.rs:1602-1621): data is `count` experts of rows x stride bytes. */
+INGOT_API ingot_status ingot_dequant_host(ingot_gpu *gpu, const void *data, size_t data_bytes, uint64_t cols,
+                                          uint64_t rows, uint64_t count, uint32_t kind, uint64_t stride,
+                                          float *out);
+
+/* Gpu::project(&Matrix, &[f32]) (src/metal.rs:1622-1632): count must be 1,
+ * input finite and of length cols. */
+INGOT_API ingot_status ingot_project_host(ingot_gpu *gpu, const void *data, size_t data_bytes, uint64_t cols,
+                                          uint64_t rows, uint64_t count, uint32_t kind, uint64_t stride,
+                                          const float *input, size_t input_len, float *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INGOT_CUDA_H */

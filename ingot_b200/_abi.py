@@ -1,0 +1,88 @@
+"""ctypes bindings of libingot_cuda.so (include/ingot_cuda.h).
+
+Loading fails loudly when the library has not been built: there is no CPU or
+framework fallback for any operator.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libingot_cuda.so")
+
+OK, INVALID, UNSUPPORTED, DEVICE, EOF, INTERRUPTED, TIMEOUT = range(7)
+OPT_PDL, OPT_FORCE_PLAIN = 1, 2
+
+vp, u32, u64, i32, f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_float
+sz = C.c_size_t
+
+# name -> argument types (every function returns ingot_status unless noted)
+SIGNATURES = {
+    "ingot_geometry": [u32, C.POINTER(u32), C.POINTER(u32)],
+    "ingot_tensor_layout": [u32, u64, u64, u64, C.POINTER(u64), C.POINTER(u64)],
+    "ingot_gpu_create": [i32, C.POINTER(vp)],
+    "ingot_gpu_set_stream": [vp, vp],
+    "ingot_gpu_set_option": [vp, i32, i32],
+    "ingot_synchronize": [vp],
+    "ingot_buffer_alloc": [vp, sz, C.POINTER(vp)],
+    "ingot_buffer_free": [vp, vp],
+    "ingot_buffer_upload": [vp, vp, vp, sz],
+    "ingot_buffer_read": [vp, vp, vp, sz],
+    "ingot_buffer_zero": [vp, vp, sz],
+    "ingot_host_alloc": [vp, sz, C.POINTER(vp)],
+    "ingot_host_free": [vp, vp],
+    "ingot_weight_upload": [vp, vp, u32, u64, u64, u64, sz, C.POINTER(vp)],
+    "ingot_dequant_rows": [vp, vp, u32, u64, u32, u32, vp],
+    "ingot_matmul": [vp, vp, u32, u32, u32, u32, u32, vp, u32, u32, vp],
+    "ingot_gate_up": [vp, vp, vp, u32, u32, u32, u32, vp, u32, u32, u32, vp],
+    "ingot_routed": [vp, vp, u32, u32, u32, u32, u32, vp, u32, vp, u32, u32, u32, vp],
+    "ingot_routed_gate_up": [vp, vp, vp, u32, u32, u32, u32, u32, vp, u32, vp, u32, u32, vp],
+    "ingot_route_topk": [vp, vp, u32, u32, u32, vp, vp],
+    "ingot_moe_sum": [vp, vp, vp, u32, u32, u32, vp],
+    "ingot_activation": [vp, vp, vp, u64, u32, vp],
+    "ingot_merge": [vp, vp, vp, vp, vp, u32, u32, vp],
+    "ingot_add_rms": [vp, vp, vp, vp, vp, vp, vp, u32, u32, f32, u32],
+    "ingot_expert_layout": [vp, vp, u32, u32, u32, vp, vp, vp, vp],
+    "ingot_combine_packed": [vp, vp, vp, vp, u32, u32, u32, vp],
+    "ingot_convert_bf16": [vp, vp, u64, vp],
+    "ingot_command_begin": [vp],
+    "ingot_command_end": [vp, C.POINTER(vp)],
+    "ingot_command_submit": [vp, vp],
+    "ingot_dequant_host": [vp, vp, sz, u64, u64, u64, u32, u64, vp],
+    "ingot_project_host": [vp, vp, sz, u64, u64, u64, u32, u64, vp, sz, vp],
+}
+# functions with another return type
+OTHER = {
+    "ingot_gpu_destroy": (None, [vp]),
+    "ingot_last_error": (C.c_char_p, [vp]),
+    "ingot_command_destroy": (None, [vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """The shared library, with argument types attached."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m ingot_b200.build` "
+            "(needs nvcc). ingot_b200 has no CPU fallback.")
+    lib = C.CDLL(LIB_PATH)
+    for name, args in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = i32
+        fn.argtypes = args
+    for name, (res, args) in OTHER.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def exported_names() -> list[str]:
+    return sorted(list(SIGNATURES) + list(OTHER))

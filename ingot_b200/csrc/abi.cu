@@ -1,0 +1,509 @@
+// C ABI of libingot_cuda.so: the handle, buffers, argument validation, and
+// the mapping from CUDA / device-status errors to ingot_status codes.
+#include "../../include/ingot_cuda.h"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+#include <string>
+#include <vector>
+
+#include "gemv_core.cuh"
+#include "kernels.h"
+
+using namespace ingot;
+
+struct ingot_gpu {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    int *status = nullptr;            // device status word
+    int *status_host = nullptr;       // pinned mirror
+    uint32_t sm_count = 0;
+    bool failed = false;              // sticky device failure
+    bool pdl = true;
+    bool force_plain = false;
+    bool capturing = false;
+    std::string error;
+};
+
+struct ingot_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+namespace {
+
+ingot_status fail(ingot_gpu *g, ingot_status code, const std::string &msg) {
+    if (g) g->error = msg;
+    return code;
+}
+
+ingot_status cuda_fail(ingot_gpu *g, cudaError_t e, const char *what) {
+    if (g) {
+        g->failed = true;
+        g->error = std::string(what) + ": " + cudaGetErrorString(e) + " (device failure; requires reload)";
+    }
+    return INGOT_DEVICE;
+}
+
+// Common entry check: handle present, not failed, right device current.
+ingot_status enter(ingot_gpu *g) {
+    if (!g) return INGOT_INVALID;
+    if (g->failed) return fail(g, INGOT_DEVICE, "device failed earlier; requires reload");
+    cudaError_t e = cudaSetDevice(g->device);
+    if (e != cudaSuccess) return cuda_fail(g, e, "cudaSetDevice");
+    return INGOT_OK;
+}
+
+LaunchCtx ctx_of(const ingot_gpu *g) {
+    LaunchCtx c;
+    c.stream = g->stream;
+    c.status = g->status;
+    c.sm_count = g->sm_count;
+    c.pdl = g->pdl;
+    c.force_plain = g->force_plain;
+    return c;
+}
+
+ingot_status after_launch(ingot_gpu *g, cudaError_t e, const char *what) {
+    if (e == cudaErrorInvalidValue) return fail(g, INGOT_INVALID, std::string(what) + ": invalid launch arguments");
+    if (e != cudaSuccess) return cuda_fail(g, e, what);
+    return INGOT_OK;
+}
+
+bool x_kind_ok(uint32_t k) { return k == INGOT_KIND_F32 || k == INGOT_KIND_BF16; }
+
+// validate_matrix (src/metal.rs:1602-1621) on the integer parameters.
+ingot_status check_matrix(ingot_gpu *g, uint32_t kind, uint64_t cols, uint64_t rows, uint64_t stride) {
+    uint32_t block, bytes;
+    if (!geometry(kind, block, bytes)) return fail(g, INGOT_UNSUPPORTED, "GGML type " + std::to_string(kind) + " is unsupported");
+    if (cols == 0 || rows == 0 || cols % block || stride != cols / block * bytes || cols > 0xffffffffull ||
+        rows > 0xffffffffull || stride > 0xffffffffull)
+        return fail(g, INGOT_INVALID, "invalid quantized matrix layout");
+    return INGOT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+ingot_status ingot_geometry(uint32_t kind, uint32_t *block, uint32_t *bytes) {
+    uint32_t b, s;
+    if (!block || !bytes) return INGOT_INVALID;
+    if (!geometry(kind, b, s)) return INGOT_UNSUPPORTED;
+    *block = b;
+    *bytes = s;
+    return INGOT_OK;
+}
+
+ingot_status ingot_tensor_layout(uint32_t kind, uint64_t cols, uint64_t rows, uint64_t count, uint64_t *stride,
+                                 uint64_t *bytes) {
+    uint32_t b, s;
+    if (!stride || !bytes) return INGOT_INVALID;
+    if (!geometry(kind, b, s)) return INGOT_UNSUPPORTED;
+    if (cols == 0 || rows == 0 || count == 0 || cols % b) return INGOT_INVALID;
+    unsigned __int128 st = (unsigned __int128)(cols / b) * s;
+    unsigned __int128 total = st * rows;
+    if (st > 0xffffffffffffffffull || total > 0xffffffffffffffffull) return INGOT_INVALID;
+    total *= count;
+    if (total > 0xffffffffffffffffull) return INGOT_INVALID;
+    *stride = (uint64_t)st;
+    *bytes = (uint64_t)total;
+    return INGOT_OK;
+}
+
+ingot_status ingot_gpu_create(int32_t device, ingot_gpu **out) {
+    if (!out) return INGOT_INVALID;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) return INGOT_DEVICE;
+    if (cudaSetDevice(device) != cudaSuccess) return INGOT_DEVICE;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return INGOT_DEVICE;
+    if (prop.major != 10) return INGOT_DEVICE;       // the kernels are built for sm_100a only
+    ingot_gpu *g = new (std::nothrow) ingot_gpu();
+    if (!g) return INGOT_DEVICE;
+    g->device = device;
+    g->sm_count = (uint32_t)prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&g->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc(&g->status, 64) != cudaSuccess || cudaMemset(g->status, 0, 64) != cudaSuccess ||
+        cudaHostAlloc(&g->status_host, 64, cudaHostAllocDefault) != cudaSuccess) {
+        ingot_gpu_destroy(g);
+        return INGOT_DEVICE;
+    }
+    g->stream = g->own_stream;
+    *out = g;
+    return INGOT_OK;
+}
+
+void ingot_gpu_destroy(ingot_gpu *g) {
+    if (!g) return;
+    cudaSetDevice(g->device);
+    if (g->own_stream) { cudaStreamSynchronize(g->own_stream); cudaStreamDestroy(g->own_stream); }
+    if (g->status) cudaFree(g->status);
+    if (g->status_host) cudaFreeHost(g->status_host);
+    delete g;
+}
+
+const char *ingot_last_error(const ingot_gpu *g) { return g ? g->error.c_str() : "null handle"; }
+
+ingot_status ingot_gpu_set_stream(ingot_gpu *g, void *cuda_stream) {
+    if (!g) return INGOT_INVALID;
+    if (g->capturing) return fail(g, INGOT_INVALID, "cannot change stream while recording");
+    g->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : g->own_stream;
+    return INGOT_OK;
+}
+
+ingot_status ingot_gpu_set_option(ingot_gpu *g, int32_t option, int32_t value) {
+    if (!g) return INGOT_INVALID;
+    switch (option) {
+    case INGOT_OPT_PDL: g->pdl = value != 0; return INGOT_OK;
+    case INGOT_OPT_FORCE_PLAIN: g->force_plain = value != 0; return INGOT_OK;
+    default: return fail(g, INGOT_INVALID, "unknown option");
+    }
+}
+
+ingot_status ingot_synchronize(ingot_gpu *g) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->capturing) return fail(g, INGOT_INVALID, "cannot synchronize while recording");
+    cudaError_t e = cudaMemcpyAsync(g->status_host, g->status, sizeof(int), cudaMemcpyDeviceToHost, g->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) return cuda_fail(g, e, "synchronize");
+    const int code = *g->status_host;
+    if (code == KERNEL_OK) return INGOT_OK;
+    e = cudaMemsetAsync(g->status, 0, sizeof(int), g->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) return cuda_fail(g, e, "status reset");
+    switch (code) {
+    case KERNEL_ERR_EXPERT_RANGE: return fail(g, INGOT_INVALID, "expert id out of range");
+    case KERNEL_ERR_ROUTER_INPUT: return fail(g, INGOT_INVALID, "invalid router scores or expert count");
+    case KERNEL_ERR_PRODUCER_TIMEOUT: return fail(g, INGOT_TIMEOUT, "GEMV producer wait ran out");
+    case KERNEL_ERR_CONSUMER_TIMEOUT: return fail(g, INGOT_TIMEOUT, "GEMV consumer wait ran out");
+    case KERNEL_ERR_GEMM_TIMEOUT: return fail(g, INGOT_TIMEOUT, "GEMM pipeline wait ran out");
+    default: return fail(g, INGOT_DEVICE, "unknown device status " + std::to_string(code));
+    }
+}
+
+// ---- buffers ----------------------------------------------------------------
+
+ingot_status ingot_buffer_alloc(ingot_gpu *g, size_t bytes, void **p) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!p) return fail(g, INGOT_INVALID, "null output pointer");
+    *p = nullptr;
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e == cudaErrorMemoryAllocation) { cudaGetLastError(); return fail(g, INGOT_INVALID, "out of device memory"); }
+    if (e != cudaSuccess) return cuda_fail(g, e, "cudaMalloc");
+    return INGOT_OK;
+}
+
+ingot_status ingot_buffer_free(ingot_gpu *g, void *p) {
+    if (!g) return INGOT_INVALID;
+    if (!p) return INGOT_OK;
+    cudaSetDevice(g->device);
+    cudaError_t e = cudaFree(p);
+    if (e != cudaSuccess && !g->failed) return cuda_fail(g, e, "cudaFree");
+    return INGOT_OK;
+}
+
+ingot_status ingot_buffer_upload(ingot_gpu *g, void *dst, const void *host, size_t bytes) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (bytes == 0) return INGOT_OK;
+    if (!dst || !host) return fail(g, INGOT_INVALID, "null pointer");
+    cudaError_t e = cudaMemcpyAsync(dst, host, bytes, cudaMemcpyHostToDevice, g->stream);
+    if (e != cudaSuccess) return cuda_fail(g, e, "upload");
+    return INGOT_OK;
+}
+
+ingot_status ingot_buffer_read(ingot_gpu *g, void *host, const void *src, size_t bytes) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (bytes == 0) return INGOT_OK;
+    if (!src || !host) return fail(g, INGOT_INVALID, "null pointer");
+    cudaError_t e = cudaMemcpyAsync(host, src, bytes, cudaMemcpyDeviceToHost, g->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) return cuda_fail(g, e, "read");
+    return INGOT_OK;
+}
+
+ingot_status ingot_buffer_zero(ingot_gpu *g, void *p, size_t bytes) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (bytes == 0) return INGOT_OK;
+    cudaError_t e = cudaMemsetAsync(p, 0, bytes, g->stream);
+    if (e != cudaSuccess) return cuda_fail(g, e, "memset");
+    return INGOT_OK;
+}
+
+ingot_status ingot_host_alloc(ingot_gpu *g, size_t bytes, void **p) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!p) return fail(g, INGOT_INVALID, "null output pointer");
+    cudaError_t e = cudaHostAlloc(p, bytes ? bytes : 16, cudaHostAllocDefault);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(g, INGOT_INVALID, "out of pinned host memory"); }
+    return INGOT_OK;
+}
+
+ingot_status ingot_host_free(ingot_gpu *g, void *p) {
+    if (!g) return INGOT_INVALID;
+    if (p) cudaFreeHost(p);
+    return INGOT_OK;
+}
+
+ingot_status ingot_weight_upload(ingot_gpu *g, const void *host, uint32_t kind, uint64_t cols, uint64_t rows,
+                                 uint64_t count, size_t bytes, void **p) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    uint64_t stride, total;
+    st = ingot_tensor_layout(kind, cols, rows, count, &stride, &total);
+    if (st == INGOT_UNSUPPORTED) return fail(g, st, "GGML type " + std::to_string(kind) + " is unsupported");
+    if (st || total != bytes || !host) return fail(g, INGOT_INVALID, "tensor bytes do not match its shape");
+    st = ingot_buffer_alloc(g, bytes, p);
+    if (st) return st;
+    st = ingot_buffer_upload(g, *p, host, bytes);
+    if (st) { cudaFree(*p); *p = nullptr; }
+    return st;
+}
+
+// ---- operators --------------------------------------------------------------
+
+ingot_status ingot_dequant_rows(ingot_gpu *g, const void *w, uint32_t cols, uint64_t rows, uint32_t stride,
+                                uint32_t kind, float *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if ((st = check_matrix(g, kind, cols, rows ? 1 : 0, stride))) return st;
+    if (!w || !y) return fail(g, INGOT_INVALID, "null pointer");
+    return after_launch(g, launch_dequant(static_cast<const uint8_t *>(w), cols, rows, stride, kind, y, ctx_of(g)), "dequant_rows");
+}
+
+static ingot_status gemv_common(ingot_gpu *g, GemvCall &c, uint32_t x_kind, const char *what) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if ((st = check_matrix(g, c.kind, c.cols, c.rows, c.stride))) return st;
+    if (!x_kind_ok(x_kind)) return fail(g, INGOT_UNSUPPORTED, "activations must be F32 (0) or BF16 (30)");
+    if (!c.w[0] || (c.nmat == 2 && !c.w[1]) || !c.x || !c.y) return fail(g, INGOT_INVALID, "null pointer");
+    c.x_bf16 = x_kind == INGOT_KIND_BF16;
+    return after_launch(g, launch_gemv(c, ctx_of(g)), what);
+}
+
+ingot_status ingot_matmul(ingot_gpu *g, const void *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind,
+                          uint32_t expert, const void *x, uint32_t x_kind, uint32_t count, float *y) {
+    GemvCall c = {};
+    c.w[0] = static_cast<const uint8_t *>(w);
+    c.x = x; c.y = y; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
+    c.expert = expert; c.count = count; c.nmat = 1;
+    return gemv_common(g, c, x_kind, "matmul");
+}
+
+ingot_status ingot_gate_up(ingot_gpu *g, const void *gate, const void *up, uint32_t cols, uint32_t rows,
+                           uint32_t stride, uint32_t kind, const void *x, uint32_t x_kind, uint32_t count,
+                           uint32_t gelu, float *y) {
+    GemvCall c = {};
+    c.w[0] = static_cast<const uint8_t *>(gate);
+    c.w[1] = static_cast<const uint8_t *>(up);
+    c.x = x; c.y = y; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
+    c.count = count; c.nmat = 2; c.glu = gelu ? 2 : 1;
+    return gemv_common(g, c, x_kind, "gate_up");
+}
+
+ingot_status ingot_routed(ingot_gpu *g, const void *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind,
+                          uint32_t experts, const void *x, uint32_t x_kind, const uint32_t *ids, uint32_t per_pair,
+                          uint32_t top, uint32_t pairs, float *y) {
+    if (g && (!ids || top == 0 || experts == 0)) return fail(g, INGOT_INVALID, "routed projection needs ids, top and experts");
+    GemvCall c = {};
+    c.w[0] = static_cast<const uint8_t *>(w);
+    c.x = x; c.y = y; c.ids = ids; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
+    c.pairs = pairs; c.top = top; c.per_pair = per_pair; c.n_experts = experts; c.nmat = 1;
+    return gemv_common(g, c, x_kind, "routed");
+}
+
+ingot_status ingot_routed_gate_up(ingot_gpu *g, const void *gate, const void *up, uint32_t cols, uint32_t rows,
+                                  uint32_t stride, uint32_t kind, uint32_t experts, const void *x, uint32_t x_kind,
+                                  const uint32_t *ids, uint32_t top, uint32_t pairs, float *y) {
+    if (g && (!ids || top == 0 || experts == 0)) return fail(g, INGOT_INVALID, "routed projection needs ids, top and experts");
+    GemvCall c = {};
+    c.w[0] = static_cast<const uint8_t *>(gate);
+    c.w[1] = static_cast<const uint8_t *>(up);
+    c.x = x; c.y = y; c.ids = ids; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
+    c.pairs = pairs; c.top = top; c.per_pair = 0; c.n_experts = experts; c.nmat = 2; c.glu = 1;
+    return gemv_common(g, c, x_kind, "routed_gate_up");
+}
+
+ingot_status ingot_route_topk(ingot_gpu *g, const float *logits, uint32_t experts, uint32_t top, uint32_t tokens,
+                              uint32_t *ids, float *weights) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (top == 0 || top > experts || experts > 512) return fail(g, INGOT_INVALID, "invalid router scores or expert count");
+    if (!logits || !ids || !weights) return fail(g, INGOT_INVALID, "null pointer");
+    return after_launch(g, launch_route_topk(logits, experts, top, tokens, ids, weights, ctx_of(g)), "route_topk");
+}
+
+ingot_status ingot_moe_sum(ingot_gpu *g, const float *routed, const float *weights, uint32_t width, uint32_t top,
+                           uint32_t tokens, float *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!routed || !weights || !y || width % 4u) return fail(g, INGOT_INVALID, "moe_sum: bad arguments");
+    return after_launch(g, launch_moe_sum(routed, weights, width, top, tokens, y, ctx_of(g)), "moe_sum");
+}
+
+ingot_status ingot_activation(ingot_gpu *g, const float *gate, const float *up, uint64_t n, uint32_t gelu, float *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!gate || !up || !y) return fail(g, INGOT_INVALID, "null pointer");
+    return after_launch(g, launch_activation(gate, up, n, gelu, y, ctx_of(g)), "activation");
+}
+
+ingot_status ingot_merge(ingot_gpu *g, const float *routed, const float *shared, const float *weights,
+                         const float *shared_logit, uint32_t width, uint32_t top, float *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!routed || !shared || !weights || !shared_logit || !y) return fail(g, INGOT_INVALID, "null pointer");
+    return after_launch(g, launch_merge(routed, shared, weights, shared_logit, width, top, y, ctx_of(g)), "merge");
+}
+
+ingot_status ingot_add_rms(ingot_gpu *g, const float *a, const float *b, const float *w, float *s, float *y,
+                           void *y_bf16, uint32_t width, uint32_t rows, float eps, uint32_t add) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!a || (add && !b) || width % 4u || width == 0) return fail(g, INGOT_INVALID, "add_rms: bad arguments");
+    return after_launch(g, launch_add_rms(a, b, w, s, y, width, rows, eps, add, y_bf16, ctx_of(g)), "add_rms");
+}
+
+ingot_status ingot_expert_layout(ingot_gpu *g, const uint32_t *ids, uint32_t pairs, uint32_t experts,
+                                 uint32_t tile_capacity, uint32_t *layout, uint32_t *tiles, uint32_t *packed,
+                                 uint32_t *inverse) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!ids || !layout || !tiles || !packed || !inverse || experts == 0 || experts > 512)
+        return fail(g, INGOT_INVALID, "expert_layout: bad arguments");
+    return after_launch(g, launch_expert_layout(ids, pairs, experts, tile_capacity, layout, tiles, packed, inverse, ctx_of(g)),
+                        "expert_layout");
+}
+
+ingot_status ingot_combine_packed(ingot_gpu *g, const float *routed, const float *weights, const uint32_t *inverse,
+                                  uint32_t width, uint32_t top, uint32_t tokens, float *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!routed || !weights || !inverse || !y || width % 4u) return fail(g, INGOT_INVALID, "combine_packed: bad arguments");
+    return after_launch(g, launch_combine_packed(routed, weights, inverse, width, top, tokens, y, ctx_of(g)), "combine_packed");
+}
+
+ingot_status ingot_convert_bf16(ingot_gpu *g, const float *x, uint64_t n, void *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!x || !y) return fail(g, INGOT_INVALID, "null pointer");
+    return after_launch(g, launch_convert_bf16(x, n, y, ctx_of(g)), "convert_bf16");
+}
+
+// ---- command recording --------------------------------------------------------
+
+ingot_status ingot_command_begin(ingot_gpu *g) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->capturing) return fail(g, INGOT_INVALID, "already recording");
+    cudaError_t e = cudaStreamBeginCapture(g->stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return cuda_fail(g, e, "begin capture");
+    g->capturing = true;
+    return INGOT_OK;
+}
+
+ingot_status ingot_command_end(ingot_gpu *g, ingot_graph **out) {
+    if (!g || !out) return INGOT_INVALID;
+    if (!g->capturing) return fail(g, INGOT_INVALID, "not recording");
+    g->capturing = false;
+    ingot_graph *gr = new (std::nothrow) ingot_graph();
+    if (!gr) return fail(g, INGOT_DEVICE, "out of host memory");
+    cudaError_t e = cudaStreamEndCapture(g->stream, &gr->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&gr->exec, gr->graph, 0);
+    if (e != cudaSuccess) {
+        if (gr->graph) cudaGraphDestroy(gr->graph);
+        delete gr;
+        return cuda_fail(g, e, "end capture");
+    }
+    *out = gr;
+    return INGOT_OK;
+}
+
+ingot_status ingot_command_submit(ingot_gpu *g, ingot_graph *gr) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!gr || !gr->exec) return fail(g, INGOT_INVALID, "null graph");
+    cudaError_t e = cudaGraphLaunch(gr->exec, g->stream);
+    if (e != cudaSuccess) return cuda_fail(g, e, "graph launch");
+    return INGOT_OK;
+}
+
+void ingot_command_destroy(ingot_graph *gr) {
+    if (!gr) return;
+    if (gr->exec) cudaGraphExecDestroy(gr->exec);
+    if (gr->graph) cudaGraphDestroy(gr->graph);
+    delete gr;
+}
+
+// ---- host-vector conveniences -------------------------------------------------
+
+static ingot_status check_host_matrix(ingot_gpu *g, size_t data_bytes, uint64_t cols, uint64_t rows, uint64_t count,
+                                      uint32_t kind, uint64_t stride) {
+    uint32_t block, bytes;
+    if (!geometry(kind, block, bytes)) return fail(g, INGOT_UNSUPPORTED, "GGML type " + std::to_string(kind) + " is unsupported");
+    unsigned __int128 total = (unsigned __int128)stride * rows * count;
+    if (cols == 0 || rows == 0 || count == 0 || cols % block || stride != cols / block * bytes ||
+        total != (unsigned __int128)data_bytes || cols > 0xffffffffull || rows > 0xffffffffull ||
+        count > 0xffffffffull || stride > 0xffffffffull)
+        return fail(g, INGOT_INVALID, "invalid quantized matrix layout");
+    return INGOT_OK;
+}
+
+ingot_status ingot_dequant_host(ingot_gpu *g, const void *data, size_t data_bytes, uint64_t cols, uint64_t rows,
+                                uint64_t count, uint32_t kind, uint64_t stride, float *out) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if ((st = check_host_matrix(g, data_bytes, cols, rows, count, kind, stride))) return st;
+    if (!data || !out) return fail(g, INGOT_INVALID, "null pointer");
+    void *w = nullptr, *y = nullptr;
+    const size_t out_bytes = (size_t)cols * rows * count * sizeof(float);
+    if ((st = ingot_buffer_alloc(g, data_bytes, &w))) return st;
+    if ((st = ingot_buffer_alloc(g, out_bytes, &y))) { cudaFree(w); return st; }
+    st = ingot_buffer_upload(g, w, data, data_bytes);
+    if (!st) st = ingot_dequant_rows(g, w, (uint32_t)cols, rows * count, (uint32_t)stride, kind, static_cast<float *>(y));
+    if (!st) st = ingot_buffer_read(g, out, y, out_bytes);
+    if (!st) st = ingot_synchronize(g);
+    cudaFree(w);
+    cudaFree(y);
+    return st;
+}
+
+ingot_status ingot_project_host(ingot_gpu *g, const void *data, size_t data_bytes, uint64_t cols, uint64_t rows,
+                                uint64_t count, uint32_t kind, uint64_t stride, const float *input, size_t input_len,
+                                float *out) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if ((st = check_host_matrix(g, data_bytes, cols, rows, count, kind, stride))) return st;
+    if (!data || !input || !out) return fail(g, INGOT_INVALID, "null pointer");
+    bool finite = true;
+    for (size_t i = 0; i < input_len; ++i) finite = finite && isfinite(input[i]);
+    if (!finite || count != 1 || cols != input_len) return fail(g, INGOT_INVALID, "projection shape mismatch");
+    void *w = nullptr, *x = nullptr, *y = nullptr;
+    if ((st = ingot_buffer_alloc(g, data_bytes, &w))) return st;
+    if ((st = ingot_buffer_alloc(g, cols * sizeof(float), &x))) { cudaFree(w); return st; }
+    if ((st = ingot_buffer_alloc(g, rows * sizeof(float), &y))) { cudaFree(w); cudaFree(x); return st; }
+    st = ingot_buffer_upload(g, w, data, data_bytes);
+    if (!st) st = ingot_buffer_upload(g, x, input, cols * sizeof(float));
+    if (!st) st = ingot_matmul(g, w, (uint32_t)cols, (uint32_t)rows, (uint32_t)stride, kind, 0, x, INGOT_KIND_F32, 1, static_cast<float *>(y));
+    if (!st) st = ingot_buffer_read(g, out, y, rows * sizeof(float));
+    if (!st) st = ingot_synchronize(g);
+    cudaFree(w);
+    cudaFree(x);
+    cudaFree(y);
+    if (!st)
+        for (uint64_t i = 0; i < rows; ++i)
+            if (!isfinite(out[i])) return fail(g, INGOT_INVALID, "output contains non-finite values");
+    return st;
+}
+
+}  // extern "C"

@@ -1,0 +1,63 @@
+// Internal launch interface between the C ABI (abi.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ingot {
+
+// Codes kernels write to the device status word (0 = ok).
+enum : int {
+    KERNEL_OK = 0,
+    KERNEL_ERR_PRODUCER_TIMEOUT = 1,   // ring stage never freed
+    KERNEL_ERR_CONSUMER_TIMEOUT = 2,   // bulk copy never landed
+    KERNEL_ERR_EXPERT_RANGE = 3,       // routed id >= number of experts
+    KERNEL_ERR_ROUTER_INPUT = 4,       // non-finite router logit
+    KERNEL_ERR_GEMM_TIMEOUT = 5        // prefill GEMM pipeline wait ran out
+};
+
+struct LaunchCtx {
+    cudaStream_t stream;
+    int *status;          // device status word
+    uint32_t sm_count;
+    bool pdl;             // launch with programmatic stream serialization
+    bool force_plain;     // test hook: skip the streaming kernel
+};
+
+// y = W x for `count` tokens (dense) or `pairs` (token, expert) pairs (routed,
+// ids != null).  nmat == 2 fuses two matrices and stores glu(gate, up).
+struct GemvCall {
+    const uint8_t *w[2];
+    const void *x;
+    float *y;
+    const uint32_t *ids;
+    uint32_t cols, rows, stride, kind;
+    uint32_t expert;       // dense
+    uint32_t count;        // dense tokens
+    uint32_t pairs, top, per_pair, n_experts;   // routed
+    uint32_t x_bf16;
+    uint32_t nmat, glu;    // glu: 1 silu, 2 tanh-gelu
+};
+cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);
+
+// out[r][j] = weight_at(row r, j) for rows*cols elements.
+cudaError_t launch_dequant(const uint8_t *w, uint32_t cols, uint64_t rows, uint32_t stride, uint32_t kind,
+                           float *out, const LaunchCtx &ctx);
+
+cudaError_t launch_route_topk(const float *logits, uint32_t experts, uint32_t top, uint32_t tokens, uint32_t *ids,
+                              float *weights, const LaunchCtx &ctx);
+cudaError_t launch_moe_sum(const float *routed, const float *w, uint32_t width, uint32_t top, uint32_t tokens,
+                           float *y, const LaunchCtx &ctx);
+cudaError_t launch_activation(const float *gate, const float *up, uint64_t n, uint32_t gelu, float *y,
+                              const LaunchCtx &ctx);
+cudaError_t launch_merge(const float *routed, const float *shared, const float *weights, const float *shared_logit,
+                         uint32_t width, uint32_t top, float *y, const LaunchCtx &ctx);
+cudaError_t launch_add_rms(const float *a, const float *b, const float *w, float *s, float *y, uint32_t width,
+                           uint32_t rows, float eps, uint32_t add, void *y_bf16, const LaunchCtx &ctx);
+cudaError_t launch_expert_layout(const uint32_t *ids, uint32_t n_pairs, uint32_t experts, uint32_t tile_capacity,
+                                 uint32_t *layout, uint32_t *tiles, uint32_t *pairs, uint32_t *inverse,
+                                 const LaunchCtx &ctx);
+cudaError_t launch_combine_packed(const float *routed, const float *w, const uint32_t *inverse, uint32_t width,
+                                  uint32_t top, uint32_t tokens, float *y, const LaunchCtx &ctx);
+cudaError_t launch_convert_bf16(const float *x, uint64_t n, void *y_bf16, const LaunchCtx &ctx);
+
+}  // namespace ingot

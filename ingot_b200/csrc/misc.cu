@@ -1,0 +1,531 @@
+// The bandwidth-trivial operators around the GEMVs: whole-matrix dequantise,
+// top-k routing, weighted expert sum, GLU activation, shared-expert merge,
+// residual RMS norm, expert grouping.  All HBM- or latency-bound; each is a
+// straight grid of threads with coalesced 16-byte accesses.
+#include "gemv_core.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace ingot {
+
+namespace {
+
+template <class K, class A>
+cudaError_t launch(K kernel, dim3 grid, dim3 block, const LaunchCtx &ctx, const A &args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = ctx.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args);
+}
+
+__device__ __forceinline__ void pdl_prologue() {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+}
+
+// N 32-bit words starting at a 2-byte aligned global address.
+template <int N>
+__device__ __forceinline__ void ld_words(const uint8_t *p, uint32_t *out) {
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *ap = reinterpret_cast<const uint32_t *>(addr & ~uintptr_t(3));
+    if (addr & 2u) {
+        uint32_t prev = ap[0];
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            uint32_t next = ap[i + 1];
+            out[i] = __funnelshift_r(prev, next, 16);
+            prev = next;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[i] = ap[i];
+    }
+}
+
+__device__ __forceinline__ float h16(const uint8_t *p) {
+    return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(p)));
+}
+
+__device__ __forceinline__ void st4(float *out, float a, float b, float c, float d) {
+    *reinterpret_cast<float4 *>(out) = make_float4(a, b, c, d);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Dequantise (reference read_rows: kernels/qwen.metal:35).  One thread per
+// 32-weight unit; every value is formed with the same fp32 operations, in the
+// same order, as weight_at, so results are bit-identical to it.
+// ---------------------------------------------------------------------------
+
+struct DequantArgs {
+    const uint8_t *w;
+    float *out;
+    uint64_t rows;
+    uint32_t cols, stride, kind;
+};
+
+__global__ void __launch_bounds__(256) dequant_units_kernel(const __grid_constant__ DequantArgs a) {
+    pdl_prologue();
+    const uint32_t upr = a.cols >> 5;                       // units per row
+    const uint64_t total = a.rows * upr;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = idx / upr;
+        const uint32_t u = (uint32_t)(idx - row * upr);
+        const uint8_t *rp = a.w + row * a.stride;
+        float *orow = a.out + row * a.cols;
+        if (a.kind == KIND_Q4_K) {
+            const uint8_t *b = rp + (size_t)(u >> 3) * 144u;
+            const uint32_t p = u & 7u, j = p >> 1, h = p & 1u;
+            uint32_t sc0, m0, sc1, m1, q[4];
+            q4k_scale_min(b + 4, 2 * j, sc0, m0);
+            q4k_scale_min(b + 4, 2 * j + 1, sc1, m1);
+            ld_words<4>(b + 16u + 16u * p, q);
+            const float d = h16(b), dmin = h16(b + 2);
+            const float ds0 = __fmul_rn(d, (float)sc0), ds1 = __fmul_rn(d, (float)sc1);
+            const float c0 = __fmul_rn(dmin, (float)m0), c1 = __fmul_rn(dmin, (float)m1);
+            float *lo = orow + (u >> 3) * 256u + j * 64u + h * 16u, *hi = lo + 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t wl = q[i] & 0x0f0f0f0fu, wh = (q[i] >> 4) & 0x0f0f0f0fu;
+                st4(lo + 4 * i, __fsub_rn(__fmul_rn(ds0, byte_f(wl, 0)), c0), __fsub_rn(__fmul_rn(ds0, byte_f(wl, 1)), c0),
+                    __fsub_rn(__fmul_rn(ds0, byte_f(wl, 2)), c0), __fsub_rn(__fmul_rn(ds0, byte_f(wl, 3)), c0));
+                st4(hi + 4 * i, __fsub_rn(__fmul_rn(ds1, byte_f(wh, 0)), c1), __fsub_rn(__fmul_rn(ds1, byte_f(wh, 1)), c1),
+                    __fsub_rn(__fmul_rn(ds1, byte_f(wh, 2)), c1), __fsub_rn(__fmul_rn(ds1, byte_f(wh, 3)), c1));
+            }
+        } else if (a.kind == KIND_Q6_K) {
+            const uint8_t *b = rp + (size_t)(u >> 3) * 210u;
+            const uint32_t r = u & 7u, n = r >> 2, k8 = r & 3u;
+            uint32_t l0[2], l1[2], hq[2];
+            ld_words<2>(b + 64u * n + 8u * k8, l0);
+            ld_words<2>(b + 64u * n + 32u + 8u * k8, l1);
+            ld_words<2>(b + 128u + 32u * n + 8u * k8, hq);
+            const float d = h16(b + 208);
+            float *o = orow + (u >> 3) * 256u + n * 128u + k8 * 8u;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int scale = (int)(int8_t)b[192u + 8u * n + (k8 >> 1) + 2u * t];
+                const float ds = __fmul_rn(d, (float)scale);
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t lo = ((t & 1) ? l1[e] : l0[e]) >> ((t >= 2) ? 4 : 0);
+                    const uint32_t qv = (lo & 0x0f0f0f0fu) | (((hq[e] >> (2 * t)) & 0x03030303u) << 4);
+                    st4(o + 32 * t + 4 * e, __fmul_rn(ds, (float)((int)((qv >> 0) & 0xff) - 32)),
+                        __fmul_rn(ds, (float)((int)((qv >> 8) & 0xff) - 32)),
+                        __fmul_rn(ds, (float)((int)((qv >> 16) & 0xff) - 32)),
+                        __fmul_rn(ds, (float)((int)((qv >> 24) & 0xff) - 32)));
+                }
+            }
+        } else if (a.kind == KIND_Q4_0) {
+            const uint8_t *b = rp + (size_t)u * 18u;
+            uint32_t q[4];
+            ld_words<4>(b + 2, q);
+            const float d = h16(b);
+            float *o = orow + u * 32u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t wl = q[i] & 0x0f0f0f0fu, wh = (q[i] >> 4) & 0x0f0f0f0fu;
+                st4(o + 4 * i, __fmul_rn(d, (float)((int)((wl >> 0) & 0xff) - 8)), __fmul_rn(d, (float)((int)((wl >> 8) & 0xff) - 8)),
+                    __fmul_rn(d, (float)((int)((wl >> 16) & 0xff) - 8)), __fmul_rn(d, (float)((int)((wl >> 24) & 0xff) - 8)));
+                st4(o + 16 + 4 * i, __fmul_rn(d, (float)((int)((wh >> 0) & 0xff) - 8)), __fmul_rn(d, (float)((int)((wh >> 8) & 0xff) - 8)),
+                    __fmul_rn(d, (float)((int)((wh >> 16) & 0xff) - 8)), __fmul_rn(d, (float)((int)((wh >> 24) & 0xff) - 8)));
+            }
+        } else {   // Q8_0
+            const uint8_t *b = rp + (size_t)u * 34u;
+            uint32_t q[8];
+            ld_words<8>(b + 2, q);
+            const float d = h16(b);
+            float *o = orow + u * 32u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                st4(o + 4 * i, __fmul_rn(d, (float)(int)(int8_t)(q[i] & 0xff)), __fmul_rn(d, (float)(int)(int8_t)((q[i] >> 8) & 0xff)),
+                    __fmul_rn(d, (float)(int)(int8_t)((q[i] >> 16) & 0xff)), __fmul_rn(d, (float)(int)(int8_t)(q[i] >> 24)));
+        }
+    }
+}
+
+// Any type, any alignment: one thread per element.
+__global__ void __launch_bounds__(256) dequant_scalar_kernel(const __grid_constant__ DequantArgs a) {
+    pdl_prologue();
+    const uint64_t total = a.rows * a.cols;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = idx / a.cols;
+        a.out[idx] = weight_at(a.w + row * a.stride, a.kind, (uint32_t)(idx - row * a.cols));
+    }
+}
+
+cudaError_t launch_dequant(const uint8_t *w, uint32_t cols, uint64_t rows, uint32_t stride, uint32_t kind, float *out,
+                           const LaunchCtx &ctx) {
+    DequantArgs a = {w, out, rows, cols, stride, kind};
+    const bool quant = kind == KIND_Q4_K || kind == KIND_Q6_K || kind == KIND_Q4_0 || kind == KIND_Q8_0;
+    const bool aligned = ((uintptr_t)w % 4u) == 0 && (stride % 2u) == 0 && ((uintptr_t)out % 16u) == 0 && (cols % 32u) == 0;
+    const uint64_t work = quant && aligned ? rows * (cols / 32u) : rows * cols;
+    uint64_t blocks = (work + 255) / 256;
+    const uint64_t cap = (uint64_t)ctx.sm_count * 32u;
+    if (blocks > cap) blocks = cap;
+    if (blocks == 0) return cudaSuccess;
+    if (quant && aligned) return launch(dequant_units_kernel, dim3((uint32_t)blocks), dim3(256), ctx, a);
+    return launch(dequant_scalar_kernel, dim3((uint32_t)blocks), dim3(256), ctx, a);
+}
+
+// ---------------------------------------------------------------------------
+// Routing (reference route_topk: kernels/generic.metal:479-494; CPU route():
+// src/lib.rs:43-60).  One warp per token, up to 512 experts in registers.
+// k rounds of arg-max, ties to the lowest expert id; weight exp(l - l_top),
+// normalised by the sum taken in selection order.
+// ---------------------------------------------------------------------------
+
+struct RouteArgs {
+    const float *logits;
+    uint32_t *ids;
+    float *weights;
+    uint32_t experts, top, tokens;
+    int *status;
+};
+
+__global__ void __launch_bounds__(128) route_topk_kernel(const __grid_constant__ RouteArgs a) {
+    pdl_prologue();
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t t = blockIdx.x * 4u + (threadIdx.x >> 5);
+    if (t >= a.tokens) return;
+    const float *l = a.logits + (size_t)t * a.experts;
+    float v[16];
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t e = lane + 32u * i;
+        v[i] = e < a.experts ? l[e] : -INFINITY;
+        if (e < a.experts && !isfinite(v[i])) bad = true;
+    }
+    if (__any_sync(0xffffffffu, bad)) {
+        if (lane == 0) atomicCAS(a.status, 0, KERNEL_ERR_ROUTER_INPUT);
+        return;
+    }
+    float top_score = 0.f, sum = 0.f, mine = 0.f;      // lane k keeps weight k (top <= 32 per pass)
+    for (uint32_t k = 0; k < a.top; ++k) {
+        float best = -INFINITY;
+        uint32_t index = 0xffffffffu;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (v[i] > best) { best = v[i]; index = lane + 32u * i; }
+        float score = best;
+        for (uint32_t off = 16; off; off >>= 1) score = fmaxf(score, __shfl_xor_sync(0xffffffffu, score, off));
+        uint32_t e = best == score ? index : 0xffffffffu;
+        for (uint32_t off = 16; off; off >>= 1) e = min(e, __shfl_xor_sync(0xffffffffu, e, off));
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (lane + 32u * i == e) v[i] = -INFINITY;
+        if (k == 0) top_score = score;
+        const float w = expf(score - top_score);
+        sum = __fadd_rn(sum, w);
+        if (lane == 0) { a.ids[(size_t)t * a.top + k] = e; a.weights[(size_t)t * a.top + k] = w; }
+        (void)mine;
+    }
+    __syncwarp();
+    for (uint32_t k = lane; k < a.top; k += 32u) a.weights[(size_t)t * a.top + k] = __fdiv_rn(a.weights[(size_t)t * a.top + k], sum);
+}
+
+cudaError_t launch_route_topk(const float *logits, uint32_t experts, uint32_t top, uint32_t tokens, uint32_t *ids,
+                              float *weights, const LaunchCtx &ctx) {
+    if (tokens == 0) return cudaSuccess;
+    RouteArgs a = {logits, ids, weights, experts, top, tokens, ctx.status};
+    return launch(route_topk_kernel, dim3((tokens + 3) / 4), dim3(128), ctx, a);
+}
+
+// ---------------------------------------------------------------------------
+// Weighted sum of each token's expert outputs in route order
+// (reference moe_sum: kernels/generic.metal:17).
+// ---------------------------------------------------------------------------
+
+struct SumArgs {
+    const float *routed, *w;
+    const uint32_t *inverse;     // packed position of each pair, or null
+    float *y;
+    uint32_t width, top, tokens;
+};
+
+__global__ void __launch_bounds__(256) moe_sum_kernel(const __grid_constant__ SumArgs a) {
+    pdl_prologue();
+    const uint32_t w4 = a.width >> 2;
+    const uint64_t total = (uint64_t)a.tokens * w4;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t t = (uint32_t)(idx / w4), j = (uint32_t)(idx - (uint64_t)t * w4);
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t e = 0; e < a.top; ++e) {
+            const uint32_t pair = t * a.top + e;
+            const size_t src = a.inverse ? a.inverse[pair] : pair;
+            const float4 r = reinterpret_cast<const float4 *>(a.routed + src * a.width)[j];
+            const float wt = a.w[pair];
+            s.x = __fmaf_rn(r.x, wt, s.x); s.y = __fmaf_rn(r.y, wt, s.y);
+            s.z = __fmaf_rn(r.z, wt, s.z); s.w = __fmaf_rn(r.w, wt, s.w);
+        }
+        reinterpret_cast<float4 *>(a.y + (size_t)t * a.width)[j] = s;
+    }
+}
+
+static cudaError_t launch_sum(const SumArgs &a, const LaunchCtx &ctx) {
+    const uint64_t total = (uint64_t)a.tokens * (a.width >> 2);
+    if (total == 0) return cudaSuccess;
+    uint64_t blocks = (total + 255) / 256, cap = (uint64_t)ctx.sm_count * 8u;
+    if (blocks > cap) blocks = cap;
+    return launch(moe_sum_kernel, dim3((uint32_t)blocks), dim3(256), ctx, a);
+}
+
+cudaError_t launch_moe_sum(const float *routed, const float *w, uint32_t width, uint32_t top, uint32_t tokens, float *y,
+                           const LaunchCtx &ctx) {
+    if (width % 4u) return cudaErrorInvalidValue;
+    SumArgs a = {routed, w, nullptr, y, width, top, tokens};
+    return launch_sum(a, ctx);
+}
+
+cudaError_t launch_combine_packed(const float *routed, const float *w, const uint32_t *inverse, uint32_t width,
+                                  uint32_t top, uint32_t tokens, float *y, const LaunchCtx &ctx) {
+    if (width % 4u) return cudaErrorInvalidValue;
+    SumArgs a = {routed, w, inverse, y, width, top, tokens};
+    return launch_sum(a, ctx);
+}
+
+// ---------------------------------------------------------------------------
+// GLU activation (reference swiglu: kernels/moe.metal:405-410; gelu_mul:
+// kernels/generic_arch.metal:7-10).
+// ---------------------------------------------------------------------------
+
+struct ActArgs {
+    const float *gate, *up;
+    float *y;
+    uint64_t n;
+    uint32_t gelu;
+};
+
+__global__ void __launch_bounds__(256) activation_kernel(const __grid_constant__ ActArgs a) {
+    pdl_prologue();
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x)
+        a.y[i] = glu_f(a.gate[i], a.up[i], a.gelu != 0);
+}
+
+cudaError_t launch_activation(const float *gate, const float *up, uint64_t n, uint32_t gelu, float *y,
+                              const LaunchCtx &ctx) {
+    if (n == 0) return cudaSuccess;
+    ActArgs a = {gate, up, y, n, gelu};
+    uint64_t blocks = (n + 255) / 256, cap = (uint64_t)ctx.sm_count * 8u;
+    if (blocks > cap) blocks = cap;
+    return launch(activation_kernel, dim3((uint32_t)blocks), dim3(256), ctx, a);
+}
+
+// ---------------------------------------------------------------------------
+// Routed sum plus sigmoid-gated shared expert, one token
+// (reference combine: kernels/moe.metal:412-422).
+// ---------------------------------------------------------------------------
+
+struct MergeArgs {
+    const float *routed, *shared, *weights, *shared_logit;
+    float *y;
+    uint32_t width, top;
+};
+
+__global__ void __launch_bounds__(256) merge_kernel(const __grid_constant__ MergeArgs a) {
+    pdl_prologue();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.width) return;
+    float s = 0.f;
+    for (uint32_t e = 0; e < a.top; ++e) s = __fmaf_rn(a.routed[(size_t)e * a.width + i], a.weights[e], s);
+    a.y[i] = s + a.shared[i] / (1.0f + expf(-a.shared_logit[0]));
+}
+
+cudaError_t launch_merge(const float *routed, const float *shared, const float *weights, const float *shared_logit,
+                         uint32_t width, uint32_t top, float *y, const LaunchCtx &ctx) {
+    if (width == 0) return cudaSuccess;
+    MergeArgs a = {routed, shared, weights, shared_logit, y, width, top};
+    return launch(merge_kernel, dim3((width + 255) / 256), dim3(256), ctx, a);
+}
+
+// ---------------------------------------------------------------------------
+// Residual add + RMS norm per row (reference add_rms:
+// kernels/generic.metal:390-404): s = a + b (when add), y = s * inv_rms * w.
+// `w` may be null (unit weight); an optional bf16 copy of y feeds GEMVs that
+// take bf16 activations.
+// ---------------------------------------------------------------------------
+
+struct RmsArgs {
+    const float *a, *b, *w;
+    float *s, *y;
+    uint16_t *y_bf16;
+    uint32_t width, add;
+    float eps;
+};
+
+__device__ __forceinline__ uint16_t f2bf(float f) {
+    uint32_t x = __float_as_uint(f);
+    if ((x & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((x >> 16) | 0x40u);
+    x += 0x7fffu + ((x >> 16) & 1u);
+    return (uint16_t)(x >> 16);
+}
+
+__global__ void __launch_bounds__(256) add_rms_kernel(const __grid_constant__ RmsArgs a) {
+    pdl_prologue();
+    __shared__ float partial[8];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x, n4 = a.width >> 2;
+    const size_t base = (size_t)row * n4;
+    const float4 *a4 = reinterpret_cast<const float4 *>(a.a) + base;
+    const float4 *b4 = a.add ? reinterpret_cast<const float4 *>(a.b) + base : nullptr;
+    float sum = 0.f;
+    for (uint32_t j = tid; j < n4; j += 256) {
+        float4 v = a4[j];
+        if (a.add) {
+            const float4 o = b4[j];
+            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+            if (a.s) reinterpret_cast<float4 *>(a.s)[base + j] = v;
+        }
+        sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    for (uint32_t off = 16; off; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if ((tid & 31u) == 0) partial[tid >> 5] = sum;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += partial[i];
+    const float inv = 1.0f / sqrtf(total / (float)a.width + a.eps);
+    for (uint32_t j = tid; j < n4; j += 256) {
+        float4 v = a4[j];
+        if (a.add) { const float4 o = b4[j]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+        float4 wv = a.w ? reinterpret_cast<const float4 *>(a.w)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
+        v.x = v.x * inv * wv.x; v.y = v.y * inv * wv.y; v.z = v.z * inv * wv.z; v.w = v.w * inv * wv.w;
+        if (a.y) reinterpret_cast<float4 *>(a.y)[base + j] = v;
+        if (a.y_bf16) {
+            uint2 o;
+            o.x = (uint32_t)f2bf(v.x) | ((uint32_t)f2bf(v.y) << 16);
+            o.y = (uint32_t)f2bf(v.z) | ((uint32_t)f2bf(v.w) << 16);
+            reinterpret_cast<uint2 *>(a.y_bf16)[base + j] = o;
+        }
+    }
+}
+
+cudaError_t launch_add_rms(const float *a, const float *b, const float *w, float *s, float *y, uint32_t width,
+                           uint32_t rows, float eps, uint32_t add, void *y_bf16, const LaunchCtx &ctx) {
+    if (width % 4u) return cudaErrorInvalidValue;
+    if (rows == 0) return cudaSuccess;
+    RmsArgs args = {a, b, w, s, y, static_cast<uint16_t *>(y_bf16), width, add, eps};
+    return launch(add_rms_kernel, dim3(rows), dim3(256), ctx, args);
+}
+
+struct CvtArgs {
+    const float *x;
+    uint16_t *y;
+    uint64_t n;
+};
+
+__global__ void __launch_bounds__(256) convert_bf16_kernel(const __grid_constant__ CvtArgs a) {
+    pdl_prologue();
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x)
+        a.y[i] = f2bf(a.x[i]);
+}
+
+cudaError_t launch_convert_bf16(const float *x, uint64_t n, void *y_bf16, const LaunchCtx &ctx) {
+    if (n == 0) return cudaSuccess;
+    CvtArgs a = {x, static_cast<uint16_t *>(y_bf16), n};
+    uint64_t blocks = (n + 255) / 256, cap = (uint64_t)ctx.sm_count * 8u;
+    if (blocks > cap) blocks = cap;
+    return launch(convert_bf16_kernel, dim3((uint32_t)blocks), dim3(256), ctx, a);
+}
+
+// ---------------------------------------------------------------------------
+// Expert grouping for packed prefill MoE (reference expert_layout /
+// expert_pairs: kernels/prefill.metal:7-35): experts ascending, pair indices
+// ascending inside an expert, tiles of at most 32 pairs.
+// ---------------------------------------------------------------------------
+
+struct LayoutArgs {
+    const uint32_t *ids;
+    uint32_t *layout, *tiles, *pairs, *inverse;
+    uint32_t n_pairs, experts, tile_capacity;
+    int *status;
+};
+
+__global__ void __launch_bounds__(256) expert_layout_kernel(const __grid_constant__ LayoutArgs a) {
+    pdl_prologue();
+    extern __shared__ uint32_t sh[];          // counts[experts], first[experts], tile0[experts + 1]
+    uint32_t *counts = sh, *first = sh + a.experts, *tile0 = first + a.experts;
+    const uint32_t tid = threadIdx.x;
+    for (uint32_t e = tid; e < a.experts; e += 256) counts[e] = 0;
+    __syncthreads();
+    for (uint32_t i = tid; i < a.n_pairs; i += 256) {
+        const uint32_t e = a.ids[i];
+        if (e < a.experts) atomicAdd(&counts[e], 1u);
+        else atomicCAS(a.status, 0, KERNEL_ERR_EXPERT_RANGE);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t at = 0, tile = 0;
+        for (uint32_t e = 0; e < a.experts; ++e) {
+            first[e] = at; tile0[e] = tile;
+            at += counts[e]; tile += (counts[e] + 31u) / 32u;
+        }
+        tile0[a.experts] = tile;
+    }
+    __syncthreads();
+    for (uint32_t e = tid; e < a.experts; e += 256) {
+        const uint32_t n = counts[e];
+        a.layout[2 * e] = n; a.layout[2 * e + 1] = first[e];
+        for (uint32_t k = 0; 32u * k < n; ++k) {
+            const uint32_t t = tile0[e] + k;
+            if (t >= a.tile_capacity) { atomicCAS(a.status, 0, KERNEL_ERR_EXPERT_RANGE); break; }
+            const uint32_t nt = n - 32u * k < 32u ? n - 32u * k : 32u;
+            a.tiles[4 * t] = e; a.tiles[4 * t + 1] = first[e] + 32u * k;
+            a.tiles[4 * t + 2] = nt; a.tiles[4 * t + 3] = nt >= 2u ? 1u : 0u;
+        }
+    }
+    for (uint32_t t = tile0[a.experts] + tid; t < a.tile_capacity; t += 256)
+        a.tiles[4 * t] = a.tiles[4 * t + 1] = a.tiles[4 * t + 2] = a.tiles[4 * t + 3] = 0;
+}
+
+// One block per expert: threads own consecutive slices of the pair list, count
+// their matches, and write them after an exclusive scan, which keeps the pair
+// order ascending inside the expert.
+__global__ void __launch_bounds__(256) expert_pairs_kernel(const __grid_constant__ LayoutArgs a) {
+    pdl_prologue();
+    __shared__ uint32_t before[256];
+    const uint32_t e = blockIdx.x, tid = threadIdx.x;
+    if (a.layout[2 * e] == 0) return;
+    const uint32_t slice = (a.n_pairs + 255u) / 256u;
+    const uint32_t start = min(a.n_pairs, tid * slice), end = min(a.n_pairs, start + slice);
+    uint32_t mine = 0;
+    for (uint32_t i = start; i < end; ++i) mine += a.ids[i] == e;
+    before[tid] = mine;
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t run = 0;
+        for (uint32_t k = 0; k < 256; ++k) { const uint32_t v = before[k]; before[k] = run; run += v; }
+    }
+    __syncthreads();
+    uint32_t at = a.layout[2 * e + 1] + before[tid];
+    for (uint32_t i = start; i < end; ++i)
+        if (a.ids[i] == e) { a.inverse[i] = at; a.pairs[at++] = i; }
+}
+
+cudaError_t launch_expert_layout(const uint32_t *ids, uint32_t n_pairs, uint32_t experts, uint32_t tile_capacity,
+                                 uint32_t *layout, uint32_t *tiles, uint32_t *pairs, uint32_t *inverse,
+                                 const LaunchCtx &ctx) {
+    if (experts == 0 || experts > 4096) return cudaErrorInvalidValue;
+    LayoutArgs a = {ids, layout, tiles, pairs, inverse, n_pairs, experts, tile_capacity, ctx.status};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = (3 * experts + 1) * sizeof(uint32_t);
+    cfg.stream = ctx.stream;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, expert_layout_kernel, a);
+    if (e != cudaSuccess) return e;
+    LaunchCtx plain = ctx;
+    plain.pdl = false;
+    return launch(expert_pairs_kernel, dim3(experts), dim3(256), plain, a);
+}
+
+}  // namespace ingot

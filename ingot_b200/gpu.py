@@ -1,0 +1,421 @@
+"""Host-side mirror of the reference's operator interface over the C ABI.
+
+Names, argument meaning and error behaviour follow the reference's Rust types
+so that tests read like the reference's own:
+
+  Gpu, Buffer, Command   src/metal.rs (Gpu::bytes/floats/output/matvec/matmul/
+                         op/activation/merge/dequant/project/finish/read_u32)
+  generic_* operators    src/metal_generic.rs:175-329
+  Tensor, Matrix         src/gguf.rs:18-25, 462-469
+  Weight                 src/weights.rs:10-45
+
+Errors: `InvalidData` (io::ErrorKind::InvalidData), `DeviceError`
+(io::Error::other, sticky), `DeviceTimeout`.  Operators without a kernel for a
+type return None / False like the reference's Ok(None) / Ok(false).
+Everything runs through libingot_cuda.so; nothing is computed on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import _abi
+from .synth import geometry, stride_of
+
+F32, F16, Q4_0, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 2, 8, 12, 14, 30
+
+
+class IngotError(Exception):
+    pass
+
+
+class InvalidData(IngotError, ValueError):
+    """Shape, layout, bounds or unsupported-format error."""
+
+
+class DeviceError(IngotError, RuntimeError):
+    """CUDA failure; the handle must be recreated ("requires reload")."""
+
+
+class DeviceTimeout(IngotError, TimeoutError):
+    """A bounded device-side wait ran out."""
+
+
+@dataclass
+class Tensor:
+    """A tensor descriptor: dims[0] = cols (contiguous), dims[1] = rows, dims[2] = experts."""
+    dims: list[int]
+    kind: int
+    offset: int = 0
+    shard: int = 0
+    stride: int = 0
+    bytes: int = 0
+
+    @staticmethod
+    def of(dims: list[int], kind: int) -> "Tensor":
+        block, size = geometry(kind)
+        if not dims or 0 in dims or dims[0] % block:
+            raise InvalidData("invalid shape/alignment")
+        stride = dims[0] // block * size
+        total = stride
+        for d in dims[1:]:
+            total *= d
+        return Tensor(list(dims), kind, 0, 0, stride, total)
+
+
+@dataclass
+class Matrix:
+    """Host bytes of `count` stacked experts of rows x stride."""
+    data: bytes | np.ndarray
+    cols: int
+    rows: int
+    count: int
+    kind: int
+    stride: int
+
+    @staticmethod
+    def of(data, cols: int, rows: int, kind: int, count: int = 1) -> "Matrix":
+        return Matrix(data, cols, rows, count, kind, stride_of(kind, cols))
+
+
+class Buffer:
+    """A device allocation or a view into one (the reference's Rc<Allocation> view)."""
+
+    def __init__(self, gpu: "Gpu", ptr: int, nbytes: int, owner: "Buffer | None" = None):
+        self.gpu, self.ptr, self.nbytes, self._owner = gpu, ptr, nbytes, owner
+        self._owned = owner is None
+
+    def view_f32(self, offset: int, count: int) -> "Buffer":
+        if offset < 0 or count < 0 or (offset + count) * 4 > self.nbytes:
+            raise InvalidData("buffer view out of range")
+        return Buffer(self.gpu, self.ptr + 4 * offset, 4 * count, self._owner or self)
+
+    def view_bytes(self, offset: int, nbytes: int) -> "Buffer":
+        if offset < 0 or nbytes < 0 or offset + nbytes > self.nbytes:
+            raise InvalidData("buffer view out of range")
+        return Buffer(self.gpu, self.ptr + offset, nbytes, self._owner or self)
+
+    def release(self) -> None:
+        if self._owned and self.ptr and self.gpu._h:
+            self.gpu._lib.ingot_buffer_free(self.gpu._h, self.ptr)
+        self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+class Command:
+    """Work issued between command() and finish()/complete(); optionally recorded."""
+
+    def __init__(self, gpu: "Gpu"):
+        self.gpu = gpu
+
+
+class Graph:
+    """A recorded command that can be replayed (one decode step in one submission)."""
+
+    def __init__(self, gpu: "Gpu", handle: int):
+        self.gpu, self._g = gpu, handle
+
+    def submit(self) -> None:
+        self.gpu._check(self.gpu._lib.ingot_command_submit(self.gpu._h, self._g))
+
+    def __del__(self):
+        try:
+            if self._g:
+                self.gpu._lib.ingot_command_destroy(self._g)
+                self._g = 0
+        except Exception:
+            pass
+
+
+@dataclass
+class Weight:
+    """A device buffer plus its tensor descriptor (src/weights.rs:10-13)."""
+    buffer: Buffer
+    t: Tensor
+
+    def require_f32(self) -> None:
+        if self.t.kind != F32:
+            raise InvalidData("normalization/state parameters require F32 weights")
+
+    @staticmethod
+    def load(gpu: "Gpu", data, shape: list[int], kind: int, expect: list[int] | None = None) -> "Weight":
+        t = Tensor.of(shape, kind)
+        if expect is not None and list(expect) != list(shape):
+            raise InvalidData(f"expected {expect}, found {shape}")
+        return Weight(gpu.load_weight(data, t), t)
+
+    def project(self, gpu: "Gpu", c: Command, x: Buffer) -> Buffer:
+        rows = self.t.dims[1] if len(self.t.dims) > 1 else 1
+        return gpu.matvec(c, self.buffer, self.t.dims[0], rows, self.t.stride, self.t.kind, x)
+
+
+def _as_u8(data) -> np.ndarray:
+    if isinstance(data, np.ndarray):
+        return np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+    return np.frombuffer(bytes(data), dtype=np.uint8)
+
+
+class Gpu:
+    """One CUDA device, one stream, one owner thread (the reference's Gpu)."""
+
+    VECTOR_KINDS = (Q4_K, Q6_K, Q4_0, Q8_0, F16, F32, BF16)
+
+    def __init__(self, device: int = 0):
+        self._lib = _abi.load()
+        h = C.c_void_p()
+        st = self._lib.ingot_gpu_create(device, C.byref(h))
+        if st != _abi.OK:
+            raise DeviceError(f"cannot create a B200 (sm_100) handle on CUDA device {device}")
+        self._h = h.value
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.ingot_gpu_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- errors ----
+    def _check(self, status: int) -> None:
+        if status == _abi.OK:
+            return
+        msg = (self._lib.ingot_last_error(self._h) or b"").decode()
+        if status in (_abi.INVALID, _abi.UNSUPPORTED, _abi.EOF):
+            raise InvalidData(msg)
+        if status == _abi.TIMEOUT:
+            raise DeviceTimeout(msg)
+        raise DeviceError(msg)
+
+    def set_option(self, option: int, value: int) -> None:
+        self._check(self._lib.ingot_gpu_set_option(self._h, option, value))
+
+    def set_stream(self, cuda_stream: int | None) -> None:
+        self._check(self._lib.ingot_gpu_set_stream(self._h, cuda_stream))
+
+    # ---- buffers ----
+    def empty_bytes(self, n: int) -> Buffer:
+        p = C.c_void_p()
+        self._check(self._lib.ingot_buffer_alloc(self._h, n, C.byref(p)))
+        return Buffer(self, p.value, n)
+
+    def bytes(self, data) -> Buffer:
+        raw = _as_u8(data)
+        b = self.empty_bytes(raw.size)
+        self._check(self._lib.ingot_buffer_upload(self._h, b.ptr, raw.ctypes.data, raw.size))
+        self._check(self._lib.ingot_synchronize(self._h))
+        return b
+
+    def floats(self, values) -> Buffer:
+        return self.bytes(np.ascontiguousarray(values, dtype=np.float32))
+
+    def bf16(self, values) -> Buffer:
+        """Uploads float32 values rounded to bfloat16."""
+        from .synth import to_bf16_bits
+        return self.bytes(to_bf16_bits(np.ascontiguousarray(values, dtype=np.float32)))
+
+    def zeros(self, n_f32: int) -> Buffer:
+        b = self.empty_bytes(4 * n_f32)
+        self._check(self._lib.ingot_buffer_zero(self._h, b.ptr, 4 * n_f32))
+        return b
+
+    def output(self, n_f32: int) -> Buffer:
+        return self.empty_bytes(4 * n_f32)
+
+    def load_weight(self, data, t: Tensor) -> Buffer:
+        raw = _as_u8(data)
+        p = C.c_void_p()
+        dims = list(t.dims) + [1] * (3 - len(t.dims))
+        count = 1
+        for d in dims[2:]:
+            count *= d
+        self._check(self._lib.ingot_weight_upload(self._h, raw.ctypes.data, t.kind, dims[0], dims[1], count,
+                                                  raw.size, C.byref(p)))
+        self._check(self._lib.ingot_synchronize(self._h))
+        return Buffer(self, p.value, raw.size)
+
+    # ---- commands ----
+    def command(self) -> Command:
+        return Command(self)
+
+    def record(self) -> None:
+        self._check(self._lib.ingot_command_begin(self._h))
+
+    def end_record(self) -> Graph:
+        g = C.c_void_p()
+        self._check(self._lib.ingot_command_end(self._h, C.byref(g)))
+        return Graph(self, g.value)
+
+    def complete(self, cmd: Command | None = None) -> None:
+        self._check(self._lib.ingot_synchronize(self._h))
+
+    def read_bytes(self, b: Buffer, n: int | None = None) -> np.ndarray:
+        n = b.nbytes if n is None else n
+        out = np.empty(n, dtype=np.uint8)
+        self._check(self._lib.ingot_buffer_read(self._h, out.ctypes.data, b.ptr, n))
+        return out
+
+    def read_f32(self, b: Buffer, n: int | None = None) -> np.ndarray:
+        n = b.nbytes // 4 if n is None else n
+        return self.read_bytes(b, 4 * n).view(np.float32)
+
+    def read_u32(self, b: Buffer, n: int) -> np.ndarray:
+        return self.read_bytes(b, 4 * n).view(np.uint32)
+
+    def finish(self, cmd: Command, out: Buffer) -> np.ndarray:
+        """Waits, checks the device status and returns `out`; rejects non-finite values."""
+        self.complete(cmd)
+        values = self.read_f32(out)
+        if not np.isfinite(values).all():
+            raise InvalidData("output contains non-finite values")
+        return values
+
+    # ---- operators on buffers ----
+    @staticmethod
+    def _xk(x_kind: int) -> int:
+        return x_kind
+
+    def matvec(self, cmd, w: Buffer, cols, rows, stride, kind, x: Buffer, x_kind: int = F32) -> Buffer:
+        return self.matmul(cmd, w, cols, rows, stride, kind, 0, x, 1, x_kind)
+
+    def matmul(self, cmd, w: Buffer, cols, rows, stride, kind, expert, x: Buffer, count, x_kind: int = F32,
+               out: Buffer | None = None) -> Buffer:
+        y = out or self.output(rows * count)
+        self._check(self._lib.ingot_matmul(self._h, w.ptr, cols, rows, stride, kind, expert, x.ptr, x_kind, count,
+                                           y.ptr))
+        return y
+
+    def generic_project(self, cmd, w: Weight, x: Buffer, count: int, x_kind: int = F32):
+        if w.t.kind not in self.VECTOR_KINDS:
+            return None
+        return self.matmul(cmd, w.buffer, w.t.dims[0], w.t.dims[1], w.t.stride, w.t.kind, 0, x, count, x_kind)
+
+    def generic_gate_up(self, cmd, gate_up, x: Buffer, count: int, gelu: bool, x_kind: int = F32):
+        gate, up = gate_up
+        same = gate.t.kind == up.t.kind and gate.t.stride == up.t.stride and gate.t.dims == up.t.dims
+        if not same or gate.t.kind not in self.VECTOR_KINDS:
+            return None
+        rows = gate.t.dims[1]
+        y = self.output(rows * count)
+        self._check(self._lib.ingot_gate_up(self._h, gate.buffer.ptr, up.buffer.ptr, gate.t.dims[0], rows,
+                                            gate.t.stride, gate.t.kind, x.ptr, x_kind, count, int(gelu), y.ptr))
+        return y
+
+    def generic_routed_gate_up(self, cmd, gate_up, x_ids, top: int, pairs: int, x_kind: int = F32):
+        gate, up = gate_up
+        x, ids = x_ids
+        same = gate.t.kind == up.t.kind and gate.t.stride == up.t.stride and gate.t.dims == up.t.dims
+        if not same or gate.t.kind not in self.VECTOR_KINDS:
+            return None
+        t = gate.t
+        experts = t.dims[2] if len(t.dims) > 2 else 1
+        y = self.output(t.dims[1] * pairs)
+        self._check(self._lib.ingot_routed_gate_up(self._h, gate.buffer.ptr, up.buffer.ptr, t.dims[0], t.dims[1],
+                                                   t.stride, t.kind, experts, x.ptr, x_kind, ids.ptr, top, pairs,
+                                                   y.ptr))
+        return y
+
+    def generic_routed(self, cmd, w: Weight, x_ids_y, per_pair: bool, top: int, pairs: int,
+                       x_kind: int = F32) -> bool:
+        x, ids, y = x_ids_y
+        if w.t.kind not in self.VECTOR_KINDS:
+            return False
+        experts = w.t.dims[2] if len(w.t.dims) > 2 else 1
+        self._check(self._lib.ingot_routed(self._h, w.buffer.ptr, w.t.dims[0], w.t.dims[1], w.t.stride, w.t.kind,
+                                           experts, x.ptr, x_kind, ids.ptr, int(per_pair), top, pairs, y.ptr))
+        return True
+
+    def activation(self, cmd, gate: Buffer, up: Buffer, count: int, gelu: bool = False) -> Buffer:
+        y = self.output(count)
+        self._check(self._lib.ingot_activation(self._h, gate.ptr, up.ptr, count, int(gelu), y.ptr))
+        return y
+
+    def merge(self, cmd, routed: Buffer, shared: Buffer, weights: Buffer, shared_logit: Buffer, width: int,
+              top: int) -> Buffer:
+        y = self.output(width)
+        self._check(self._lib.ingot_merge(self._h, routed.ptr, shared.ptr, weights.ptr, shared_logit.ptr, width,
+                                          top, y.ptr))
+        return y
+
+    def add_rms(self, cmd, a: Buffer, b: Buffer | None, w: Buffer | None, width: int, rows: int, eps: float,
+                add: bool = True, bf16_out: bool = False):
+        """(s, y[, y_bf16]) like the reference's add_rms (src/metal_generic.rs:94-125)."""
+        s = self.output(width * rows) if add else None
+        y = self.output(width * rows)
+        yb = self.empty_bytes(2 * width * rows) if bf16_out else None
+        self._check(self._lib.ingot_add_rms(self._h, a.ptr, b.ptr if b else None, w.ptr if w else None,
+                                            s.ptr if s else None, y.ptr, yb.ptr if yb else None, width, rows,
+                                            float(eps), int(add)))
+        return (s, y, yb) if bf16_out else (s, y)
+
+    def op(self, cmd, name: str, buffers, params, width: int = 1, height: int = 1) -> None:
+        """String-dispatched launcher for the reference's `Gpu::op` call sites on this
+        path (src/metal.rs:686); `params` are the kernel's p[] words."""
+        p = [int(v) for v in params]
+        b = buffers
+        if name == "read_rows":               # p: cols, rows, stride, kind
+            self._check(self._lib.ingot_dequant_rows(self._h, b[0].ptr, p[0], p[1], p[2], p[3], b[1].ptr))
+        elif name in ("route_topk", "route_gpu", "route_gpu_batch"):   # p: experts, top ; height/width tokens
+            tokens = max(width, height) if name != "route_gpu" else 1
+            self._check(self._lib.ingot_route_topk(self._h, b[0].ptr, p[0], p[1], tokens, b[1].ptr, b[2].ptr))
+        elif name == "moe_sum":               # p: width, top, tokens
+            self._check(self._lib.ingot_moe_sum(self._h, b[0].ptr, b[1].ptr, p[0], p[1], p[2], b[2].ptr))
+        elif name == "project_routed_batch":  # p: cols, rows, stride, kind, top, per_pair ; height = pairs
+            experts = b[0].nbytes // (p[1] * p[2])
+            self._check(self._lib.ingot_routed(self._h, b[0].ptr, p[0], p[1], p[2], p[3], experts, b[1].ptr, F32,
+                                               b[2].ptr, p[5], p[4], height, b[3].ptr))
+        else:
+            raise InvalidData(f"no operator named {name} on this path")
+
+    def route_topk(self, logits: Buffer, experts: int, top: int, tokens: int):
+        ids = self.empty_bytes(4 * top * tokens)
+        w = self.output(top * tokens)
+        self._check(self._lib.ingot_route_topk(self._h, logits.ptr, experts, top, tokens, ids.ptr, w.ptr))
+        return ids, w
+
+    def moe_sum(self, routed: Buffer, weights: Buffer, width: int, top: int, tokens: int) -> Buffer:
+        y = self.output(width * tokens)
+        self._check(self._lib.ingot_moe_sum(self._h, routed.ptr, weights.ptr, width, top, tokens, y.ptr))
+        return y
+
+    def expert_layout(self, ids: Buffer, pairs: int, experts: int, tile_capacity: int):
+        layout = self.empty_bytes(8 * experts)
+        tiles = self.empty_bytes(16 * max(tile_capacity, 1))
+        packed = self.empty_bytes(4 * max(pairs, 1))
+        inverse = self.empty_bytes(4 * max(pairs, 1))
+        self._check(self._lib.ingot_expert_layout(self._h, ids.ptr, pairs, experts, tile_capacity, layout.ptr,
+                                                  tiles.ptr, packed.ptr, inverse.ptr))
+        return layout, tiles, packed, inverse
+
+    def combine_packed(self, routed: Buffer, weights: Buffer, inverse: Buffer, width: int, top: int,
+                       tokens: int) -> Buffer:
+        y = self.output(width * tokens)
+        self._check(self._lib.ingot_combine_packed(self._h, routed.ptr, weights.ptr, inverse.ptr, width, top,
+                                                   tokens, y.ptr))
+        return y
+
+    # ---- host-vector conveniences (the reference's public parity hooks) ----
+    def dequant(self, m: Matrix) -> np.ndarray:
+        raw = _as_u8(m.data)
+        out = np.empty(max(m.cols * m.rows * m.count, 1), dtype=np.float32)
+        self._check(self._lib.ingot_dequant_host(self._h, raw.ctypes.data, raw.size, m.cols, m.rows, m.count,
+                                                 m.kind, m.stride, out.ctypes.data))
+        return out[: m.cols * m.rows * m.count]
+
+    def project(self, m: Matrix, x) -> np.ndarray:
+        raw = _as_u8(m.data)
+        xv = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+        out = np.empty(max(m.rows, 1), dtype=np.float32)
+        self._check(self._lib.ingot_project_host(self._h, raw.ctypes.data, raw.size, m.cols, m.rows, m.count,
+                                                 m.kind, m.stride, xv.ctypes.data, xv.size, out.ctypes.data))
+        return out[: m.rows]
