@@ -1,0 +1,417 @@
+"""Benchmark of the decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+Workload (N = 1): the Qwen3-8B Q4_K_M-shaped dense decode chain — 36 layers of
+q/k/v/o, fused gate/up + SwiGLU and down projections plus the 4096 x 151936
+output head, random Q4_K / Q6_K blocks, bf16 activations — one token step per
+"step".  `value` is tokens/s with everything resident in HBM (one recorded
+command replayed per step); `e2e` is the same step driven through the C ABI with
+the step's input copied from pinned host memory and the logits read back to the
+host inside the timed region.  `roofline` is measured on the dominant kernel
+(fused Q4_K gate/up GEMV) with CUDA events in this process, rotating over every
+layer's weights so reads come from HBM, not L2.  `cpu_baseline` times the CPU
+oracle (the restated reference arithmetic) on one layer of the same weights on
+the host cores.
+
+With N > 1 (launched by torch.distributed.run, one process per GPU) output rows
+are sharded tensor-parallel and activations are re-assembled with an NCCL
+all-gather after every projection: strong scaling of the same token step.
+
+`--impl reference` times only the CPU oracle with all host threads (the
+reference has no CPU implementation of this path; the oracle is its restated
+shader arithmetic).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s, Qwen3-8B Q4_K_M shape (Q4_K/Q6_K GEMV chain)"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while timing."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.proc, self.path = device, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.device)], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                p = [c.strip() for c in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    smax.append(float(p[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, p[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_layer_baseline(host_layer, threads: int, repeats: int = 2):
+    """Seconds for the oracle to run one layer's seven GEMVs (scalar dequantise + fp32
+    dot, rows over `threads`), best of `repeats`; and that layer's weight bytes."""
+    from oracle import oracle as O
+    best, nbytes = None, 0
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        nbytes = 0
+        for raw, cols, rows, kind in host_layer:
+            x = np.ones(cols, np.float32)
+            O.matvec_f32(raw, cols, rows, kind, x, threads=threads)
+            nbytes += raw.size
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best, nbytes
+
+
+def run_reference(args):
+    """The CPU arm: the oracle on the host cores, one layer per step as the bounded sample."""
+    from ingot_b200 import synth
+    from ingot_b200.chain import QWEN3_8B, layer_roles, weight_bytes_per_token
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    shape = QWEN3_8B
+    threads = os.cpu_count() or 1
+    layer = [(synth.random_matrix(shape.kinds[r], c, n, seed=i), c, n, shape.kinds[r])
+             for i, (r, c, n) in enumerate(layer_roles(shape))]
+    total = weight_bytes_per_token(shape)
+    for _ in range(max(args.warmup, 1)):
+        cpu_layer_baseline(layer, threads, repeats=1)
+    times = []
+    for _ in range(args.steps):
+        dt, nbytes = cpu_layer_baseline(layer, threads, repeats=1)
+        times.append(dt * total / nbytes)             # seconds per full token step
+    sec = sum(times) / len(times)
+    value = args.batch / sec
+    sample = "one decoder layer (7 GEMVs, 122.6 MB of Q4_K/Q6_K blocks) per step, scaled by bytes to the 4.92 GB token step"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen3-8b-q4_k_m dense decode GEMV chain, batch %d" % args.batch,
+                       "note": "CPU oracle: restated reference shader arithmetic; the reference itself has no CPU path"},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--layers", type=int, default=None, help="debug: fewer layers (invalid as a benchmark)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-kernel", default=None,
+                    help="run only this GEMV (gate_up_q4k, down_q6k, q_q4k, k_q4k, v_q6k, head_q6k) over --layers "
+                         "layers, a small case for ncu; prints its timing and exits")
+    ap.add_argument("--reps", type=int, default=2, help="sweeps over the layers in --profile-kernel mode")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from ingot_b200 import BF16, Gpu, _abi
+    from ingot_b200.chain import QWEN3_8B, DecodeChain, weight_bytes_per_token
+    from ingot_b200.gpu import Buffer
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    stream = torch.cuda.Stream(device=local)
+    torch.cuda.set_stream(stream)
+    gpu = Gpu(local)
+    gpu.set_stream(stream.cuda_stream)
+
+    shape = QWEN3_8B
+    if args.profile_kernel:
+        chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=BF16, seed=0, layers=args.layers or 4)
+        peaks, peak_src = measured_peaks()
+        roof, per = kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=args.profile_kernel,
+                                     reps=args.reps)
+        print(json.dumps({"profile_kernel": args.profile_kernel, "layers": chain.n_layers, **per[args.profile_kernel]}))
+        gpu.close()
+        return
+
+    def all_gather(part: Buffer, full: Buffer, batch: int, rows_local: int):
+        n = batch * rows_local
+        src = _tensor_view(torch, part.ptr, n, local)
+        dst = _tensor_view(torch, full.ptr, n * world, local)
+        dist.all_gather_into_tensor(dst, src)
+
+    chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=BF16, seed=0, rank=rank, world=world,
+                        all_gather=all_gather if world > 1 else None, layers=args.layers,
+                        keep_host=1 if (rank == 0 and world == 1 and not args.no_cpu) else 0)
+    h0 = np.random.default_rng(1).normal(0, 1, (args.batch, shape.hidden)).astype(np.float32)
+    gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.h_in.ptr, h0.ctypes.data, h0.nbytes))
+    gpu.complete()
+
+    use_graph = world == 1
+    graph = chain.record() if use_graph else None
+
+    def one_step():
+        if graph is not None:
+            graph.submit()
+        else:
+            chain.step()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        one_step()
+    gpu.complete()
+    launches_per_step = chain.launches_per_step
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        one_step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    gpu.complete()
+    ms_per_step = ms / args.steps
+    value = args.batch * 1000.0 / ms_per_step
+
+    # ---- end to end through the C ABI: pinned host input in, logits out, every step ----
+    host_in, host_out = _pinned(gpu, h0.nbytes), _pinned(gpu, 4 * args.batch * shape.vocab)
+    C_memmove(host_in, h0)
+    for _ in range(2):
+        _e2e_step(gpu, chain, one_step, host_in, h0.nbytes, host_out)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _e2e_step(gpu, chain, one_step, host_in, h0.nbytes, host_out)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- roofline of the dominant kernel, measured here with CUDA events ----
+    peaks, peak_src = measured_peaks()
+    roof, per_kernel = None, None
+    if world == 1:
+        roof, per_kernel = kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu and chain.host:
+        threads = os.cpu_count() or 1
+        layer = [chain.host[(0, r)] for r in ("q", "k", "v", "o", "gate", "up", "down")]
+        dt, nbytes = cpu_layer_baseline(layer, threads, repeats=2)
+        total = weight_bytes_per_token(shape)
+        cpu = {"value": args.batch / (dt * total / nbytes), "unit": "tok/s", "cores": threads, "kind": "port",
+               "sample": "layer 0 of the same weights (7 GEMVs, %.1f MB), best of 2, scaled by bytes to the %.2f GB token step"
+                         % (nbytes / 1e6, total / 1e9)}
+
+    if rank == 0:
+        total_bytes = weight_bytes_per_token(shape) if args.layers is None else chain.bytes_streamed
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen3-8b-q4_k_m dense decode GEMV chain (configs[1]), batch %d" % args.batch,
+                       "layers": chain.n_layers, "hidden": shape.hidden, "ffn": shape.ffn, "vocab": shape.vocab,
+                       "weights": "random Q4_K/Q6_K blocks", "activations": "bf16 in HBM, fp32 accumulate",
+                       "parallelism": "tp%d rows" % world if world > 1 else "single GPU",
+                       "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (total_bytes * 1.0 / 1e9 / world),
+                       "launch": "one recorded command (CUDA graph) per step" if use_graph else "eager launches + NCCL all-gather"},
+            "hbm_gbs_effective": total_bytes / world / (ms_per_step * 1e-3) / 1e9,
+            "hbm_frac_of_peak_chain": total_bytes / world / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "e2e": {"value": args.batch * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(h0.nbytes), "d2h_bytes_per_step": int(4 * args.batch * shape.vocab)},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks, "roofline": roof, "kernels": per_kernel, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    gpu.close()
+
+
+# ---- helpers ------------------------------------------------------------------------
+
+def _tensor_view(torch, ptr: int, n_f32: int, device: int):
+    """A float32 torch tensor over `n_f32` elements of device memory owned by the library
+    (used only to hand activation buffers to NCCL)."""
+    class _Holder:
+        pass
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": (n_f32,), "typestr": "<f4", "data": (ptr, False), "version": 3,
+                                  "strides": None}
+    return torch.as_tensor(h, device=f"cuda:{device}")
+
+
+def _pinned(gpu, nbytes: int) -> int:
+    import ctypes as C
+    p = C.c_void_p()
+    gpu._check(gpu._lib.ingot_host_alloc(gpu._h, nbytes, C.byref(p)))
+    return p.value
+
+
+def C_memmove(dst_ptr: int, arr: np.ndarray) -> None:
+    import ctypes as C
+    C.memmove(dst_ptr, arr.ctypes.data, arr.nbytes)
+
+
+def _e2e_step(gpu, chain, one_step, host_in: int, in_bytes: int, host_out: int) -> None:
+    gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.h_in.ptr, host_in, in_bytes))
+    one_step()
+    gpu._check(gpu._lib.ingot_buffer_read(gpu._h, host_out, chain.logits.ptr, chain.logits.nbytes))
+
+
+def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps=None):
+    """Times each distinct GEMV of the step alone (CUDA events on the launching stream),
+    rotating over all layers' weights so every launch streams from HBM."""
+    from ingot_b200 import synth
+    s, b = chain.shape, chain.batch
+    xb = 2
+    lib, h = gpu._lib, gpu._h
+
+    def timed(fn, reps):
+        for i in range(len(chain.weights)):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        n = 0
+        for _ in range(reps):
+            for i in range(len(chain.weights)):
+                fn(i)
+                n += 1
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / n
+
+    def proj(role, x, y):
+        def fn(i):
+            w = chain.weights[i][role]
+            t = w.t
+            xp, xk = chain._x(x)
+            gpu._check(lib.ingot_matmul(h, w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, xp, xk, b, y.ptr))
+        return fn
+
+    def gate_up(i):
+        g, u = chain.weights[i]["gate"], chain.weights[i]["up"]
+        t = g.t
+        xp, xk = chain._x(chain.xn)
+        gpu._check(lib.ingot_gate_up(h, g.buffer.ptr, u.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, xp, xk, b, 0,
+                                     chain.act.ptr))
+
+    out = {}
+    reps = reps or max(1, 144 // max(len(chain.weights), 1))
+    cases = [("gate_up_q4k", gate_up, 2 * s.ffn * synth.stride_of(s.kinds["gate"], s.hidden), s.hidden, s.ffn),
+             ("down_q6k", proj("down", chain.actn, chain.d), s.hidden * synth.stride_of(s.kinds["down"], s.ffn), s.ffn, s.hidden),
+             ("q_q4k", proj("q", chain.xn, chain.q), s.q * synth.stride_of(s.kinds["q"], s.hidden), s.hidden, s.q),
+             ("k_q4k", proj("k", chain.xn, chain.k), s.kv * synth.stride_of(s.kinds["k"], s.hidden), s.hidden, s.kv),
+             ("v_q6k", proj("v", chain.xn, chain.v), s.kv * synth.stride_of(s.kinds["v"], s.hidden), s.hidden, s.kv)]
+    for name, fn, wbytes, cols, rows in cases:
+        if only and name != only:
+            continue
+        sec = timed(fn, reps)
+        algo = wbytes + b * cols * xb + b * rows * 4
+        out[name] = {"us": sec * 1e6, "bytes": algo, "gbs": algo / sec / 1e9, "frac": algo / sec / 1e9 / peaks["hbm_gbs"]}
+    if only and only != "head_q6k":
+        return None, out
+    # the head: one matrix of 510 MB, far larger than L2 on its own
+    t = chain.head.t
+    def head(i):
+        xp, xk = chain._x(chain.xn)
+        gpu._check(lib.ingot_matmul(h, chain.head.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, xp, xk, b,
+                                    chain.logits.ptr))
+    for _ in range(2):
+        head(0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(8):
+        head(0)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) * 1e-3 / 8
+    algo = t.dims[1] * t.stride + b * t.dims[0] * xb + b * t.dims[1] * 4
+    out["head_q6k"] = {"us": sec * 1e6, "bytes": algo, "gbs": algo / sec / 1e9, "frac": algo / sec / 1e9 / peaks["hbm_gbs"]}
+    if only:
+        return None, out
+    g = out["gate_up_q4k"]
+    roof = {"bound": "hbm", "kernel": "gemv_stream_kernel<Q4_K, 1 token, gate+up fused> 4096 -> 2 x 12288",
+            "achieved": g["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": g["frac"], "peak_source": peak_src,
+            "bytes_per_launch": g["bytes"], "us_per_launch": g["us"], "traffic": None}
+    return roof, out
+
+
+if __name__ == "__main__":
+    main()

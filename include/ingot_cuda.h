@@ -62,6 +62,9 @@ enum {
     INGOT_KIND_Q4_K = 12, INGOT_KIND_Q6_K = 14, INGOT_KIND_BF16 = 30
 };
 
+/* x_kind of activation rows already packed by ingot_pack_x */
+enum { INGOT_X_PACKED = 256 };
+
 typedef struct ingot_gpu ingot_gpu;      /* opaque; the reference's `Gpu` */
 typedef struct ingot_graph ingot_graph;  /* opaque; a recorded `Command` */
 
@@ -96,8 +99,10 @@ INGOT_API ingot_status ingot_gpu_set_stream(ingot_gpu *gpu, void *cuda_stream);
 /* Options: INGOT_OPT_PDL (default 1) launches kernels with programmatic
  * dependent launch so a kernel's weight prefetch overlaps its predecessor's
  * tail; INGOT_OPT_FORCE_PLAIN (default 0) routes every GEMV through the plain
- * one-warp-per-row kernel (a test hook). */
-enum { INGOT_OPT_PDL = 1, INGOT_OPT_FORCE_PLAIN = 2 };
+ * one-warp-per-row kernel (a test hook); INGOT_OPT_NO_MMA (default 0) keeps the
+ * streaming GEMV on the fp32 CUDA-core kernel instead of the one whose inner
+ * products run on the tensor cores (a test and comparison hook). */
+enum { INGOT_OPT_PDL = 1, INGOT_OPT_FORCE_PLAIN = 2, INGOT_OPT_NO_MMA = 3 };
 INGOT_API ingot_status ingot_gpu_set_option(ingot_gpu *gpu, int32_t option, int32_t value);
 
 /* Command::wait / Gpu::complete (src/metal.rs:1224-1235): blocks until the
@@ -208,6 +213,18 @@ INGOT_API ingot_status ingot_combine_packed(ingot_gpu *gpu, const float *routed,
 
 /* float32 -> bfloat16 (round to nearest even) for activations. */
 INGOT_API ingot_status ingot_convert_bf16(ingot_gpu *gpu, const float *x, uint64_t n, void *y_bf16);
+
+/* Activations in the order the tensor-core GEMV consumes them.  No counterpart in
+ * the reference (its kernels read float32 x directly); on B200 packing once and
+ * handing the same packed row to every projection that reads it (q, k, v; gate
+ * and up) removes the conversion from each GEMV.  A packed row holds, for `cols`
+ * (a multiple of 64) activations: binary16 (high, low) halves, the fp32 sum of
+ * every 16 columns, and a power-of-two scale.  Pass it with x_kind =
+ * INGOT_X_PACKED to ingot_matmul (count 1), ingot_gate_up (count 1), ingot_routed
+ * and ingot_routed_gate_up; row r of `packed` starts at r * ingot_packed_x_bytes. */
+INGOT_API ingot_status ingot_packed_x_bytes(uint32_t cols, uint64_t *bytes);
+INGOT_API ingot_status ingot_pack_x(ingot_gpu *gpu, const void *x, uint32_t x_kind, uint32_t rows, uint32_t cols,
+                                    void *packed);
 
 /* ---- command recording (Command: src/metal.rs:659-673; a whole decode step
  *      is one command buffer, src/generic.rs:701-704) ---------------------- */

@@ -1,0 +1,187 @@
+"""The per-token GEMV chain of a dense decoder, issued through the C ABI.
+
+This is the projection skeleton of the reference's `Generic::hidden`
+(src/generic.rs:664-763) at decode: per layer q, k, v, o, fused gate/up + GLU,
+down; then the output head.  Attention itself is not on this path: the
+attention output is stood in for by the (normalised) q projection so that every
+weight byte of a token step is still streamed exactly once and magnitudes stay
+O(1) through the layers.  Between projections an unweighted RMS normalisation
+(`add_rms`, kernels/generic.metal:390-404) carries the residual stream in
+float32 and hands bfloat16 (or float32) activations to the next projection.
+
+Rows can be sharded tensor-parallel: rank r of n owns rows [r*N/n, (r+1)*N/n) of
+every matrix (block quantisation runs along K, so a row split keeps the GGUF
+layout) and an `all_gather` callback rebuilds full activations where the next
+operator needs them.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import synth
+from .gpu import BF16, F32, X_PACKED, Buffer, Gpu, Tensor, Weight
+
+
+@dataclass
+class DenseShape:
+    name: str
+    layers: int
+    hidden: int
+    q: int            # rows of the q projection (= o's cols)
+    kv: int
+    ffn: int
+    vocab: int
+    kinds: dict       # role -> GGML kind
+    gelu: bool = False
+
+
+QWEN3_8B = DenseShape("qwen3-8b-q4_k_m", 36, 4096, 4096, 1024, 12288, 151936,
+                      {"q": synth.Q4_K, "k": synth.Q4_K, "v": synth.Q6_K, "o": synth.Q4_K, "gate": synth.Q4_K,
+                       "up": synth.Q4_K, "down": synth.Q6_K, "head": synth.Q6_K})
+GEMMA3_4B = DenseShape("gemma3-4b-q4_0", 34, 2560, 2048, 1024, 10240, 262144,
+                       {r: synth.Q4_0 for r in ("q", "k", "v", "o", "gate", "up", "down", "head")}, gelu=True)
+
+
+def layer_roles(s: DenseShape):
+    """(role, cols, rows) of one layer."""
+    return [("q", s.hidden, s.q), ("k", s.hidden, s.kv), ("v", s.hidden, s.kv), ("o", s.q, s.hidden),
+            ("gate", s.hidden, s.ffn), ("up", s.hidden, s.ffn), ("down", s.ffn, s.hidden)]
+
+
+def weight_bytes_per_token(s: DenseShape) -> int:
+    per_layer = sum(synth.stride_of(s.kinds[r], c) * n for r, c, n in layer_roles(s))
+    return s.layers * per_layer + synth.stride_of(s.kinds["head"], s.hidden) * s.vocab
+
+
+def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Rows [begin, end) that `rank` owns out of `world`."""
+    return rows * rank // world, rows * (rank + 1) // world
+
+
+class DecodeChain:
+    """Weights of one dense model (or this rank's row shard) resident in HBM and the
+    buffers of one decode step for `batch` tokens."""
+
+    def __init__(self, gpu: Gpu, shape: DenseShape, batch: int = 1, x_kind: int = BF16, seed: int = 0,
+                 rank: int = 0, world: int = 1, all_gather=None, layers: int | None = None,
+                 keep_host: int = 0):
+        self.gpu, self.shape, self.batch, self.x_kind = gpu, shape, batch, x_kind
+        self.rank, self.world, self.all_gather = rank, world, all_gather
+        self.n_layers = shape.layers if layers is None else layers
+        self.host = {}                 # (layer, role) -> (bytes, cols, rows, kind) kept for checks/baselines
+        self.weights: list[dict[str, Weight]] = []
+        self.bytes_streamed = 0
+        for layer in range(self.n_layers):
+            ws = {}
+            for role, cols, rows in layer_roles(shape):
+                ws[role] = self._make(layer, role, cols, rows, shape.kinds[role], seed, layer < keep_host)
+            self.weights.append(ws)
+        self.head = self._make(self.n_layers, "head", shape.hidden, shape.vocab, shape.kinds["head"], seed,
+                               keep_host > 0)
+        b, h = batch, shape.hidden
+        xb = 2 if x_kind == BF16 else 4
+        self.h_in = gpu.zeros(b * h)                  # the step's input hidden state (float32)
+        self.h = gpu.zeros(b * h)                     # residual stream
+        self.xn = gpu.empty_bytes(b * h * xb)
+        self.q, self.k, self.v = gpu.zeros(b * shape.q), gpu.zeros(b * shape.kv), gpu.zeros(b * shape.kv)
+        self.a = gpu.empty_bytes(b * shape.q * xb)
+        self.o = gpu.zeros(b * h)
+        self.act = gpu.zeros(b * shape.ffn)
+        self.actn = gpu.empty_bytes(b * shape.ffn * xb)
+        self.d = gpu.zeros(b * h)
+        self.logits = gpu.zeros(b * shape.vocab)
+        # per-rank partial outputs when sharded
+        self.part = gpu.zeros(b * max(shape.ffn, shape.vocab) // world + b * 8) if world > 1 else None
+        # activations packed once per distinct GEMV input (one token: the tensor-core GEMV)
+        self.packed = batch == 1
+        if self.packed:
+            self.xn_p = gpu.empty_bytes(gpu.packed_x_bytes(h))
+            self.a_p = gpu.empty_bytes(gpu.packed_x_bytes(shape.q))
+            self.actn_p = gpu.empty_bytes(gpu.packed_x_bytes(shape.ffn))
+        self.launches_per_step = 0
+
+    def _make(self, layer, role, cols, rows, kind, seed, keep) -> Weight:
+        r0, r1 = shard_rows(rows, self.rank, self.world)
+        stride = synth.stride_of(kind, cols)
+        role_id = ["q", "k", "v", "o", "gate", "up", "down", "head"].index(role)
+        full_seed = (seed * 1000003 + layer * 64 + role_id) & 0x7FFFFFFF
+        if self.world == 1:
+            raw = synth.random_matrix(kind, cols, rows, seed=full_seed)
+        else:   # every rank draws the same full matrix stream and keeps its rows
+            raw = synth.random_matrix(kind, cols, rows, seed=full_seed).reshape(rows, stride)[r0:r1].reshape(-1)
+        if keep:
+            self.host[(layer, role)] = (raw, cols, r1 - r0, kind)
+        self.bytes_streamed += raw.size
+        return Weight(self.gpu.load_weight(raw, Tensor.of([cols, r1 - r0], kind)), Tensor.of([cols, r1 - r0], kind))
+
+    # ---- one decode step -------------------------------------------------------
+    def _norm(self, a: Buffer, b: Buffer | None, s: Buffer | None, out: Buffer, width: int) -> None:
+        g = self.gpu
+        y32 = out.ptr if self.x_kind == F32 else None
+        y16 = out.ptr if self.x_kind == BF16 else None
+        g._check(g._lib.ingot_add_rms(g._h, a.ptr, b.ptr if b else None, None, s.ptr if s else None, y32, y16,
+                                      width, self.batch, 1e-6, 1 if b else 0))
+        self.launches_per_step += 1
+        if self.packed:
+            dst = {self.xn.ptr: self.xn_p, self.a.ptr: self.a_p, self.actn.ptr: self.actn_p}[out.ptr]
+            g._check(g._lib.ingot_pack_x(g._h, out.ptr, self.x_kind, 1, width, dst.ptr))
+            self.launches_per_step += 1
+
+    def _x(self, x: Buffer):
+        """(pointer, x_kind) of a GEMV input: the packed copy when there is one."""
+        if self.packed:
+            return {self.xn.ptr: self.xn_p, self.a.ptr: self.a_p, self.actn.ptr: self.actn_p}[x.ptr].ptr, X_PACKED
+        return x.ptr, self.x_kind
+
+    def _project(self, w: Weight, x: Buffer, y: Buffer) -> None:
+        g, t = self.gpu, w.t
+        dst = y if self.world == 1 else self.part
+        xp, xk = self._x(x)
+        g._check(g._lib.ingot_matmul(g._h, w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, xp, xk, self.batch,
+                                     dst.ptr))
+        self.launches_per_step += 1
+        if self.world > 1:
+            self.all_gather(dst, y, self.batch, t.dims[1])
+
+    def _gate_up(self, gate: Weight, up: Weight, x: Buffer, y: Buffer) -> None:
+        g, t = self.gpu, gate.t
+        dst = y if self.world == 1 else self.part
+        xp, xk = self._x(x)
+        g._check(g._lib.ingot_gate_up(g._h, gate.buffer.ptr, up.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind,
+                                      xp, xk, self.batch, int(self.shape.gelu), dst.ptr))
+        self.launches_per_step += 1
+        if self.world > 1:
+            self.all_gather(dst, y, self.batch, t.dims[1])
+
+    def step(self) -> None:
+        """Issues one token step on the handle's stream (asynchronous)."""
+        s = self.shape
+        self.launches_per_step = 0
+        delta = None
+        src = self.h_in
+        for ws in self.weights:
+            self._norm(src, delta, self.h if delta else None, self.xn, s.hidden)
+            if delta is None and src is self.h_in:
+                resid = self.h_in
+            else:
+                resid = self.h
+            self._project(ws["q"], self.xn, self.q)
+            self._project(ws["k"], self.xn, self.k)
+            self._project(ws["v"], self.xn, self.v)
+            self._norm(self.q, None, None, self.a, s.q)
+            self._project(ws["o"], self.a, self.o)
+            self._norm(resid, self.o, self.h, self.xn, s.hidden)
+            self._gate_up(ws["gate"], ws["up"], self.xn, self.act)
+            self._norm(self.act, None, None, self.actn, s.ffn)
+            self._project(ws["down"], self.actn, self.d)
+            src, delta = self.h, self.d
+        self._norm(src, delta, self.h if delta else None, self.xn, s.hidden)
+        self._project(self.head, self.xn, self.logits)
+
+    def record(self):
+        """Records one step as a replayable command (a CUDA graph)."""
+        self.gpu.record()
+        self.step()
+        return self.gpu.end_record()

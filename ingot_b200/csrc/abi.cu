@@ -21,10 +21,13 @@ struct ingot_gpu {
     cudaStream_t stream = nullptr;
     int *status = nullptr;            // device status word
     int *status_host = nullptr;       // pinned mirror
+    void *workspace = nullptr;        // scratch for packed activations
+    size_t workspace_bytes = 0;
     uint32_t sm_count = 0;
     bool failed = false;              // sticky device failure
     bool pdl = true;
     bool force_plain = false;
+    bool no_mma = false;
     bool capturing = false;
     std::string error;
 };
@@ -65,6 +68,9 @@ LaunchCtx ctx_of(const ingot_gpu *g) {
     c.sm_count = g->sm_count;
     c.pdl = g->pdl;
     c.force_plain = g->force_plain;
+    c.no_mma = g->no_mma;
+    c.workspace = g->workspace;
+    c.workspace_bytes = g->workspace_bytes;
     return c;
 }
 
@@ -74,7 +80,9 @@ ingot_status after_launch(ingot_gpu *g, cudaError_t e, const char *what) {
     return INGOT_OK;
 }
 
-bool x_kind_ok(uint32_t k) { return k == INGOT_KIND_F32 || k == INGOT_KIND_BF16; }
+bool x_kind_ok(uint32_t k) { return k == INGOT_KIND_F32 || k == INGOT_KIND_BF16 || k == INGOT_X_PACKED; }
+
+constexpr size_t WORKSPACE_BYTES = 16u << 20;
 
 // validate_matrix (src/metal.rs:1602-1621) on the integer parameters.
 ingot_status check_matrix(ingot_gpu *g, uint32_t kind, uint64_t cols, uint64_t rows, uint64_t stride) {
@@ -130,10 +138,12 @@ ingot_status ingot_gpu_create(int32_t device, ingot_gpu **out) {
     g->sm_count = (uint32_t)prop.multiProcessorCount;
     if (cudaStreamCreateWithFlags(&g->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc(&g->status, 64) != cudaSuccess || cudaMemset(g->status, 0, 64) != cudaSuccess ||
-        cudaHostAlloc(&g->status_host, 64, cudaHostAllocDefault) != cudaSuccess) {
+        cudaHostAlloc(&g->status_host, 64, cudaHostAllocDefault) != cudaSuccess ||
+        cudaMalloc(&g->workspace, WORKSPACE_BYTES) != cudaSuccess) {
         ingot_gpu_destroy(g);
         return INGOT_DEVICE;
     }
+    g->workspace_bytes = WORKSPACE_BYTES;
     g->stream = g->own_stream;
     *out = g;
     return INGOT_OK;
@@ -144,6 +154,7 @@ void ingot_gpu_destroy(ingot_gpu *g) {
     cudaSetDevice(g->device);
     if (g->own_stream) { cudaStreamSynchronize(g->own_stream); cudaStreamDestroy(g->own_stream); }
     if (g->status) cudaFree(g->status);
+    if (g->workspace) cudaFree(g->workspace);
     if (g->status_host) cudaFreeHost(g->status_host);
     delete g;
 }
@@ -162,6 +173,7 @@ ingot_status ingot_gpu_set_option(ingot_gpu *g, int32_t option, int32_t value) {
     switch (option) {
     case INGOT_OPT_PDL: g->pdl = value != 0; return INGOT_OK;
     case INGOT_OPT_FORCE_PLAIN: g->force_plain = value != 0; return INGOT_OK;
+    case INGOT_OPT_NO_MMA: g->no_mma = value != 0; return INGOT_OK;
     default: return fail(g, INGOT_INVALID, "unknown option");
     }
 }
@@ -285,9 +297,17 @@ static ingot_status gemv_common(ingot_gpu *g, GemvCall &c, uint32_t x_kind, cons
     ingot_status st = enter(g);
     if (st) return st;
     if ((st = check_matrix(g, c.kind, c.cols, c.rows, c.stride))) return st;
-    if (!x_kind_ok(x_kind)) return fail(g, INGOT_UNSUPPORTED, "activations must be F32 (0) or BF16 (30)");
+    if (!x_kind_ok(x_kind)) return fail(g, INGOT_UNSUPPORTED, "activations must be F32 (0), BF16 (30) or packed");
     if (!c.w[0] || (c.nmat == 2 && !c.w[1]) || !c.x || !c.y) return fail(g, INGOT_INVALID, "null pointer");
     c.x_bf16 = x_kind == INGOT_KIND_BF16;
+    c.x_packed = x_kind == INGOT_X_PACKED;
+    if (c.x_packed) {
+        // packed rows only feed the tensor-core GEMV: one token, a block-quantised type, 16-byte aligned rows
+        cudaError_t e = cudaSuccess;
+        if (((uintptr_t)c.x % 16u) || !try_launch_gemv_mma(c, ctx_of(g), e))
+            return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": packed activations need one token and a quantised weight");
+        return after_launch(g, e, what);
+    }
     return after_launch(g, launch_gemv(c, ctx_of(g)), what);
 }
 
@@ -398,6 +418,20 @@ ingot_status ingot_convert_bf16(ingot_gpu *g, const float *x, uint64_t n, void *
     if (st) return st;
     if (!x || !y) return fail(g, INGOT_INVALID, "null pointer");
     return after_launch(g, launch_convert_bf16(x, n, y, ctx_of(g)), "convert_bf16");
+}
+
+ingot_status ingot_packed_x_bytes(uint32_t cols, uint64_t *bytes) {
+    if (!bytes || cols == 0 || cols % 64u) return INGOT_INVALID;
+    *bytes = packed_x_bytes(cols);
+    return INGOT_OK;
+}
+
+ingot_status ingot_pack_x(ingot_gpu *g, const void *x, uint32_t x_kind, uint32_t rows, uint32_t cols, void *packed) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!x || !packed || cols == 0 || cols % 64u || ((uintptr_t)packed % 16u)) return fail(g, INGOT_INVALID, "pack_x: bad arguments");
+    if (x_kind != INGOT_KIND_F32 && x_kind != INGOT_KIND_BF16) return fail(g, INGOT_UNSUPPORTED, "pack_x: activations must be F32 or BF16");
+    return after_launch(g, launch_pack_x(x, x_kind == INGOT_KIND_BF16, rows, cols, packed, ctx_of(g)), "pack_x");
 }
 
 // ---- command recording --------------------------------------------------------

@@ -1,6 +1,7 @@
 // GEMV kernels: the bulk-copy streaming kernel for block-quantised weights and
 // the plain one-warp-per-row kernel for everything else (float weights,
 // unaligned rows).  Dense, fused gate/up and expert-routed forms share both.
+#include "dev_common.cuh"
 #include "gemv_core.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -25,10 +26,6 @@ struct GemvArgs {
     int *status;              // device status word (0 = ok)
 };
 
-__device__ __forceinline__ void set_status(int *status, int code) {
-    if (status) atomicCAS(status, 0, code);
-}
-
 template <uint32_t KIND>
 __device__ __forceinline__ void stage_x(F4 *xs, const GemvArgs &a, uint32_t x_row0, uint32_t ntok, uint32_t tid,
                                         uint32_t nthreads) {
@@ -40,13 +37,11 @@ __device__ __forceinline__ void stage_x(F4 *xs, const GemvArgs &a, uint32_t x_ro
             F4 v;
             if (a.x_bf16) {
                 const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(a.x) + base + 4u * f);
-                v.x = __uint_as_float(raw.x << 16);
-                v.y = __uint_as_float(raw.x & 0xffff0000u);
-                v.z = __uint_as_float(raw.y << 16);
-                v.w = __uint_as_float(raw.y & 0xffff0000u);
+                v = permute_x(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                              __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
             } else {
                 const float4 raw = *reinterpret_cast<const float4 *>(static_cast<const float *>(a.x) + base + 4u * f);
-                v.x = raw.x; v.y = raw.y; v.z = raw.z; v.w = raw.w;
+                v = permute_x(raw.x, raw.y, raw.z, raw.w);
             }
             uint32_t u, i;
             Unit<KIND>::locate(4u * f, u, i);
@@ -98,7 +93,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_stream_kernel(const __gr
                 bool ok = true;
                 if (lane == 0) ok = ptx::mbar_wait(&empty[s], ph ^ 1u);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) { if (lane == 0) set_status(a.status, KERNEL_ERR_PRODUCER_TIMEOUT); return; }
+                if (!ok) { if (lane == 0) set_status_word(a.status, KERNEL_ERR_PRODUCER_TIMEOUT); return; }
                 const uint32_t cb = (c + 1 == p.chunks) ? p.last_chunk_bytes : p.chunk_bytes;
                 uint8_t *dst = stages + (size_t)s * p.stage_bytes;
                 if (lane == 0) ptx::mbar_expect_tx(&full[s], cb * nrows * NMAT);
@@ -125,7 +120,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_stream_kernel(const __gr
     uint32_t x_row0 = 0;
     if (a.ids) {
         if (a.ids[pair] >= a.n_experts) {
-            if (threadIdx.x == 0) set_status(a.status, KERNEL_ERR_EXPERT_RANGE);
+            if (threadIdx.x == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
             return;
         }
         x_row0 = a.per_pair ? pair : pair / a.top;
@@ -150,7 +145,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_stream_kernel(const __gr
         for (uint32_t c = 0; c < p.chunks; ++c, ++it) {
             const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
             if (!ptx::mbar_wait(&full[s], ph)) {
-                if (lane == 0) set_status(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
+                if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
                 return;
             }
             consume_chunk<KIND, NTOK, NMAT>(stages + (size_t)s * p.stage_bytes, xs, p, warp, lane, c, nrows, acc);
@@ -193,10 +188,6 @@ struct PlainArgs {
     int *status;
 };
 
-__device__ __forceinline__ float load_x(const void *x, size_t i, uint32_t bf16) {
-    return bf16 ? __uint_as_float((uint32_t)static_cast<const uint16_t *>(x)[i] << 16) : static_cast<const float *>(x)[i];
-}
-
 __global__ void __launch_bounds__(128) gemv_plain_kernel(const __grid_constant__ PlainArgs a) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
@@ -208,7 +199,7 @@ __global__ void __launch_bounds__(128) gemv_plain_kernel(const __grid_constant__
     if (a.ids) {
         expert = a.ids[item];
         if (expert >= a.n_experts) {
-            if (lane == 0 && row == 0) set_status(a.status, KERNEL_ERR_EXPERT_RANGE);
+            if (lane == 0 && row == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
             return;
         }
         x_row = a.per_pair ? item : item / a.top;
@@ -297,6 +288,10 @@ cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx) {
     if (items == 0) return cudaSuccess;
     const bool aligned = ((uintptr_t)c.w[0] % 16u) == 0 && (c.nmat < 2 || ((uintptr_t)c.w[1] % 16u) == 0) &&
                          ((uintptr_t)c.x % 16u) == 0 && ((size_t)c.rows * c.stride) % 16u == 0;
+    if (!ctx.force_plain && !ctx.no_mma && aligned) {
+        cudaError_t e = cudaSuccess;
+        if (try_launch_gemv_mma(c, ctx, e)) return e;
+    }
     if (!ctx.force_plain && aligned) {
         // tokens go through in groups the activations' shared-memory area can hold
         uint32_t group = routed ? 1u : (c.count < 4u ? c.count : 4u);

@@ -156,6 +156,11 @@ IG_HD void consume_chunk(const uint8_t *stage, const F4 *xs, const GemvPlan &p, 
     }
 }
 
+// Bytes of one activation row packed for the tensor-core GEMV: binary16 (xh, xl)
+// pairs in B-operand order, fp32 sums of each 16 columns, and 16 bytes holding
+// 1/scale.  cols must be a multiple of 64.
+IG_HD uint32_t packed_x_bytes(uint32_t cols) { return cols * 4u + cols / 4u + 16u; }
+
 // silu(g)*u or tanh-GeLU(g)*u (reference glu: kernels/generic.metal:298).
 IG_HD float glu_f(float g, float u, bool gelu) {
     if (gelu) {

@@ -1,0 +1,680 @@
+// Streaming GEMV whose inner products run on the tensor cores from registers.
+//
+// Why: on sm_100 an fp32 multiply-add per weight needs an integer extract, an
+// int->float step and an FMA — at least 3.7 issued instructions per weight, with
+// the half-rate integer pipe the first to saturate — which caps 4-bit formats
+// near half of HBM bandwidth (measured; see the profile summaries).  Here a lane
+// turns packed quants into binary16 operand registers with one logic op and one
+// packed subtract per TWO weights ((w & 0x000f000f) | 0x64006400 is the pair
+// (1024+q0, 1024+q2); minus 1024 is exact) and a warp-level mma.sync m16n8k16
+// (f16 x f16 -> f32) multiplies 16 rows by 16 columns at once.  Nothing is staged
+// through shared memory in decoded form and the kernel stays a bandwidth-bound
+// GEMV: one CTA streams a contiguous range of rows through a ring of bulk-copy
+// stages, eight warps split the columns of each 16-row tile.
+//
+// Numerics: quants are small integers, exact in binary16.  An activation x is
+// split into xh = f16(x) and xl = f16(x - xh) (two columns of the B operand), so
+// q * x keeps 22 bits of x; products are exact and accumulate in fp32.  Scales
+// are applied in fp32 outside the MMA, group by group, in the factored forms the
+// reference's kernels use (kernels/iq3_mix.metal:104-123,
+// kernels/decode.metal:66-83, kernels/generic.metal:242-269).
+//
+// One m16n8k16 covers 16 consecutive columns [16 mi, 16 mi + 16) of 16 rows.  For
+// lane (g = lane / 4, t = lane % 4):
+//   A (rows x k): a0 = row g,   k {2t, 2t+1};   a1 = row g+8, same k;
+//                 a2 = row g,   k {2t+8, 2t+9}; a3 = row g+8, same k
+//   B (k x n):    b0 = k {2t, 2t+1}, n = g;     b1 = k {2t+8, 2t+9}, n = g
+//   C (rows x n): c0,c1 = row g, n {2t, 2t+1};  c2,c3 = row g+8, same n
+// Lane t supplies columns 16 mi + 4t .. +3 from ONE 32-bit word of quants: bytes
+// (0,2) form one operand register and bytes (1,3) the other, i.e. k slots
+// {2t, 2t+1, 2t+8, 2t+9} = bytes {0, 2, 1, 3}.  Activations are pre-packed to
+// match (pack_x_kernel): [mi][part: xh, xl][t][4 halves].  Even columns n carry xh
+// and odd ones xl, replicated over the quads, so every lane ends with (sum q xh,
+// sum q xl) in (c0, c1) and the four lanes of a quad share the scale work.
+#include <cuda_fp16.h>
+
+#include "dev_common.cuh"
+#include "gemv_core.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace ingot {
+
+static constexpr int MMA_WARPS = 8;                       // consumer warps
+static constexpr int MMA_THREADS = (MMA_WARPS + 1) * 32;  // + producer warp
+static constexpr uint32_t MMA_SMEM_BUDGET = 112u * 1024u; // two CTAs per SM
+static constexpr uint32_t MMA_SMEM_MAX = 224u * 1024u;
+static constexpr uint32_t MMA_STAGE_TARGET = 40u * 1024u;
+static constexpr int MMA_MAX_STAGES = 6;                  // barriers: full[6], empty[6], x
+
+struct MmaPlan {
+    uint32_t kind, cols, rows, stride, nmat;
+    uint32_t step_cols;      // columns one warp handles per step (format dependent)
+    uint32_t step_bytes;     // bytes of a row in one step
+    uint32_t nsteps;         // cols / step_cols
+    uint32_t kw_log2;        // warps splitting K: 1 << kw_log2
+    uint32_t row_tiles;      // 16-row tiles per stage = 8 >> kw_log2
+    uint32_t spw;            // steps per warp per chunk
+    uint32_t chunks, chunk_bytes;
+    uint32_t row_pitch;      // bytes between rows inside a stage (16 mod 128: conflict-free word loads)
+    uint32_t stages, stage_bytes;
+    uint32_t x_bytes;        // packed activations of one token
+    uint32_t red_bytes, smem_bytes;
+    uint32_t ctas;
+};
+
+struct MmaArgs {
+    MmaPlan plan;
+    const uint8_t *w[2];
+    const uint8_t *xp;        // packed activations [row][packed_x_bytes(cols)]
+    float *y;
+    const uint32_t *ids;
+    uint32_t expert, n_experts, per_pair, top, glu;
+    int *status;
+};
+
+static bool mma_kind(uint32_t kind) { return kind == KIND_Q4_K || kind == KIND_Q6_K || kind == KIND_Q4_0 || kind == KIND_Q8_0; }
+
+static void step_geometry(uint32_t kind, uint32_t &cols, uint32_t &bytes) {
+    switch (kind) {
+    case KIND_Q4_K: cols = 256; bytes = 144; break;
+    case KIND_Q6_K: cols = 256; bytes = 210; break;
+    case KIND_Q4_0: cols = 128; bytes = 72; break;
+    default: cols = 128; bytes = 136; break;     // Q8_0
+    }
+}
+
+static uint32_t pitch_of(uint32_t chunk_bytes) { return chunk_bytes + ((16u + 128u - (chunk_bytes % 128u)) % 128u); }
+
+static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t nmat, uint32_t max_ctas,
+                     uint32_t budget, MmaPlan &p) {
+    if (!mma_kind(kind)) return false;
+    uint32_t block, bytes;
+    geometry(kind, block, bytes);
+    if (cols == 0 || rows == 0 || cols % block || stride != cols / block * bytes) return false;
+    step_geometry(kind, p.step_cols, p.step_bytes);
+    if (cols % p.step_cols || stride % 16u) return false;
+    p.kind = kind; p.cols = cols; p.rows = rows; p.stride = stride; p.nmat = nmat;
+    p.nsteps = cols / p.step_cols;
+    uint32_t kw = 3;
+    while (kw > 0 && (p.nsteps % (1u << kw))) --kw;
+    p.kw_log2 = kw;
+    p.row_tiles = (uint32_t)MMA_WARPS >> kw;
+    const uint32_t per_warp = p.nsteps >> kw;                 // steps each warp owns per row
+    p.x_bytes = packed_x_bytes(cols);
+    p.red_bytes = 2u * MMA_WARPS * 2u * 16u * 4u;             // [parity][warp][mat][row]
+    const uint32_t fixed = GEMV_BAR_BYTES + ((p.x_bytes + 127u) & ~127u) + p.red_bytes;
+    if (fixed >= budget) return false;
+    // chunk = the most steps per warp whose stage stays near the target, leaves at least
+    // two stages, and keeps every copy 16-byte aligned
+    const uint32_t room = budget - fixed;
+    uint32_t pick = 0;
+    for (uint32_t spw = 1; spw <= per_warp; ++spw) {
+        if (per_warp % spw) continue;
+        const uint32_t cb = spw * (1u << kw) * p.step_bytes;
+        if (cb % 16u) continue;
+        const uint32_t sb = (pitch_of(cb) * 16u * p.row_tiles * nmat + 64u + 127u) & ~127u;
+        if (room / sb < 2) break;
+        if (pick == 0 || sb <= MMA_STAGE_TARGET) pick = spw;
+    }
+    if (pick == 0) return false;
+    p.spw = pick;
+    p.chunks = per_warp / pick;
+    p.chunk_bytes = pick * (1u << kw) * p.step_bytes;
+    p.row_pitch = pitch_of(p.chunk_bytes);
+    p.stage_bytes = (p.row_pitch * 16u * p.row_tiles * nmat + 64u + 127u) & ~127u;
+    p.stages = room / p.stage_bytes;
+    if (p.stages > (uint32_t)MMA_MAX_STAGES) p.stages = MMA_MAX_STAGES;
+    if (p.stages < 2) return false;
+    p.smem_bytes = fixed + p.stages * p.stage_bytes;
+    const uint32_t want = (rows + 7u) / 8u;
+    p.ctas = want < max_ctas ? want : max_ctas;
+    if (p.ctas == 0) p.ctas = 1;
+    return true;
+}
+
+// ---------------------------------------------------------------------------
+// Packing activations into the B-operand order.  One CTA per activation row.
+// Packed row: [cols/16 MMAs][2 parts][4 lanes][4 halves] | cols/16 fp32 sums of
+// each 16 (scaled) activations | 16 bytes: 1/scale.  x is pre-multiplied by a
+// power of two when its magnitude would overflow binary16.
+// ---------------------------------------------------------------------------
+
+struct PackArgs {
+    const void *x;
+    uint8_t *out;
+    uint32_t cols, bf16;
+};
+
+__global__ void __launch_bounds__(256) pack_x_kernel(const __grid_constant__ PackArgs a) {
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+    __shared__ float part_max[8];
+    const uint32_t tid = threadIdx.x;
+    const size_t base = (size_t)blockIdx.x * a.cols;
+    uint8_t *row = a.out + (size_t)blockIdx.x * packed_x_bytes(a.cols);
+    float mx = 0.f;
+    for (uint32_t c = tid; c < a.cols; c += 256) mx = fmaxf(mx, fabsf(load_x(a.x, base + c, a.bf16)));
+    for (uint32_t off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if ((tid & 31u) == 0) part_max[tid >> 5] = mx;
+    __syncthreads();
+    mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, part_max[i]);
+    float scale = 1.0f;
+    if (mx >= 16384.0f && mx < INFINITY) {
+        int e;
+        frexpf(mx, &e);                       // mx = f * 2^e, f in [0.5, 1)
+        scale = ldexpf(1.0f, 14 - e);         // mx * scale in [2^13, 2^14)
+    }
+    __half *xf = reinterpret_cast<__half *>(row);
+    float *sx = reinterpret_cast<float *>(row + (size_t)a.cols * 4u);
+    // one thread per 4 consecutive columns = one lane's word of one MMA; every thread
+    // runs the same number of rounds so the quad shuffles always have all lanes
+    const uint32_t n4 = a.cols / 4u;
+    for (uint32_t q0 = 0; q0 < n4; q0 += 256) {
+        const uint32_t q = q0 + tid;
+        const bool live = q < n4;
+        const uint32_t mi = q >> 2, t = q & 3u;
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = live ? load_x(a.x, base + 4u * q + i, a.bf16) * scale : 0.f;
+        __half h[4], l[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            h[i] = __float2half_rn(v[i]);
+            l[i] = __float2half_rn(v[i] - __half2float(h[i]));
+        }
+        if (live) {
+            // slots: byte 0 -> b0.lo, byte 2 -> b0.hi, byte 1 -> b1.lo, byte 3 -> b1.hi
+            __half2 *dh = reinterpret_cast<__half2 *>(xf + ((mi * 2u + 0u) * 4u + t) * 4u);
+            __half2 *dl = reinterpret_cast<__half2 *>(xf + ((mi * 2u + 1u) * 4u + t) * 4u);
+            dh[0] = __halves2half2(h[0], h[2]); dh[1] = __halves2half2(h[1], h[3]);
+            dl[0] = __halves2half2(l[0], l[2]); dl[1] = __halves2half2(l[1], l[3]);
+        }
+        // the 16-column sum: four lanes, fixed order
+        float s = (v[0] + v[1]) + (v[2] + v[3]);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        if (live && t == 0) sx[mi] = s;
+    }
+    if (tid == 0) *reinterpret_cast<float *>(row + (size_t)a.cols * 4u + a.cols / 4u) = 1.0f / scale;
+}
+
+cudaError_t launch_pack_x(const void *x, uint32_t bf16, uint32_t rows, uint32_t cols, void *packed, const LaunchCtx &ctx) {
+    if (rows == 0) return cudaSuccess;
+    if (cols % 64u) return cudaErrorInvalidValue;
+    PackArgs a = {x, static_cast<uint8_t *>(packed), cols, bf16};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, pack_x_kernel, a);
+}
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// d = A B (accumulator starts at zero without zeroing registers first)
+__device__ __forceinline__ void mma16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// two binary16 magic numbers (bias + v) -> the two integers v, exactly
+template <unsigned short BIAS_BITS>
+__device__ __forceinline__ uint32_t unmagic(uint32_t h2) {
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2 *>(&h2), __half2half2(__ushort_as_half(BIAS_BITS)));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+// 32-bit word at a 2-byte aligned shared address
+__device__ __forceinline__ uint32_t lds32_u2(const uint8_t *p) {
+    const uint32_t a = (uint32_t)(uintptr_t)p;
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(p - (a & 2u));
+    return __funnelshift_r(q[0], q[1], (a & 2u) * 8u);
+}
+__device__ __forceinline__ uint32_t lds32(const uint8_t *p) { return *reinterpret_cast<const uint32_t *>(p); }
+__device__ __forceinline__ float lds_half(const uint8_t *p) { return __half2float(*reinterpret_cast<const __half *>(p)); }
+__device__ __forceinline__ uint32_t lds16(const uint8_t *p) { return *reinterpret_cast<const unsigned short *>(p); }
+
+// ---------------------------------------------------------------------------
+// per-format warp steps.  r0 / r1: the step's bytes of rows g and g+8 in shared
+// memory; xf: B operands of the step's first MMA; sx: its 16-column sums.
+// (acc0, acc1): this lane's share of rows g and g+8 (summed over the quad later).
+// ---------------------------------------------------------------------------
+
+#define IG_BFRAG(mi) (*reinterpret_cast<const uint2 *>(xf + (((mi) * 2u + part) * 4u + t) * 4u))
+#define IG_LO(w) unmagic<0x6400>(((w) & 0x000f000fu) | MAGIC_H2)
+#define IG_HI(w) unmagic<0x6400>(((w) & 0x00f000f0u) | MAGIC_H2)     /* 16 * nibble */
+
+template <uint32_t KIND> struct MmaStep;
+
+// Q4_K: 256 columns = 4 groups j of 64: 32 bytes whose low nibbles are sub-block 2j
+// and high nibbles sub-block 2j+1.  MMAs 4j+h (low, h = 0,1) share one scale and
+// chain into one accumulator; so do 4j+2+h (high).  Lane t owns group j = t's
+// scales and mins.
+template <> struct MmaStep<KIND_Q4_K> {
+    // (d * sc_2t, d * sc_2t+1 / 16, dmin * m_2t, dmin * m_2t+1) of sub-block group j = t of one row's block
+    static __device__ __forceinline__ void scales(const uint8_t *r, uint32_t t, float &dsc0, float &dsc1, float &dm0, float &dm1) {
+        const U4 hdr = *reinterpret_cast<const U4 *>(r);
+        const uint32_t sh = (t & 1u) * 16u;
+        const uint32_t a = hdr.y >> sh, bb = hdr.z >> sh, c = hdr.w >> sh;
+        uint32_t sc, m;
+        if (t < 2) { sc = a & 0x3f3fu; m = bb & 0x3f3fu; }
+        else { sc = (c & 0x0f0fu) | ((a >> 2) & 0x3030u); m = ((c >> 4) & 0x0f0fu) | ((bb >> 2) & 0x3030u); }
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));      // (d, dmin)
+        dsc0 = mul_rn(dd.x, (float)(sc & 0xffu));
+        dsc1 = mul_rn(mul_rn(dd.x, (float)(sc >> 8)), 0.0625f);
+        dm0 = mul_rn(dd.y, (float)(m & 0xffu));
+        dm1 = mul_rn(dd.y, (float)(m >> 8));
+    }
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const __half *xf, const float *sx,
+                                               uint32_t g, uint32_t t, float &acc0, float &acc1) {
+        const uint32_t part = g & 1u;
+        float s00, s01, m00, m01, s10, s11, m10, m11;
+        scales(r0, t, s00, s01, m00, m01);
+        scales(r1, t, s10, s11, m10, m11);
+        const uint8_t *q0 = r0 + 16u + 4u * t, *q1 = r1 + 16u + 4u * t;
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            float lo[4], hi[4];
+            {
+                const uint32_t a = lds32(q0 + 32u * j), b = lds32(q1 + 32u * j);
+                const uint32_t as = a >> 8, bs = b >> 8;
+                const uint2 bl = IG_BFRAG(4u * j), bh = IG_BFRAG(4u * j + 2u);
+                mma16816_first(lo, IG_LO(a), IG_LO(b), IG_LO(as), IG_LO(bs), bl.x, bl.y);
+                mma16816_first(hi, IG_HI(a), IG_HI(b), IG_HI(as), IG_HI(bs), bh.x, bh.y);
+            }
+            {
+                const uint32_t a = lds32(q0 + 32u * j + 16u), b = lds32(q1 + 32u * j + 16u);
+                const uint32_t as = a >> 8, bs = b >> 8;
+                const uint2 bl = IG_BFRAG(4u * j + 1u), bh = IG_BFRAG(4u * j + 3u);
+                mma16816(lo, IG_LO(a), IG_LO(b), IG_LO(as), IG_LO(bs), bl.x, bl.y);
+                mma16816(hi, IG_HI(a), IG_HI(b), IG_HI(as), IG_HI(bs), bh.x, bh.y);
+            }
+            if (t == j) {
+                acc0 = fma_rn(s00, add_rn(lo[0], lo[1]), acc0);
+                acc0 = fma_rn(s01, add_rn(hi[0], hi[1]), acc0);
+                acc1 = fma_rn(s10, add_rn(lo[2], lo[3]), acc1);
+                acc1 = fma_rn(s11, add_rn(hi[2], hi[3]), acc1);
+            }
+        }
+        // - dmin * (m_2t * sum x over sub-block 2t + m_2t+1 * sum x over sub-block 2t+1)
+        const float4 sq = *reinterpret_cast<const float4 *>(sx + 4u * t);
+        const float sa = add_rn(sq.x, sq.y), sb = add_rn(sq.z, sq.w);
+        acc0 = sub_rn(acc0, fma_rn(m01, sb, mul_rn(m00, sa)));
+        acc1 = sub_rn(acc1, fma_rn(m11, sb, mul_rn(m10, sa)));
+    }
+};
+
+// Q6_K: 256 columns = 2 halves n of 128 = 4 quarters q of 32 = 2 runs h of 16, each
+// run with its own int8 scale (index 8n + 2q + h).  A run's 6-bit values come from
+// a word of ql (low nibble for q < 2, high nibble — kept in place, times 16 — for
+// q >= 2; ql + 32 for odd q) and two bits of a word of qh.  Lane t owns quarter
+// q = t's scales.  Blocks are only 2-byte aligned.
+template <> struct MmaStep<KIND_Q6_K> {
+    template <int Q>
+    static __device__ __forceinline__ uint32_t six(uint32_t L, uint32_t H) {       // bytes (0,2) of the words
+        constexpr uint32_t nib = (Q >= 2) ? 0x00f000f0u : 0x000f000fu;
+        constexpr uint32_t hmask = 0x00030003u << (2 * Q);
+        constexpr uint32_t mult = (Q == 0 || Q == 2) ? 16u : 4u;                 // two high bits to bit 4 (q < 2) or 8
+        return unmagic<0x6400>((L & nib) | ((H & hmask) * mult + MAGIC_H2));
+    }
+    template <int Q>
+    static __device__ __forceinline__ void quarter(uint32_t la, uint32_t lb, uint32_t ha, uint32_t hb, uint2 bf, float (&c)[4]) {
+        mma16816_first(c, six<Q>(la, ha), six<Q>(lb, hb), six<Q>(la >> 8, ha >> 8), six<Q>(lb >> 8, hb >> 8), bf.x, bf.y);
+    }
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const __half *xf, const float *sx,
+                                               uint32_t g, uint32_t t, float &acc0, float &acc1) {
+        const uint32_t part = g & 1u;
+        const float d0 = lds_half(r0 + 208u), d1 = lds_half(r1 + 208u);
+#pragma unroll
+        for (uint32_t n = 0; n < 2; ++n) {
+            // scales of quarter q = t: runs h = 0, 1 are consecutive bytes 8n + 2t, 8n + 2t + 1
+            const uint32_t s0 = lds16(r0 + 192u + 8u * n + 2u * t), s1 = lds16(r1 + 192u + 8u * n + 2u * t);
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t o = 64u * n + 16u * h + 4u * t;
+                const uint32_t a_lo = lds32_u2(r0 + o), a_hi = lds32_u2(r0 + o + 32u), a_h = lds32_u2(r0 + 128u + 32u * n + 16u * h + 4u * t);
+                const uint32_t b_lo = lds32_u2(r1 + o), b_hi = lds32_u2(r1 + o + 32u), b_h = lds32_u2(r1 + 128u + 32u * n + 16u * h + 4u * t);
+                float c[4][4];
+                quarter<0>(a_lo, b_lo, a_h, b_h, IG_BFRAG(8u * n + 0u + h), c[0]);
+                quarter<1>(a_hi, b_hi, a_h, b_h, IG_BFRAG(8u * n + 2u + h), c[1]);
+                quarter<2>(a_lo, b_lo, a_h, b_h, IG_BFRAG(8u * n + 4u + h), c[2]);
+                quarter<3>(a_hi, b_hi, a_h, b_h, IG_BFRAG(8u * n + 6u + h), c[3]);
+                // lane t applies quarter q = t: value - 32 via the run's activation sum; x16 undone for q >= 2
+                const float sc0 = (float)(int)(int8_t)((s0 >> (8u * h)) & 0xffu), sc1 = (float)(int)(int8_t)((s1 >> (8u * h)) & 0xffu);
+                const float sxv = sx[8u * n + 2u * t + h];
+                float q0, q1;
+                if (t == 0) { q0 = add_rn(c[0][0], c[0][1]); q1 = add_rn(c[0][2], c[0][3]); }
+                else if (t == 1) { q0 = add_rn(c[1][0], c[1][1]); q1 = add_rn(c[1][2], c[1][3]); }
+                else if (t == 2) { q0 = mul_rn(add_rn(c[2][0], c[2][1]), 0.0625f); q1 = mul_rn(add_rn(c[2][2], c[2][3]), 0.0625f); }
+                else { q0 = mul_rn(add_rn(c[3][0], c[3][1]), 0.0625f); q1 = mul_rn(add_rn(c[3][2], c[3][3]), 0.0625f); }
+                acc0 = fma_rn(mul_rn(d0, sc0), fma_rn(-32.0f, sxv, q0), acc0);
+                acc1 = fma_rn(mul_rn(d1, sc1), fma_rn(-32.0f, sxv, q1), acc1);
+            }
+        }
+    }
+};
+
+// Q4_0: step = 4 blocks of 32 (18 bytes each, 2-byte aligned): MMA 2b is the block's
+// low nibbles (elements 0..15), MMA 2b+1 its high nibbles (16..31).  Lane t owns
+// block b = t's scale.
+template <> struct MmaStep<KIND_Q4_0> {
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const __half *xf, const float *sx,
+                                               uint32_t g, uint32_t t, float &acc0, float &acc1) {
+        const uint32_t part = g & 1u;
+        const float d0 = lds_half(r0 + 18u * t), d1 = lds_half(r1 + 18u * t);
+        const float sxv = add_rn(sx[2u * t], sx[2u * t + 1u]);
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            const uint32_t wa = lds32_u2(r0 + 18u * b + 2u + 4u * t), wb = lds32_u2(r1 + 18u * b + 2u + 4u * t);
+            const uint32_t as = wa >> 8, bs = wb >> 8;
+            float lo[4], hi[4];
+            const uint2 bl = IG_BFRAG(2u * b), bh = IG_BFRAG(2u * b + 1u);
+            mma16816_first(lo, IG_LO(wa), IG_LO(wb), IG_LO(as), IG_LO(bs), bl.x, bl.y);
+            mma16816_first(hi, IG_HI(wa), IG_HI(wb), IG_HI(as), IG_HI(bs), bh.x, bh.y);
+            if (t == b) {
+                const float q0 = fma_rn(add_rn(hi[0], hi[1]), 0.0625f, add_rn(lo[0], lo[1]));
+                const float q1 = fma_rn(add_rn(hi[2], hi[3]), 0.0625f, add_rn(lo[2], lo[3]));
+                acc0 = fma_rn(d0, fma_rn(-8.0f, sxv, q0), acc0);
+                acc1 = fma_rn(d1, fma_rn(-8.0f, sxv, q1), acc1);
+            }
+        }
+    }
+};
+
+// Q8_0: step = 4 blocks of 32 int8 (34 bytes each, 2-byte aligned): MMAs 2b and 2b+1
+// chain (one scale).  Lane t owns block b = t's scale.
+template <> struct MmaStep<KIND_Q8_0> {
+    static __device__ __forceinline__ uint32_t s8(uint32_t w) { return unmagic<0x6480>((w & 0x00ff00ffu) ^ 0x64806480u); }
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const __half *xf, const float *,
+                                               uint32_t g, uint32_t t, float &acc0, float &acc1) {
+        const uint32_t part = g & 1u;
+        const float d0 = lds_half(r0 + 34u * t), d1 = lds_half(r1 + 34u * t);
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            float c[4];
+            {
+                const uint32_t wa = lds32_u2(r0 + 34u * b + 2u + 4u * t), wb = lds32_u2(r1 + 34u * b + 2u + 4u * t);
+                const uint2 bf = IG_BFRAG(2u * b);
+                mma16816_first(c, s8(wa), s8(wb), s8(wa >> 8), s8(wb >> 8), bf.x, bf.y);
+            }
+            {
+                const uint32_t wa = lds32_u2(r0 + 34u * b + 18u + 4u * t), wb = lds32_u2(r1 + 34u * b + 18u + 4u * t);
+                const uint2 bf = IG_BFRAG(2u * b + 1u);
+                mma16816(c, s8(wa), s8(wb), s8(wa >> 8), s8(wb >> 8), bf.x, bf.y);
+            }
+            if (t == b) {
+                acc0 = fma_rn(d0, add_rn(c[0], c[1]), acc0);
+                acc1 = fma_rn(d1, add_rn(c[2], c[3]), acc1);
+            }
+        }
+    }
+};
+
+#undef IG_BFRAG
+#undef IG_LO
+#undef IG_HI
+
+// ---------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------
+
+template <uint32_t KIND, int NMAT>
+__global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const MmaPlan &p = a.plan;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *empty = full + MMA_MAX_STAGES;
+    uint64_t *xbar = empty + MMA_MAX_STAGES;
+    uint8_t *xrow = smem + GEMV_BAR_BYTES;
+    const __half *xf = reinterpret_cast<const __half *>(xrow);
+    const float *sx = reinterpret_cast<const float *>(xrow + (size_t)p.cols * 4u);
+    float *red = reinterpret_cast<float *>(xrow + ((p.x_bytes + 127u) & ~127u));
+    uint8_t *stages = reinterpret_cast<uint8_t *>(red) + p.red_bytes;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            ptx::mbar_init(&full[s], 1);
+            ptx::mbar_init(&empty[s], MMA_WARPS);
+        }
+        ptx::mbar_init(xbar, 1);
+        ptx::mbar_init_fence();
+    }
+    __syncthreads();
+    ptx::pdl_launch_dependents();
+
+    uint32_t r_begin, r_end;
+    cta_rows(p.rows, blockIdx.x, gridDim.x, r_begin, r_end);
+    const uint32_t stage_rows = 16u * p.row_tiles;
+    const uint32_t n_tiles = (r_end - r_begin + stage_rows - 1) / stage_rows;
+    const uint32_t pair = blockIdx.y;
+
+    if (warp == MMA_WARPS) {
+        // ---- producer warp: weights first (they do not depend on the previous kernel),
+        // then, once the ring is primed, wait for the previous kernel and fetch the
+        // packed activations ----
+        uint32_t expert = a.expert, x_row = 0;
+        if (a.ids) {                                   // routing comes from the previous kernel
+            ptx::pdl_wait();
+            expert = a.ids[pair];
+            if (expert >= a.n_experts) return;         // consumers report it
+            x_row = a.per_pair ? pair : pair / a.top;
+        }
+        const size_t mat_off = (size_t)expert * p.rows * p.stride;
+        bool x_sent = false;
+        uint32_t it = 0;
+        for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+            const uint32_t row0 = r_begin + tile * stage_rows;
+            const uint32_t nrows = (r_end - row0) < stage_rows ? (r_end - row0) : stage_rows;
+            for (uint32_t c = 0; c < p.chunks; ++c, ++it) {
+                if (!x_sent && it == p.stages) {       // ring primed: the next wait needs the consumers
+                    if (!a.ids) ptx::pdl_wait();
+                    if (lane == 0) {
+                        ptx::mbar_expect_tx(xbar, p.x_bytes);
+                        ptx::bulk_g2s(xrow, a.xp + (size_t)x_row * p.x_bytes, p.x_bytes, xbar);
+                    }
+                    x_sent = true;
+                }
+                const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                bool ok = true;
+                if (lane == 0) ok = ptx::mbar_wait(&empty[s], ph ^ 1u);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { if (lane == 0) set_status_word(a.status, KERNEL_ERR_PRODUCER_TIMEOUT); return; }
+                uint8_t *dst = stages + (size_t)s * p.stage_bytes;
+                if (lane == 0) ptx::mbar_expect_tx(&full[s], p.chunk_bytes * nrows * NMAT);
+                __syncwarp();
+                for (uint32_t i = lane; i < nrows * NMAT; i += 32u) {
+                    const uint32_t m = i / nrows, r = i - m * nrows;
+                    ptx::bulk_g2s(dst + (size_t)(m * stage_rows + r) * p.row_pitch,
+                                  a.w[m] + mat_off + (size_t)(row0 + r) * p.stride + (size_t)c * p.chunk_bytes,
+                                  p.chunk_bytes, &full[s]);
+                }
+            }
+        }
+        if (!x_sent) {                                   // fewer stage fills than ring slots
+            if (!a.ids) ptx::pdl_wait();
+            if (lane == 0) {
+                ptx::mbar_expect_tx(xbar, p.x_bytes);
+                ptx::bulk_g2s(xrow, a.xp + (size_t)x_row * p.x_bytes, p.x_bytes, xbar);
+            }
+        }
+        return;
+    }
+
+    // ---- consumer warps ----
+    if (a.ids) {
+        ptx::pdl_wait();
+        if (a.ids[pair] >= a.n_experts) {
+            if (threadIdx.x == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
+            return;
+        }
+    }
+    if (!ptx::mbar_wait(xbar, 0)) {
+        if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
+        return;
+    }
+    ptx::pdl_wait();          // outputs may be read by the previous kernel until it ends
+    const float unscale = *reinterpret_cast<const float *>(xrow + (size_t)p.cols * 4u + p.cols / 4u);
+
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t kw = warp & ((1u << p.kw_log2) - 1u), rt = warp >> p.kw_log2;
+    constexpr uint32_t STEP_BYTES = KIND == KIND_Q4_K ? 144u : KIND == KIND_Q6_K ? 210u : KIND == KIND_Q4_0 ? 72u : 136u;
+    constexpr uint32_t MMAS = (KIND == KIND_Q4_K || KIND == KIND_Q6_K) ? 16u : 8u;     // MMAs per step
+    const uint32_t step_stride = STEP_BYTES << p.kw_log2;                               // this warp's next step
+    const uint32_t x_stride = (MMAS * 32u) << p.kw_log2, s_stride = MMAS << p.kw_log2;
+    const size_t mat_pitch = (size_t)stage_rows * p.row_pitch;
+    float *y = a.y + (a.ids ? (size_t)pair * p.rows : 0);
+    uint32_t it = 0;
+    for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+        const uint32_t row0 = r_begin + tile * stage_rows;
+        const uint32_t nrows = (r_end - row0) < stage_rows ? (r_end - row0) : stage_rows;
+        const uint32_t lr0 = rt * 16u + g, lr1 = lr0 + 8u;             // rows of this lane inside the stage
+        const uint32_t ur0 = lr0 < nrows ? lr0 : rt * 16u;              // rows past the end read the tile's first row
+        const uint32_t ur1 = lr1 < nrows ? lr1 : rt * 16u;
+        float acc[NMAT][2];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) acc[m][0] = acc[m][1] = 0.f;
+        for (uint32_t c = 0; c < p.chunks; ++c, ++it) {
+            const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+            if (!ptx::mbar_wait(&full[s], ph)) {
+                if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
+                return;
+            }
+            const uint8_t *st = stages + (size_t)s * p.stage_bytes;
+            if (rt * 16u < nrows) {
+                const uint8_t *b0 = st + (size_t)ur0 * p.row_pitch + kw * STEP_BYTES;
+                const uint8_t *b1 = st + (size_t)ur1 * p.row_pitch + kw * STEP_BYTES;
+                const uint32_t gs0 = c * (p.spw << p.kw_log2) + kw;            // first step inside the row
+                const __half *xs = xf + (size_t)gs0 * MMAS * 32u;
+                const float *ss = sx + gs0 * MMAS;
+                for (uint32_t i = 0; i < p.spw; ++i) {
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m)
+                        MmaStep<KIND>::run(b0 + (size_t)m * mat_pitch, b1 + (size_t)m * mat_pitch, xs, ss, g, t, acc[m][0], acc[m][1]);
+                    b0 += step_stride; b1 += step_stride;
+                    xs += x_stride; ss += s_stride;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&empty[s]);
+        }
+        // quad reduce (the four lanes hold different scale groups), then across the K warps
+        float *slot = red + (size_t)(tile & 1u) * MMA_WARPS * 2u * 16u;
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float v = acc[m][h];
+                v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+                v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+                if (t == 0) slot[(warp * 2u + m) * 16u + g + 8u * h] = v;
+            }
+        ptx::named_bar_sync(1, MMA_WARPS * 32);
+        if (kw == 0 && lane < 16u) {
+            const uint32_t lrow = rt * 16u + lane;
+            if (lrow < nrows) {
+                float v[NMAT];
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) {
+                    float sum = 0.f;
+                    for (uint32_t k = 0; k < (1u << p.kw_log2); ++k) sum = add_rn(sum, slot[((warp + k) * 2u + m) * 16u + lane]);
+                    v[m] = mul_rn(sum, unscale);
+                }
+                y[row0 + lrow] = NMAT == 2 ? glu_f(v[0], v[NMAT - 1], a.glu == 2) : v[0];
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// launch
+// ---------------------------------------------------------------------------
+
+template <uint32_t KIND, int NMAT>
+static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
+    auto kernel = gemv_mma_kernel<KIND, NMAT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_MAX);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(MMA_THREADS);
+    cfg.dynamicSmemBytes = a.plan.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
+template <uint32_t KIND>
+static cudaError_t launch_mma_k(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
+    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2>(a, grid, stream, pdl) : launch_mma_t<KIND, 1>(a, grid, stream, pdl);
+}
+
+// True when this call was taken (launched or failed); false to let the caller use
+// another kernel.  Unpacked activations are packed into the handle's workspace first.
+bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err) {
+    const bool routed = c.ids != nullptr;
+    if (!mma_kind(c.kind)) return false;
+    if (!routed && c.count != 1) return false;
+    if (c.cols % 64u) return false;
+    const uint32_t gy = routed ? c.pairs : 1u;
+    uint32_t max_ctas = (2u * ctx.sm_count + gy - 1) / gy;
+    if (max_ctas < 1) max_ctas = 1;
+    MmaPlan plan;
+    bool ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_BUDGET, plan);
+    if (!ok) {
+        max_ctas = (ctx.sm_count + gy - 1) / gy;
+        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas ? max_ctas : 1, MMA_SMEM_MAX, plan);
+    }
+    if (!ok) return false;
+    const uint8_t *xp = static_cast<const uint8_t *>(c.x);
+    if (!c.x_packed) {
+        const uint32_t x_rows = routed ? (c.per_pair ? c.pairs : (c.pairs + (c.top ? c.top : 1u) - 1) / (c.top ? c.top : 1u)) : 1u;
+        const size_t need = (size_t)x_rows * packed_x_bytes(c.cols);
+        if (!ctx.workspace || need > ctx.workspace_bytes) return false;
+        err = launch_pack_x(c.x, c.x_bf16, x_rows, c.cols, ctx.workspace, ctx);
+        if (err != cudaSuccess) return true;
+        xp = static_cast<const uint8_t *>(ctx.workspace);
+    }
+    MmaArgs a = {};
+    a.plan = plan;
+    a.w[0] = c.w[0]; a.w[1] = c.w[1]; a.xp = xp; a.y = c.y;
+    a.ids = c.ids; a.expert = c.expert; a.n_experts = c.n_experts;
+    a.per_pair = c.per_pair; a.top = c.top ? c.top : 1u; a.glu = c.glu;
+    a.status = ctx.status;
+    const dim3 grid(plan.ctas, gy);
+    switch (c.kind) {
+    case KIND_Q4_K: err = launch_mma_k<KIND_Q4_K>(a, grid, ctx.stream, ctx.pdl); break;
+    case KIND_Q6_K: err = launch_mma_k<KIND_Q6_K>(a, grid, ctx.stream, ctx.pdl); break;
+    case KIND_Q4_0: err = launch_mma_k<KIND_Q4_0>(a, grid, ctx.stream, ctx.pdl); break;
+    default: err = launch_mma_k<KIND_Q8_0>(a, grid, ctx.stream, ctx.pdl); break;
+    }
+    return true;
+}
+
+}  // namespace ingot

@@ -20,7 +20,10 @@ struct LaunchCtx {
     int *status;          // device status word
     uint32_t sm_count;
     bool pdl;             // launch with programmatic stream serialization
-    bool force_plain;     // test hook: skip the streaming kernel
+    bool force_plain;     // test hook: skip the streaming kernels
+    bool no_mma;          // test hook: use the fp32 CUDA-core streaming kernel instead of the MMA one
+    void *workspace;      // device scratch of the handle (packed activations)
+    size_t workspace_bytes;
 };
 
 // y = W x for `count` tokens (dense) or `pairs` (token, expert) pairs (routed,
@@ -35,9 +38,14 @@ struct GemvCall {
     uint32_t count;        // dense tokens
     uint32_t pairs, top, per_pair, n_experts;   // routed
     uint32_t x_bf16;
+    uint32_t x_packed;     // x is already in packed_x_bytes(cols) rows (launch_pack_x)
     uint32_t nmat, glu;    // glu: 1 silu, 2 tanh-gelu
 };
 cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);
+// The tensor-core-assisted streaming GEMV; false when the call is not one it handles.
+bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
+// Packs `rows` activation rows (f32 or bf16) for the tensor-core GEMV.
+cudaError_t launch_pack_x(const void *x, uint32_t bf16, uint32_t rows, uint32_t cols, void *packed, const LaunchCtx &ctx);
 
 // out[r][j] = weight_at(row r, j) for rows*cols elements.
 cudaError_t launch_dequant(const uint8_t *w, uint32_t cols, uint64_t rows, uint32_t stride, uint32_t kind,

@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const __grid_constant__
         if (lane == 0) atomicCAS(a.status, 0, KERNEL_ERR_ROUTER_INPUT);
         return;
     }
-    float top_score = 0.f, sum = 0.f, mine = 0.f;      // lane k keeps weight k (top <= 32 per pass)
+    float top_score = 0.f, sum = 0.f;
     for (uint32_t k = 0; k < a.top; ++k) {
         float best = -INFINITY;
         uint32_t index = 0xffffffffu;
@@ -227,7 +227,6 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const __grid_constant__
         const float w = expf(score - top_score);
         sum = __fadd_rn(sum, w);
         if (lane == 0) { a.ids[(size_t)t * a.top + k] = e; a.weights[(size_t)t * a.top + k] = w; }
-        (void)mine;
     }
     __syncwarp();
     for (uint32_t k = lane; k < a.top; k += 32u) a.weights[(size_t)t * a.top + k] = __fdiv_rn(a.weights[(size_t)t * a.top + k], sum);
@@ -395,8 +394,12 @@ __global__ void __launch_bounds__(256) add_rms_kernel(const __grid_constant__ Rm
     for (int i = 0; i < 8; ++i) total += partial[i];
     const float inv = 1.0f / sqrtf(total / (float)a.width + a.eps);
     for (uint32_t j = tid; j < n4; j += 256) {
-        float4 v = a4[j];
-        if (a.add) { const float4 o = b4[j]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+        float4 v;
+        if (a.add && a.s) v = reinterpret_cast<const float4 *>(a.s)[base + j];   // written above by this thread; s may alias a
+        else {
+            v = a4[j];
+            if (a.add) { const float4 o = b4[j]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+        }
         float4 wv = a.w ? reinterpret_cast<const float4 *>(a.w)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
         v.x = v.x * inv * wv.x; v.y = v.y * inv * wv.y; v.z = v.z * inv * wv.z; v.w = v.w * inv * wv.w;
         if (a.y) reinterpret_cast<float4 *>(a.y)[base + j] = v;

@@ -1,7 +1,7 @@
 // Inline-PTX helpers for sm_100a: mbarrier, 1-D bulk async copies (TMA without
 // a tensor map), programmatic dependent launch, cache-hinted loads.
 //
-// Every wait is bounded: after WAIT_LIMIT polls the caller records an error
+// Every wait is bounded: after WAIT_LIMIT_NS the caller records an error
 // code in the device status word and leaves, so a lost copy or a mis-sized
 // transaction can never hang the GPU.
 #pragma once
@@ -10,7 +10,7 @@
 namespace ingot {
 namespace ptx {
 
-static constexpr uint32_t WAIT_LIMIT = 1u << 22;   // polls; each poll may suspend briefly
+static constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // two seconds of wall time
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -47,11 +47,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: polls until the phase completes or WAIT_LIMIT_NS of wall time
+// have passed; false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
 }
 
 // Global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte

@@ -190,21 +190,59 @@ IG_HD float weight_at(const uint8_t *row, uint32_t kind, uint32_t j) {
 struct alignas(16) F4 { float x, y, z, w; };
 struct alignas(16) U4 { uint32_t x, y, z, w; };
 
-IG_HD uint32_t ld32(const uint8_t *p) {          // p is 4-byte aligned
-    return *reinterpret_cast<const uint32_t *>(p);
-}
+// Activation float4s are stored PERMUTED as (e0, e2, e1, e3): a 32-bit word of
+// quants holds bytes 0..3, and the decoders below turn bytes (0,2) and (1,3)
+// into pairs of floats, so (.x,.y) and (.z,.w) are the matching activation pairs.
+IG_HD F4 permute_x(float e0, float e1, float e2, float e3) { F4 v = {e0, e2, e1, e3}; return v; }
 
 IG_HD float byte_f(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xffu); }
-
-// sum_e x[e] * byte e of `w` added to acc (bytes hold small unsigned ints)
-IG_HD float dot4_bytes(const F4 &x, uint32_t w, float acc) {
-    acc = fma_rn(x.x, byte_f(w, 0), acc);
-    acc = fma_rn(x.y, byte_f(w, 1), acc);
-    acc = fma_rn(x.z, byte_f(w, 2), acc);
-    acc = fma_rn(x.w, byte_f(w, 3), acc);
-    return acc;
-}
 IG_HD float sum4(const F4 &v) { return add_rn(add_rn(v.x, v.y), add_rn(v.z, v.w)); }
+
+// Integer -> float without the conversion pipe.  `h2` holds two binary16
+// "magic" numbers 0x6400 | v (= 1024 + v for v < 1024); adding `bias` in fp32
+// gives the two integers (times whatever power of two v carries) exactly.
+// On sm_100 this is one mixed-precision add per value.
+IG_HD void halves_plus(uint32_t h2, float bias, float &lo, float &hi) {
+#if defined(__CUDA_ARCH__)
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tadd.f32.f16 %0, l, %3;\n\tadd.f32.f16 %1, h, %3;\n\t}"
+        : "=f"(lo), "=f"(hi)
+        : "r"(h2), "f"(bias));
+#else
+    lo = half_bits_to_float(h2 & 0xffffu) + bias;
+    hi = half_bits_to_float(h2 >> 16) + bias;
+#endif
+}
+
+// Two independent fused multiply-adds, (ax, ay) += (px, py) * (qx, qy); one
+// packed fma.rn.f32x2 on sm_100.
+IG_HD void fma2(float &ax, float &ay, float px, float py, float qx, float qy) {
+#if defined(__CUDA_ARCH__)
+    asm("{\n\t.reg .b64 a, b, c;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\tmov.b64 c, {%0, %1};\n\t"
+        "fma.rn.f32x2 c, a, b, c;\n\tmov.b64 {%0, %1}, c;\n\t}"
+        : "+f"(ax), "+f"(ay)
+        : "f"(px), "f"(py), "f"(qx), "f"(qy));
+#else
+    ax = fmaf(px, qx, ax);
+    ay = fmaf(py, qy, ay);
+#endif
+}
+
+static constexpr uint32_t MAGIC_H2 = 0x64006400u;   // two binary16 1024.0
+
+// (a0,a1) += low nibbles of the 4 bytes of `w` times xa; (b0,b1) += 16 * high
+// nibbles times xb.  xa/xb are permuted float4s.
+IG_HD void dot_nibbles(uint32_t w, const F4 &xa, const F4 &xb, float &a0, float &a1, float &b0, float &b1) {
+    const uint32_t s = w >> 8;
+    float f0, f1, f2, f3;
+    halves_plus((w & 0x000f000fu) | MAGIC_H2, -1024.0f, f0, f2);      // bytes 0, 2
+    halves_plus((s & 0x000f000fu) | MAGIC_H2, -1024.0f, f1, f3);      // bytes 1, 3
+    fma2(a0, a1, f0, f2, xa.x, xa.y);
+    fma2(a0, a1, f1, f3, xa.z, xa.w);
+    halves_plus((w & 0x00f000f0u) | MAGIC_H2, -1024.0f, f0, f2);      // 16 * high nibble
+    halves_plus((s & 0x00f000f0u) | MAGIC_H2, -1024.0f, f1, f3);
+    fma2(b0, b1, f0, f2, xb.x, xb.y);
+    fma2(b0, b1, f1, f3, xb.z, xb.w);
+}
 
 template <uint32_t KIND> struct Unit;
 
@@ -229,7 +267,8 @@ template <> struct Unit<KIND_Q4_K> {
         a.sb = add_rn(add_rn(sum4(x[4]), sum4(x[5])), add_rn(sum4(x[6]), sum4(x[7])));
         return a;
     }
-    // Decoded once per row, used for every token.
+    // Decoded once per row, used for every token.  dsc1 carries the 1/16 that
+    // undoes the in-place high nibbles.
     struct W { uint32_t q[4]; float dsc0, dsc1, dm0, dm1; };
     static IG_HD W load(const uint8_t *chunk, uint32_t u) {
         const uint8_t *b = chunk + (u >> 3) * 144u;
@@ -248,20 +287,20 @@ template <> struct Unit<KIND_Q4_K> {
             m = ((c >> 4) & 0x0f0fu) | ((bb >> 2) & 0x3030u);
         }
         float d = half_bits_to_float(h0 & 0xffffu), dmin = half_bits_to_float(h0 >> 16);
-        w.dsc0 = mul_rn(d, (float)(sc & 0xffu));
-        w.dsc1 = mul_rn(d, (float)(sc >> 8));
-        w.dm0 = mul_rn(dmin, (float)(m & 0xffu));
-        w.dm1 = mul_rn(dmin, (float)(m >> 8));
+        float s0, s1, m0, m1;
+        halves_plus(((sc & 0xffu) | ((sc & 0xff00u) << 8)) | MAGIC_H2, -1024.0f, s0, s1);
+        halves_plus(((m & 0xffu) | ((m & 0xff00u) << 8)) | MAGIC_H2, -1024.0f, m0, m1);
+        w.dsc0 = mul_rn(d, s0);
+        w.dsc1 = mul_rn(mul_rn(d, s1), 0.0625f);
+        w.dm0 = mul_rn(dmin, m0);
+        w.dm1 = mul_rn(dmin, m1);
         return w;
     }
     static IG_HD float dot(const W &w, const F4 *x, const Aux &ax) {
-        float a = 0.f, b = 0.f;
+        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            a = dot4_bytes(x[i], w.q[i] & 0x0f0f0f0fu, a);
-            b = dot4_bytes(x[4 + i], (w.q[i] >> 4) & 0x0f0f0f0fu, b);
-        }
-        float pos = fma_rn(w.dsc1, b, mul_rn(w.dsc0, a));
+        for (int i = 0; i < 4; ++i) dot_nibbles(w.q[i], x[i], x[4 + i], a0, a1, b0, b1);
+        float pos = fma_rn(w.dsc1, add_rn(b0, b1), mul_rn(w.dsc0, add_rn(a0, a1)));
         float neg = fma_rn(w.dm1, ax.sb, mul_rn(w.dm0, ax.sa));
         return sub_rn(pos, neg);
     }
@@ -293,13 +332,11 @@ template <> struct Unit<KIND_Q4_0> {
         return w;
     }
     static IG_HD float dot(const W &w, const F4 *x, const Aux &ax) {
-        float a = 0.f, b = 0.f;
+        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            a = dot4_bytes(x[i], w.q[i] & 0x0f0f0f0fu, a);
-            b = dot4_bytes(x[4 + i], (w.q[i] >> 4) & 0x0f0f0f0fu, b);
-        }
-        return mul_rn(w.d, fma_rn(-8.0f, ax.s, add_rn(a, b)));
+        for (int i = 0; i < 4; ++i) dot_nibbles(w.q[i], x[i], x[4 + i], a0, a1, b0, b1);
+        float sum = fma_rn(add_rn(b0, b1), 0.0625f, add_rn(a0, a1));
+        return mul_rn(w.d, fma_rn(-8.0f, ax.s, sum));
     }
 };
 
@@ -323,21 +360,18 @@ template <> struct Unit<KIND_Q8_0> {
         for (int i = 0; i < 8; ++i) w.q[i] = funnel_r(v[i], v[i + 1], 16u + sh);
         return w;
     }
-    static IG_HD float sbyte_f(uint32_t w, int i) { return (float)(int)(int8_t)((w >> (8 * i)) & 0xffu); }
     static IG_HD float dot(const W &w, const F4 *x, const Aux &) {
-        float a = 0.f, b = 0.f;
+        float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            a = fma_rn(x[i].x, sbyte_f(w.q[i], 0), a);
-            a = fma_rn(x[i].y, sbyte_f(w.q[i], 1), a);
-            a = fma_rn(x[i].z, sbyte_f(w.q[i], 2), a);
-            a = fma_rn(x[i].w, sbyte_f(w.q[i], 3), a);
-            b = fma_rn(x[i + 1].x, sbyte_f(w.q[i + 1], 0), b);
-            b = fma_rn(x[i + 1].y, sbyte_f(w.q[i + 1], 1), b);
-            b = fma_rn(x[i + 1].z, sbyte_f(w.q[i + 1], 2), b);
-            b = fma_rn(x[i + 1].w, sbyte_f(w.q[i + 1], 3), b);
+        for (int i = 0; i < 8; ++i) {
+            // signed byte b -> 1024 + (b ^ 0x80) = 1152 + b
+            float f0, f1, f2, f3;
+            halves_plus((w.q[i] & 0x00ff00ffu) ^ 0x64806480u, -1152.0f, f0, f2);
+            halves_plus(((w.q[i] >> 8) & 0x00ff00ffu) ^ 0x64806480u, -1152.0f, f1, f3);
+            fma2(a0, a1, f0, f2, x[i].x, x[i].y);
+            fma2(a0, a1, f1, f3, x[i].z, x[i].w);
         }
-        return mul_rn(w.d, add_rn(a, b));
+        return mul_rn(w.d, add_rn(a0, a1));
     }
 };
 
@@ -361,6 +395,7 @@ template <> struct Unit<KIND_Q6_K> {
         for (int t = 0; t < 4; ++t) a.s[t] = add_rn(sum4(x[2 * t]), sum4(x[2 * t + 1]));
         return a;
     }
+    // ds[t] = d * scale_t, times 1/16 for the quarters decoded from high nibbles
     struct W { uint32_t l0[2], l1[2], h[2]; float ds[4]; };
     // two consecutive 32-bit words starting at byte `off` (2-byte aligned) of chunk
     static IG_HD void ld64(const uint8_t *chunk, uint32_t off, uint32_t *out) {
@@ -381,29 +416,41 @@ template <> struct Unit<KIND_Q6_K> {
         uint32_t doff = base + 208u;
         uint32_t dw = *reinterpret_cast<const uint32_t *>(chunk + (doff & ~3u));
         float d = half_bits_to_float((dw >> ((doff & 2u) * 8u)) & 0xffffu);
-        uint32_t sel = k8 >> 1;                             // scale index = sel + 2t
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            uint32_t idx = sel + 2u * t;                    // 0..7
-            uint32_t word = idx < 4 ? sc[0] : sc[1];
-            int s = (int)(int8_t)((word >> (8u * (idx & 3u))) & 0xffu);
-            w.ds[t] = mul_rn(d, (float)s);
-        }
+        // scale index = (k8 >> 1) + 2t: bytes 0,2,4,6 or 1,3,5,7 of the eight
+        uint32_t s0 = sc[0] >> ((k8 >> 1) * 8u), s1 = sc[1] >> ((k8 >> 1) * 8u);
+        float f0, f1, f2, f3;
+        halves_plus((s0 & 0x00ff00ffu) ^ 0x64806480u, -1152.0f, f0, f1);    // t = 0, 1
+        halves_plus((s1 & 0x00ff00ffu) ^ 0x64806480u, -1152.0f, f2, f3);    // t = 2, 3
+        w.ds[0] = mul_rn(d, f0);
+        w.ds[1] = mul_rn(d, f1);
+        w.ds[2] = mul_rn(mul_rn(d, f2), 0.0625f);
+        w.ds[3] = mul_rn(mul_rn(d, f3), 0.0625f);
         return w;
+    }
+    // one quarter t of one word e: 4 six-bit values (x16 when t >= 2) against one permuted float4
+    template <int T>
+    static IG_HD void quarter(uint32_t L, uint32_t H, const F4 &x, float &a0, float &a1) {
+        constexpr uint32_t nib = (T >= 2) ? 0x00f000f0u : 0x000f000fu;
+        constexpr uint32_t hmask = 0x00030003u << (2 * T);
+        // the two high bits land at bit 4 (t < 2) or bit 8 (t >= 2): shift by 4-2t or 8-2t
+        constexpr uint32_t mult = (T == 0 || T == 2) ? 16u : 4u;
+        const uint32_t Ls = L >> 8, Hs = H >> 8;
+        float f0, f1, f2, f3;
+        halves_plus((L & nib) | ((H & hmask) * mult + MAGIC_H2), -1024.0f, f0, f2);     // bytes 0, 2
+        halves_plus((Ls & nib) | ((Hs & hmask) * mult + MAGIC_H2), -1024.0f, f1, f3);   // bytes 1, 3
+        fma2(a0, a1, f0, f2, x.x, x.y);
+        fma2(a0, a1, f1, f3, x.z, x.w);
     }
     static IG_HD float dot(const W &w, const F4 *x, const Aux &ax) {
         float total = 0.f;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            float a = 0.f;
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                uint32_t lo = ((t & 1) ? w.l1[e] : w.l0[e]) >> ((t >= 2) ? 4 : 0);
-                uint32_t q = (lo & 0x0f0f0f0fu) | (((w.h[e] >> (2 * t)) & 0x03030303u) << 4);
-                a = dot4_bytes(x[2 * t + e], q, a);
-            }
-            total = fma_rn(w.ds[t], fma_rn(-32.0f, ax.s[t], a), total);
-        }
+        float a0, a1;
+#define IG_Q6_QUARTER(T)                                                             \
+        a0 = 0.f; a1 = 0.f;                                                          \
+        quarter<T>((T & 1) ? w.l1[0] : w.l0[0], w.h[0], x[2 * T], a0, a1);           \
+        quarter<T>((T & 1) ? w.l1[1] : w.l0[1], w.h[1], x[2 * T + 1], a0, a1);       \
+        total = fma_rn(w.ds[T], fma_rn((T >= 2) ? -512.0f : -32.0f, ax.s[T], add_rn(a0, a1)), total);
+        IG_Q6_QUARTER(0) IG_Q6_QUARTER(1) IG_Q6_QUARTER(2) IG_Q6_QUARTER(3)
+#undef IG_Q6_QUARTER
         return total;
     }
 };

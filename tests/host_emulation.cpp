@@ -28,7 +28,7 @@ int run(const GemvPlan &p, const uint8_t *w0, const uint8_t *w1, uint32_t expert
             Unit<KIND>::locate(4u * f, u, i);
             if (Unit<KIND>::col(u, i) != 4u * f) return -10;         // locate must invert col
             const float *s = x + (size_t)t * p.cols + 4u * f;
-            F4 v = {s[0], s[1], s[2], s[3]};
+            F4 v = permute_x(s[0], s[1], s[2], s[3]);
             xs[x_slot(p, t, u, i)] = v;
         }
     void *raw = nullptr;

@@ -1,0 +1,416 @@
+"""GPU parity: every operator of the path, through the C ABI, against the oracle
+on the same seeded inputs, the committed golden vectors and the reference's own
+synthetic fixtures.  Integer/byte work (dequantisation, routing ids, grouping) is
+bit-exact; floating-point GEMV outputs are held to the reference's bound
+|a - e| <= 1e-4 + 5e-5 |e| against an f64 dot of the dequantised weights."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from conftest import (lcg_q4k_fixture, q4_0_hand_expected, q4_0_hand_fixture, standard_x, tol_contract, tol_ref)
+from ingot_b200 import (BF16, F16, F32, Q4_0, Q4_K, Q6_K, Q8_0, InvalidData, Matrix, Tensor, Weight, synth)
+from ingot_b200 import _abi
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "decode_kind*.npz")))
+QUANT = [Q4_K, Q6_K, Q4_0, Q8_0]
+
+
+# ---- dequantisation: bit-exact ----------------------------------------------
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_dequant_matches_reference_golden_bits(gpu, path):
+    g = np.load(path)
+    m = Matrix.of(g["raw"], int(g["cols"]), int(g["rows"]), int(g["kind"]))
+    got = gpu.dequant(m)
+    assert np.array_equal(got.view(np.uint32), g["expected_bits"].reshape(-1))
+
+
+@pytest.mark.parametrize("kind", [F32, F16, BF16] + QUANT)
+def test_dequant_bit_exact_with_experts_and_tails(gpu, kind):
+    for cols, rows, count in ((256, 1, 1), (512, 3, 2), (2560, 37, 3), (4096, 64, 1)):
+        raw = synth.random_matrix(kind, cols, rows, count, seed=cols + kind)
+        got = gpu.dequant(Matrix.of(raw, cols, rows, kind, count)).reshape(rows * count, cols)
+        want = O.dequant(raw, cols, rows * count, kind)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (kind, cols, rows, count)
+
+
+def test_dequant_config1_full_size_bit_exact(gpu):
+    # configuration 1: W 4096x4096 Q4_K, seed 0; every one of the 16.7M weights
+    raw = synth.random_matrix(Q4_K, 4096, 4096, seed=0)
+    got = gpu.dequant(Matrix.of(raw, 4096, 4096, Q4_K)).reshape(4096, 4096)
+    want = O.dequant(raw, 4096, 4096, Q4_K)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_dequant_unaligned_view_uses_scalar_path(gpu):
+    raw = synth.random_matrix(Q6_K, 512, 5, seed=3)
+    buf = gpu.bytes(np.concatenate([np.zeros(2, np.uint8), raw]))
+    out = gpu.output(512 * 5)
+    gpu.op(None, "read_rows", [buf.view_bytes(2, raw.size), out], [512, 5, 420, Q6_K])
+    got = gpu.finish(None, out).reshape(5, 512)
+    assert np.array_equal(got.view(np.uint32), O.dequant(raw, 512, 5, Q6_K).view(np.uint32))
+
+
+def test_invalid_matrix_layouts_are_rejected(gpu):
+    raw = synth.random_matrix(Q4_K, 512, 2, seed=0)
+    with pytest.raises(InvalidData):
+        gpu.dequant(Matrix(raw, 512, 2, 1, Q4_K, 144))            # wrong stride
+    with pytest.raises(InvalidData):
+        gpu.dequant(Matrix(raw[:-1], 512, 2, 1, Q4_K, 288))       # short data
+    with pytest.raises(InvalidData):
+        gpu.dequant(Matrix(raw, 512, 2, 1, 13, 288))              # Q5_K: outside this path
+    with pytest.raises(InvalidData):
+        gpu.project(Matrix.of(raw, 512, 2, Q4_K), np.zeros(511, np.float32))
+    x = np.zeros(512, np.float32)
+    x[3] = np.nan
+    with pytest.raises(InvalidData):
+        gpu.project(Matrix.of(raw, 512, 2, Q4_K), x)
+    with pytest.raises(InvalidData):
+        gpu.project(Matrix.of(synth.random_matrix(Q4_K, 512, 2, 2), 512, 2, Q4_K, 2), np.zeros(512, np.float32))
+
+
+# ---- GEMV ----------------------------------------------------------------------
+
+def gemv(gpu, raw, cols, rows, kind, x, expert=0, count_experts=1, x_kind=F32, plain=False, mma=True):
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, cols)
+    w = gpu.bytes(raw)
+    xb = gpu.floats(x) if x_kind == F32 else gpu.bf16(x)
+    gpu.set_option(_abi.OPT_FORCE_PLAIN, int(plain))
+    gpu.set_option(_abi.OPT_NO_MMA, int(not mma))
+    try:
+        y = gpu.matmul(None, w, cols, rows, synth.stride_of(kind, cols), kind, expert, xb, x.shape[0], x_kind)
+        return gpu.finish(None, y).reshape(x.shape[0], rows)
+    finally:
+        gpu.set_option(_abi.OPT_FORCE_PLAIN, 0)
+        gpu.set_option(_abi.OPT_NO_MMA, 0)
+
+
+def test_config1_q4k_matvec(gpu):
+    # configuration 1: 4096x4096 Q4_K, x ~ N(0,1) fp32, seed 0
+    raw = synth.random_matrix(Q4_K, 4096, 4096, seed=0)
+    x = synth.activations(1, 4096, seed=0)
+    y = gemv(gpu, raw, 4096, 4096, Q4_K, x)
+    e = O.matvec_f64(raw, 4096, 4096, Q4_K, x)
+    err = np.abs(y - e)
+    assert (err <= tol_contract(e)).all()
+    assert (err <= tol_ref(e)).all(), float(err.max())      # also the reference's tighter bound
+
+
+SHAPES = {Q4_K: [(4096, 4096), (4096, 1024), (2560, 37), (768, 2048), (2048, 768), (256, 7), (12288, 33)],
+          Q6_K: [(4096, 1024), (12288, 65), (2048, 5), (256, 3), (2560, 37)],
+          Q4_0: [(2560, 2048), (10240, 33), (2048, 2560), (64, 7), (32, 1)],
+          Q8_0: [(4096, 128), (2560, 37), (1024, 5), (32, 3)]}
+
+
+@pytest.mark.parametrize("kind", QUANT)
+@pytest.mark.parametrize("path", ["mma", "fp32", "plain"])
+def test_gemv_matches_oracle(gpu, kind, path):
+    plain = path == "plain"
+    for cols, rows in SHAPES[kind]:
+        raw = synth.random_matrix(kind, cols, rows, seed=rows)
+        x = synth.activations(1, cols, seed=1)
+        y = gemv(gpu, raw, cols, rows, kind, x, plain=plain, mma=path == "mma")
+        e = O.matvec_f64(raw, cols, rows, kind, x)
+        # the plain kernel sums 32 long lane-strided chains: held to the stated contract, not the tighter bound
+        tol = tol_contract(e) if plain else tol_ref(e)
+        assert (np.abs(y - e) <= tol).all(), (kind, cols, rows, float(np.abs(y - e).max()))
+
+
+@pytest.mark.parametrize("kind", [F32, F16, BF16])
+def test_float_weight_gemv(gpu, kind):
+    for cols, rows in ((2048, 128), (32, 33), (100, 7)):
+        raw = synth.random_matrix(kind, cols, rows, seed=5)
+        x = synth.activations(3, cols, seed=2)
+        y = gemv(gpu, raw, cols, rows, kind, x)
+        e = O.matvec_f64(raw, cols, rows, kind, x)
+        assert (np.abs(y - e) <= tol_ref(e)).all()
+
+
+def test_f32_matmul_tails_and_expert_offsets(gpu):
+    # src/metal/tests.rs:13-34
+    for rows in (1, 3, 4, 5, 7, 33):
+        raw = np.array([i // 32 + 1 for i in range(2 * rows * 32)], np.float32)
+        w = gpu.floats(raw)
+        for count in (1, 2, 4, 5, 8):
+            x = gpu.floats(np.array([i // 32 + 1 for i in range(32 * count)], np.float32))
+            y = gpu.finish(None, gpu.matmul(None, w, 32, rows, 128, F32, 1, x, count))
+            exp = np.array([(rows + i % rows + 1) * 32 * (i // rows + 1) for i in range(rows * count)], float)
+            assert np.abs(y - exp).max() < 2e-5
+
+
+@pytest.mark.parametrize("kind,cols", [(Q4_K, 2560), (Q6_K, 4096), (Q4_0, 2560), (Q8_0, 1024), (Q4_K, 12288)])
+def test_token_counts_agree_bitwise_and_with_oracle(gpu, kind, cols):
+    # counts 2..8 bitwise equal to count 1 (src/expert_bench.rs:698-712) and tails of tokens
+    rows = 37
+    raw = synth.random_matrix(kind, cols, rows, seed=4)
+    x = synth.activations(8, cols, seed=5)
+    # one kernel family at a time: the fp32 streaming kernel here
+    singles = np.concatenate([gemv(gpu, raw, cols, rows, kind, x[t], mma=False) for t in range(8)])
+    for n in (2, 3, 4, 5, 7, 8):
+        y = gemv(gpu, raw, cols, rows, kind, x[:n], mma=False)
+        assert np.array_equal(y.view(np.uint32), singles[:n].view(np.uint32)), (kind, n)
+    e = O.matvec_f64(raw, cols, rows, kind, x)
+    assert (np.abs(singles - e) <= tol_ref(e)).all()
+
+
+@pytest.mark.parametrize("kind,cols,rows", [(Q4_K, 4096, 77), (Q6_K, 4096, 50), (Q4_0, 2560, 33), (Q8_0, 1024, 19)])
+def test_packed_activations_match_the_automatic_path(gpu, kind, cols, rows):
+    from ingot_b200 import X_PACKED
+    raw = synth.random_matrix(kind, cols, rows, seed=11)
+    x = synth.activations(1, cols, seed=12)
+    x[0, 5] = 70000.0                     # beyond binary16: exercises the power-of-two pre-scale
+    w, xb = gpu.bytes(raw), gpu.floats(x)
+    auto = gpu.finish(None, gpu.matmul(None, w, cols, rows, synth.stride_of(kind, cols), kind, 0, xb, 1))
+    packed = gpu.pack_x(xb, 1, cols)
+    y = gpu.finish(None, gpu.matmul(None, w, cols, rows, synth.stride_of(kind, cols), kind, 0, packed, 1, X_PACKED))
+    assert np.array_equal(y.view(np.uint32), auto.view(np.uint32))
+    e = O.matvec_f64(raw, cols, rows, kind, x)[0]
+    assert (np.abs(y - e) <= tol_contract(e)).all()
+    with pytest.raises(InvalidData):       # packed rows carry one token
+        gpu.matmul(None, w, cols, rows, synth.stride_of(kind, cols), kind, 0, packed, 2, X_PACKED)
+
+
+def test_expert_offset_and_lcg_fixture(gpu):
+    # src/expert_bench.rs:648-749: LCG seed 23 blocks, cols 2560, rows 37, experts 3, expert 1
+    data = lcg_q4k_fixture()
+    x = standard_x(2560 * 4).reshape(4, 2560)
+    y = gemv(gpu, data, 2560, 37, Q4_K, x, expert=1)
+    e = O.matvec_f64(data, 2560, 37, Q4_K, x, expert=1)
+    assert (np.abs(y - e) <= tol_ref(e)).all()
+    w = gpu.dequant(Matrix.of(data, 2560, 37, Q4_K, 3)).reshape(3 * 37, 2560)
+    assert np.array_equal(w.view(np.uint32), O.dequant(data, 2560, 3 * 37, Q4_K).view(np.uint32))
+
+
+@pytest.mark.parametrize("kind", [Q4_K, Q6_K])
+def test_bf16_activations(gpu, kind):
+    cols, rows = 4096, 130
+    raw = synth.random_matrix(kind, cols, rows, seed=8)
+    x = synth.activations(2, cols, seed=9)
+    xr = synth.from_bf16_bits(synth.to_bf16_bits(x))            # the oracle sees the same rounded x
+    y = gemv(gpu, raw, cols, rows, kind, x, x_kind=BF16)
+    e = O.matvec_f64(raw, cols, rows, kind, xr)
+    assert (np.abs(y - e) <= tol_ref(e)).all()
+    yp = gemv(gpu, raw, cols, rows, kind, x, x_kind=BF16, plain=True)
+    assert (np.abs(yp - e) <= tol_contract(e)).all()
+
+
+def test_project_host_and_weight_project(gpu):
+    raw = synth.random_matrix(Q6_K, 4096, 77, seed=2)
+    x = standard_x(4096)
+    e = O.matvec_f64(raw, 4096, 77, Q6_K, x)[0]
+    y = gpu.project(Matrix.of(raw, 4096, 77, Q6_K), x)
+    assert (np.abs(y - e) <= tol_ref(e)).all()
+    w = Weight.load(gpu, raw, [4096, 77], Q6_K)
+    y2 = gpu.finish(None, w.project(gpu, gpu.command(), gpu.floats(x)))
+    assert np.array_equal(y2.view(np.uint32), y.view(np.uint32))
+    with pytest.raises(InvalidData):
+        Weight.load(gpu, raw, [4096, 77], Q6_K, expect=[4096, 78])
+    with pytest.raises(InvalidData):
+        gpu.load_weight(raw[:-1], Tensor.of([4096, 77], Q6_K))
+
+
+# ---- fused gate/up ---------------------------------------------------------------
+
+@pytest.mark.parametrize("kind,cols,rows", [(Q4_K, 4096, 300), (Q4_0, 2560, 77), (Q6_K, 4096, 33), (Q8_0, 1024, 9)])
+@pytest.mark.parametrize("gelu", [False, True], ids=["silu", "gelu"])
+def test_gate_up_fused_equals_separate_and_oracle(gpu, kind, cols, rows, gelu):
+    g, u = synth.random_matrix(kind, cols, rows, seed=1), synth.random_matrix(kind, cols, rows, seed=2)
+    # scale inputs so the GLU is not saturated everywhere
+    x = synth.activations(3, cols, seed=3) * np.float32(0.02 if kind in (Q4_K,) else 0.2)
+    t = Tensor.of([cols, rows], kind)
+    wg, wu = Weight(gpu.bytes(g), t), Weight(gpu.bytes(u), t)
+    xb = gpu.floats(x)
+    fused = gpu.finish(None, gpu.generic_gate_up(None, [wg, wu], xb, 3, gelu)).reshape(3, rows)
+    yg = gpu.generic_project(None, wg, xb, 3)
+    yu = gpu.generic_project(None, wu, xb, 3)
+    sep = gpu.finish(None, gpu.activation(None, yg, yu, 3 * rows, gelu)).reshape(3, rows)
+    assert np.array_equal(fused.view(np.uint32), sep.view(np.uint32))      # src/metal/tests.rs fused_gate_up_matches_separate
+    eg, eu = O.matvec_f64(g, cols, rows, kind, x), O.matvec_f64(u, cols, rows, kind, x)
+    e = O.glu(eg.astype(np.float32), eu.astype(np.float32), gelu=gelu).astype(np.float64)
+    assert (np.abs(fused - e) <= tol_contract(e)).all(), float(np.abs(fused - e).max())
+    other = Weight(wu.buffer, Tensor.of([cols, rows + 1], kind)) if rows > 1 else None
+    assert gpu.generic_gate_up(None, [wg, other], xb, 3, gelu) is None      # shape mismatch -> no kernel
+
+
+# ---- routed ------------------------------------------------------------------------
+
+@pytest.mark.parametrize("plain", [False, True], ids=["stream", "plain"])
+def test_routed_q4_0_hand_fixture(gpu, plain):
+    # src/metal/tests.rs:35-93: 7 rows x 64 cols x 5 experts, top 3, shared and per-pair inputs
+    rows, cols, experts, top = 7, 64, 5, 3
+    w = gpu.bytes(q4_0_hand_fixture(rows, cols, experts))
+    gpu.set_option(_abi.OPT_FORCE_PLAIN, int(plain))
+    try:
+        for tokens in (1, 2, 3, 5, 8):
+            pairs = tokens * top
+            ids = np.array([(i * 7 + 1) % experts for i in range(pairs)], np.uint32)
+            idb = gpu.bytes(ids)
+            for per in (False, True):
+                inputs = np.array([(i % 19) * 0.125 - 1.0 for i in range(cols * (pairs if per else tokens))], np.float32)
+                y = gpu.output(rows * pairs)
+                gpu.op(None, "project_routed_batch", [w, gpu.floats(inputs), idb, y], [cols, rows, 36, 2, top, int(per)],
+                       rows, pairs)
+                got = gpu.finish(None, y).reshape(pairs, rows)
+                assert np.abs(got - q4_0_hand_expected(ids, rows, cols, top, per, inputs)).max() < 2e-5
+    finally:
+        gpu.set_option(_abi.OPT_FORCE_PLAIN, 0)
+
+
+def test_routed_moe_shapes_match_oracle(gpu):
+    # configuration 4 shapes: 128 experts, gate/up 2048->768, down 768->2048, Q4_K, top 8
+    experts, hidden, ffn, top = 16, 2048, 768, 8          # 16 experts keep the upload small
+    tg = Tensor.of([hidden, ffn, experts], Q4_K)
+    td = Tensor.of([ffn, hidden, experts], Q4_K)
+    g, u = synth.random_matrix(Q4_K, hidden, ffn, experts, 1), synth.random_matrix(Q4_K, hidden, ffn, experts, 2)
+    d = synth.random_matrix(Q4_K, ffn, hidden, experts, 3)
+    wg, wu, wd = Weight(gpu.bytes(g), tg), Weight(gpu.bytes(u), tg), Weight(gpu.bytes(d), td)
+    for tokens in (1, 4):
+        pairs = tokens * top
+        rng = np.random.default_rng(tokens)
+        ids = np.stack([rng.permutation(experts)[:top] for _ in range(tokens)]).astype(np.uint32).reshape(-1)
+        x = synth.activations(tokens, hidden, seed=7) * np.float32(0.01)
+        idb, xb = gpu.bytes(ids), gpu.floats(x)
+        act_b = gpu.generic_routed_gate_up(None, [wg, wu], [xb, idb], top, pairs)
+        act = gpu.finish(None, act_b).reshape(pairs, ffn)
+        out_b = gpu.output(pairs * hidden)
+        assert gpu.generic_routed(None, wd, [act_b, idb, out_b], True, top, pairs)
+        out = gpu.finish(None, out_b).reshape(pairs, hidden)
+        for p in range(pairs):
+            e_id, t = int(ids[p]), p // top
+            eg = O.matvec_f64(g, hidden, ffn, Q4_K, x[t], expert=e_id)[0]
+            eu = O.matvec_f64(u, hidden, ffn, Q4_K, x[t], expert=e_id)[0]
+            ea = O.glu(eg.astype(np.float32), eu.astype(np.float32)).astype(np.float64)
+            assert (np.abs(act[p] - ea) <= tol_contract(ea)).all()
+            ed = O.matvec_f64(d, ffn, hidden, Q4_K, act[p], expert=e_id)[0]     # same input as the GPU's down-proj
+            assert (np.abs(out[p] - ed) <= tol_contract(ed)).all()
+            assert (np.abs(out[p] - ed) <= tol_ref(ed)).mean() > 0.99
+
+
+def test_routed_expert_id_out_of_range_is_an_error_not_a_fault(gpu):
+    t = Tensor.of([256, 4, 2], Q4_K)
+    w = Weight(gpu.bytes(synth.random_matrix(Q4_K, 256, 4, 2)), t)
+    ids = gpu.bytes(np.array([0, 5], np.uint32))
+    y = gpu.zeros(8)
+    assert gpu.generic_routed(None, w, [gpu.floats(np.ones(256, np.float32)), ids, y], False, 2, 2)
+    with pytest.raises(InvalidData, match="expert id out of range"):
+        gpu.complete()
+    # the handle stays usable and the valid pair was computed
+    gpu.complete()
+    assert np.isfinite(gpu.read_f32(y)).all()
+
+
+# ---- routing, combine, grouping ---------------------------------------------------
+
+@pytest.mark.parametrize("count", [1, 31, 33, 128, 288, 512])
+@pytest.mark.parametrize("ties", [False, True])
+def test_route_topk_ids_exact_weights_close(gpu, count, ties):
+    # src/metal/tests.rs:94-137
+    logits = np.array([1000.0 if ties else float((i * 17) % 23) - 11.0 for i in range(count)], np.float32)
+    top = min(count, 10)
+    ids_b, w_b = gpu.route_topk(gpu.floats(logits), count, top, 1)
+    gpu.complete()
+    e_ids, e_w = O.route(logits, top)
+    assert gpu.read_u32(ids_b, top).tolist() == e_ids.tolist()
+    assert np.abs(gpu.read_f32(w_b, top) - e_w).max() < 2e-5
+
+
+def test_route_topk_batch_of_random_tokens(gpu):
+    # configuration 4: 128 experts, N(0,1) logits, top-8 softmax renormalised, 32 tokens
+    logits = np.random.default_rng(0).normal(0, 1, (32, 128)).astype(np.float32)
+    ids_b, w_b = gpu.route_topk(gpu.floats(logits), 128, 8, 32)
+    gpu.complete()
+    ids, w = gpu.read_u32(ids_b, 256).reshape(32, 8), gpu.read_f32(w_b, 256).reshape(32, 8)
+    for t in range(32):
+        e_ids, e_w = O.route(logits[t], 8)
+        assert ids[t].tolist() == e_ids.tolist()
+        assert np.abs(w[t] - e_w).max() < 2e-6
+    assert np.abs(w.sum(1) - 1).max() < 1e-6
+
+
+def test_route_rejects_bad_requests(gpu):
+    l = gpu.floats(np.zeros(8, np.float32))
+    for experts, top in ((8, 0), (8, 9), (1024, 4)):
+        with pytest.raises(InvalidData):
+            gpu.route_topk(l, experts, top, 1)
+    bad = gpu.floats(np.array([0.0, np.nan, 1.0, 2.0], np.float32))
+    gpu.route_topk(bad, 4, 2, 1)
+    with pytest.raises(InvalidData, match="invalid router scores"):
+        gpu.complete()
+    gpu.complete()
+
+
+def test_moe_sum_and_merge(gpu):
+    rng = np.random.default_rng(3)
+    tokens, top, width = 5, 8, 2048
+    routed = rng.normal(0, 1, (tokens * top, width)).astype(np.float32)
+    w = rng.random((tokens, top)).astype(np.float32)
+    y = gpu.finish(None, gpu.moe_sum(gpu.floats(routed), gpu.floats(w), width, top, tokens)).reshape(tokens, width)
+    assert np.abs(y - O.moe_sum(routed, w, width, top)).max() < 1e-5
+    shared = rng.normal(0, 1, width).astype(np.float32)
+    out = gpu.finish(None, gpu.merge(None, gpu.floats(routed[:top]), gpu.floats(shared), gpu.floats(w[0]),
+                                     gpu.floats(np.array([0.3], np.float32)), width, top))
+    assert np.abs(out - O.combine(routed[:top], shared, w[0], 0.3, width)).max() < 1e-5
+
+
+def test_expert_layout_and_combine_packed(gpu):
+    rng = np.random.default_rng(11)
+    for pairs, experts in ((8, 128), (64, 128), (256, 128), (100, 6), (1, 1)):
+        ids = rng.integers(0, experts, pairs).astype(np.uint32)
+        cap = pairs + experts
+        layout, tiles, packed, inverse = gpu.expert_layout(gpu.bytes(ids), pairs, experts, cap)
+        gpu.complete()
+        e_layout, e_tiles, e_pairs, e_inv, n = O.expert_layout(ids, experts, cap)
+        assert np.array_equal(gpu.read_u32(layout, 2 * experts).reshape(-1, 2), e_layout)
+        assert np.array_equal(gpu.read_u32(tiles, 4 * cap).reshape(-1, 4), e_tiles)
+        assert np.array_equal(gpu.read_u32(packed, pairs), e_pairs)
+        assert np.array_equal(gpu.read_u32(inverse, pairs), e_inv)
+    top, tokens, width = 8, 8, 256
+    ids = rng.integers(0, 16, top * tokens).astype(np.uint32)
+    _, _, packed, inverse = gpu.expert_layout(gpu.bytes(ids), top * tokens, 16, 80)
+    gpu.complete()
+    inv = gpu.read_u32(inverse, top * tokens)
+    routed_packed = rng.normal(0, 1, (top * tokens, width)).astype(np.float32)
+    w = rng.random(top * tokens).astype(np.float32)
+    y = gpu.finish(None, gpu.combine_packed(gpu.floats(routed_packed), gpu.floats(w), inverse, width, top, tokens))
+    assert np.abs(y.reshape(tokens, width) - O.combine_packed(routed_packed, w, inv, width, top)).max() < 1e-5
+
+
+def test_add_rms(gpu):
+    rng = np.random.default_rng(1)
+    a, b = rng.normal(0, 1, (3, 4096)).astype(np.float32), rng.normal(0, 1, (3, 4096)).astype(np.float32)
+    w = rng.random(4096).astype(np.float32) + 0.5
+    s_b, y_b, yb_b = gpu.add_rms(None, gpu.floats(a), gpu.floats(b), gpu.floats(w), 4096, 3, 1e-6, True, bf16_out=True)
+    y = gpu.finish(None, y_b).reshape(3, 4096)
+    e_s, e_y = O.add_rms(a, b, w, 1e-6)
+    assert np.array_equal(gpu.read_f32(s_b).reshape(3, 4096), e_s)
+    assert np.abs(y - e_y).max() < 1e-5
+    assert np.array_equal(gpu.read_bytes(yb_b).view(np.uint16).reshape(3, 4096), synth.to_bf16_bits(y))
+
+
+# ---- recorded commands ---------------------------------------------------------------
+
+def test_recorded_chain_replays_identically(gpu):
+    # a small q -> o style chain recorded once (one Command per decode step) and replayed
+    cols = 1024
+    w1 = Weight(gpu.bytes(synth.random_matrix(Q4_K, cols, cols, seed=1)), Tensor.of([cols, cols], Q4_K))
+    w2 = Weight(gpu.bytes(synth.random_matrix(Q6_K, cols, 256, seed=2)), Tensor.of([cols, 256], Q6_K))
+    x = gpu.floats(synth.activations(1, cols, seed=3))
+    h, n, y = gpu.output(cols), gpu.output(cols), gpu.output(256)
+    def chain():
+        gpu.matmul(None, w1.buffer, cols, cols, w1.t.stride, Q4_K, 0, x, 1, out=h)
+        gpu._check(gpu._lib.ingot_add_rms(gpu._h, h.ptr, None, None, None, n.ptr, None, cols, 1, 1e-6, 0))
+        gpu.matmul(None, w2.buffer, cols, 256, w2.t.stride, Q6_K, 0, n, 1, out=y)
+    chain()
+    eager = gpu.finish(None, y).copy()
+    gpu.record()
+    chain()
+    graph = gpu.end_record()
+    for _ in range(3):
+        gpu._check(gpu._lib.ingot_buffer_zero(gpu._h, y.ptr, y.nbytes))
+        graph.submit()
+        assert np.array_equal(gpu.finish(None, y).view(np.uint32), eager.view(np.uint32))
