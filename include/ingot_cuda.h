@@ -198,6 +198,14 @@ INGOT_API ingot_status ingot_add_rms(ingot_gpu *gpu, const float *a, const float
                                      float *y, void *y_bf16, uint32_t width, uint32_t rows, float eps,
                                      uint32_t add);
 
+/* add_rms that also writes y in the packed order of ingot_pack_x (`y_packed`, rows of
+ * ingot_packed_x_bytes(width); width a multiple of 64), so the projections that
+ * follow need no separate packing pass.  pack_from_bf16 != 0 packs the bfloat16
+ * rounding of y (what packing `y_bf16` would give). */
+INGOT_API ingot_status ingot_add_rms_packed(ingot_gpu *gpu, const float *a, const float *b, const float *w, float *s,
+                                            float *y, void *y_bf16, void *y_packed, uint32_t pack_from_bf16,
+                                            uint32_t width, uint32_t rows, float eps, uint32_t add);
+
 /* expert_layout + expert_pairs (kernels/prefill.metal:7-35): stable
  * expert-major grouping of `pairs` ids.  layout [experts][2] = (count, first),
  * tiles [tile_capacity][4] = (expert, first, n <= 32, mode), packed[pos] =

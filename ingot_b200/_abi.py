@@ -44,6 +44,7 @@ SIGNATURES = {
     "ingot_activation": [vp, vp, vp, u64, u32, vp],
     "ingot_merge": [vp, vp, vp, vp, vp, u32, u32, vp],
     "ingot_add_rms": [vp, vp, vp, vp, vp, vp, vp, u32, u32, f32, u32],
+    "ingot_add_rms_packed": [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, u32],
     "ingot_expert_layout": [vp, vp, u32, u32, u32, vp, vp, vp, vp],
     "ingot_combine_packed": [vp, vp, vp, vp, u32, u32, u32, vp],
     "ingot_convert_bf16": [vp, vp, u64, vp],

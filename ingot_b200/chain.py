@@ -121,13 +121,12 @@ class DecodeChain:
         g = self.gpu
         y32 = out.ptr if self.x_kind == F32 else None
         y16 = out.ptr if self.x_kind == BF16 else None
-        g._check(g._lib.ingot_add_rms(g._h, a.ptr, b.ptr if b else None, None, s.ptr if s else None, y32, y16,
-                                      width, self.batch, 1e-6, 1 if b else 0))
-        self.launches_per_step += 1
+        packed = None
         if self.packed:
-            dst = {self.xn.ptr: self.xn_p, self.a.ptr: self.a_p, self.actn.ptr: self.actn_p}[out.ptr]
-            g._check(g._lib.ingot_pack_x(g._h, out.ptr, self.x_kind, 1, width, dst.ptr))
-            self.launches_per_step += 1
+            packed = {self.xn.ptr: self.xn_p, self.a.ptr: self.a_p, self.actn.ptr: self.actn_p}[out.ptr].ptr
+        g._check(g._lib.ingot_add_rms_packed(g._h, a.ptr, b.ptr if b else None, None, s.ptr if s else None, y32, y16,
+                                             packed, int(self.x_kind == BF16), width, self.batch, 1e-6, 1 if b else 0))
+        self.launches_per_step += 1
 
     def _x(self, x: Buffer):
         """(pointer, x_kind) of a GEMV input: the packed copy when there is one."""

@@ -388,10 +388,18 @@ ingot_status ingot_merge(ingot_gpu *g, const float *routed, const float *shared,
 
 ingot_status ingot_add_rms(ingot_gpu *g, const float *a, const float *b, const float *w, float *s, float *y,
                            void *y_bf16, uint32_t width, uint32_t rows, float eps, uint32_t add) {
+    return ingot_add_rms_packed(g, a, b, w, s, y, y_bf16, nullptr, 0, width, rows, eps, add);
+}
+
+ingot_status ingot_add_rms_packed(ingot_gpu *g, const float *a, const float *b, const float *w, float *s, float *y,
+                                  void *y_bf16, void *y_packed, uint32_t pack_from_bf16, uint32_t width, uint32_t rows,
+                                  float eps, uint32_t add) {
     ingot_status st = enter(g);
     if (st) return st;
-    if (!a || (add && !b) || width % 4u || width == 0) return fail(g, INGOT_INVALID, "add_rms: bad arguments");
-    return after_launch(g, launch_add_rms(a, b, w, s, y, width, rows, eps, add, y_bf16, ctx_of(g)), "add_rms");
+    if (!a || (add && !b) || width % 4u || width == 0 || (y_packed && (width % 64u || ((uintptr_t)y_packed % 16u))))
+        return fail(g, INGOT_INVALID, "add_rms: bad arguments");
+    return after_launch(g, launch_add_rms(a, b, w, s, y, width, rows, eps, add, y_bf16, y_packed, pack_from_bf16, ctx_of(g)),
+                        "add_rms");
 }
 
 ingot_status ingot_expert_layout(ingot_gpu *g, const uint32_t *ids, uint32_t pairs, uint32_t experts,

@@ -226,7 +226,7 @@ static cudaError_t launch_stream_t(const GemvArgs &a, dim3 grid, cudaStream_t st
     auto kernel = gemv_stream_kernel<KIND, NTOK, NMAT>;
     static bool configured = false;          // per instantiation; the attribute is per device function
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_BUDGET);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_MAX);
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -300,8 +300,16 @@ cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx) {
         uint32_t max_ctas = (2u * ctx.sm_count + gy - 1) / gy;
         if (max_ctas < 1) max_ctas = 1;
         bool ok = false;
+        uint32_t budget = GEMV_SMEM_BUDGET;
         for (; group >= 1; --group)
-            if ((ok = plan_gemv(c.kind, c.cols, c.rows, c.stride, group, c.nmat, max_ctas, plan))) break;
+            if ((ok = plan_gemv(c.kind, c.cols, c.rows, c.stride, group, c.nmat, max_ctas, plan, budget))) break;
+        if (!ok) {                                   // one CTA per SM with the whole shared memory
+            budget = GEMV_SMEM_MAX;
+            max_ctas = (ctx.sm_count + gy - 1) / gy;
+            if (max_ctas < 1) max_ctas = 1;
+            for (group = routed ? 1u : (c.count < 4u ? c.count : 4u); group >= 1; --group)
+                if ((ok = plan_gemv(c.kind, c.cols, c.rows, c.stride, group, c.nmat, max_ctas, plan, budget))) break;
+        }
         if (ok) {
             GemvArgs a = {};
             a.w[0] = c.w[0]; a.w[1] = c.w[1];
@@ -315,7 +323,7 @@ cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx) {
             const size_t xb = c.x_bf16 ? 2 : 4;
             for (uint32_t t0 = 0; t0 < c.count;) {
                 uint32_t n = c.count - t0 < group ? c.count - t0 : group;
-                if (n != plan.ntok && !plan_gemv(c.kind, c.cols, c.rows, c.stride, n, c.nmat, max_ctas, plan))
+                if (n != plan.ntok && !plan_gemv(c.kind, c.cols, c.rows, c.stride, n, c.nmat, max_ctas, plan, budget))
                     return cudaErrorInvalidValue;
                 a.plan = plan;
                 a.x = static_cast<const uint8_t *>(c.x) + (size_t)t0 * c.cols * xb;

@@ -23,6 +23,7 @@ static constexpr int GEMV_THREADS = (GEMV_CONSUMER_WARPS + 1) * 32;   // + produ
 static constexpr int GEMV_NR = 2;                  // rows per lane group sharing one x load
 static constexpr int GEMV_MAX_STAGES = 8;
 static constexpr uint32_t GEMV_SMEM_BUDGET = 112u * 1024u;   // two CTAs per SM
+static constexpr uint32_t GEMV_SMEM_MAX = 224u * 1024u;      // one CTA per SM, for shapes that need the room
 static constexpr uint32_t GEMV_STAGE_TARGET = 20u * 1024u;
 static constexpr uint32_t GEMV_BAR_BYTES = 128;
 
@@ -49,7 +50,7 @@ inline uint32_t units_per_block(uint32_t kind) { return (kind == KIND_Q4_K || ki
 // Builds the plan; false when the shape needs the plain kernel instead
 // (unaligned rows, a float weight type, or activations that do not fit).
 inline bool plan_gemv(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t ntok,
-                      uint32_t nmat, uint32_t max_ctas, GemvPlan &p) {
+                      uint32_t nmat, uint32_t max_ctas, GemvPlan &p, uint32_t budget = GEMV_SMEM_BUDGET) {
     uint32_t block, bytes;
     if (!geometry(kind, block, bytes) || block == 1) return false;
     if (cols == 0 || rows == 0 || cols % block || stride != cols / block * bytes) return false;
@@ -67,7 +68,7 @@ inline bool plan_gemv(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stri
     p.steps = (p.units + lpr - 1) / lpr;
     p.tile_rows = GEMV_CONSUMER_WARPS * GEMV_NR * (32u / lpr);
     p.x_bytes = ntok * p.steps * lpr * 8u * 16u;
-    if (p.x_bytes + GEMV_BAR_BYTES >= GEMV_SMEM_BUDGET) return false;
+    if (p.x_bytes + GEMV_BAR_BYTES >= budget) return false;
     // chunk: the largest aligned number of steps whose stage stays near the target
     uint32_t pick = 0;
     for (uint32_t spc = 1; spc <= p.steps; ++spc) {
@@ -89,7 +90,7 @@ inline bool plan_gemv(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stri
     p.last_chunk_bytes = stride - (p.chunks - 1) * p.chunk_bytes;
     p.stage_bytes = (p.chunk_bytes * p.tile_rows * nmat + 16u + 127u) & ~127u;
     uint32_t x_al = (p.x_bytes + 127u) & ~127u;
-    uint32_t room = GEMV_SMEM_BUDGET - GEMV_BAR_BYTES - x_al;
+    uint32_t room = budget - GEMV_BAR_BYTES - x_al;
     p.stages = room / p.stage_bytes;
     if (p.stages > GEMV_MAX_STAGES) p.stages = GEMV_MAX_STAGES;
     if (p.stages < 2) return false;

@@ -36,6 +36,7 @@
 #include "dev_common.cuh"
 #include "gemv_core.cuh"
 #include "kernels.h"
+#include "pack.cuh"
 #include "ptx.cuh"
 
 namespace ingot {
@@ -43,9 +44,13 @@ namespace ingot {
 static constexpr int MMA_WARPS = 8;                       // consumer warps
 static constexpr int MMA_THREADS = (MMA_WARPS + 1) * 32;  // + producer warp
 static constexpr uint32_t MMA_SMEM_BUDGET = 112u * 1024u; // two CTAs per SM
+static constexpr uint32_t MMA_SMEM_SMALL = 74u * 1024u;   // three CTAs per SM
 static constexpr uint32_t MMA_SMEM_MAX = 224u * 1024u;
-static constexpr uint32_t MMA_STAGE_TARGET = 40u * 1024u;
-static constexpr int MMA_MAX_STAGES = 6;                  // barriers: full[6], empty[6], x
+static constexpr uint32_t MMA_STAGE_TARGET = 24u * 1024u;
+static constexpr int MMA_MAX_STAGES = 6;                  // barriers: full[6], empty[6], x, tile[8] (<= 128 bytes... 21 x 8)
+static constexpr uint32_t MMA_RED_SLOTS = 8;              // > MMA_MAX_STAGES: a warp is never that many tiles ahead
+static constexpr uint32_t MMA_ZERO_BYTES = 1024;          // B operands of one step, all zero
+static constexpr uint32_t MMA_BAR_BYTES = 256;
 
 struct MmaPlan {
     uint32_t kind, cols, rows, stride, nmat;
@@ -61,6 +66,7 @@ struct MmaPlan {
     uint32_t x_bytes;        // packed activations of one token
     uint32_t red_bytes, smem_bytes;
     uint32_t ctas;
+    uint32_t red_slots;      // ring of partial-sum buffers, > stages
 };
 
 struct MmaArgs {
@@ -102,8 +108,9 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     p.row_tiles = (uint32_t)MMA_WARPS >> kw;
     const uint32_t per_warp = p.nsteps >> kw;                 // steps each warp owns per row
     p.x_bytes = packed_x_bytes(cols);
-    p.red_bytes = 2u * MMA_WARPS * 2u * 16u * 4u;             // [parity][warp][mat][row]
-    const uint32_t fixed = GEMV_BAR_BYTES + ((p.x_bytes + 127u) & ~127u) + p.red_bytes;
+    p.red_slots = budget <= MMA_SMEM_SMALL ? 4u : MMA_RED_SLOTS;
+    p.red_bytes = p.red_slots * MMA_WARPS * 2u * 16u * 4u + MMA_ZERO_BYTES;   // [slot][warp][mat][row] + zeros
+    const uint32_t fixed = MMA_BAR_BYTES + ((p.x_bytes + 127u) & ~127u) + p.red_bytes;
     if (fixed >= budget) return false;
     // chunk = the most steps per warp whose stage stays near the target, leaves at least
     // two stages, and keeps every copy 16-byte aligned
@@ -113,7 +120,7 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
         if (per_warp % spw) continue;
         const uint32_t cb = spw * (1u << kw) * p.step_bytes;
         if (cb % 16u) continue;
-        const uint32_t sb = (pitch_of(cb) * 16u * p.row_tiles * nmat + 64u + 127u) & ~127u;
+        const uint32_t sb = (pitch_of(cb) * 16u * p.row_tiles + 64u + 127u) & ~127u;      // one matrix per stage
         if (room / sb < 2) break;
         if (pick == 0 || sb <= MMA_STAGE_TARGET) pick = spw;
     }
@@ -122,9 +129,10 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     p.chunks = per_warp / pick;
     p.chunk_bytes = pick * (1u << kw) * p.step_bytes;
     p.row_pitch = pitch_of(p.chunk_bytes);
-    p.stage_bytes = (p.row_pitch * 16u * p.row_tiles * nmat + 64u + 127u) & ~127u;
+    p.stage_bytes = (p.row_pitch * 16u * p.row_tiles + 64u + 127u) & ~127u;
     p.stages = room / p.stage_bytes;
     if (p.stages > (uint32_t)MMA_MAX_STAGES) p.stages = MMA_MAX_STAGES;
+    if (p.stages > p.red_slots - 2u) p.stages = p.red_slots - 2u;
     if (p.stages < 2) return false;
     p.smem_bytes = fixed + p.stages * p.stage_bytes;
     const uint32_t want = (rows + 7u) / 8u;
@@ -161,44 +169,19 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const __grid_constant__ Pac
     mx = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) mx = fmaxf(mx, part_max[i]);
-    float scale = 1.0f;
-    if (mx >= 16384.0f && mx < INFINITY) {
-        int e;
-        frexpf(mx, &e);                       // mx = f * 2^e, f in [0.5, 1)
-        scale = ldexpf(1.0f, 14 - e);         // mx * scale in [2^13, 2^14)
-    }
-    __half *xf = reinterpret_cast<__half *>(row);
-    float *sx = reinterpret_cast<float *>(row + (size_t)a.cols * 4u);
+    const float scale = pack_scale(mx);
     // one thread per 4 consecutive columns = one lane's word of one MMA; every thread
     // runs the same number of rounds so the quad shuffles always have all lanes
     const uint32_t n4 = a.cols / 4u;
     for (uint32_t q0 = 0; q0 < n4; q0 += 256) {
         const uint32_t q = q0 + tid;
         const bool live = q < n4;
-        const uint32_t mi = q >> 2, t = q & 3u;
         float v[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = live ? load_x(a.x, base + 4u * q + i, a.bf16) * scale : 0.f;
-        __half h[4], l[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            h[i] = __float2half_rn(v[i]);
-            l[i] = __float2half_rn(v[i] - __half2float(h[i]));
-        }
-        if (live) {
-            // slots: byte 0 -> b0.lo, byte 2 -> b0.hi, byte 1 -> b1.lo, byte 3 -> b1.hi
-            __half2 *dh = reinterpret_cast<__half2 *>(xf + ((mi * 2u + 0u) * 4u + t) * 4u);
-            __half2 *dl = reinterpret_cast<__half2 *>(xf + ((mi * 2u + 1u) * 4u + t) * 4u);
-            dh[0] = __halves2half2(h[0], h[2]); dh[1] = __halves2half2(h[1], h[3]);
-            dl[0] = __halves2half2(l[0], l[2]); dl[1] = __halves2half2(l[1], l[3]);
-        }
-        // the 16-column sum: four lanes, fixed order
-        float s = (v[0] + v[1]) + (v[2] + v[3]);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        if (live && t == 0) sx[mi] = s;
+        pack_store_quad(row, a.cols, q, v, live);
     }
-    if (tid == 0) *reinterpret_cast<float *>(row + (size_t)a.cols * 4u + a.cols / 4u) = 1.0f / scale;
+    if (tid == 0) pack_store_unscale(row, a.cols, scale);
 }
 
 cudaError_t launch_pack_x(const void *x, uint32_t bf16, uint32_t rows, uint32_t cols, void *packed, const LaunchCtx &ctx) {
@@ -258,18 +241,27 @@ __device__ __forceinline__ uint32_t lds16(const uint8_t *p) { return *reinterpre
 // (acc0, acc1): this lane's share of rows g and g+8 (summed over the quad later).
 // ---------------------------------------------------------------------------
 
-#define IG_BFRAG(mi) (*reinterpret_cast<const uint2 *>(xf + (((mi) * 2u + part) * 4u + t) * 4u))
-#define IG_LO(w) unmagic<0x6400>(((w) & 0x000f000fu) | MAGIC_H2)
-#define IG_HI(w) unmagic<0x6400>(((w) & 0x00f000f0u) | MAGIC_H2)     /* 16 * nibble */
+// xb[grp]: this lane's B-operand pointer for scale group `grp` of the step — the real
+// packed activations when the lane's quad position owns that group, else a block of
+// zeros.  A group's MMAs therefore add to the accumulator only in the lane that owns
+// it, so all groups of a step chain into the same accumulator registers and each lane
+// applies its own group's scale once, without selects.
+#define IG_BFRAG(grp, mi) (*reinterpret_cast<const uint2 *>(xb[grp] + (mi) * 64u))
+// A binary16 whose exponent field is zero is subnormal: its value is mantissa * 2^-24,
+// exactly, with no implicit one.  So the masked quant bits ARE the operand (times
+// 2^-24, undone in the scale); no bias to subtract.  The tensor cores take binary16
+// subnormals at full rate.
+#define IG_LO(w) ((w) & 0x000f000fu)
+#define IG_HI(w) ((w) & 0x00f000f0u)     /* 16 * nibble */
+static constexpr float SUBNORMAL_SCALE = 16777216.0f;       // 2^24
 
 template <uint32_t KIND> struct MmaStep;
 
 // Q4_K: 256 columns = 4 groups j of 64: 32 bytes whose low nibbles are sub-block 2j
-// and high nibbles sub-block 2j+1.  MMAs 4j+h (low, h = 0,1) share one scale and
-// chain into one accumulator; so do 4j+2+h (high).  Lane t owns group j = t's
-// scales and mins.
+// and high nibbles sub-block 2j+1.  Lane t owns group j = t: its low-nibble MMAs
+// (4j, 4j+1) and high-nibble MMAs (4j+2, 4j+3).
 template <> struct MmaStep<KIND_Q4_K> {
-    // (d * sc_2t, d * sc_2t+1 / 16, dmin * m_2t, dmin * m_2t+1) of sub-block group j = t of one row's block
+    // (d * sc_2t, d * sc_2t+1 / 16, dmin * m_2t, dmin * m_2t+1) of group j = t of one row's block
     static __device__ __forceinline__ void scales(const uint8_t *r, uint32_t t, float &dsc0, float &dsc1, float &dm0, float &dm1) {
         const U4 hdr = *reinterpret_cast<const U4 *>(r);
         const uint32_t sh = (t & 1u) * 16u;
@@ -278,47 +270,40 @@ template <> struct MmaStep<KIND_Q4_K> {
         if (t < 2) { sc = a & 0x3f3fu; m = bb & 0x3f3fu; }
         else { sc = (c & 0x0f0fu) | ((a >> 2) & 0x3030u); m = ((c >> 4) & 0x0f0fu) | ((bb >> 2) & 0x3030u); }
         const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));      // (d, dmin)
-        dsc0 = mul_rn(dd.x, (float)(sc & 0xffu));
-        dsc1 = mul_rn(mul_rn(dd.x, (float)(sc >> 8)), 0.0625f);
+        dsc0 = mul_rn(mul_rn(dd.x, (float)(sc & 0xffu)), SUBNORMAL_SCALE);
+        dsc1 = mul_rn(mul_rn(dd.x, (float)(sc >> 8)), SUBNORMAL_SCALE * 0.0625f);
         dm0 = mul_rn(dd.y, (float)(m & 0xffu));
         dm1 = mul_rn(dd.y, (float)(m >> 8));
     }
-    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const __half *xf, const float *sx,
-                                               uint32_t g, uint32_t t, float &acc0, float &acc1) {
-        const uint32_t part = g & 1u;
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
+                                               uint32_t t, float &acc0, float &acc1) {
         float s00, s01, m00, m01, s10, s11, m10, m11;
         scales(r0, t, s00, s01, m00, m01);
         scales(r1, t, s10, s11, m10, m11);
         const uint8_t *q0 = r0 + 16u + 4u * t, *q1 = r1 + 16u + 4u * t;
+        float lo[4], hi[4];
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
-            float lo[4], hi[4];
-            {
-                const uint32_t a = lds32(q0 + 32u * j), b = lds32(q1 + 32u * j);
+        for (uint32_t j = 0; j < 4; ++j)
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t a = lds32(q0 + 32u * j + 16u * h), b = lds32(q1 + 32u * j + 16u * h);
                 const uint32_t as = a >> 8, bs = b >> 8;
-                const uint2 bl = IG_BFRAG(4u * j), bh = IG_BFRAG(4u * j + 2u);
-                mma16816_first(lo, IG_LO(a), IG_LO(b), IG_LO(as), IG_LO(bs), bl.x, bl.y);
-                mma16816_first(hi, IG_HI(a), IG_HI(b), IG_HI(as), IG_HI(bs), bh.x, bh.y);
+                const uint2 bl = IG_BFRAG(j, 4u * j + h), bh = IG_BFRAG(j, 4u * j + 2u + h);
+                if (j == 0 && h == 0) {
+                    mma16816_first(lo, IG_LO(a), IG_LO(b), IG_LO(as), IG_LO(bs), bl.x, bl.y);
+                    mma16816_first(hi, IG_HI(a), IG_HI(b), IG_HI(as), IG_HI(bs), bh.x, bh.y);
+                } else {
+                    mma16816(lo, IG_LO(a), IG_LO(b), IG_LO(as), IG_LO(bs), bl.x, bl.y);
+                    mma16816(hi, IG_HI(a), IG_HI(b), IG_HI(as), IG_HI(bs), bh.x, bh.y);
+                }
             }
-            {
-                const uint32_t a = lds32(q0 + 32u * j + 16u), b = lds32(q1 + 32u * j + 16u);
-                const uint32_t as = a >> 8, bs = b >> 8;
-                const uint2 bl = IG_BFRAG(4u * j + 1u), bh = IG_BFRAG(4u * j + 3u);
-                mma16816(lo, IG_LO(a), IG_LO(b), IG_LO(as), IG_LO(bs), bl.x, bl.y);
-                mma16816(hi, IG_HI(a), IG_HI(b), IG_HI(as), IG_HI(bs), bh.x, bh.y);
-            }
-            if (t == j) {
-                acc0 = fma_rn(s00, add_rn(lo[0], lo[1]), acc0);
-                acc0 = fma_rn(s01, add_rn(hi[0], hi[1]), acc0);
-                acc1 = fma_rn(s10, add_rn(lo[2], lo[3]), acc1);
-                acc1 = fma_rn(s11, add_rn(hi[2], hi[3]), acc1);
-            }
-        }
         // - dmin * (m_2t * sum x over sub-block 2t + m_2t+1 * sum x over sub-block 2t+1)
         const float4 sq = *reinterpret_cast<const float4 *>(sx + 4u * t);
         const float sa = add_rn(sq.x, sq.y), sb = add_rn(sq.z, sq.w);
-        acc0 = sub_rn(acc0, fma_rn(m01, sb, mul_rn(m00, sa)));
-        acc1 = sub_rn(acc1, fma_rn(m11, sb, mul_rn(m10, sa)));
+        acc0 = add_rn(acc0, sub_rn(fma_rn(s01, add_rn(hi[0], hi[1]), mul_rn(s00, add_rn(lo[0], lo[1]))),
+                                   fma_rn(m01, sb, mul_rn(m00, sa))));
+        acc1 = add_rn(acc1, sub_rn(fma_rn(s11, add_rn(hi[2], hi[3]), mul_rn(s10, add_rn(lo[2], lo[3]))),
+                                   fma_rn(m11, sb, mul_rn(m10, sa))));
     }
 };
 
@@ -326,23 +311,25 @@ template <> struct MmaStep<KIND_Q4_K> {
 // run with its own int8 scale (index 8n + 2q + h).  A run's 6-bit values come from
 // a word of ql (low nibble for q < 2, high nibble — kept in place, times 16 — for
 // q >= 2; ql + 32 for odd q) and two bits of a word of qh.  Lane t owns quarter
-// q = t's scales.  Blocks are only 2-byte aligned.
+// q = t.  Blocks are only 2-byte aligned.
 template <> struct MmaStep<KIND_Q6_K> {
     template <int Q>
     static __device__ __forceinline__ uint32_t six(uint32_t L, uint32_t H) {       // bytes (0,2) of the words
         constexpr uint32_t nib = (Q >= 2) ? 0x00f000f0u : 0x000f000fu;
         constexpr uint32_t hmask = 0x00030003u << (2 * Q);
         constexpr uint32_t mult = (Q == 0 || Q == 2) ? 16u : 4u;                 // two high bits to bit 4 (q < 2) or 8
-        return unmagic<0x6400>((L & nib) | ((H & hmask) * mult + MAGIC_H2));
+        return (L & nib) | ((H & hmask) * mult);            // subnormal binary16 pair: value * 2^-24
     }
-    template <int Q>
+    template <int Q, bool FIRST>
     static __device__ __forceinline__ void quarter(uint32_t la, uint32_t lb, uint32_t ha, uint32_t hb, uint2 bf, float (&c)[4]) {
-        mma16816_first(c, six<Q>(la, ha), six<Q>(lb, hb), six<Q>(la >> 8, ha >> 8), six<Q>(lb >> 8, hb >> 8), bf.x, bf.y);
+        if (FIRST) mma16816_first(c, six<Q>(la, ha), six<Q>(lb, hb), six<Q>(la >> 8, ha >> 8), six<Q>(lb >> 8, hb >> 8), bf.x, bf.y);
+        else mma16816(c, six<Q>(la, ha), six<Q>(lb, hb), six<Q>(la >> 8, ha >> 8), six<Q>(lb >> 8, hb >> 8), bf.x, bf.y);
     }
-    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const __half *xf, const float *sx,
-                                               uint32_t g, uint32_t t, float &acc0, float &acc1) {
-        const uint32_t part = g & 1u;
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
+                                               uint32_t t, float &acc0, float &acc1) {
         const float d0 = lds_half(r0 + 208u), d1 = lds_half(r1 + 208u);
+        const float up = t < 2 ? SUBNORMAL_SCALE : SUBNORMAL_SCALE * 0.0625f;       // x16 of the in-place high nibble undone
+        float t0 = 0.f, t1 = 0.f;
 #pragma unroll
         for (uint32_t n = 0; n < 2; ++n) {
             // scales of quarter q = t: runs h = 0, 1 are consecutive bytes 8n + 2t, 8n + 2t + 1
@@ -352,79 +339,73 @@ template <> struct MmaStep<KIND_Q6_K> {
                 const uint32_t o = 64u * n + 16u * h + 4u * t;
                 const uint32_t a_lo = lds32_u2(r0 + o), a_hi = lds32_u2(r0 + o + 32u), a_h = lds32_u2(r0 + 128u + 32u * n + 16u * h + 4u * t);
                 const uint32_t b_lo = lds32_u2(r1 + o), b_hi = lds32_u2(r1 + o + 32u), b_h = lds32_u2(r1 + 128u + 32u * n + 16u * h + 4u * t);
-                float c[4][4];
-                quarter<0>(a_lo, b_lo, a_h, b_h, IG_BFRAG(8u * n + 0u + h), c[0]);
-                quarter<1>(a_hi, b_hi, a_h, b_h, IG_BFRAG(8u * n + 2u + h), c[1]);
-                quarter<2>(a_lo, b_lo, a_h, b_h, IG_BFRAG(8u * n + 4u + h), c[2]);
-                quarter<3>(a_hi, b_hi, a_h, b_h, IG_BFRAG(8u * n + 6u + h), c[3]);
-                // lane t applies quarter q = t: value - 32 via the run's activation sum; x16 undone for q >= 2
+                float c[4];
+                quarter<0, true>(a_lo, b_lo, a_h, b_h, IG_BFRAG(0, 8u * n + 0u + h), c);
+                quarter<1, false>(a_hi, b_hi, a_h, b_h, IG_BFRAG(1, 8u * n + 2u + h), c);
+                quarter<2, false>(a_lo, b_lo, a_h, b_h, IG_BFRAG(2, 8u * n + 4u + h), c);
+                quarter<3, false>(a_hi, b_hi, a_h, b_h, IG_BFRAG(3, 8u * n + 6u + h), c);
+                // value - 32 through the run's activation sum
                 const float sc0 = (float)(int)(int8_t)((s0 >> (8u * h)) & 0xffu), sc1 = (float)(int)(int8_t)((s1 >> (8u * h)) & 0xffu);
-                const float sxv = sx[8u * n + 2u * t + h];
-                float q0, q1;
-                if (t == 0) { q0 = add_rn(c[0][0], c[0][1]); q1 = add_rn(c[0][2], c[0][3]); }
-                else if (t == 1) { q0 = add_rn(c[1][0], c[1][1]); q1 = add_rn(c[1][2], c[1][3]); }
-                else if (t == 2) { q0 = mul_rn(add_rn(c[2][0], c[2][1]), 0.0625f); q1 = mul_rn(add_rn(c[2][2], c[2][3]), 0.0625f); }
-                else { q0 = mul_rn(add_rn(c[3][0], c[3][1]), 0.0625f); q1 = mul_rn(add_rn(c[3][2], c[3][3]), 0.0625f); }
-                acc0 = fma_rn(mul_rn(d0, sc0), fma_rn(-32.0f, sxv, q0), acc0);
-                acc1 = fma_rn(mul_rn(d1, sc1), fma_rn(-32.0f, sxv, q1), acc1);
+                const float sxv = mul_rn(sx[8u * n + 2u * t + h], -32.0f);
+                t0 = fma_rn(sc0, fma_rn(add_rn(c[0], c[1]), up, sxv), t0);
+                t1 = fma_rn(sc1, fma_rn(add_rn(c[2], c[3]), up, sxv), t1);
             }
         }
+        acc0 = fma_rn(d0, t0, acc0);
+        acc1 = fma_rn(d1, t1, acc1);
     }
 };
 
 // Q4_0: step = 4 blocks of 32 (18 bytes each, 2-byte aligned): MMA 2b is the block's
 // low nibbles (elements 0..15), MMA 2b+1 its high nibbles (16..31).  Lane t owns
-// block b = t's scale.
+// block b = t.
 template <> struct MmaStep<KIND_Q4_0> {
-    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const __half *xf, const float *sx,
-                                               uint32_t g, uint32_t t, float &acc0, float &acc1) {
-        const uint32_t part = g & 1u;
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
+                                               uint32_t t, float &acc0, float &acc1) {
         const float d0 = lds_half(r0 + 18u * t), d1 = lds_half(r1 + 18u * t);
-        const float sxv = add_rn(sx[2u * t], sx[2u * t + 1u]);
+        const float sxv = mul_rn(add_rn(sx[2u * t], sx[2u * t + 1u]), -8.0f);
+        float lo[4], hi[4];
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
             const uint32_t wa = lds32_u2(r0 + 18u * b + 2u + 4u * t), wb = lds32_u2(r1 + 18u * b + 2u + 4u * t);
             const uint32_t as = wa >> 8, bs = wb >> 8;
-            float lo[4], hi[4];
-            const uint2 bl = IG_BFRAG(2u * b), bh = IG_BFRAG(2u * b + 1u);
-            mma16816_first(lo, IG_LO(wa), IG_LO(wb), IG_LO(as), IG_LO(bs), bl.x, bl.y);
-            mma16816_first(hi, IG_HI(wa), IG_HI(wb), IG_HI(as), IG_HI(bs), bh.x, bh.y);
-            if (t == b) {
-                const float q0 = fma_rn(add_rn(hi[0], hi[1]), 0.0625f, add_rn(lo[0], lo[1]));
-                const float q1 = fma_rn(add_rn(hi[2], hi[3]), 0.0625f, add_rn(lo[2], lo[3]));
-                acc0 = fma_rn(d0, fma_rn(-8.0f, sxv, q0), acc0);
-                acc1 = fma_rn(d1, fma_rn(-8.0f, sxv, q1), acc1);
+            const uint2 bl = IG_BFRAG(b, 2u * b), bh = IG_BFRAG(b, 2u * b + 1u);
+            if (b == 0) {
+                mma16816_first(lo, IG_LO(wa), IG_LO(wb), IG_LO(as), IG_LO(bs), bl.x, bl.y);
+                mma16816_first(hi, IG_HI(wa), IG_HI(wb), IG_HI(as), IG_HI(bs), bh.x, bh.y);
+            } else {
+                mma16816(lo, IG_LO(wa), IG_LO(wb), IG_LO(as), IG_LO(bs), bl.x, bl.y);
+                mma16816(hi, IG_HI(wa), IG_HI(wb), IG_HI(as), IG_HI(bs), bh.x, bh.y);
             }
         }
+        const float q0 = mul_rn(fma_rn(add_rn(hi[0], hi[1]), 0.0625f, add_rn(lo[0], lo[1])), SUBNORMAL_SCALE);
+        const float q1 = mul_rn(fma_rn(add_rn(hi[2], hi[3]), 0.0625f, add_rn(lo[2], lo[3])), SUBNORMAL_SCALE);
+        acc0 = fma_rn(d0, add_rn(q0, sxv), acc0);
+        acc1 = fma_rn(d1, add_rn(q1, sxv), acc1);
     }
 };
 
-// Q8_0: step = 4 blocks of 32 int8 (34 bytes each, 2-byte aligned): MMAs 2b and 2b+1
-// chain (one scale).  Lane t owns block b = t's scale.
+// Q8_0: step = 4 blocks of 32 int8 (34 bytes each, 2-byte aligned): MMAs 2b and 2b+1.
+// Lane t owns block b = t.  A byte b becomes (b + 128) * 2^-24; the 128 comes off
+// through the block's activation sum.
 template <> struct MmaStep<KIND_Q8_0> {
-    static __device__ __forceinline__ uint32_t s8(uint32_t w) { return unmagic<0x6480>((w & 0x00ff00ffu) ^ 0x64806480u); }
-    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const __half *xf, const float *,
-                                               uint32_t g, uint32_t t, float &acc0, float &acc1) {
-        const uint32_t part = g & 1u;
+    static __device__ __forceinline__ uint32_t s8(uint32_t w) { return (w & 0x00ff00ffu) ^ 0x00800080u; }
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
+                                               uint32_t t, float &acc0, float &acc1) {
         const float d0 = lds_half(r0 + 34u * t), d1 = lds_half(r1 + 34u * t);
+        const float sxv = mul_rn(add_rn(sx[2u * t], sx[2u * t + 1u]), -128.0f);
+        float c[4];
 #pragma unroll
-        for (uint32_t b = 0; b < 4; ++b) {
-            float c[4];
-            {
-                const uint32_t wa = lds32_u2(r0 + 34u * b + 2u + 4u * t), wb = lds32_u2(r1 + 34u * b + 2u + 4u * t);
-                const uint2 bf = IG_BFRAG(2u * b);
-                mma16816_first(c, s8(wa), s8(wb), s8(wa >> 8), s8(wb >> 8), bf.x, bf.y);
+        for (uint32_t b = 0; b < 4; ++b)
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t wa = lds32_u2(r0 + 34u * b + 2u + 16u * h + 4u * t), wb = lds32_u2(r1 + 34u * b + 2u + 16u * h + 4u * t);
+                const uint2 bf = IG_BFRAG(b, 2u * b + h);
+                if (b == 0 && h == 0) mma16816_first(c, s8(wa), s8(wb), s8(wa >> 8), s8(wb >> 8), bf.x, bf.y);
+                else mma16816(c, s8(wa), s8(wb), s8(wa >> 8), s8(wb >> 8), bf.x, bf.y);
             }
-            {
-                const uint32_t wa = lds32_u2(r0 + 34u * b + 18u + 4u * t), wb = lds32_u2(r1 + 34u * b + 18u + 4u * t);
-                const uint2 bf = IG_BFRAG(2u * b + 1u);
-                mma16816(c, s8(wa), s8(wb), s8(wa >> 8), s8(wb >> 8), bf.x, bf.y);
-            }
-            if (t == b) {
-                acc0 = fma_rn(d0, add_rn(c[0], c[1]), acc0);
-                acc1 = fma_rn(d1, add_rn(c[2], c[3]), acc1);
-            }
-        }
+        acc0 = fma_rn(d0, fma_rn(add_rn(c[0], c[1]), SUBNORMAL_SCALE, sxv), acc0);
+        acc1 = fma_rn(d1, fma_rn(add_rn(c[2], c[3]), SUBNORMAL_SCALE, sxv), acc1);
     }
 };
 
@@ -436,17 +417,19 @@ template <> struct MmaStep<KIND_Q8_0> {
 // kernel
 // ---------------------------------------------------------------------------
 
-template <uint32_t KIND, int NMAT>
-__global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
+template <uint32_t KIND, int NMAT, int OCC>
+__global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const MmaPlan &p = a.plan;
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MMA_MAX_STAGES;
     uint64_t *xbar = empty + MMA_MAX_STAGES;
-    uint8_t *xrow = smem + GEMV_BAR_BYTES;
+    uint64_t *tbar = xbar + 1;                                   // [MMA_RED_SLOTS]
+    uint8_t *xrow = smem + MMA_BAR_BYTES;
     const __half *xf = reinterpret_cast<const __half *>(xrow);
     const float *sx = reinterpret_cast<const float *>(xrow + (size_t)p.cols * 4u);
     float *red = reinterpret_cast<float *>(xrow + ((p.x_bytes + 127u) & ~127u));
+    uint8_t *zeros = reinterpret_cast<uint8_t *>(red) + p.red_bytes - MMA_ZERO_BYTES;
     uint8_t *stages = reinterpret_cast<uint8_t *>(red) + p.red_bytes;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -456,8 +439,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_c
             ptx::mbar_init(&empty[s], MMA_WARPS);
         }
         ptx::mbar_init(xbar, 1);
+        for (uint32_t i = 0; i < p.red_slots; ++i) ptx::mbar_init(&tbar[i], MMA_WARPS);
         ptx::mbar_init_fence();
     }
+    for (uint32_t i = threadIdx.x; i < MMA_ZERO_BYTES / 4u; i += MMA_THREADS) reinterpret_cast<uint32_t *>(zeros)[i] = 0u;
     __syncthreads();
     ptx::pdl_launch_dependents();
 
@@ -484,7 +469,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_c
         for (uint32_t tile = 0; tile < n_tiles; ++tile) {
             const uint32_t row0 = r_begin + tile * stage_rows;
             const uint32_t nrows = (r_end - row0) < stage_rows ? (r_end - row0) : stage_rows;
-            for (uint32_t c = 0; c < p.chunks; ++c, ++it) {
+            for (uint32_t cm = 0; cm < p.chunks * NMAT; ++cm, ++it) {
+                const uint32_t c = cm / NMAT, m = cm - c * NMAT;
                 if (!x_sent && it == p.stages) {       // ring primed: the next wait needs the consumers
                     if (!a.ids) ptx::pdl_wait();
                     if (lane == 0) {
@@ -495,18 +481,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_c
                 }
                 const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
                 bool ok = true;
-                if (lane == 0) ok = ptx::mbar_wait(&empty[s], ph ^ 1u);
+                if (lane == 0) ok = ptx::mbar_wait_sleep<128>(&empty[s], ph ^ 1u);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { if (lane == 0) set_status_word(a.status, KERNEL_ERR_PRODUCER_TIMEOUT); return; }
                 uint8_t *dst = stages + (size_t)s * p.stage_bytes;
-                if (lane == 0) ptx::mbar_expect_tx(&full[s], p.chunk_bytes * nrows * NMAT);
+                if (lane == 0) ptx::mbar_expect_tx(&full[s], p.chunk_bytes * nrows);
                 __syncwarp();
-                for (uint32_t i = lane; i < nrows * NMAT; i += 32u) {
-                    const uint32_t m = i / nrows, r = i - m * nrows;
-                    ptx::bulk_g2s(dst + (size_t)(m * stage_rows + r) * p.row_pitch,
+                for (uint32_t r = lane; r < nrows; r += 32u)
+                    ptx::bulk_g2s(dst + (size_t)r * p.row_pitch,
                                   a.w[m] + mat_off + (size_t)(row0 + r) * p.stride + (size_t)c * p.chunk_bytes,
                                   p.chunk_bytes, &full[s]);
-                }
             }
         }
         if (!x_sent) {                                   // fewer stage fills than ring slots
@@ -539,8 +523,13 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_c
     constexpr uint32_t STEP_BYTES = KIND == KIND_Q4_K ? 144u : KIND == KIND_Q6_K ? 210u : KIND == KIND_Q4_0 ? 72u : 136u;
     constexpr uint32_t MMAS = (KIND == KIND_Q4_K || KIND == KIND_Q6_K) ? 16u : 8u;     // MMAs per step
     const uint32_t step_stride = STEP_BYTES << p.kw_log2;                               // this warp's next step
-    const uint32_t x_stride = (MMAS * 32u) << p.kw_log2, s_stride = MMAS << p.kw_log2;
-    const size_t mat_pitch = (size_t)stage_rows * p.row_pitch;
+    const uint32_t x_stride = (MMAS * 64u) << p.kw_log2, s_stride = MMAS << p.kw_log2;     // bytes, floats
+    // B operands: column n = g of the MMA belongs to lane g; columns 2j, 2j+1 carry (xh, xl)
+    // for group j only, so this lane reads the real activations for group own = g / 2 and
+    // zeros for the others
+    const uint32_t own = g >> 1;
+    const uint8_t *xlane = xrow + ((g & 1u) * 4u + t) * 8u;
+    const uint8_t *zlane = zeros + ((g & 1u) * 4u + t) * 8u;
     float *y = a.y + (a.ids ? (size_t)pair * p.rows : 0);
     uint32_t it = 0;
     for (uint32_t tile = 0; tile < n_tiles; ++tile) {
@@ -552,32 +541,36 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_c
         float acc[NMAT][2];
 #pragma unroll
         for (int m = 0; m < NMAT; ++m) acc[m][0] = acc[m][1] = 0.f;
-        for (uint32_t c = 0; c < p.chunks; ++c, ++it) {
-            const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
-            if (!ptx::mbar_wait(&full[s], ph)) {
-                if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
-                return;
-            }
-            const uint8_t *st = stages + (size_t)s * p.stage_bytes;
-            if (rt * 16u < nrows) {
-                const uint8_t *b0 = st + (size_t)ur0 * p.row_pitch + kw * STEP_BYTES;
-                const uint8_t *b1 = st + (size_t)ur1 * p.row_pitch + kw * STEP_BYTES;
-                const uint32_t gs0 = c * (p.spw << p.kw_log2) + kw;            // first step inside the row
-                const __half *xs = xf + (size_t)gs0 * MMAS * 32u;
-                const float *ss = sx + gs0 * MMAS;
-                for (uint32_t i = 0; i < p.spw; ++i) {
+        for (uint32_t c = 0; c < p.chunks; ++c) {
+            const uint32_t gs0 = c * (p.spw << p.kw_log2) + kw;                // first step inside the row
 #pragma unroll
-                    for (int m = 0; m < NMAT; ++m)
-                        MmaStep<KIND>::run(b0 + (size_t)m * mat_pitch, b1 + (size_t)m * mat_pitch, xs, ss, g, t, acc[m][0], acc[m][1]);
-                    b0 += step_stride; b1 += step_stride;
-                    xs += x_stride; ss += s_stride;
+            for (int m = 0; m < NMAT; ++m, ++it) {
+                const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                if (!ptx::mbar_wait_sleep<20>(&full[s], ph)) {
+                    if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
+                    return;
                 }
+                const uint8_t *st = stages + (size_t)s * p.stage_bytes;
+                if (rt * 16u < nrows) {
+                    const uint8_t *b0 = st + (size_t)ur0 * p.row_pitch + kw * STEP_BYTES;
+                    const uint8_t *b1 = st + (size_t)ur1 * p.row_pitch + kw * STEP_BYTES;
+                    const uint8_t *xs = xlane + (size_t)gs0 * MMAS * 64u;
+                    const float *ss = sx + gs0 * MMAS;
+                    for (uint32_t i = 0; i < p.spw; ++i) {
+                        const uint8_t *const xb[4] = {own == 0 ? xs : zlane, own == 1 ? xs : zlane, own == 2 ? xs : zlane,
+                                                      own == 3 ? xs : zlane};
+                        MmaStep<KIND>::run(b0, b1, xb, ss, t, acc[m][0], acc[m][1]);
+                        b0 += step_stride; b1 += step_stride;
+                        xs += x_stride; ss += s_stride;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&empty[s]);
             }
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&empty[s]);
         }
         // quad reduce (the four lanes hold different scale groups), then across the K warps
-        float *slot = red + (size_t)(tile & 1u) * MMA_WARPS * 2u * 16u;
+        const uint32_t slot_id = tile % p.red_slots;
+        float *slot = red + (size_t)slot_id * MMA_WARPS * 2u * 16u;
 #pragma unroll
         for (int m = 0; m < NMAT; ++m)
 #pragma unroll
@@ -587,10 +580,15 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_c
                 v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
                 if (t == 0) slot[(warp * 2u + m) * 16u + g + 8u * h] = v;
             }
-        ptx::named_bar_sync(1, MMA_WARPS * 32);
-        if (kw == 0 && lane < 16u) {
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&tbar[slot_id]);
+        if (kw == 0) {                       // only the warp that sums waits for the others
+            if (!ptx::mbar_wait_sleep<20>(&tbar[slot_id], (tile / p.red_slots) & 1u)) {
+                if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
+                return;
+            }
             const uint32_t lrow = rt * 16u + lane;
-            if (lrow < nrows) {
+            if (lane < 16u && lrow < nrows) {
                 float v[NMAT];
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
@@ -608,12 +606,13 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_kernel(const __grid_c
 // launch
 // ---------------------------------------------------------------------------
 
-template <uint32_t KIND, int NMAT>
+template <uint32_t KIND, int NMAT, int OCC>
 static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
-    auto kernel = gemv_mma_kernel<KIND, NMAT>;
+    auto kernel = gemv_mma_kernel<KIND, NMAT, OCC>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_MAX);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)(OCC == 3 ? MMA_SMEM_SMALL : MMA_SMEM_MAX));
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -631,8 +630,10 @@ static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream
 }
 
 template <uint32_t KIND>
-static cudaError_t launch_mma_k(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
-    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2>(a, grid, stream, pdl) : launch_mma_t<KIND, 1>(a, grid, stream, pdl);
+static cudaError_t launch_mma_k(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl, int occ) {
+    if (occ == 3)
+        return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 3>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 3>(a, grid, stream, pdl);
+    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 2>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 2>(a, grid, stream, pdl);
 }
 
 // True when this call was taken (launched or failed); false to let the caller use
@@ -643,10 +644,16 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     if (!routed && c.count != 1) return false;
     if (c.cols % 64u) return false;
     const uint32_t gy = routed ? c.pairs : 1u;
-    uint32_t max_ctas = (2u * ctx.sm_count + gy - 1) / gy;
-    if (max_ctas < 1) max_ctas = 1;
     MmaPlan plan;
-    bool ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_BUDGET, plan);
+    int occ = 3;
+    uint32_t max_ctas = (3u * ctx.sm_count + gy - 1) / gy;
+    bool ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, plan);
+    if (!ok) {
+        occ = 2;
+        max_ctas = (2u * ctx.sm_count + gy - 1) / gy;
+        if (max_ctas < 1) max_ctas = 1;
+        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_BUDGET, plan);
+    }
     if (!ok) {
         max_ctas = (ctx.sm_count + gy - 1) / gy;
         ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas ? max_ctas : 1, MMA_SMEM_MAX, plan);
@@ -669,10 +676,10 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     a.status = ctx.status;
     const dim3 grid(plan.ctas, gy);
     switch (c.kind) {
-    case KIND_Q4_K: err = launch_mma_k<KIND_Q4_K>(a, grid, ctx.stream, ctx.pdl); break;
-    case KIND_Q6_K: err = launch_mma_k<KIND_Q6_K>(a, grid, ctx.stream, ctx.pdl); break;
-    case KIND_Q4_0: err = launch_mma_k<KIND_Q4_0>(a, grid, ctx.stream, ctx.pdl); break;
-    default: err = launch_mma_k<KIND_Q8_0>(a, grid, ctx.stream, ctx.pdl); break;
+    case KIND_Q4_K: err = launch_mma_k<KIND_Q4_K>(a, grid, ctx.stream, ctx.pdl, occ); break;
+    case KIND_Q6_K: err = launch_mma_k<KIND_Q6_K>(a, grid, ctx.stream, ctx.pdl, occ); break;
+    case KIND_Q4_0: err = launch_mma_k<KIND_Q4_0>(a, grid, ctx.stream, ctx.pdl, occ); break;
+    default: err = launch_mma_k<KIND_Q8_0>(a, grid, ctx.stream, ctx.pdl, occ); break;
     }
     return true;
 }

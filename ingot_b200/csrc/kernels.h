@@ -60,7 +60,8 @@ cudaError_t launch_activation(const float *gate, const float *up, uint64_t n, ui
 cudaError_t launch_merge(const float *routed, const float *shared, const float *weights, const float *shared_logit,
                          uint32_t width, uint32_t top, float *y, const LaunchCtx &ctx);
 cudaError_t launch_add_rms(const float *a, const float *b, const float *w, float *s, float *y, uint32_t width,
-                           uint32_t rows, float eps, uint32_t add, void *y_bf16, const LaunchCtx &ctx);
+                           uint32_t rows, float eps, uint32_t add, void *y_bf16, void *y_packed, uint32_t pack_bf16,
+                           const LaunchCtx &ctx);
 cudaError_t launch_expert_layout(const uint32_t *ids, uint32_t n_pairs, uint32_t experts, uint32_t tile_capacity,
                                  uint32_t *layout, uint32_t *tiles, uint32_t *pairs, uint32_t *inverse,
                                  const LaunchCtx &ctx);

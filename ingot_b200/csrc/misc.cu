@@ -4,6 +4,7 @@
 // straight grid of threads with coalesced 16-byte accesses.
 #include "gemv_core.cuh"
 #include "kernels.h"
+#include "pack.cuh"
 #include "ptx.cuh"
 
 namespace ingot {
@@ -358,7 +359,8 @@ struct RmsArgs {
     const float *a, *b, *w;
     float *s, *y;
     uint16_t *y_bf16;
-    uint32_t width, add;
+    uint8_t *y_packed;          // rows of packed_x_bytes(width) for the tensor-core GEMV, or null
+    uint32_t width, add, pack_bf16;
     float eps;
 };
 
@@ -393,6 +395,7 @@ __global__ void __launch_bounds__(256) add_rms_kernel(const __grid_constant__ Rm
 #pragma unroll
     for (int i = 0; i < 8; ++i) total += partial[i];
     const float inv = 1.0f / sqrtf(total / (float)a.width + a.eps);
+    float mx = 0.f;
     for (uint32_t j = tid; j < n4; j += 256) {
         float4 v;
         if (a.add && a.s) v = reinterpret_cast<const float4 *>(a.s)[base + j];   // written above by this thread; s may alias a
@@ -409,14 +412,51 @@ __global__ void __launch_bounds__(256) add_rms_kernel(const __grid_constant__ Rm
             o.y = (uint32_t)f2bf(v.z) | ((uint32_t)f2bf(v.w) << 16);
             reinterpret_cast<uint2 *>(a.y_bf16)[base + j] = o;
         }
+        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
     }
+    if (!a.y_packed) return;
+    // the same activations in the tensor-core GEMV's operand order (what ingot_pack_x
+    // would produce from y, or from its bf16 rounding when pack_bf16 is set)
+    __syncthreads();
+    for (uint32_t off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if ((tid & 31u) == 0) partial[tid >> 5] = mx;
+    __syncthreads();
+    mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, partial[i]);
+    const float scale = pack_scale(mx);
+    uint8_t *prow = a.y_packed + (size_t)row * packed_x_bytes(a.width);
+    for (uint32_t j0 = 0; j0 < n4; j0 += 256) {
+        const uint32_t j = j0 + tid;
+        const bool live = j < n4;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            float4 u;
+            if (a.add && a.s) u = reinterpret_cast<const float4 *>(a.s)[base + j];
+            else {
+                u = a4[j];
+                if (a.add) { const float4 o = b4[j]; u.x += o.x; u.y += o.y; u.z += o.z; u.w += o.w; }
+            }
+            float4 wv = a.w ? reinterpret_cast<const float4 *>(a.w)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
+            v[0] = u.x * inv * wv.x; v[1] = u.y * inv * wv.y; v[2] = u.z * inv * wv.z; v[3] = u.w * inv * wv.w;
+            if (a.pack_bf16) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] = __uint_as_float((uint32_t)f2bf(v[i]) << 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] *= scale;
+        }
+        pack_store_quad(prow, a.width, j, v, live);
+    }
+    if (tid == 0) pack_store_unscale(prow, a.width, scale);
 }
 
 cudaError_t launch_add_rms(const float *a, const float *b, const float *w, float *s, float *y, uint32_t width,
-                           uint32_t rows, float eps, uint32_t add, void *y_bf16, const LaunchCtx &ctx) {
-    if (width % 4u) return cudaErrorInvalidValue;
+                           uint32_t rows, float eps, uint32_t add, void *y_bf16, void *y_packed, uint32_t pack_bf16,
+                           const LaunchCtx &ctx) {
+    if (width % 4u || (y_packed && width % 64u)) return cudaErrorInvalidValue;
     if (rows == 0) return cudaSuccess;
-    RmsArgs args = {a, b, w, s, y, static_cast<uint16_t *>(y_bf16), width, add, eps};
+    RmsArgs args = {a, b, w, s, y, static_cast<uint16_t *>(y_bf16), static_cast<uint8_t *>(y_packed), width, add, pack_bf16, eps};
     return launch(add_rms_kernel, dim3(rows), dim3(256), ctx, args);
 }
 

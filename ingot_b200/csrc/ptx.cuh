@@ -53,17 +53,22 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
-// Bounded wait: polls until the phase completes or WAIT_LIMIT_NS of wall time
-// have passed; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+// Bounded wait: polls until the phase completes or WAIT_LIMIT_NS of wall time have
+// passed; false when the limit ran out.  Between polls the warp sleeps SLEEP_NS so a
+// waiting warp does not take issue slots from the warps doing the arithmetic.
+template <uint32_t SLEEP_NS>
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t *bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 32; ++i) {
+            if (SLEEP_NS) __nanosleep(SLEEP_NS);
             if (mbar_try_wait(bar, parity)) return true;
+        }
         if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
     }
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) { return mbar_wait_sleep<0>(bar, parity); }
 
 // Global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte
 // aligned) that signals `bar` with complete_tx.  No multicast.

@@ -23,6 +23,14 @@ def tol_ref(expected: np.ndarray) -> np.ndarray:
     return 1e-4 + 5e-5 * np.abs(expected)
 
 
+def tol_ref_scaled(expected: np.ndarray) -> np.ndarray:
+    """tol_ref with its absolute part scaled by the output RMS (when above 1): the reference's
+    bound was written for model weights with O(1) outputs; the synthetic benchmark blocks give
+    outputs of magnitude ~300, where fp32 accumulation alone exceeds 1e-4 absolute."""
+    rms = float(np.sqrt(np.mean(np.square(expected)))) if expected.size else 0.0
+    return 1e-4 * max(1.0, rms) + 5e-5 * np.abs(expected)
+
+
 def tol_contract(expected: np.ndarray) -> np.ndarray:
     """The stated contract: 1e-3 relative / 1e-4 absolute.  The absolute part is
     scaled by the output's RMS when that exceeds 1, because the synthetic
