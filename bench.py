@@ -333,6 +333,17 @@ def _e2e_step(gpu, chain, one_step, host_in: int, in_bytes: int, host_out: int) 
     gpu._check(gpu._lib.ingot_buffer_read(gpu._h, host_out, chain.logits.ptr, chain.logits.nbytes))
 
 
+def ncu_traffic(kernel: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of `kernel` from the committed ncu
+    summary (profiles/ncu_traffic.json), or None when it has not been captured."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f).get(kernel)
+    except (OSError, ValueError):
+        return None
+
+
 def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps=None):
     """Times each distinct GEMV of the step alone (CUDA events on the launching stream),
     rotating over all layers' weights so every launch streams from HBM."""
@@ -342,19 +353,24 @@ def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps
     lib, h = gpu._lib, gpu._h
 
     def timed(fn, reps):
+        """Seconds per launch: one sweep over all layers recorded as a command and replayed, so
+        host launch cost is out of the picture and consecutive launches chain as in a token step."""
         for i in range(len(chain.weights)):
             fn(i)
+        gpu.complete()
+        gpu.record()
+        for i in range(len(chain.weights)):
+            fn(i)
+        graph = gpu.end_record()
+        graph.submit()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        n = 0
         for _ in range(reps):
-            for i in range(len(chain.weights)):
-                fn(i)
-                n += 1
+            graph.submit()
         e1.record(stream)
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1) * 1e-3 / n
+        return e0.elapsed_time(e1) * 1e-3 / (reps * len(chain.weights))
 
     def proj(role, x, y):
         def fn(i):
@@ -409,7 +425,7 @@ def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps
     g = out["gate_up_q4k"]
     roof = {"bound": "hbm", "kernel": "gemv_stream_kernel<Q4_K, 1 token, gate+up fused> 4096 -> 2 x 12288",
             "achieved": g["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": g["frac"], "peak_source": peak_src,
-            "bytes_per_launch": g["bytes"], "us_per_launch": g["us"], "traffic": None}
+            "bytes_per_launch": g["bytes"], "us_per_launch": g["us"], "traffic": ncu_traffic("gate_up_q4k")}
     return roof, out
 
 

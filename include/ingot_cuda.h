@@ -219,6 +219,16 @@ INGOT_API ingot_status ingot_combine_packed(ingot_gpu *gpu, const float *routed,
                                             const uint32_t *inverse, uint32_t width, uint32_t top,
                                             uint32_t tokens, float *y);
 
+/* Expert-parallel sharding of a routing result (no counterpart in the reference,
+ * which keeps every expert on one device).  Pairs whose expert id lies in
+ * [first_expert, first_expert + local_experts) keep their weight and get the local
+ * id; the others get id 0xffffffff and weight 0.  ingot_routed / ingot_routed_gate_up
+ * write zero rows for id 0xffffffff, so ingot_moe_sum then yields this device's partial
+ * sum and an all-reduce over the devices the full one. */
+INGOT_API ingot_status ingot_ep_localize(ingot_gpu *gpu, const uint32_t *ids, const float *weights, uint32_t pairs,
+                                         uint32_t first_expert, uint32_t local_experts, uint32_t *ids_out,
+                                         float *weights_out);
+
 /* float32 -> bfloat16 (round to nearest even) for activations. */
 INGOT_API ingot_status ingot_convert_bf16(ingot_gpu *gpu, const float *x, uint64_t n, void *y_bf16);
 

@@ -47,6 +47,7 @@ SIGNATURES = {
     "ingot_add_rms_packed": [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, u32],
     "ingot_expert_layout": [vp, vp, u32, u32, u32, vp, vp, vp, vp],
     "ingot_combine_packed": [vp, vp, vp, vp, u32, u32, u32, vp],
+    "ingot_ep_localize": [vp, vp, vp, u32, u32, u32, vp, vp],
     "ingot_convert_bf16": [vp, vp, u64, vp],
     "ingot_packed_x_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_x": [vp, vp, u32, u32, u32, vp],

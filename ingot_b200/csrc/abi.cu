@@ -421,6 +421,15 @@ ingot_status ingot_combine_packed(ingot_gpu *g, const float *routed, const float
     return after_launch(g, launch_combine_packed(routed, weights, inverse, width, top, tokens, y, ctx_of(g)), "combine_packed");
 }
 
+ingot_status ingot_ep_localize(ingot_gpu *g, const uint32_t *ids, const float *weights, uint32_t pairs, uint32_t first_expert,
+                               uint32_t local_experts, uint32_t *ids_out, float *weights_out) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!ids || !weights || !ids_out || !weights_out || local_experts == 0) return fail(g, INGOT_INVALID, "ep_localize: bad arguments");
+    return after_launch(g, launch_ep_localize(ids, weights, pairs, first_expert, local_experts, ids_out, weights_out, ctx_of(g)),
+                        "ep_localize");
+}
+
 ingot_status ingot_convert_bf16(ingot_gpu *g, const float *x, uint64_t n, void *y) {
     ingot_status st = enter(g);
     if (st) return st;

@@ -4,6 +4,9 @@
 
 namespace ingot {
 
+// Routed pair that this device does not own (expert-parallel sharding): its output row is zero.
+static constexpr uint32_t ROUTE_SKIP = 0xffffffffu;
+
 // Records the first error of a launch in the device status word.
 __device__ __forceinline__ void set_status_word(int *status, int code) {
     if (status) atomicCAS(status, 0, code);

@@ -119,8 +119,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_stream_kernel(const __gr
     ptx::pdl_wait();
     uint32_t x_row0 = 0;
     if (a.ids) {
-        if (a.ids[pair] >= a.n_experts) {
-            if (threadIdx.x == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
+        const uint32_t e = a.ids[pair];
+        if (e >= a.n_experts) {
+            if (e == ROUTE_SKIP) {                      // not this device's expert: the row is zero
+                float *yz = a.y + (size_t)pair * p.rows;
+                for (uint32_t r = r_begin + threadIdx.x; r < r_end; r += GEMV_CONSUMER_WARPS * 32) yz[r] = 0.f;
+            } else if (threadIdx.x == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
             return;
         }
         x_row0 = a.per_pair ? pair : pair / a.top;
@@ -199,7 +203,8 @@ __global__ void __launch_bounds__(128) gemv_plain_kernel(const __grid_constant__
     if (a.ids) {
         expert = a.ids[item];
         if (expert >= a.n_experts) {
-            if (lane == 0 && row == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
+            if (expert == ROUTE_SKIP) { if (lane == 0) a.y[(size_t)item * a.rows + row] = 0.f; }
+            else if (lane == 0 && row == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
             return;
         }
         x_row = a.per_pair ? item : item / a.top;

@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
         if (a.ids) {                                   // routing comes from the previous kernel
             ptx::pdl_wait();
             expert = a.ids[pair];
-            if (expert >= a.n_experts) return;         // consumers report it
+            if (expert >= a.n_experts) return;         // skipped pair, or out of range: consumers handle it
             x_row = a.per_pair ? pair : pair / a.top;
         }
         const size_t mat_off = (size_t)expert * p.rows * p.stride;
@@ -506,8 +506,12 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
     // ---- consumer warps ----
     if (a.ids) {
         ptx::pdl_wait();
-        if (a.ids[pair] >= a.n_experts) {
-            if (threadIdx.x == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
+        const uint32_t e = a.ids[pair];
+        if (e >= a.n_experts) {
+            if (e == ROUTE_SKIP) {                      // not this device's expert: the row is zero
+                float *yz = a.y + (size_t)pair * p.rows;
+                for (uint32_t r = r_begin + threadIdx.x; r < r_end; r += MMA_WARPS * 32) yz[r] = 0.f;
+            } else if (threadIdx.x == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
             return;
         }
     }

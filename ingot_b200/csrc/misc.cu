@@ -2,6 +2,7 @@
 // top-k routing, weighted expert sum, GLU activation, shared-expert merge,
 // residual RMS norm, expert grouping.  All HBM- or latency-bound; each is a
 // straight grid of threads with coalesced 16-byte accesses.
+#include "dev_common.cuh"
 #include "gemv_core.cuh"
 #include "kernels.h"
 #include "pack.cuh"
@@ -478,6 +479,38 @@ cudaError_t launch_convert_bf16(const float *x, uint64_t n, void *y_bf16, const 
     uint64_t blocks = (n + 255) / 256, cap = (uint64_t)ctx.sm_count * 8u;
     if (blocks > cap) blocks = cap;
     return launch(convert_bf16_kernel, dim3((uint32_t)blocks), dim3(256), ctx, a);
+}
+
+// ---------------------------------------------------------------------------
+// Expert-parallel sharding: keep the pairs whose expert lies in [first, first + count)
+// (ids become local), mark the others ROUTE_SKIP with weight 0.  The routed GEMVs
+// write zero rows for skipped pairs, so the weighted sum is this device's partial
+// result and an all-reduce over the devices gives the full one.
+// ---------------------------------------------------------------------------
+
+struct LocalizeArgs {
+    const uint32_t *ids;
+    const float *w;
+    uint32_t *ids_out;
+    float *w_out;
+    uint32_t pairs, first, count;
+};
+
+__global__ void __launch_bounds__(256) ep_localize_kernel(const __grid_constant__ LocalizeArgs a) {
+    pdl_prologue();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.pairs) return;
+    const uint32_t e = a.ids[i];
+    const bool mine = e >= a.first && e - a.first < a.count;
+    a.ids_out[i] = mine ? e - a.first : ROUTE_SKIP;
+    a.w_out[i] = mine ? a.w[i] : 0.f;
+}
+
+cudaError_t launch_ep_localize(const uint32_t *ids, const float *w, uint32_t pairs, uint32_t first, uint32_t count,
+                               uint32_t *ids_out, float *w_out, const LaunchCtx &ctx) {
+    if (pairs == 0) return cudaSuccess;
+    LocalizeArgs a = {ids, w, ids_out, w_out, pairs, first, count};
+    return launch(ep_localize_kernel, dim3((pairs + 255) / 256), dim3(256), ctx, a);
 }
 
 // ---------------------------------------------------------------------------

@@ -1,0 +1,122 @@
+"""Expert-routed FFN of a MoE decoder at decode time, issued through the C ABI.
+
+The data flow is the MoE branch of the reference's `Generic::ffn`
+(src/generic.rs:508-574): router logits -> `route_topk` -> routed gate/up + SiLU
+(`generic_routed_gate_up`) -> routed down projection with one input row per pair
+(`generic_routed`, per_pair) -> `moe_sum` in route order.  Ids and weights never
+leave the device.
+
+Expert parallelism (not in the reference, which keeps all experts on one device):
+rank r of n owns experts [r*E/n, (r+1)*E/n).  Every rank sees the same tokens and
+routing; `ep_localize` keeps a rank's own pairs, the routed GEMVs write zero rows for
+the others, `moe_sum` gives the rank's partial output and an all-reduce (the
+`all_reduce` callback) completes it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import synth
+from .gpu import F32, Buffer, Gpu, Tensor, Weight
+
+
+@dataclass
+class MoeShape:
+    name: str
+    layers: int
+    hidden: int
+    experts: int
+    top: int
+    ffn: int
+    kind: int
+
+
+QWEN3_30B_A3B = MoeShape("qwen3-30b-a3b-q4_k", 48, 2048, 128, 8, 768, synth.Q4_K)
+
+
+def expert_range(experts: int, rank: int, world: int) -> tuple[int, int]:
+    """Experts [first, end) that `rank` owns out of `world`."""
+    return experts * rank // world, experts * (rank + 1) // world
+
+
+def expert_bytes(s: MoeShape) -> int:
+    """Bytes of one expert's three matrices."""
+    return 2 * synth.stride_of(s.kind, s.hidden) * s.ffn + synth.stride_of(s.kind, s.ffn) * s.hidden
+
+
+class MoeChain:
+    """`layers` MoE FFN layers (this rank's experts) resident in HBM and the buffers of one
+    decode step for `tokens` tokens."""
+
+    def __init__(self, gpu: Gpu, shape: MoeShape, tokens: int = 1, seed: int = 0, rank: int = 0, world: int = 1,
+                 all_reduce=None, layers: int | None = None, keep_host: bool = False):
+        self.gpu, self.shape, self.tokens = gpu, shape, tokens
+        self.rank, self.world, self.all_reduce = rank, world, all_reduce
+        self.n_layers = shape.layers if layers is None else layers
+        self.first, end = expert_range(shape.experts, rank, world)
+        self.local = end - self.first
+        self.host = []
+        self.weights = []
+        s = shape
+        for layer in range(self.n_layers):
+            mats = {}
+            for i, (role, cols, rows) in enumerate((("gate", s.hidden, s.ffn), ("up", s.hidden, s.ffn),
+                                                    ("down", s.ffn, s.hidden))):
+                raw = synth.random_matrix(s.kind, cols, rows, s.experts, seed=(seed * 7919 + layer * 8 + i) & 0x7FFFFFFF)
+                per = synth.stride_of(s.kind, cols) * rows
+                mine = raw[self.first * per:end * per]
+                t = Tensor.of([cols, rows, self.local], s.kind)
+                mats[role] = Weight(gpu.load_weight(mine, t), t)
+                if keep_host:
+                    mats[role + "_host"] = raw
+            self.weights.append(mats)
+        pairs = tokens * s.top
+        self.x = gpu.zeros(tokens * s.hidden)                 # FFN input (float32, replicated on every rank)
+        self.logits = gpu.zeros(tokens * s.experts)           # router logits (synthetic N(0,1) in the benchmark)
+        self.ids = gpu.empty_bytes(4 * pairs)
+        self.w = gpu.zeros(pairs)
+        self.ids_l = gpu.empty_bytes(4 * pairs)
+        self.w_l = gpu.zeros(pairs)
+        self.act = gpu.zeros(pairs * s.ffn)
+        self.out = gpu.zeros(pairs * s.hidden)
+        self.y = gpu.zeros(tokens * s.hidden)
+        self.launches_per_step = 0
+
+    def layer(self, i: int) -> None:
+        """One MoE FFN layer on the handle's stream: y = sum_k w_k * down_k(silu(gate_k x) * up_k x)."""
+        g, s, lib, h = self.gpu, self.shape, self.gpu._lib, self.gpu._h
+        pairs = self.tokens * s.top
+        ws = self.weights[i]
+        g._check(lib.ingot_route_topk(h, self.logits.ptr, s.experts, s.top, self.tokens, self.ids.ptr, self.w.ptr))
+        ids, w = self.ids, self.w
+        n = 1
+        if self.world > 1:
+            g._check(lib.ingot_ep_localize(h, self.ids.ptr, self.w.ptr, pairs, self.first, self.local, self.ids_l.ptr,
+                                           self.w_l.ptr))
+            ids, w = self.ids_l, self.w_l
+            n += 1
+        tg, td = ws["gate"].t, ws["down"].t
+        g._check(lib.ingot_routed_gate_up(h, ws["gate"].buffer.ptr, ws["up"].buffer.ptr, tg.dims[0], tg.dims[1], tg.stride,
+                                          tg.kind, self.local, self.x.ptr, F32, ids.ptr, s.top, pairs, self.act.ptr))
+        g._check(lib.ingot_routed(h, ws["down"].buffer.ptr, td.dims[0], td.dims[1], td.stride, td.kind, self.local,
+                                  self.act.ptr, F32, ids.ptr, 1, s.top, pairs, self.out.ptr))
+        g._check(lib.ingot_moe_sum(h, self.out.ptr, w.ptr, s.hidden, s.top, self.tokens, self.y.ptr))
+        self.launches_per_step += n + 3
+        if self.world > 1:
+            self.all_reduce(self.y, self.tokens * s.hidden)
+
+    def step(self) -> None:
+        self.launches_per_step = 0
+        for i in range(self.n_layers):
+            self.layer(i)
+
+    def record(self):
+        self.gpu.record()
+        self.step()
+        return self.gpu.end_record()
+
+    def unique_expert_bytes(self, ids: np.ndarray) -> int:
+        """Algorithmic weight bytes of one layer for routing `ids`: unique experts x 3 matrices."""
+        return len(np.unique(ids)) * expert_bytes(self.shape)

@@ -434,3 +434,35 @@ def test_recorded_chain_replays_identically(gpu):
         gpu._check(gpu._lib.ingot_buffer_zero(gpu._h, y.ptr, y.nbytes))
         graph.submit()
         assert np.array_equal(gpu.finish(None, y).view(np.uint32), eager.view(np.uint32))
+
+
+# ---- MoE layer and its expert-parallel split -------------------------------------------
+
+def test_moe_layer_matches_oracle_and_expert_shards_sum_to_it(gpu):
+    from ingot_b200.moe import MoeChain, MoeShape
+    shape = MoeShape("test", 1, 512, 16, 4, 256, Q4_K)
+    tokens = 3
+    rng = np.random.default_rng(7)
+    logits = rng.normal(0, 1, (tokens, shape.experts)).astype(np.float32)
+    x = synth.activations(tokens, shape.hidden, seed=8) * np.float32(0.02)
+
+    def run(rank, world):
+        c = MoeChain(gpu, shape, tokens=tokens, seed=3, rank=rank, world=world, all_reduce=lambda buf, n: None,
+                     keep_host=True)
+        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, c.logits.ptr, logits.ctypes.data, logits.nbytes))
+        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, c.x.ptr, x.ctypes.data, x.nbytes))
+        c.layer(0)
+        return gpu.finish(None, c.y).reshape(tokens, shape.hidden).copy(), c
+
+    full, chain = run(0, 1)
+    ws = chain.weights[0]
+    e = np.zeros((tokens, shape.hidden))
+    for t in range(tokens):
+        ids, w = O.route(logits[t], shape.top)
+        for k, wt in zip(ids, w):
+            a = O.glu(O.matvec_f64(ws["gate_host"], 512, 256, Q4_K, x[t], expert=int(k))[0].astype(np.float32),
+                      O.matvec_f64(ws["up_host"], 512, 256, Q4_K, x[t], expert=int(k))[0].astype(np.float32))
+            e[t] += float(wt) * O.matvec_f64(ws["down_host"], 256, 512, Q4_K, a, expert=int(k))[0]
+    assert (np.abs(full - e) <= tol_contract(e)).all(), float(np.abs(full - e).max())
+    parts = sum(run(r, 4)[0].astype(np.float64) for r in range(4))       # four expert shards, one after the other
+    assert np.abs(parts - full).max() <= 1e-5 * max(1.0, float(np.abs(full).max()))
