@@ -244,6 +244,23 @@ INGOT_API ingot_status ingot_packed_x_bytes(uint32_t cols, uint64_t *bytes);
 INGOT_API ingot_status ingot_pack_x(ingot_gpu *gpu, const void *x, uint32_t x_kind, uint32_t rows, uint32_t cols,
                                     void *packed);
 
+/* No counterpart in the reference.  y = W[expert] x for ONE float32 activation row, for
+ * callers that must not allocate: it takes no handle and calls neither cudaMalloc nor
+ * cudaFree nor any allocating routine.  The scratch of the tensor-core GEMV (the packed
+ * copy of x) and its error word live in file-scope __device__ arrays of the library
+ * (about 70 KB per GPU, held until the process exits), so cols is limited to 16384
+ * (INGOT_INVALID beyond that; ingot_matvec_static_error() gives the text).  Served:
+ * kinds 2, 8, 12, 14 with cols % 64 == 0 and 16-byte aligned rows (INGOT_UNSUPPORTED
+ * otherwise).  The first call on a device looks up the arrays' device addresses
+ * (cudaGetSymbolAddress) — make that first call outside any stream capture.  Work is
+ * enqueued on `cuda_stream` of the CURRENT device; wait != 0 also waits for it and
+ * reports a device-side time-out.  Every call uses the same scratch: two calls that
+ * overlap on the GPU (different streams, no ordering) race — serialise them. */
+INGOT_API ingot_status ingot_matvec_static(const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
+                                           uint32_t kind, uint32_t expert, const float *x, float *y,
+                                           void *cuda_stream, int32_t wait);
+INGOT_API const char *ingot_matvec_static_error(void);
+
 /* ---- command recording (Command: src/metal.rs:659-673; a whole decode step
  *      is one command buffer, src/generic.rs:701-704) ---------------------- */
 

@@ -51,6 +51,7 @@ SIGNATURES = {
     "ingot_convert_bf16": [vp, vp, u64, vp],
     "ingot_packed_x_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_x": [vp, vp, u32, u32, u32, vp],
+    "ingot_matvec_static": [vp, u32, u32, u32, u32, u32, vp, vp, vp, i32],
     "ingot_command_begin": [vp],
     "ingot_command_end": [vp, C.POINTER(vp)],
     "ingot_command_submit": [vp, vp],
@@ -62,6 +63,7 @@ OTHER = {
     "ingot_gpu_destroy": (None, [vp]),
     "ingot_last_error": (C.c_char_p, [vp]),
     "ingot_command_destroy": (None, [vp]),
+    "ingot_matvec_static_error": (C.c_char_p, []),
 }
 
 _lib = None
