@@ -206,12 +206,27 @@ def main():
     gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.h_in.ptr, h0.ctypes.data, h0.nbytes))
     gpu.complete()
 
-    use_graph = world == 1
-    graph = chain.record() if use_graph else None
+    use_graph = True
+    tgraph = None
+    if world == 1:
+        graph = chain.record()
+    else:
+        # the step contains NCCL all-gathers: let torch record it (its NCCL bindings join the
+        # capture), after eager steps have created the communicator
+        graph = None
+        for _ in range(2):
+            chain.step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        tgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(tgraph, stream=stream, capture_error_mode="thread_local"):
+            chain.step()
 
     def one_step():
         if graph is not None:
             graph.submit()
+        elif tgraph is not None:
+            tgraph.replay()
         else:
             chain.step()
 
@@ -288,7 +303,7 @@ def main():
                        "weights": "random Q4_K/Q6_K blocks", "activations": "bf16 in HBM, fp32 accumulate",
                        "parallelism": "tp%d rows" % world if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (total_bytes * 1.0 / 1e9 / world),
-                       "launch": "one recorded command (CUDA graph) per step" if use_graph else "eager launches + NCCL all-gather"},
+                       "launch": "one recorded command (CUDA graph) per step" + (" incl. NCCL all-gathers" if world > 1 else "")},
             "hbm_gbs_effective": total_bytes / world / (ms_per_step * 1e-3) / 1e9,
             "hbm_frac_of_peak_chain": total_bytes / world / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "e2e": {"value": args.batch * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
@@ -296,9 +311,14 @@ def main():
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks, "roofline": roof, "kernels": per_kernel, "cpu_baseline": cpu,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing the communicator down: the recorded step holds NCCL work, and
+        # destroying the process group under it can block; every rank is past its last collective
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
     gpu.close()
 
 
