@@ -140,12 +140,22 @@ INGOT_API ingot_status ingot_dequant_rows(ingot_gpu *gpu, const void *w, uint32_
 
 /* Gpu::matmul (src/metal.rs:877-1107) / Gpu::generic_project
  * (src/metal_generic.rs:175-228) / Gpu::matvec (src/metal.rs:846-875):
- * y[t][r] = sum_j W[expert][r][j] x[t][j] for `count` tokens.  count <= 4 runs
- * the fp32 GEMV; larger counts run in groups of four until the tensor-core
- * GEMM (ingot_gemm) is asked for explicitly. */
+ * y[t][r] = sum_j W[expert][r][j] x[t][j] for `count` tokens.  count <= 4 runs the
+ * GEMV (fp32 products of exactly dequantised weights); count > 4 runs ingot_gemm where
+ * it applies (binary16 operand staging, as the reference does), else GEMV groups of four. */
 INGOT_API ingot_status ingot_matmul(ingot_gpu *gpu, const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
                                     uint32_t kind, uint32_t expert, const void *x, uint32_t x_kind,
                                     uint32_t count, float *y);
+
+/* Gpu::generic_project for count > 4 (src/metal_generic.rs:182-206; kernels gemm_q4k / gemm_q6k,
+ * kernels/generic.metal:315-388): Y[t][r] = sum_j W[expert][r][j] x[t][j] on the tensor cores
+ * (tcgen05), weights and activations rounded to binary16 before the product like the reference's
+ * staging, fp32 accumulation.  Q4_K and Q6_K with cols % 256 == 0; INGOT_UNSUPPORTED otherwise.
+ * ingot_matmul takes this path by itself for count > 4.  Uses the handle's scratch for the
+ * binary16 copy of x (count * cols * 2 bytes, grown on demand; not while recording). */
+INGOT_API ingot_status ingot_gemm(ingot_gpu *gpu, const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
+                                  uint32_t kind, uint32_t expert, const void *x, uint32_t x_kind, uint32_t count,
+                                  float *y);
 
 /* Gpu::generic_gate_up (src/metal_generic.rs:231-261): y[t][r] =
  * glu(gate x, up x); gelu != 0 selects tanh-GeLU, else SiLU. */

@@ -36,6 +36,7 @@ SIGNATURES = {
     "ingot_weight_upload": [vp, vp, u32, u64, u64, u64, sz, C.POINTER(vp)],
     "ingot_dequant_rows": [vp, vp, u32, u64, u32, u32, vp],
     "ingot_matmul": [vp, vp, u32, u32, u32, u32, u32, vp, u32, u32, vp],
+    "ingot_gemm": [vp, vp, u32, u32, u32, u32, u32, vp, u32, u32, vp],
     "ingot_gate_up": [vp, vp, vp, u32, u32, u32, u32, vp, u32, u32, u32, vp],
     "ingot_routed": [vp, vp, u32, u32, u32, u32, u32, vp, u32, vp, u32, u32, u32, vp],
     "ingot_routed_gate_up": [vp, vp, vp, u32, u32, u32, u32, u32, vp, u32, vp, u32, u32, vp],

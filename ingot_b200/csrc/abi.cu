@@ -317,7 +317,43 @@ ingot_status ingot_matmul(ingot_gpu *g, const void *w, uint32_t cols, uint32_t r
     c.w[0] = static_cast<const uint8_t *>(w);
     c.x = x; c.y = y; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
     c.expert = expert; c.count = count; c.nmat = 1;
+    // more than four tokens: the reference switches to its GEMM (src/metal_generic.rs:182-206)
+    if (g && !g->no_mma && !g->force_plain && count > 4 && (kind == INGOT_KIND_Q4_K || kind == INGOT_KIND_Q6_K) && cols % 256u == 0 &&
+        ((uintptr_t)w % 16u) == 0 && (x_kind == INGOT_KIND_F32 || x_kind == INGOT_KIND_BF16))
+        return ingot_gemm(g, w, cols, rows, stride, kind, expert, x, x_kind, count, y);
     return gemv_common(g, c, x_kind, "matmul");
+}
+
+// Grows the handle's scratch (never while recording: cudaMalloc cannot be captured).
+static ingot_status ensure_workspace(ingot_gpu *g, size_t bytes) {
+    if (bytes <= g->workspace_bytes) return INGOT_OK;
+    if (g->capturing) return fail(g, INGOT_INVALID, "scratch too small for this call while recording; run it once before recording");
+    cudaError_t e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) return cuda_fail(g, e, "synchronize");
+    void *p = nullptr;
+    e = cudaMalloc(&p, bytes);
+    if (e == cudaErrorMemoryAllocation) { cudaGetLastError(); return fail(g, INGOT_INVALID, "out of device memory"); }
+    if (e != cudaSuccess) return cuda_fail(g, e, "cudaMalloc");
+    cudaFree(g->workspace);
+    g->workspace = p;
+    g->workspace_bytes = bytes;
+    return INGOT_OK;
+}
+
+ingot_status ingot_gemm(ingot_gpu *g, const void *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind,
+                        uint32_t expert, const void *x, uint32_t x_kind, uint32_t count, float *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if ((st = check_matrix(g, kind, cols, rows, stride))) return st;
+    if (x_kind != INGOT_KIND_F32 && x_kind != INGOT_KIND_BF16) return fail(g, INGOT_UNSUPPORTED, "gemm: activations must be F32 or BF16");
+    if (!w || !x || !y || count == 0) return fail(g, INGOT_INVALID, "gemm: bad arguments");
+    if ((kind != INGOT_KIND_Q4_K && kind != INGOT_KIND_Q6_K) || cols % 256u || ((uintptr_t)w % 16u))
+        return fail(g, INGOT_UNSUPPORTED, "gemm: no tensor-core kernel for this type or shape");
+    if ((st = ensure_workspace(g, (size_t)count * cols * 2u))) return st;
+    cudaError_t e = launch_gemm_dequant(static_cast<const uint8_t *>(w), cols, rows, stride, kind, expert, x,
+                                        x_kind == INGOT_KIND_BF16, count, y, g->workspace, ctx_of(g));
+    if (e == cudaErrorNotSupported) { cudaGetLastError(); return fail(g, INGOT_UNSUPPORTED, "gemm: no tensor-core kernel for this type or shape"); }
+    return after_launch(g, e, "gemm");
 }
 
 ingot_status ingot_gate_up(ingot_gpu *g, const void *gate, const void *up, uint32_t cols, uint32_t rows,

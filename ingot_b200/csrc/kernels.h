@@ -67,6 +67,10 @@ cudaError_t launch_expert_layout(const uint32_t *ids, uint32_t n_pairs, uint32_t
                                  const LaunchCtx &ctx);
 cudaError_t launch_combine_packed(const float *routed, const float *w, const uint32_t *inverse, uint32_t width,
                                   uint32_t top, uint32_t tokens, float *y, const LaunchCtx &ctx);
+// Y[T][N] = X[T][K] W^T with binary16 operand staging on tcgen05 (Q4_K, Q6_K).  x_half_scratch: tokens*cols*2 bytes.
+cudaError_t launch_gemm_dequant(const uint8_t *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind, uint32_t expert,
+                                const void *x, uint32_t x_bf16, uint32_t tokens, float *y, void *x_half_scratch,
+                                const LaunchCtx &ctx);
 cudaError_t launch_ep_localize(const uint32_t *ids, const float *w, uint32_t pairs, uint32_t first, uint32_t count,
                                uint32_t *ids_out, float *w_out, const LaunchCtx &ctx);
 cudaError_t launch_convert_bf16(const float *x, uint64_t n, void *y_bf16, const LaunchCtx &ctx);

@@ -296,6 +296,13 @@ class Gpu:
                                            y.ptr))
         return y
 
+    def gemm(self, cmd, w: Buffer, cols, rows, stride, kind, expert, x: Buffer, count, x_kind: int = F32,
+             out: Buffer | None = None) -> Buffer:
+        """The tensor-core prefill GEMM (the reference's gemm_q4k / gemm_q6k)."""
+        y = out or self.output(rows * count)
+        self._check(self._lib.ingot_gemm(self._h, w.ptr, cols, rows, stride, kind, expert, x.ptr, x_kind, count, y.ptr))
+        return y
+
     def generic_project(self, cmd, w: Weight, x: Buffer, count: int, x_kind: int = F32):
         if w.t.kind not in self.VECTOR_KINDS:
             return None

@@ -466,3 +466,40 @@ def test_moe_layer_matches_oracle_and_expert_shards_sum_to_it(gpu):
     assert (np.abs(full - e) <= tol_contract(e)).all(), float(np.abs(full - e).max())
     parts = sum(run(r, 4)[0].astype(np.float64) for r in range(4))       # four expert shards, one after the other
     assert np.abs(parts - full).max() <= 1e-5 * max(1.0, float(np.abs(full).max()))
+
+
+# ---- prefill GEMM on the tensor cores ------------------------------------------------------
+
+@pytest.mark.parametrize("kind", [Q4_K, Q6_K])
+@pytest.mark.parametrize("cols,rows,tokens", [(256, 128, 16), (512, 200, 70), (1024, 128, 256), (2560, 37, 32), (4096, 300, 513)])
+def test_gemm_matches_f16_staged_expectation(gpu, kind, cols, rows, tokens):
+    # src/expert_bench.rs:734-749: wide GEMM against an f64 dot of F16-rounded weights (and activations)
+    raw = synth.random_matrix(kind, cols, rows, 2, seed=cols + rows)
+    x = standard_x(cols * tokens).reshape(tokens, cols)             # multiples of 1/32: exact in binary16
+    w, xb = gpu.bytes(raw), gpu.floats(x)
+    y = gpu.finish(None, gpu.gemm(None, w, cols, rows, synth.stride_of(kind, cols), kind, 1, xb, tokens)).reshape(tokens, rows)
+    e = O.gemm_f16_f64(raw, cols, rows, kind, x, expert=1)
+    assert (np.abs(y - e) <= tol_ref_scaled(e)).all(), float(np.abs(y - e).max())
+    # the same through Gpu::matmul, which takes the GEMM for more than four tokens, and with bf16 activations
+    if tokens > 4:
+        y2 = gpu.finish(None, gpu.matmul(None, w, cols, rows, synth.stride_of(kind, cols), kind, 1, xb, tokens))
+        assert np.array_equal(y2.view(np.uint32), y.reshape(-1).view(np.uint32))
+        y3 = gpu.finish(None, gpu.gemm(None, w, cols, rows, synth.stride_of(kind, cols), kind, 1, gpu.bf16(x), tokens, BF16))
+        assert np.array_equal(y3.view(np.uint32), y.reshape(-1).view(np.uint32))      # these x are exact in bf16 too
+
+
+def test_gemm_random_activations_and_unsupported_shapes(gpu):
+    cols, rows, tokens = 2048, 256, 130
+    raw = synth.random_matrix(Q4_K, cols, rows, seed=3)
+    x = synth.activations(tokens, cols, seed=4)
+    w, xb = gpu.bytes(raw), gpu.floats(x)
+    y = gpu.finish(None, gpu.gemm(None, w, cols, rows, synth.stride_of(Q4_K, cols), Q4_K, 0, xb, tokens)).reshape(tokens, rows)
+    e = O.gemm_f16_f64(raw, cols, rows, Q4_K, x)
+    assert (np.abs(y - e) <= tol_ref_scaled(e)).all(), float(np.abs(y - e).max())
+    exact = O.matvec_f64(raw, cols, rows, Q4_K, x)
+    assert np.abs(y - exact).max() <= 2e-3 * np.abs(exact).max()                       # F16 staging: ~1e-3 of full precision
+    with pytest.raises(InvalidData):
+        gpu.gemm(None, w, cols, rows, synth.stride_of(Q4_K, cols), Q4_0, 0, xb, tokens)          # layout mismatch
+    w0 = gpu.bytes(synth.random_matrix(Q4_0, 256, 8, seed=1))
+    with pytest.raises(InvalidData):
+        gpu.gemm(None, w0, 256, 8, synth.stride_of(Q4_0, 256), Q4_0, 0, xb, 8)                   # no tensor-core kernel
