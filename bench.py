@@ -159,6 +159,11 @@ def main():
                     help="run only this GEMV (gate_up_q4k, down_q6k, q_q4k, k_q4k, v_q6k, head_q6k) over --layers "
                          "layers, a small case for ncu; prints its timing and exits")
     ap.add_argument("--reps", type=int, default=2, help="sweeps over the layers in --profile-kernel mode")
+    ap.add_argument("--activations", default="bf16", choices=["bf16", "f32"],
+                    help="activation type between the projections (bf16 is the benchmark configuration)")
+    ap.add_argument("--workload", default="chain", choices=["chain", "gemm"],
+                    help="chain: the dense decode step (the headline line); gemm: the prefill dequant-GEMM table")
+    ap.add_argument("--tokens", type=int, nargs="*", default=[512, 2048, 8192], help="token counts of --workload gemm")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -166,7 +171,7 @@ def main():
         args.warmup = 3
 
     import torch
-    from ingot_b200 import BF16, Gpu, _abi
+    from ingot_b200 import BF16, F32, Gpu, _abi
     from ingot_b200.chain import QWEN3_8B, DecodeChain, weight_bytes_per_token
     from ingot_b200.gpu import Buffer
 
@@ -184,8 +189,13 @@ def main():
     gpu.set_stream(stream.cuda_stream)
 
     shape = QWEN3_8B
+    x_kind = BF16 if args.activations == "bf16" else F32
+    if args.workload == "gemm":
+        print(json.dumps(run_gemm(torch, gpu, stream, args)), flush=True)
+        gpu.close()
+        return
     if args.profile_kernel:
-        chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=BF16, seed=0, layers=args.layers or 4)
+        chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, layers=args.layers or 4)
         peaks, peak_src = measured_peaks()
         roof, per = kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=args.profile_kernel,
                                      reps=args.reps)
@@ -199,7 +209,7 @@ def main():
         dst = _tensor_view(torch, full.ptr, n * world, local)
         dist.all_gather_into_tensor(dst, src)
 
-    chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=BF16, seed=0, rank=rank, world=world,
+    chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, rank=rank, world=world,
                         all_gather=all_gather if world > 1 else None, layers=args.layers,
                         keep_host=1 if (rank == 0 and world == 1 and not args.no_cpu) else 0)
     h0 = np.random.default_rng(1).normal(0, 1, (args.batch, shape.hidden)).astype(np.float32)
@@ -300,7 +310,7 @@ def main():
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "qwen3-8b-q4_k_m dense decode GEMV chain (configs[1]), batch %d" % args.batch,
                        "layers": chain.n_layers, "hidden": shape.hidden, "ffn": shape.ffn, "vocab": shape.vocab,
-                       "weights": "random Q4_K/Q6_K blocks", "activations": "bf16 in HBM, fp32 accumulate",
+                       "weights": "random Q4_K/Q6_K blocks", "activations": "%s in HBM, fp32 accumulate" % args.activations,
                        "parallelism": "tp%d rows" % world if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (total_bytes * 1.0 / 1e9 / world),
                        "launch": "one recorded command (CUDA graph) per step" + (" incl. NCCL all-gathers" if world > 1 else "")},
@@ -323,6 +333,44 @@ def main():
 
 
 # ---- helpers ------------------------------------------------------------------------
+
+def run_gemm(torch, gpu, stream, args):
+    """The batched prefill dequant-GEMM: Q4_K 4096 -> 12288 and Q6_K 12288 -> 4096 against bf16
+    activations of `--tokens` rows, timed alone with CUDA events; TFLOP/s against the measured
+    dense bf16 peak (burst figure: each shape is timed in isolation)."""
+    from ingot_b200 import BF16, synth
+    peaks, peak_src = measured_peaks()
+    rows_out = []
+    launches = 0
+    for kind, name, cols, rows in ((synth.Q4_K, "q4_k", 4096, 12288), (synth.Q6_K, "q6_k", 12288, 4096)):
+        raw = synth.random_matrix(kind, cols, rows, seed=5)
+        w = gpu.bytes(raw)
+        stride = synth.stride_of(kind, cols)
+        for m in args.tokens:
+            x = np.random.default_rng(m).normal(0, 1, (m, cols)).astype(np.float32)
+            xb = gpu.bf16(x)
+            y = gpu.zeros(m * rows)
+            for _ in range(args.warmup):
+                gpu.gemm(None, w, cols, rows, stride, kind, 0, xb, m, BF16, out=y)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                gpu.gemm(None, w, cols, rows, stride, kind, 0, xb, m, BF16, out=y)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            sec = e0.elapsed_time(e1) * 1e-3 / args.steps
+            launches += 2 * args.steps
+            flops = 2.0 * m * cols * rows
+            rows_out.append({"kind": name, "cols": cols, "rows": rows, "tokens": m, "us": sec * 1e6,
+                             "tflops": flops / sec / 1e12, "frac": flops / sec / 1e12 / peaks["bf16_tflops"],
+                             "tok_per_s": m / sec})
+            for b in (xb, y):
+                b.release()
+        w.release()
+    return {"workload": "prefill dequant-GEMM (configs[4])", "unit": "TFLOP/s", "peak": peaks["bf16_tflops"],
+            "peak_source": peak_src, "bound": "tensor", "gpu_launches": launches, "shapes": rows_out}
+
 
 def _tensor_view(torch, ptr: int, n_f32: int, device: int):
     """A float32 torch tensor over `n_f32` elements of device memory owned by the library

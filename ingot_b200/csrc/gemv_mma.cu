@@ -4,10 +4,12 @@
 // int->float step and an FMA — at least 3.7 issued instructions per weight, with
 // the half-rate integer pipe the first to saturate — which caps 4-bit formats
 // near half of HBM bandwidth (measured; see the profile summaries).  Here a lane
-// turns packed quants into binary16 operand registers with one logic op and one
-// packed subtract per TWO weights ((w & 0x000f000f) | 0x64006400 is the pair
-// (1024+q0, 1024+q2); minus 1024 is exact) and a warp-level mma.sync m16n8k16
-// (f16 x f16 -> f32) multiplies 16 rows by 16 columns at once.  Nothing is staged
+// turns packed quants into binary16 operand registers with ONE logic op per TWO
+// weights — masked in place, the bits of a quant are a subnormal binary16 whose
+// value is the quant times 2^-24 (undone in the scale) — and a warp-level mma.sync
+// m16n8k16 (f16 x f16 -> f32) multiplies 16 rows by 16 columns at once.  (The e4m3
+// mma.sync, which would take four weights per register, is emulated on sm_100 by
+// unpacking to binary16 — measured slower — so it is not used.)  Nothing is staged
 // through shared memory in decoded form and the kernel stays a bandwidth-bound
 // GEMV: one CTA streams a contiguous range of rows through a ring of bulk-copy
 // stages, eight warps split the columns of each 16-row tile.
@@ -426,7 +428,6 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
     uint64_t *xbar = empty + MMA_MAX_STAGES;
     uint64_t *tbar = xbar + 1;                                   // [MMA_RED_SLOTS]
     uint8_t *xrow = smem + MMA_BAR_BYTES;
-    const __half *xf = reinterpret_cast<const __half *>(xrow);
     const float *sx = reinterpret_cast<const float *>(xrow + (size_t)p.cols * 4u);
     float *red = reinterpret_cast<float *>(xrow + ((p.x_bytes + 127u) & ~127u));
     uint8_t *zeros = reinterpret_cast<uint8_t *>(red) + p.red_bytes - MMA_ZERO_BYTES;
@@ -535,6 +536,33 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
     const uint8_t *xlane = xrow + ((g & 1u) * 4u + t) * 8u;
     const uint8_t *zlane = zeros + ((g & 1u) * 4u + t) * 8u;
     float *y = a.y + (a.ids ? (size_t)pair * p.rows : 0);
+    const uint32_t kmask = (1u << p.kw_log2) - 1u;
+
+    // Sum of a finished tile's partials over the K warps -> y.  The warp that sums rotates with
+    // the tile, and it sums tile T only after its own work on tile T + 1, when the partials are
+    // long complete: no warp falls behind the others at a tile boundary.
+    auto sum_tile = [&](uint32_t tile) -> bool {
+        if (((tile ^ kw) & kmask) != 0u) return true;                  // another warp's turn
+        const uint32_t slot_id = tile % p.red_slots;
+        const float *slot = red + (size_t)slot_id * MMA_WARPS * 2u * 16u;
+        if (!ptx::mbar_wait_sleep<20>(&tbar[slot_id], (tile / p.red_slots) & 1u)) {
+            if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
+            return false;
+        }
+        const uint32_t row0 = r_begin + tile * stage_rows;
+        const uint32_t nrows = (r_end - row0) < stage_rows ? (r_end - row0) : stage_rows;
+        const uint32_t lrow = rt * 16u + (lane & 15u), first = rt << p.kw_log2;
+        // NMAT == 2: lanes 0..15 sum matrix 0 and lanes 16..31 matrix 1, then exchange
+        const uint32_t m = NMAT == 2 ? (lane >> 4) : 0u;
+        float sum = 0.f;
+        if (lrow < nrows && (NMAT == 2 || lane < 16u))
+            for (uint32_t k = 0; k <= kmask; ++k) sum = add_rn(sum, slot[((first + k) * 2u + m) * 16u + (lane & 15u)]);
+        sum = mul_rn(sum, unscale);
+        const float other = NMAT == 2 ? __shfl_xor_sync(0xffffffffu, sum, 16) : 0.f;
+        if (lrow < nrows && lane < 16u) y[row0 + lrow] = NMAT == 2 ? glu_f(sum, other, a.glu == 2) : sum;
+        return true;
+    };
+
     uint32_t it = 0;
     for (uint32_t tile = 0; tile < n_tiles; ++tile) {
         const uint32_t row0 = r_begin + tile * stage_rows;
@@ -586,24 +614,9 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
             }
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&tbar[slot_id]);
-        if (kw == 0) {                       // only the warp that sums waits for the others
-            if (!ptx::mbar_wait_sleep<20>(&tbar[slot_id], (tile / p.red_slots) & 1u)) {
-                if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
-                return;
-            }
-            const uint32_t lrow = rt * 16u + lane;
-            if (lane < 16u && lrow < nrows) {
-                float v[NMAT];
-#pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    float sum = 0.f;
-                    for (uint32_t k = 0; k < (1u << p.kw_log2); ++k) sum = add_rn(sum, slot[((warp + k) * 2u + m) * 16u + lane]);
-                    v[m] = mul_rn(sum, unscale);
-                }
-                y[row0 + lrow] = NMAT == 2 ? glu_f(v[0], v[NMAT - 1], a.glu == 2) : v[0];
-            }
-        }
+        if (tile > 0 && !sum_tile(tile - 1)) return;
     }
+    if (n_tiles > 0) sum_tile(n_tiles - 1);
 }
 
 // ---------------------------------------------------------------------------

@@ -59,13 +59,17 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 template <uint32_t SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait_sleep(uint64_t *bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    // the clock is read only every 1024 polls: reading it costs hundreds of cycles, and an
+    // ordinary wait ends within a few polls
+    uint64_t t0 = 0;
     for (;;) {
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 1024; ++i) {
             if (SLEEP_NS) __nanosleep(SLEEP_NS);
             if (mbar_try_wait(bar, parity)) return true;
         }
-        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > WAIT_LIMIT_NS) return false;
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) { return mbar_wait_sleep<0>(bar, parity); }
