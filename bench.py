@@ -161,6 +161,7 @@ def main():
     ap.add_argument("--reps", type=int, default=2, help="sweeps over the layers in --profile-kernel mode")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "f32"],
                     help="activation type between the projections (bf16 is the benchmark configuration)")
+    ap.add_argument("--tcgen05-gemv", type=int, default=0, help="1: Q4_K one-token GEMVs on the tcgen05 int8 kernel")
     ap.add_argument("--workload", default="chain", choices=["chain", "gemm"],
                     help="chain: the dense decode step (the headline line); gemm: the prefill dequant-GEMM table")
     ap.add_argument("--tokens", type=int, nargs="*", default=[512, 2048, 8192], help="token counts of --workload gemm")
@@ -187,6 +188,7 @@ def main():
     torch.cuda.set_stream(stream)
     gpu = Gpu(local)
     gpu.set_stream(stream.cuda_stream)
+    gpu.set_option(_abi.OPT_TCGEN05_GEMV, args.tcgen05_gemv)
 
     shape = QWEN3_8B
     x_kind = BF16 if args.activations == "bf16" else F32
@@ -198,7 +200,7 @@ def main():
         chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, layers=args.layers or 4)
         peaks, peak_src = measured_peaks()
         roof, per = kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=args.profile_kernel,
-                                     reps=args.reps)
+                                     reps=args.reps, digits=bool(args.tcgen05_gemv))
         print(json.dumps({"profile_kernel": args.profile_kernel, "layers": chain.n_layers, **per[args.profile_kernel]}))
         gpu.close()
         return
@@ -412,7 +414,7 @@ def ncu_traffic(kernel: str):
         return None
 
 
-def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps=None):
+def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps=None, digits=False):
     """Times each distinct GEMV of the step alone (CUDA events on the launching stream),
     rotating over all layers' weights so every launch streams from HBM."""
     from ingot_b200 import synth
@@ -440,18 +442,28 @@ def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e-3 / (reps * len(chain.weights))
 
+    xd = None
+    if digits:      # the tcgen05 int8 GEMV reads activations as digit rows (Q4_K weights)
+        from ingot_b200 import X_DIGITS
+        xd = gpu.pack_digits(chain.xn, 1, s.hidden, chain.x_kind)
+
+    def x_of(x, kind):
+        if xd is not None and kind == synth.Q4_K and x is chain.xn:
+            return xd.ptr, X_DIGITS
+        return chain._x(x)
+
     def proj(role, x, y):
         def fn(i):
             w = chain.weights[i][role]
             t = w.t
-            xp, xk = chain._x(x)
+            xp, xk = x_of(x, t.kind)
             gpu._check(lib.ingot_matmul(h, w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, xp, xk, b, y.ptr))
         return fn
 
     def gate_up(i):
         g, u = chain.weights[i]["gate"], chain.weights[i]["up"]
         t = g.t
-        xp, xk = chain._x(chain.xn)
+        xp, xk = x_of(chain.xn, t.kind)
         gpu._check(lib.ingot_gate_up(h, g.buffer.ptr, u.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, xp, xk, b, 0,
                                      chain.act.ptr))
 

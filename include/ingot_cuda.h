@@ -62,8 +62,8 @@ enum {
     INGOT_KIND_Q4_K = 12, INGOT_KIND_Q6_K = 14, INGOT_KIND_BF16 = 30
 };
 
-/* x_kind of activation rows already packed by ingot_pack_x */
-enum { INGOT_X_PACKED = 256 };
+/* x_kind of activation rows already packed by ingot_pack_x / ingot_pack_digits */
+enum { INGOT_X_PACKED = 256, INGOT_X_DIGITS = 258 };
 
 typedef struct ingot_gpu ingot_gpu;      /* opaque; the reference's `Gpu` */
 typedef struct ingot_graph ingot_graph;  /* opaque; a recorded `Command` */
@@ -101,8 +101,11 @@ INGOT_API ingot_status ingot_gpu_set_stream(ingot_gpu *gpu, void *cuda_stream);
  * tail; INGOT_OPT_FORCE_PLAIN (default 0) routes every GEMV through the plain
  * one-warp-per-row kernel (a test hook); INGOT_OPT_NO_MMA (default 0) keeps the
  * streaming GEMV on the fp32 CUDA-core kernel instead of the one whose inner
- * products run on the tensor cores (a test and comparison hook). */
-enum { INGOT_OPT_PDL = 1, INGOT_OPT_FORCE_PLAIN = 2, INGOT_OPT_NO_MMA = 3 };
+ * products run on the tensor cores (a test and comparison hook);
+ * INGOT_OPT_TCGEN05_GEMV sends one-token GEMVs over Q4_K weights to the kernel
+ * that multiplies on the tcgen05 int8 tensor cores (rows unpacked into tensor
+ * memory, activations as base-256 digits). */
+enum { INGOT_OPT_PDL = 1, INGOT_OPT_FORCE_PLAIN = 2, INGOT_OPT_NO_MMA = 3, INGOT_OPT_TCGEN05_GEMV = 4 };
 INGOT_API ingot_status ingot_gpu_set_option(ingot_gpu *gpu, int32_t option, int32_t value);
 
 /* Command::wait / Gpu::complete (src/metal.rs:1224-1235): blocks until the
@@ -253,6 +256,16 @@ INGOT_API ingot_status ingot_convert_bf16(ingot_gpu *gpu, const float *x, uint64
 INGOT_API ingot_status ingot_packed_x_bytes(uint32_t cols, uint64_t *bytes);
 INGOT_API ingot_status ingot_pack_x(ingot_gpu *gpu, const void *x, uint32_t x_kind, uint32_t rows, uint32_t cols,
                                     void *packed);
+
+/* Activations as the operand of the tcgen05 int8 GEMV (INGOT_OPT_TCGEN05_GEMV): every
+ * value is round(x * S), S the power of two that puts the row's largest magnitude in
+ * [2^21, 2^22), written as three signed base-256 digits in the shared-memory layout of
+ * an N = 8 tensor-core operand, followed by the fp32 sum of every 16 columns and 1/S.
+ * cols a multiple of 256; rows of ingot_packed_digits_bytes(cols); pass them with
+ * x_kind = INGOT_X_DIGITS (one token).  No counterpart in the reference. */
+INGOT_API ingot_status ingot_packed_digits_bytes(uint32_t cols, uint64_t *bytes);
+INGOT_API ingot_status ingot_pack_digits(ingot_gpu *gpu, const void *x, uint32_t x_kind, uint32_t rows, uint32_t cols,
+                                         void *packed);
 
 /* No counterpart in the reference.  y = W[expert] x for ONE float32 activation row, for
  * callers that must not allocate: it takes no handle and calls neither cudaMalloc nor

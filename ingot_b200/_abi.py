@@ -12,8 +12,9 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libingot_cuda.so")
 
 OK, INVALID, UNSUPPORTED, DEVICE, EOF, INTERRUPTED, TIMEOUT = range(7)
-OPT_PDL, OPT_FORCE_PLAIN, OPT_NO_MMA = 1, 2, 3
+OPT_PDL, OPT_FORCE_PLAIN, OPT_NO_MMA, OPT_TCGEN05_GEMV = 1, 2, 3, 4
 X_PACKED = 256
+X_DIGITS = 258
 
 vp, u32, u64, i32, f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_float
 sz = C.c_size_t
@@ -52,6 +53,8 @@ SIGNATURES = {
     "ingot_convert_bf16": [vp, vp, u64, vp],
     "ingot_packed_x_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_x": [vp, vp, u32, u32, u32, vp],
+    "ingot_packed_digits_bytes": [u32, C.POINTER(u64)],
+    "ingot_pack_digits": [vp, vp, u32, u32, u32, vp],
     "ingot_matvec_static": [vp, u32, u32, u32, u32, u32, vp, vp, vp, i32],
     "ingot_command_begin": [vp],
     "ingot_command_end": [vp, C.POINTER(vp)],

@@ -23,6 +23,8 @@ struct ingot_gpu {
     int *status_host = nullptr;       // pinned mirror
     void *workspace = nullptr;        // scratch for packed activations
     size_t workspace_bytes = 0;
+    void *tc_scratch = nullptr;       // tile counters and partial rows of the tcgen05 GEMV
+    bool use_tc = false;
     uint32_t sm_count = 0;
     bool failed = false;              // sticky device failure
     bool pdl = true;
@@ -61,6 +63,8 @@ ingot_status enter(ingot_gpu *g) {
     return INGOT_OK;
 }
 
+constexpr size_t TC_SCRATCH_BYTES = 8u << 20;
+
 LaunchCtx ctx_of(const ingot_gpu *g) {
     LaunchCtx c;
     c.stream = g->stream;
@@ -71,6 +75,9 @@ LaunchCtx ctx_of(const ingot_gpu *g) {
     c.no_mma = g->no_mma;
     c.workspace = g->workspace;
     c.workspace_bytes = g->workspace_bytes;
+    c.use_tc = g->use_tc;
+    c.tc_scratch = g->tc_scratch;
+    c.tc_scratch_bytes = TC_SCRATCH_BYTES;
     return c;
 }
 
@@ -80,7 +87,7 @@ ingot_status after_launch(ingot_gpu *g, cudaError_t e, const char *what) {
     return INGOT_OK;
 }
 
-bool x_kind_ok(uint32_t k) { return k == INGOT_KIND_F32 || k == INGOT_KIND_BF16 || k == INGOT_X_PACKED; }
+bool x_kind_ok(uint32_t k) { return k == INGOT_KIND_F32 || k == INGOT_KIND_BF16 || k == INGOT_X_PACKED || k == INGOT_X_DIGITS; }
 
 constexpr size_t WORKSPACE_BYTES = 16u << 20;
 
@@ -139,7 +146,8 @@ ingot_status ingot_gpu_create(int32_t device, ingot_gpu **out) {
     if (cudaStreamCreateWithFlags(&g->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc(&g->status, 64) != cudaSuccess || cudaMemset(g->status, 0, 64) != cudaSuccess ||
         cudaHostAlloc(&g->status_host, 64, cudaHostAllocDefault) != cudaSuccess ||
-        cudaMalloc(&g->workspace, WORKSPACE_BYTES) != cudaSuccess) {
+        cudaMalloc(&g->workspace, WORKSPACE_BYTES) != cudaSuccess ||
+        cudaMalloc(&g->tc_scratch, TC_SCRATCH_BYTES) != cudaSuccess || cudaMemset(g->tc_scratch, 0, TC_COUNTER_BYTES) != cudaSuccess) {
         ingot_gpu_destroy(g);
         return INGOT_DEVICE;
     }
@@ -155,6 +163,7 @@ void ingot_gpu_destroy(ingot_gpu *g) {
     if (g->own_stream) { cudaStreamSynchronize(g->own_stream); cudaStreamDestroy(g->own_stream); }
     if (g->status) cudaFree(g->status);
     if (g->workspace) cudaFree(g->workspace);
+    if (g->tc_scratch) cudaFree(g->tc_scratch);
     if (g->status_host) cudaFreeHost(g->status_host);
     delete g;
 }
@@ -174,6 +183,7 @@ ingot_status ingot_gpu_set_option(ingot_gpu *g, int32_t option, int32_t value) {
     case INGOT_OPT_PDL: g->pdl = value != 0; return INGOT_OK;
     case INGOT_OPT_FORCE_PLAIN: g->force_plain = value != 0; return INGOT_OK;
     case INGOT_OPT_NO_MMA: g->no_mma = value != 0; return INGOT_OK;
+    case INGOT_OPT_TCGEN05_GEMV: g->use_tc = value != 0; return INGOT_OK;
     default: return fail(g, INGOT_INVALID, "unknown option");
     }
 }
@@ -300,7 +310,13 @@ static ingot_status gemv_common(ingot_gpu *g, GemvCall &c, uint32_t x_kind, cons
     if (!x_kind_ok(x_kind)) return fail(g, INGOT_UNSUPPORTED, "activations must be F32 (0), BF16 (30) or packed");
     if (!c.w[0] || (c.nmat == 2 && !c.w[1]) || !c.x || !c.y) return fail(g, INGOT_INVALID, "null pointer");
     c.x_bf16 = x_kind == INGOT_KIND_BF16;
-    c.x_packed = x_kind == INGOT_X_PACKED;
+    c.x_packed = x_kind == INGOT_X_PACKED ? 1u : x_kind == INGOT_X_DIGITS ? 3u : 0u;
+    if (c.x_packed == 3u) {
+        cudaError_t e = cudaSuccess;
+        if (!try_launch_gemv_tc(c, ctx_of(g), e))
+            return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": digit rows need one token and a weight type the tcgen05 GEMV takes");
+        return after_launch(g, e, what);
+    }
     if (c.x_packed) {
         // packed rows only feed the tensor-core GEMV: one token, a block-quantised type, 16-byte aligned rows
         cudaError_t e = cudaSuccess;
@@ -485,6 +501,20 @@ ingot_status ingot_pack_x(ingot_gpu *g, const void *x, uint32_t x_kind, uint32_t
     if (!x || !packed || cols == 0 || cols % 64u || ((uintptr_t)packed % 16u)) return fail(g, INGOT_INVALID, "pack_x: bad arguments");
     if (x_kind != INGOT_KIND_F32 && x_kind != INGOT_KIND_BF16) return fail(g, INGOT_UNSUPPORTED, "pack_x: activations must be F32 or BF16");
     return after_launch(g, launch_pack_x(x, x_kind == INGOT_KIND_BF16, rows, cols, packed, ctx_of(g)), "pack_x");
+}
+
+ingot_status ingot_packed_digits_bytes(uint32_t cols, uint64_t *bytes) {
+    if (!bytes || cols == 0 || cols % 256u) return INGOT_INVALID;
+    *bytes = packed_digits_bytes(cols);
+    return INGOT_OK;
+}
+
+ingot_status ingot_pack_digits(ingot_gpu *g, const void *x, uint32_t x_kind, uint32_t rows, uint32_t cols, void *packed) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!x || !packed || cols == 0 || cols % 256u || ((uintptr_t)packed % 16u)) return fail(g, INGOT_INVALID, "pack_digits: bad arguments");
+    if (x_kind != INGOT_KIND_F32 && x_kind != INGOT_KIND_BF16) return fail(g, INGOT_UNSUPPORTED, "pack_digits: activations must be F32 or BF16");
+    return after_launch(g, launch_pack_digits(x, x_kind == INGOT_KIND_BF16, rows, cols, packed, ctx_of(g)), "pack_digits");
 }
 
 // ---- command recording --------------------------------------------------------

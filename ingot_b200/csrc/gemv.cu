@@ -295,6 +295,7 @@ cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx) {
                          ((uintptr_t)c.x % 16u) == 0 && ((size_t)c.rows * c.stride) % 16u == 0;
     if (!ctx.force_plain && !ctx.no_mma && aligned) {
         cudaError_t e = cudaSuccess;
+        if (ctx.use_tc && try_launch_gemv_tc(c, ctx, e)) return e;
         if (try_launch_gemv_mma(c, ctx, e)) return e;
     }
     if (!ctx.force_plain && aligned) {

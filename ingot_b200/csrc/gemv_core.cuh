@@ -162,6 +162,11 @@ IG_HD void consume_chunk(const uint8_t *stage, const F4 *xs, const GemvPlan &p, 
 // 1/scale.  cols must be a multiple of 64.
 IG_HD uint32_t packed_x_bytes(uint32_t cols) { return cols * 4u + cols / 4u + 16u; }
 
+// Bytes of one activation row as base-256 digits for the int8 tensor-core GEMV: the
+// N = 8 operand image (8 bytes per column), fp32 sums of each 16 columns, 16 bytes
+// holding 1/scale.  cols must be a multiple of 256.
+IG_HD uint32_t packed_digits_bytes(uint32_t cols) { return cols * 8u + cols / 4u + 16u; }
+
 // silu(g)*u or tanh-GeLU(g)*u (reference glu: kernels/generic.metal:298).
 IG_HD float glu_f(float g, float u, bool gelu) {
     if (gelu) {

@@ -24,7 +24,11 @@ struct LaunchCtx {
     bool no_mma;          // test hook: use the fp32 CUDA-core streaming kernel instead of the MMA one
     void *workspace;      // device scratch of the handle (packed activations)
     size_t workspace_bytes;
+    bool use_tc;          // one-token Q4_K GEMVs go to the tcgen05 int8 kernel
+    void *tc_scratch;     // its tile counters (TC_COUNTER_BYTES, zero between launches) and partial rows
+    size_t tc_scratch_bytes;
 };
+static constexpr size_t TC_COUNTER_BYTES = 64u * 1024u;
 
 // y = W x for `count` tokens (dense) or `pairs` (token, expert) pairs (routed,
 // ids != null).  nmat == 2 fuses two matrices and stores glu(gate, up).
@@ -38,12 +42,16 @@ struct GemvCall {
     uint32_t count;        // dense tokens
     uint32_t pairs, top, per_pair, n_experts;   // routed
     uint32_t x_bf16;
-    uint32_t x_packed;     // x is already in packed_x_bytes(cols) rows (launch_pack_x)
+    uint32_t x_packed;     // x is already packed: 1 = packed_x_bytes(cols) rows (launch_pack_x), 3 = digit rows (launch_pack_digits)
     uint32_t nmat, glu;    // glu: 1 silu, 2 tanh-gelu
 };
 cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);
 // The tensor-core-assisted streaming GEMV; false when the call is not one it handles.
 bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
+// The tcgen05 int8 GEMV (one token, Q4_K); false when the call is not one it handles.
+bool try_launch_gemv_tc(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
+// Packs `rows` activation rows (f32 or bf16) as base-256 digits for it.
+cudaError_t launch_pack_digits(const void *x, uint32_t bf16, uint32_t rows, uint32_t cols, void *packed, const LaunchCtx &ctx);
 // Packs `rows` activation rows (f32 or bf16) for the tensor-core GEMV.
 cudaError_t launch_pack_x(const void *x, uint32_t bf16, uint32_t rows, uint32_t cols, void *packed, const LaunchCtx &ctx);
 

@@ -42,6 +42,48 @@ __device__ __forceinline__ void pack_store_quad(uint8_t *row, uint32_t cols, uin
     if (live && t == 0) reinterpret_cast<float *>(row + (size_t)cols * 4u)[mi] = s;
 }
 
+// ---- base-256 digits for the int8 tensor-core GEMV ----
+// Power of two that puts max|x| = mx into [2^21, 2^22) (1 for an all-zero or non-finite row).
+__device__ __forceinline__ float digits_scale(float mx) {
+    if (!(mx > 0.f) || !(mx < INFINITY)) return 1.0f;
+    int e;
+    frexpf(mx, &e);
+    return ldexpf(1.0f, 22 - e);
+}
+
+// One thread stores columns 4q..4q+3 (v already scaled) of the digit image: q = round(v) =
+// d0 + 256 d1 + 65536 d2 with digits in [-128, 127]; rows 0..2 of the column's 16-column chunk
+// get the digits, rows 3..5 get them again in odd chunks (zero in even ones), rows 6, 7 are zero.
+// The four threads of a quad call this together: the chunk sum uses quad shuffles.
+__device__ __forceinline__ void digits_store_quad(uint8_t *row, uint32_t cols, uint32_t q, const float (&v)[4], bool live) {
+    uint32_t w0 = 0, w1 = 0, w2 = 0;
+    int total = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int x = __float2int_rn(v[i]);
+        const int r1 = (x + 128) >> 8, r2 = (r1 + 128) >> 8;
+        w0 |= (uint32_t)(x & 0xff) << (8 * i);
+        w1 |= (uint32_t)(r1 & 0xff) << (8 * i);
+        w2 |= (uint32_t)(r2 & 0xff) << (8 * i);
+        total += x;
+    }
+    if (live) {
+        const uint32_t chunk = q >> 2;
+        uint32_t *dst = reinterpret_cast<uint32_t *>(row + (size_t)chunk * 128u + (q & 3u) * 4u);
+        const bool odd = chunk & 1u;
+        dst[0] = w0; dst[4] = w1; dst[8] = w2;
+        dst[12] = odd ? w0 : 0u; dst[16] = odd ? w1 : 0u; dst[20] = odd ? w2 : 0u;
+        dst[24] = 0u; dst[28] = 0u;
+    }
+    total += __shfl_xor_sync(0xffffffffu, total, 1);
+    total += __shfl_xor_sync(0xffffffffu, total, 2);
+    if (live && (q & 3u) == 0) reinterpret_cast<float *>(row + (size_t)cols * 8u)[q >> 2] = (float)total;
+}
+
+__device__ __forceinline__ void digits_store_unscale(uint8_t *row, uint32_t cols, float scale) {
+    *reinterpret_cast<float *>(row + (size_t)cols * 8u + cols / 4u) = 1.0f / scale;
+}
+
 __device__ __forceinline__ void pack_store_unscale(uint8_t *row, uint32_t cols, float scale) {
     *reinterpret_cast<float *>(row + (size_t)cols * 4u + cols / 4u) = 1.0f / scale;
 }

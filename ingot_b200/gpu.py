@@ -26,6 +26,7 @@ from .synth import geometry, stride_of
 
 F32, F16, Q4_0, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 2, 8, 12, 14, 30
 X_PACKED = _abi.X_PACKED     # x_kind of rows produced by Gpu.pack_x
+X_DIGITS = _abi.X_DIGITS     # x_kind of rows produced by Gpu.pack_digits (tcgen05 int8 GEMV)
 
 
 class IngotError(Exception):
@@ -394,6 +395,17 @@ class Gpu:
         """Packs activation rows for the tensor-core GEMV; pass the result with x_kind=X_PACKED."""
         p = out or self.empty_bytes(rows * self.packed_x_bytes(cols))
         self._check(self._lib.ingot_pack_x(self._h, x.ptr, x_kind, rows, cols, p.ptr))
+        return p
+
+    def packed_digits_bytes(self, cols: int) -> int:
+        n = C.c_uint64()
+        self._check(self._lib.ingot_packed_digits_bytes(cols, C.byref(n)))
+        return n.value
+
+    def pack_digits(self, x: Buffer, rows: int, cols: int, x_kind: int = F32, out: Buffer | None = None) -> Buffer:
+        """Packs activation rows as base-256 digits for the tcgen05 int8 GEMV; pass the result with x_kind=X_DIGITS."""
+        p = out or self.empty_bytes(rows * self.packed_digits_bytes(cols))
+        self._check(self._lib.ingot_pack_digits(self._h, x.ptr, x_kind, rows, cols, p.ptr))
         return p
 
     def route_topk(self, logits: Buffer, experts: int, top: int, tokens: int):

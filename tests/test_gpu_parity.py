@@ -503,3 +503,27 @@ def test_gemm_random_activations_and_unsupported_shapes(gpu):
     w0 = gpu.bytes(synth.random_matrix(Q4_0, 256, 8, seed=1))
     with pytest.raises(InvalidData):
         gpu.gemm(None, w0, 256, 8, synth.stride_of(Q4_0, 256), Q4_0, 0, xb, 8)                   # no tensor-core kernel
+
+
+# ---- one-token GEMV on the tcgen05 int8 tensor cores -----------------------------------------
+
+def _tc_gemv(gpu, raw, cols, rows, x, x_kind=F32, expert=0):
+    w = gpu.bytes(raw)
+    xb = gpu.floats(x) if x_kind == F32 else gpu.bf16(x)
+    gpu.set_option(_abi.OPT_TCGEN05_GEMV, 1)
+    try:
+        return gpu.finish(None, gpu.matmul(None, w, cols, rows, synth.stride_of(Q4_K, cols), Q4_K, expert, xb, 1, x_kind))
+    finally:
+        gpu.set_option(_abi.OPT_TCGEN05_GEMV, 0)
+
+
+@pytest.mark.parametrize("cols,rows", [(256, 128), (512, 100), (4096, 300), (2560, 37), (4096, 4096), (12288, 256)])
+def test_tcgen05_gemv_q4k_matches_oracle(gpu, cols, rows):
+    raw = synth.random_matrix(Q4_K, cols, rows, 2, seed=cols + rows)
+    x = synth.activations(1, cols, seed=5) / 256.0
+    y = _tc_gemv(gpu, raw, cols, rows, x, expert=1)
+    e = O.matvec_f64(raw, cols, rows, Q4_K, x, expert=1)[0]
+    assert (np.abs(y - e) <= tol_ref(e)).all(), float(np.abs(y - e).max())
+    # run to run the result is the same bits (the tile sums do not depend on arrival order)
+    y2 = _tc_gemv(gpu, raw, cols, rows, x, expert=1)
+    assert np.array_equal(y.view(np.uint32), y2.view(np.uint32))
