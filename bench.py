@@ -161,6 +161,9 @@ def main():
     ap.add_argument("--reps", type=int, default=2, help="sweeps over the layers in --profile-kernel mode")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "f32"],
                     help="activation type between the projections (bf16 is the benchmark configuration)")
+    ap.add_argument("--pdl", type=int, default=1, help="0: launch without programmatic dependent launch (comparison)")
+    ap.add_argument("--graph", type=int, default=1, help="0: issue every step's launches instead of replaying a recorded command")
+    ap.add_argument("--no-mma", type=int, default=0, help="1: streaming GEMVs on the fp32 CUDA-core kernel (comparison)")
     ap.add_argument("--tcgen05-gemv", type=int, default=0, help="1: Q4_K one-token GEMVs on the tcgen05 int8 kernel")
     ap.add_argument("--workload", default="chain", choices=["chain", "gemm"],
                     help="chain: the dense decode step (the headline line); gemm: the prefill dequant-GEMM table")
@@ -189,6 +192,8 @@ def main():
     gpu = Gpu(local)
     gpu.set_stream(stream.cuda_stream)
     gpu.set_option(_abi.OPT_TCGEN05_GEMV, args.tcgen05_gemv)
+    gpu.set_option(_abi.OPT_NO_MMA, args.no_mma)
+    gpu.set_option(_abi.OPT_PDL, args.pdl)
 
     shape = QWEN3_8B
     x_kind = BF16 if args.activations == "bf16" else F32
@@ -197,7 +202,7 @@ def main():
         gpu.close()
         return
     if args.profile_kernel:
-        chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, layers=args.layers or 4)
+        chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, layers=args.layers or 4, packed=not args.no_mma)
         peaks, peak_src = measured_peaks()
         roof, per = kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=args.profile_kernel,
                                      reps=args.reps, digits=bool(args.tcgen05_gemv))
@@ -212,7 +217,7 @@ def main():
         dist.all_gather_into_tensor(dst, src)
 
     chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, rank=rank, world=world,
-                        all_gather=all_gather if world > 1 else None, layers=args.layers,
+                        all_gather=all_gather if world > 1 else None, layers=args.layers, packed=not args.no_mma,
                         keep_host=1 if (rank == 0 and world == 1 and not args.no_cpu) else 0)
     h0 = np.random.default_rng(1).normal(0, 1, (args.batch, shape.hidden)).astype(np.float32)
     gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.h_in.ptr, h0.ctypes.data, h0.nbytes))
@@ -221,7 +226,7 @@ def main():
     use_graph = True
     tgraph = None
     if world == 1:
-        graph = chain.record()
+        graph = chain.record() if args.graph else None
     else:
         # the step contains NCCL all-gathers: let torch record it (its NCCL bindings join the
         # capture), after eager steps have created the communicator

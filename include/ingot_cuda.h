@@ -96,6 +96,15 @@ INGOT_API const char *ingot_last_error(const ingot_gpu *gpu);
  * src/metal.rs:659-673. */
 INGOT_API ingot_status ingot_gpu_set_stream(ingot_gpu *gpu, void *cuda_stream);
 
+/* Gpu::independent_projections, src/metal.rs:1371-1396: between begin and end only
+ * operators that do not consume each other's results may be issued (no buffer
+ * upload, read or synchronize either); they run concurrently — on B200 the launches
+ * rotate over the handle's stream and three side streams forked from it — and
+ * everything issued after end is ordered after all of them.  Works inside a
+ * recorded command. */
+INGOT_API ingot_status ingot_independent_begin(ingot_gpu *gpu);
+INGOT_API ingot_status ingot_independent_end(ingot_gpu *gpu);
+
 /* Options: INGOT_OPT_PDL (default 1) launches kernels with programmatic
  * dependent launch so a kernel's weight prefetch overlaps its predecessor's
  * tail; INGOT_OPT_FORCE_PLAIN (default 0) routes every GEMV through the plain

@@ -66,7 +66,7 @@ class DecodeChain:
 
     def __init__(self, gpu: Gpu, shape: DenseShape, batch: int = 1, x_kind: int = BF16, seed: int = 0,
                  rank: int = 0, world: int = 1, all_gather=None, layers: int | None = None,
-                 keep_host: int = 0):
+                 keep_host: int = 0, packed: bool = True, independent_qkv: bool = True):
         self.gpu, self.shape, self.batch, self.x_kind = gpu, shape, batch, x_kind
         self.rank, self.world, self.all_gather = rank, world, all_gather
         self.n_layers = shape.layers if layers is None else layers
@@ -95,7 +95,10 @@ class DecodeChain:
         # per-rank partial outputs when sharded
         self.part = gpu.zeros(b * max(shape.ffn, shape.vocab) // world + b * 8) if world > 1 else None
         # activations packed once per distinct GEMV input (one token: the tensor-core GEMV)
-        self.packed = batch == 1
+        self.packed = batch == 1 and packed
+        # q, k and v read the same activations and write different buffers: issue them concurrently
+        # (the reference's independent_projections scope) when nothing has to be gathered between them
+        self.independent_qkv = independent_qkv and world == 1 and self.packed
         if self.packed:
             self.xn_p = gpu.empty_bytes(gpu.packed_x_bytes(h))
             self.a_p = gpu.empty_bytes(gpu.packed_x_bytes(shape.q))
@@ -166,9 +169,15 @@ class DecodeChain:
                 resid = self.h_in
             else:
                 resid = self.h
-            self._project(ws["q"], self.xn, self.q)
-            self._project(ws["k"], self.xn, self.k)
-            self._project(ws["v"], self.xn, self.v)
+            if self.independent_qkv:
+                with self.gpu.independent():
+                    self._project(ws["q"], self.xn, self.q)
+                    self._project(ws["k"], self.xn, self.k)
+                    self._project(ws["v"], self.xn, self.v)
+            else:
+                self._project(ws["q"], self.xn, self.q)
+                self._project(ws["k"], self.xn, self.k)
+                self._project(ws["v"], self.xn, self.v)
             self._norm(self.q, None, None, self.a, s.q)
             self._project(ws["o"], self.a, self.o)
             self._norm(resid, self.o, self.h, self.xn, s.hidden)

@@ -31,6 +31,13 @@ struct ingot_gpu {
     bool force_plain = false;
     bool no_mma = false;
     bool capturing = false;
+    // independent-projection scope: launches rotate over the main stream and side streams
+    static constexpr int SIDE_STREAMS = 3;
+    cudaStream_t side[SIDE_STREAMS] = {};
+    cudaEvent_t fork_event = nullptr, join_event[SIDE_STREAMS] = {};
+    bool in_scope = false;
+    int scope_next = 0;               // stream of the next launch inside the scope: 0 = main, i > 0 = side[i - 1]
+    int scope_used = 0;               // side streams touched in this scope (bit mask)
     std::string error;
 };
 
@@ -65,9 +72,23 @@ ingot_status enter(ingot_gpu *g) {
 
 constexpr size_t TC_SCRATCH_BYTES = 8u << 20;
 
-LaunchCtx ctx_of(const ingot_gpu *g) {
+// The stream of the next launch: inside an independent-projection scope launches take the
+// main stream and the side streams in turn.
+cudaStream_t next_stream(ingot_gpu *g) {
+    if (!g->in_scope) return g->stream;
+    const int i = g->scope_next;
+    g->scope_next = (i + 1) % (ingot_gpu::SIDE_STREAMS + 1);
+    if (i == 0) return g->stream;
+    if (!(g->scope_used & (1 << (i - 1)))) {            // first use in this scope: order it after the fork point
+        if (cudaStreamWaitEvent(g->side[i - 1], g->fork_event, 0) != cudaSuccess) return g->stream;
+        g->scope_used |= 1 << (i - 1);
+    }
+    return g->side[i - 1];
+}
+
+LaunchCtx ctx_of(ingot_gpu *g) {
     LaunchCtx c;
-    c.stream = g->stream;
+    c.stream = next_stream(g);
     c.status = g->status;
     c.sm_count = g->sm_count;
     c.pdl = g->pdl;
@@ -78,6 +99,12 @@ LaunchCtx ctx_of(const ingot_gpu *g) {
     c.use_tc = g->use_tc;
     c.tc_scratch = g->tc_scratch;
     c.tc_scratch_bytes = TC_SCRATCH_BYTES;
+    if (g->in_scope) {            // concurrent launches must not share the handle's scratch areas
+        c.workspace = nullptr;
+        c.workspace_bytes = 0;
+        c.tc_scratch = nullptr;
+        c.tc_scratch_bytes = 0;
+    }
     return c;
 }
 
@@ -161,6 +188,11 @@ void ingot_gpu_destroy(ingot_gpu *g) {
     if (!g) return;
     cudaSetDevice(g->device);
     if (g->own_stream) { cudaStreamSynchronize(g->own_stream); cudaStreamDestroy(g->own_stream); }
+    for (int i = 0; i < ingot_gpu::SIDE_STREAMS; ++i) {
+        if (g->side[i]) cudaStreamDestroy(g->side[i]);
+        if (g->join_event[i]) cudaEventDestroy(g->join_event[i]);
+    }
+    if (g->fork_event) cudaEventDestroy(g->fork_event);
     if (g->status) cudaFree(g->status);
     if (g->workspace) cudaFree(g->workspace);
     if (g->tc_scratch) cudaFree(g->tc_scratch);
@@ -192,6 +224,7 @@ ingot_status ingot_synchronize(ingot_gpu *g) {
     ingot_status st = enter(g);
     if (st) return st;
     if (g->capturing) return fail(g, INGOT_INVALID, "cannot synchronize while recording");
+    if (g->in_scope) return fail(g, INGOT_INVALID, "cannot synchronize inside an independent scope");
     cudaError_t e = cudaMemcpyAsync(g->status_host, g->status, sizeof(int), cudaMemcpyDeviceToHost, g->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
     if (e != cudaSuccess) return cuda_fail(g, e, "synchronize");
@@ -359,6 +392,8 @@ static ingot_status ensure_workspace(ingot_gpu *g, size_t bytes) {
 ingot_status ingot_gemm(ingot_gpu *g, const void *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind,
                         uint32_t expert, const void *x, uint32_t x_kind, uint32_t count, float *y) {
     ingot_status st = enter(g);
+    if (!st && g->in_scope) return fail(g, INGOT_INVALID, "gemm: not inside an independent scope (it uses the handle's scratch)");
+    
     if (st) return st;
     if ((st = check_matrix(g, kind, cols, rows, stride))) return st;
     if (x_kind != INGOT_KIND_F32 && x_kind != INGOT_KIND_BF16) return fail(g, INGOT_UNSUPPORTED, "gemm: activations must be F32 or BF16");
@@ -517,6 +552,41 @@ ingot_status ingot_pack_digits(ingot_gpu *g, const void *x, uint32_t x_kind, uin
     return after_launch(g, launch_pack_digits(x, x_kind == INGOT_KIND_BF16, rows, cols, packed, ctx_of(g)), "pack_digits");
 }
 
+// ---- independent projections ----------------------------------------------------------------
+
+ingot_status ingot_independent_begin(ingot_gpu *g) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->in_scope) return fail(g, INGOT_INVALID, "independent scope already open");
+    if (!g->fork_event) {
+        cudaError_t e = cudaEventCreateWithFlags(&g->fork_event, cudaEventDisableTiming);
+        for (int i = 0; i < ingot_gpu::SIDE_STREAMS && e == cudaSuccess; ++i) {
+            e = cudaStreamCreateWithFlags(&g->side[i], cudaStreamNonBlocking);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&g->join_event[i], cudaEventDisableTiming);
+        }
+        if (e != cudaSuccess) return cuda_fail(g, e, "independent scope setup");
+    }
+    cudaError_t e = cudaEventRecord(g->fork_event, g->stream);
+    if (e != cudaSuccess) return cuda_fail(g, e, "independent scope fork");
+    g->in_scope = true;
+    g->scope_next = 0;
+    g->scope_used = 0;
+    return INGOT_OK;
+}
+
+ingot_status ingot_independent_end(ingot_gpu *g) {
+    if (!g) return INGOT_INVALID;
+    if (!g->in_scope) return fail(g, INGOT_INVALID, "no independent scope open");
+    g->in_scope = false;
+    for (int i = 0; i < ingot_gpu::SIDE_STREAMS; ++i) {
+        if (!(g->scope_used & (1 << i))) continue;
+        cudaError_t e = cudaEventRecord(g->join_event[i], g->side[i]);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(g->stream, g->join_event[i], 0);
+        if (e != cudaSuccess) return cuda_fail(g, e, "independent scope join");
+    }
+    return INGOT_OK;
+}
+
 // ---- command recording --------------------------------------------------------
 
 ingot_status ingot_command_begin(ingot_gpu *g) {
@@ -532,6 +602,7 @@ ingot_status ingot_command_begin(ingot_gpu *g) {
 ingot_status ingot_command_end(ingot_gpu *g, ingot_graph **out) {
     if (!g || !out) return INGOT_INVALID;
     if (!g->capturing) return fail(g, INGOT_INVALID, "not recording");
+    if (g->in_scope) return fail(g, INGOT_INVALID, "independent scope still open");
     g->capturing = false;
     ingot_graph *gr = new (std::nothrow) ingot_graph();
     if (!gr) return fail(g, INGOT_DEVICE, "out of host memory");

@@ -452,12 +452,96 @@ __global__ void __launch_bounds__(256) add_rms_kernel(const __grid_constant__ Rm
     if (tid == 0) pack_store_unscale(prow, a.width, scale);
 }
 
+// The same with every element held in registers between the passes: one read of the inputs,
+// two block-wide reductions (sum of squares; largest magnitude for the packing scale).  A
+// decode step runs four of these per layer on a single CTA each, so their latency, not their
+// bandwidth, is what counts.  Rows of up to RMS_FAST_THREADS * 4 * RMS_FAST_VEC elements.
+static constexpr uint32_t RMS_FAST_THREADS = 512, RMS_FAST_VEC = 8;
+
+__device__ __forceinline__ float block_reduce_512(float v, float *partial, bool is_max) {
+    for (uint32_t off = 16; off; off >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, off);
+        v = is_max ? fmaxf(v, o) : v + o;
+    }
+    __syncthreads();                                   // partial[] may still be read from the previous reduction
+    if ((threadIdx.x & 31u) == 0) partial[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = partial[0];
+#pragma unroll
+    for (int i = 1; i < (int)(RMS_FAST_THREADS / 32u); ++i) r = is_max ? fmaxf(r, partial[i]) : r + partial[i];
+    return r;
+}
+
+__global__ void __launch_bounds__(RMS_FAST_THREADS) add_rms_fast_kernel(const __grid_constant__ RmsArgs a) {
+    pdl_prologue();
+    __shared__ float partial[RMS_FAST_THREADS / 32u];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x, n4 = a.width >> 2;
+    const size_t base = (size_t)row * n4;
+    const float4 *a4 = reinterpret_cast<const float4 *>(a.a) + base;
+    const float4 *b4 = a.add ? reinterpret_cast<const float4 *>(a.b) + base : nullptr;
+    float4 v[RMS_FAST_VEC];
+    float sum = 0.f;
+#pragma unroll
+    for (uint32_t i = 0; i < RMS_FAST_VEC; ++i) {
+        const uint32_t j = tid + i * RMS_FAST_THREADS;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < n4) {
+            v[i] = a4[j];
+            if (a.add) {
+                const float4 o = b4[j];
+                v[i].x += o.x; v[i].y += o.y; v[i].z += o.z; v[i].w += o.w;
+                if (a.s) reinterpret_cast<float4 *>(a.s)[base + j] = v[i];
+            }
+            sum += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    }
+    const float total = block_reduce_512(sum, partial, false);
+    const float inv = 1.0f / sqrtf(total / (float)a.width + a.eps);
+    float mx = 0.f;
+#pragma unroll
+    for (uint32_t i = 0; i < RMS_FAST_VEC; ++i) {
+        const uint32_t j = tid + i * RMS_FAST_THREADS;
+        if (j < n4) {
+            const float4 wv = a.w ? reinterpret_cast<const float4 *>(a.w)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
+            v[i].x = v[i].x * inv * wv.x; v[i].y = v[i].y * inv * wv.y; v[i].z = v[i].z * inv * wv.z; v[i].w = v[i].w * inv * wv.w;
+            if (a.y) reinterpret_cast<float4 *>(a.y)[base + j] = v[i];
+            if (a.y_bf16) {
+                uint2 o;
+                o.x = (uint32_t)f2bf(v[i].x) | ((uint32_t)f2bf(v[i].y) << 16);
+                o.y = (uint32_t)f2bf(v[i].z) | ((uint32_t)f2bf(v[i].w) << 16);
+                reinterpret_cast<uint2 *>(a.y_bf16)[base + j] = o;
+            }
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+        }
+    }
+    if (!a.y_packed) return;
+    mx = block_reduce_512(mx, partial, true);
+    const float scale = pack_scale(mx);
+    uint8_t *prow = a.y_packed + (size_t)row * packed_x_bytes(a.width);
+#pragma unroll
+    for (uint32_t i = 0; i < RMS_FAST_VEC; ++i) {
+        const uint32_t j = tid + i * RMS_FAST_THREADS;
+        if (i * RMS_FAST_THREADS >= n4) break;             // uniform over the block: the quad shuffles keep all lanes
+        const bool live = j < n4;
+        float u[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+        if (a.pack_bf16) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) u[k] = __uint_as_float((uint32_t)f2bf(u[k]) << 16);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) u[k] *= scale;
+        pack_store_quad(prow, a.width, j, u, live);
+    }
+    if (tid == 0) pack_store_unscale(prow, a.width, scale);
+}
+
 cudaError_t launch_add_rms(const float *a, const float *b, const float *w, float *s, float *y, uint32_t width,
                            uint32_t rows, float eps, uint32_t add, void *y_bf16, void *y_packed, uint32_t pack_bf16,
                            const LaunchCtx &ctx) {
     if (width % 4u || (y_packed && width % 64u)) return cudaErrorInvalidValue;
     if (rows == 0) return cudaSuccess;
     RmsArgs args = {a, b, w, s, y, static_cast<uint16_t *>(y_bf16), static_cast<uint8_t *>(y_packed), width, add, pack_bf16, eps};
+    if (width <= RMS_FAST_THREADS * 4u * RMS_FAST_VEC) return launch(add_rms_fast_kernel, dim3(rows), dim3(RMS_FAST_THREADS), ctx, args);
     return launch(add_rms_kernel, dim3(rows), dim3(256), ctx, args);
 }
 

@@ -386,6 +386,21 @@ class Gpu:
         else:
             raise InvalidData(f"no operator named {name} on this path")
 
+    def independent(self):
+        """Scope in which only operators that do not consume each other's results are issued; they run
+        concurrently (Gpu::independent_projections, src/metal.rs:1371-1396)."""
+        gpu = self
+
+        class _Scope:
+            def __enter__(self_inner):
+                gpu._check(gpu._lib.ingot_independent_begin(gpu._h))
+
+            def __exit__(self_inner, *exc):
+                gpu._check(gpu._lib.ingot_independent_end(gpu._h))
+                return False
+
+        return _Scope()
+
     def packed_x_bytes(self, cols: int) -> int:
         n = C.c_uint64()
         self._check(self._lib.ingot_packed_x_bytes(cols, C.byref(n)))

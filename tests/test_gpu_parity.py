@@ -527,3 +527,46 @@ def test_tcgen05_gemv_q4k_matches_oracle(gpu, cols, rows):
     # run to run the result is the same bits (the tile sums do not depend on arrival order)
     y2 = _tc_gemv(gpu, raw, cols, rows, x, expert=1)
     assert np.array_equal(y.view(np.uint32), y2.view(np.uint32))
+
+
+# ---- independent projections ---------------------------------------------------------------
+
+def test_independent_scope_matches_serial_issue_and_records(gpu):
+    # q, k, v style: three projections of the same packed activations, issued concurrently
+    from ingot_b200 import X_PACKED
+    cols = 4096
+    shapes = [(Q4_K, 512), (Q4_K, 128), (Q6_K, 128)]
+    raws = [synth.random_matrix(k, cols, r, seed=60 + i) for i, (k, r) in enumerate(shapes)]
+    ws = [gpu.bytes(r) for r in raws]
+    x = synth.activations(1, cols, seed=61) / 256.0
+    packed = gpu.pack_x(gpu.floats(x), 1, cols)
+
+    def issue():
+        return [gpu.matmul(None, w, cols, r, synth.stride_of(k, cols), k, 0, packed, 1, X_PACKED) for w, (k, r) in zip(ws, shapes)]
+
+    serial = [gpu.finish(None, y) for y in issue()]
+    with gpu.independent():
+        ys = issue()
+    par = [gpu.finish(None, y) for y in ys]
+    for a, b, raw, (k, r) in zip(serial, par, raws, shapes):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        e = O.matvec_f64(raw, cols, r, k, x)[0]
+        assert (np.abs(b - e) <= tol_ref(e)).all()
+    # inside a recorded command, replayed twice
+    outs = [gpu.output(r) for _, r in shapes]
+    gpu.record()
+    with gpu.independent():
+        for w, (k, r), y in zip(ws, shapes, outs):
+            gpu._check(gpu._lib.ingot_matmul(gpu._h, w.ptr, cols, r, synth.stride_of(k, cols), k, 0, packed.ptr, X_PACKED, 1, y.ptr))
+    graph = gpu.end_record()
+    for _ in range(2):
+        for y in outs:
+            gpu._check(gpu._lib.ingot_buffer_zero(gpu._h, y.ptr, y.nbytes))
+        graph.submit()
+        gpu.complete()
+        for a, y in zip(serial, outs):
+            assert np.array_equal(a.view(np.uint32), gpu.read_f32(y).view(np.uint32))
+    with pytest.raises(InvalidData):          # a scope cannot be left open at the end of a recording, nor nested
+        with gpu.independent():
+            with gpu.independent():
+                pass
