@@ -163,6 +163,7 @@ def main():
                     help="activation type between the projections (bf16 is the benchmark configuration)")
     ap.add_argument("--pdl", type=int, default=1, help="0: launch without programmatic dependent launch (comparison)")
     ap.add_argument("--graph", type=int, default=1, help="0: issue every step's launches instead of replaying a recorded command")
+    ap.add_argument("--fused-norm", type=int, default=1, help="0: add_rms as separate launches (comparison)")
     ap.add_argument("--no-mma", type=int, default=0, help="1: streaming GEMVs on the fp32 CUDA-core kernel (comparison)")
     ap.add_argument("--tcgen05-gemv", type=int, default=0, help="1: Q4_K one-token GEMVs on the tcgen05 int8 kernel")
     ap.add_argument("--workload", default="chain", choices=["chain", "gemm"],
@@ -217,7 +218,7 @@ def main():
         dist.all_gather_into_tensor(dst, src)
 
     chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, rank=rank, world=world,
-                        all_gather=all_gather if world > 1 else None, layers=args.layers, packed=not args.no_mma,
+                        all_gather=all_gather if world > 1 else None, layers=args.layers, packed=not args.no_mma, fused_norm=bool(args.fused_norm),
                         keep_host=1 if (rank == 0 and world == 1 and not args.no_cpu) else 0)
     h0 = np.random.default_rng(1).normal(0, 1, (args.batch, shape.hidden)).astype(np.float32)
     gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.h_in.ptr, h0.ctypes.data, h0.nbytes))

@@ -228,6 +228,23 @@ INGOT_API ingot_status ingot_add_rms_packed(ingot_gpu *gpu, const float *a, cons
                                             float *y, void *y_bf16, void *y_packed, uint32_t pack_from_bf16,
                                             uint32_t width, uint32_t rows, float eps, uint32_t add);
 
+/* add_rms fused into the one-token projection that consumes it: x = rms_norm(a + b) * w (w
+ * may be NULL; b is ignored unless add), rounded to bfloat16 when round_bf16, then y = W x
+ * (or glu(gate x, up x)).  Every CTA of the GEMV computes the normalised row for itself, so
+ * the step loses a launch and a round trip through memory; `s` (may be NULL) receives a + b
+ * and must not alias a or b.  INGOT_UNSUPPORTED when the weight type has no tensor-core GEMV
+ * (Q4_0, Q8_0, Q4_K, Q6_K with 16-byte aligned rows have one): call ingot_add_rms and the
+ * plain projection instead.  No counterpart in the reference, whose add_rms
+ * (kernels/generic.metal:390-404) is always a separate dispatch. */
+INGOT_API ingot_status ingot_matmul_normed(ingot_gpu *gpu, const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
+                                           uint32_t kind, uint32_t expert, const float *a, const float *b,
+                                           const float *norm_w, float *s, float eps, uint32_t add,
+                                           uint32_t round_bf16, float *y);
+INGOT_API ingot_status ingot_gate_up_normed(ingot_gpu *gpu, const void *gate, const void *up, uint32_t cols,
+                                            uint32_t rows, uint32_t stride, uint32_t kind, const float *a,
+                                            const float *b, const float *norm_w, float *s, float eps, uint32_t add,
+                                            uint32_t round_bf16, uint32_t gelu, float *y);
+
 /* expert_layout + expert_pairs (kernels/prefill.metal:7-35): stable
  * expert-major grouping of `pairs` ids.  layout [experts][2] = (count, first),
  * tiles [tile_capacity][4] = (expert, first, n <= 32, mode), packed[pos] =

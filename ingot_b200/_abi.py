@@ -53,6 +53,8 @@ SIGNATURES = {
     "ingot_convert_bf16": [vp, vp, u64, vp],
     "ingot_packed_x_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_x": [vp, vp, u32, u32, u32, vp],
+    "ingot_matmul_normed": [vp, vp, u32, u32, u32, u32, u32, vp, vp, vp, vp, C.c_float, u32, u32, vp],
+    "ingot_gate_up_normed": [vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, vp, C.c_float, u32, u32, u32, vp],
     "ingot_independent_begin": [vp],
     "ingot_independent_end": [vp],
     "ingot_packed_digits_bytes": [u32, C.POINTER(u64)],

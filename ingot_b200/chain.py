@@ -60,13 +60,21 @@ def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
     return rows * rank // world, rows * (rank + 1) // world
 
 
+class _null_scope:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
 class DecodeChain:
     """Weights of one dense model (or this rank's row shard) resident in HBM and the
     buffers of one decode step for `batch` tokens."""
 
     def __init__(self, gpu: Gpu, shape: DenseShape, batch: int = 1, x_kind: int = BF16, seed: int = 0,
                  rank: int = 0, world: int = 1, all_gather=None, layers: int | None = None,
-                 keep_host: int = 0, packed: bool = True, independent_qkv: bool = True):
+                 keep_host: int = 0, packed: bool = True, independent_qkv: bool = True, fused_norm: bool = True):
         self.gpu, self.shape, self.batch, self.x_kind = gpu, shape, batch, x_kind
         self.rank, self.world, self.all_gather = rank, world, all_gather
         self.n_layers = shape.layers if layers is None else layers
@@ -99,6 +107,11 @@ class DecodeChain:
         # q, k and v read the same activations and write different buffers: issue them concurrently
         # (the reference's independent_projections scope) when nothing has to be gathered between them
         self.independent_qkv = independent_qkv and world == 1 and self.packed
+        # add_rms fused into the projections that consume it (one token, tensor-core GEMV kinds only)
+        tc_kinds = (synth.Q4_0, synth.Q8_0, synth.Q4_K, synth.Q6_K)
+        self.fused_norm = (fused_norm and self.packed and world == 1 and all(k in tc_kinds for k in shape.kinds.values())
+                           and all(synth.stride_of(shape.kinds[r], c) % 16 == 0 for r, c, _ in layer_roles(shape)))
+        self.h2 = gpu.zeros(b * h) if self.fused_norm else None        # the residual stream alternates between h and h2
         if self.packed:
             self.xn_p = gpu.empty_bytes(gpu.packed_x_bytes(h))
             self.a_p = gpu.empty_bytes(gpu.packed_x_bytes(shape.q))
@@ -157,8 +170,46 @@ class DecodeChain:
         if self.world > 1:
             self.all_gather(dst, y, self.batch, t.dims[1])
 
+    # ---- the same step with every add_rms fused into its consumers ------------------------
+    def _normed(self, w: Weight, a: Buffer, b: Buffer | None, s: Buffer | None, y: Buffer) -> None:
+        g, t = self.gpu, w.t
+        g._check(g._lib.ingot_matmul_normed(g._h, w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, a.ptr,
+                                            b.ptr if b else None, None, s.ptr if s else None, 1e-6, 1 if b else 0,
+                                            int(self.x_kind == BF16), y.ptr))
+        self.launches_per_step += 1
+
+    def _step_fused(self) -> None:
+        s, g = self.shape, self.gpu
+        self.launches_per_step = 0
+        cur, delta = self.h_in, None            # residual stream so far and the update not yet added to it
+        bufs = [self.h, self.h2]
+        nxt = 0
+        for ws in self.weights:
+            # q, k, v read rms_norm(cur + delta); q also stores the sum
+            summed = bufs[nxt] if delta else None
+            with g.independent() if self.independent_qkv else _null_scope():
+                # the two small projections first: their CTAs leave room for q's to start beside them
+                self._normed(ws["k"], cur, delta, None, self.k)
+                self._normed(ws["v"], cur, delta, None, self.v)
+                self._normed(ws["q"], cur, delta, summed, self.q)
+            if delta:
+                cur, nxt = summed, nxt ^ 1
+            self._normed(ws["o"], self.q, None, None, self.o)                 # stands in for attention: o(rms_norm(q))
+            t = ws["gate"].t
+            after = bufs[nxt]
+            g._check(g._lib.ingot_gate_up_normed(g._h, ws["gate"].buffer.ptr, ws["up"].buffer.ptr, t.dims[0], t.dims[1],
+                                                 t.stride, t.kind, cur.ptr, self.o.ptr, None, after.ptr, 1e-6, 1,
+                                                 int(self.x_kind == BF16), int(s.gelu), self.act.ptr))
+            self.launches_per_step += 1
+            cur, nxt = after, nxt ^ 1
+            self._normed(ws["down"], self.act, None, None, self.d)
+            delta = self.d
+        self._normed(self.head, cur, delta, None, self.logits)
+
     def step(self) -> None:
         """Issues one token step on the handle's stream (asynchronous)."""
+        if self.fused_norm:
+            return self._step_fused()
         s = self.shape
         self.launches_per_step = 0
         delta = None

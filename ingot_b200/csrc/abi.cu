@@ -418,6 +418,45 @@ ingot_status ingot_gate_up(ingot_gpu *g, const void *gate, const void *up, uint3
     return gemv_common(g, c, x_kind, "gate_up");
 }
 
+// add_rms fused into the projection that consumes it (one token, tensor-core GEMV only).
+static ingot_status normed_common(ingot_gpu *g, GemvCall &c, const float *a, const float *b, const float *norm_w, float *s,
+                                  float eps, uint32_t add, uint32_t round_bf16, const char *what) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if ((st = check_matrix(g, c.kind, c.cols, c.rows, c.stride))) return st;
+    if (!c.w[0] || (c.nmat == 2 && !c.w[1]) || !a || (add && !b) || !c.y) return fail(g, INGOT_INVALID, "null pointer");
+    if (s && (s == a || s == b)) return fail(g, INGOT_INVALID, std::string(what) + ": the sum cannot be stored over an input that every CTA still reads");
+    if (((uintptr_t)a % 16u) || (b && ((uintptr_t)b % 16u)) || (s && ((uintptr_t)s % 16u)) || (norm_w && ((uintptr_t)norm_w % 16u)))
+        return fail(g, INGOT_INVALID, std::string(what) + ": vectors must be 16-byte aligned");
+    c.norm_a = a; c.norm_b = add ? b : nullptr; c.norm_w = norm_w; c.norm_s = add ? s : nullptr;
+    c.norm_eps = eps; c.norm_round_bf16 = round_bf16;
+    c.count = 1;
+    cudaError_t e = cudaSuccess;
+    const bool aligned = ((uintptr_t)c.w[0] % 16u) == 0 && (c.nmat < 2 || ((uintptr_t)c.w[1] % 16u) == 0) && ((size_t)c.rows * c.stride) % 16u == 0;
+    if (g->no_mma || g->force_plain || !aligned || !try_launch_gemv_mma(c, ctx_of(g), e))
+        return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": no fused kernel for this weight; use add_rms and the plain projection");
+    return after_launch(g, e, what);
+}
+
+ingot_status ingot_matmul_normed(ingot_gpu *g, const void *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind,
+                                 uint32_t expert, const float *a, const float *b, const float *norm_w, float *s, float eps,
+                                 uint32_t add, uint32_t round_bf16, float *y) {
+    GemvCall c = {};
+    c.w[0] = static_cast<const uint8_t *>(w);
+    c.y = y; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind; c.expert = expert; c.nmat = 1;
+    return normed_common(g, c, a, b, norm_w, s, eps, add, round_bf16, "matmul_normed");
+}
+
+ingot_status ingot_gate_up_normed(ingot_gpu *g, const void *gate, const void *up, uint32_t cols, uint32_t rows, uint32_t stride,
+                                  uint32_t kind, const float *a, const float *b, const float *norm_w, float *s, float eps,
+                                  uint32_t add, uint32_t round_bf16, uint32_t gelu, float *y) {
+    GemvCall c = {};
+    c.w[0] = static_cast<const uint8_t *>(gate);
+    c.w[1] = static_cast<const uint8_t *>(up);
+    c.y = y; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind; c.nmat = 2; c.glu = gelu ? 2 : 1;
+    return normed_common(g, c, a, b, norm_w, s, eps, add, round_bf16, "gate_up_normed");
+}
+
 ingot_status ingot_routed(ingot_gpu *g, const void *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind,
                           uint32_t experts, const void *x, uint32_t x_kind, const uint32_t *ids, uint32_t per_pair,
                           uint32_t top, uint32_t pairs, float *y) {

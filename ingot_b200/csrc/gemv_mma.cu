@@ -79,6 +79,12 @@ struct MmaArgs {
     const uint32_t *ids;
     uint32_t expert, n_experts, per_pair, top, glu;
     int *status;
+    // optional fused normalisation of the activations (dense, one token): x = rms_norm(na + nb) * nw
+    // computed by every CTA into its own packed row instead of fetching one; CTA 0 stores the sum
+    const float *na, *nb, *nw;
+    float *ns;
+    float neps;
+    uint32_t nround_bf16;
 };
 
 static bool mma_kind(uint32_t kind) { return kind == KIND_Q4_K || kind == KIND_Q6_K || kind == KIND_Q4_0 || kind == KIND_Q8_0; }
@@ -472,7 +478,7 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
             const uint32_t nrows = (r_end - row0) < stage_rows ? (r_end - row0) : stage_rows;
             for (uint32_t cm = 0; cm < p.chunks * NMAT; ++cm, ++it) {
                 const uint32_t c = cm / NMAT, m = cm - c * NMAT;
-                if (!x_sent && it == p.stages) {       // ring primed: the next wait needs the consumers
+                if (!x_sent && it == p.stages && !a.na) {       // ring primed: the next wait needs the consumers
                     if (!a.ids) ptx::pdl_wait();
                     if (lane == 0) {
                         ptx::mbar_expect_tx(xbar, p.x_bytes);
@@ -494,7 +500,7 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
                                   p.chunk_bytes, &full[s]);
             }
         }
-        if (!x_sent) {                                   // fewer stage fills than ring slots
+        if (!x_sent && !a.na) {                          // fewer stage fills than ring slots
             if (!a.ids) ptx::pdl_wait();
             if (lane == 0) {
                 ptx::mbar_expect_tx(xbar, p.x_bytes);
@@ -516,7 +522,111 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
             return;
         }
     }
-    if (!ptx::mbar_wait(xbar, 0)) {
+    if (a.na) {
+        // ---- fused add + RMS normalisation + packing (what add_rms with a packed output computes,
+        // kernels/generic.metal:390-404): the 256 consumer threads of every CTA build the packed row ----
+        ptx::pdl_wait();
+        const uint32_t tid = threadIdx.x, n4 = p.cols >> 2;
+        const float4 *a4 = reinterpret_cast<const float4 *>(a.na), *b4 = reinterpret_cast<const float4 *>(a.nb);
+        float *scratch = red;                          // the partial-sum area is idle until the first tile ends
+        auto load = [&](uint32_t j) {
+            float4 v = a4[j];
+            if (b4) { const float4 o = b4[j]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+            return v;
+        };
+        auto reduce = [&](float v, bool is_max) {
+            for (uint32_t off = 16; off; off >>= 1) {
+                const float o = __shfl_xor_sync(0xffffffffu, v, off);
+                v = is_max ? fmaxf(v, o) : v + o;
+            }
+            ptx::named_bar_sync(1, MMA_WARPS * 32);
+            if (lane == 0) scratch[warp] = v;
+            ptx::named_bar_sync(1, MMA_WARPS * 32);
+            float r = scratch[0];
+#pragma unroll
+            for (int i = 1; i < MMA_WARPS; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
+            return r;
+        };
+        constexpr uint32_t NV = 12, NT = MMA_WARPS * 32;           // rows of up to 12288 columns stay in registers
+        auto finish = [&](float (&u)[4], uint32_t j, float inv) {
+            const float4 wv = a.nw ? reinterpret_cast<const float4 *>(a.nw)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
+            u[0] = u[0] * inv * wv.x; u[1] = u[1] * inv * wv.y; u[2] = u[2] * inv * wv.z; u[3] = u[3] * inv * wv.w;
+            if (a.nround_bf16) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint32_t x = __float_as_uint(u[k]);
+                    if ((x & 0x7fffffffu) <= 0x7f800000u) x += 0x7fffu + ((x >> 16) & 1u);       // round to nearest even
+                    u[k] = __uint_as_float(x & 0xffff0000u);
+                }
+            }
+        };
+        if (n4 <= NV * NT) {
+            float4 v[NV];
+            float sum = 0.f;
+#pragma unroll
+            for (uint32_t i = 0; i < NV; ++i) {
+                const uint32_t j = tid + i * NT;
+                v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (j < n4) {
+                    v[i] = load(j);
+                    if (a.ns && blockIdx.x == 0) reinterpret_cast<float4 *>(a.ns)[j] = v[i];
+                    sum += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+                }
+            }
+            const float inv = 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
+            float mx = 0.f;
+#pragma unroll
+            for (uint32_t i = 0; i < NV; ++i) {
+                const uint32_t j = tid + i * NT;
+                if (j < n4) {
+                    float u[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+                    finish(u, j, inv);
+                    v[i] = make_float4(u[0], u[1], u[2], u[3]);
+                    mx = fmaxf(mx, fmaxf(fmaxf(fabsf(u[0]), fabsf(u[1])), fmaxf(fabsf(u[2]), fabsf(u[3]))));
+                }
+            }
+            const float scale = pack_scale(reduce(mx, true));
+#pragma unroll
+            for (uint32_t i = 0; i < NV; ++i) {
+                if (i * NT >= n4) break;                               // uniform: the quad shuffles keep all lanes
+                const uint32_t j = tid + i * NT;
+                float u[4] = {v[i].x * scale, v[i].y * scale, v[i].z * scale, v[i].w * scale};
+                pack_store_quad(xrow, p.cols, j, u, j < n4);
+            }
+            if (tid == 0) pack_store_unscale(xrow, p.cols, scale);
+        } else {
+            float sum = 0.f;
+            for (uint32_t j = tid; j < n4; j += NT) {
+                const float4 v = load(j);
+                if (a.ns && blockIdx.x == 0) reinterpret_cast<float4 *>(a.ns)[j] = v;
+                sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            const float inv = 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
+            float mx = 0.f;
+            for (uint32_t j = tid; j < n4; j += NT) {
+                const float4 v = load(j);
+                float u[4] = {v.x, v.y, v.z, v.w};
+                finish(u, j, inv);
+                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(u[0]), fabsf(u[1])), fmaxf(fabsf(u[2]), fabsf(u[3]))));
+            }
+            const float scale = pack_scale(reduce(mx, true));
+            for (uint32_t j0 = 0; j0 < n4; j0 += NT) {                 // uniform trip count: the quad shuffles keep all lanes
+                const uint32_t j = j0 + tid;
+                const bool live = j < n4;
+                float u[4] = {0.f, 0.f, 0.f, 0.f};
+                if (live) {
+                    const float4 v = load(j);
+                    u[0] = v.x; u[1] = v.y; u[2] = v.z; u[3] = v.w;
+                    finish(u, j, inv);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) u[k] *= scale;
+                }
+                pack_store_quad(xrow, p.cols, j, u, live);
+            }
+            if (tid == 0) pack_store_unscale(xrow, p.cols, scale);
+        }
+        ptx::named_bar_sync(1, MMA_WARPS * 32);
+    } else if (!ptx::mbar_wait(xbar, 0)) {
         if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
         return;
     }
@@ -677,7 +787,10 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     }
     if (!ok) return false;
     const uint8_t *xp = static_cast<const uint8_t *>(c.x);
-    if (!c.x_packed) {
+    if (c.norm_a) {
+        if (routed || c.cols % 64u) return false;
+        xp = nullptr;
+    } else if (!c.x_packed) {
         const uint32_t x_rows = routed ? (c.per_pair ? c.pairs : (c.pairs + (c.top ? c.top : 1u) - 1) / (c.top ? c.top : 1u)) : 1u;
         const size_t need = (size_t)x_rows * packed_x_bytes(c.cols);
         if (!ctx.workspace || need > ctx.workspace_bytes) return false;
@@ -691,6 +804,7 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     a.ids = c.ids; a.expert = c.expert; a.n_experts = c.n_experts;
     a.per_pair = c.per_pair; a.top = c.top ? c.top : 1u; a.glu = c.glu;
     a.status = ctx.status;
+    a.na = c.norm_a; a.nb = c.norm_b; a.nw = c.norm_w; a.ns = c.norm_s; a.neps = c.norm_eps; a.nround_bf16 = c.norm_round_bf16;
     const dim3 grid(plan.ctas, gy);
     switch (c.kind) {
     case KIND_Q4_K: err = launch_mma_k<KIND_Q4_K>(a, grid, ctx.stream, ctx.pdl, occ); break;

@@ -44,6 +44,12 @@ struct GemvCall {
     uint32_t x_bf16;
     uint32_t x_packed;     // x is already packed: 1 = packed_x_bytes(cols) rows (launch_pack_x), 3 = digit rows (launch_pack_digits)
     uint32_t nmat, glu;    // glu: 1 silu, 2 tanh-gelu
+    // fused input normalisation (tensor-core GEMV, dense, one token): x = rms_norm(norm_a + norm_b) * norm_w,
+    // optionally rounded to bfloat16; norm_s receives norm_a + norm_b.  x is ignored when norm_a is set.
+    const float *norm_a, *norm_b, *norm_w;
+    float *norm_s;
+    float norm_eps;
+    uint32_t norm_round_bf16;
 };
 cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);
 // The tensor-core-assisted streaming GEMV; false when the call is not one it handles.

@@ -570,3 +570,50 @@ def test_independent_scope_matches_serial_issue_and_records(gpu):
         with gpu.independent():
             with gpu.independent():
                 pass
+
+
+# ---- add_rms fused into the projection ------------------------------------------------------
+
+@pytest.mark.parametrize("kind,cols,rows", [(Q4_K, 4096, 300), (Q6_K, 4096, 130), (Q4_0, 2560, 77), (Q4_K, 12288, 64)])
+@pytest.mark.parametrize("add,bf16", [(0, 0), (1, 1)])
+def test_normed_projection_matches_add_rms_then_matmul(gpu, kind, cols, rows, add, bf16):
+    from ingot_b200 import X_PACKED
+    raw = synth.random_matrix(kind, cols, rows, seed=71)
+    rng = np.random.default_rng(72)
+    a, b = rng.normal(0, 3, (1, cols)).astype(np.float32), rng.normal(0, 1, (1, cols)).astype(np.float32)
+    w, ab, bb = gpu.bytes(raw), gpu.floats(a), gpu.floats(b)
+    stride = synth.stride_of(kind, cols)
+    s_f, y_f = gpu.output(cols), gpu.output(rows)
+    gpu._check(gpu._lib.ingot_matmul_normed(gpu._h, w.ptr, cols, rows, stride, kind, 0, ab.ptr, bb.ptr, None, s_f.ptr, 1e-6, add, bf16, y_f.ptr))
+    fused = gpu.finish(None, y_f)
+    # separately: add_rms with a packed output, then the projection
+    s_s, packed = gpu.output(cols), gpu.empty_bytes(gpu.packed_x_bytes(cols))
+    gpu._check(gpu._lib.ingot_add_rms_packed(gpu._h, ab.ptr, bb.ptr, None, s_s.ptr, None, None, packed.ptr, bf16, cols, 1, 1e-6, add))
+    sep = gpu.finish(None, gpu.matmul(None, w, cols, rows, stride, kind, 0, packed, 1, X_PACKED))
+    e_s, e_x = O.add_rms(a, b, None, 1e-6, add=bool(add))
+    if bf16:
+        e_x = synth.from_bf16_bits(synth.to_bf16_bits(e_x.astype(np.float32)))
+    e = O.matvec_f64(raw, cols, rows, kind, e_x.astype(np.float32).reshape(1, cols))[0]
+    # the two differ only by the order of the sum of squares (256 against 512 threads)
+    assert (np.abs(fused - sep) <= 4 * tol_ref_scaled(e)).all(), float(np.abs(fused - sep).max())
+    assert (np.abs(fused - e) <= 8 * tol_ref_scaled(e)).all(), float(np.abs(fused - e).max())
+    if add:
+        assert np.array_equal(gpu.read_f32(s_f).view(np.uint32), gpu.read_f32(s_s).view(np.uint32))
+        with pytest.raises(InvalidData):        # the sum cannot go over an input
+            gpu._check(gpu._lib.ingot_matmul_normed(gpu._h, w.ptr, cols, rows, stride, kind, 0, ab.ptr, bb.ptr, None, ab.ptr, 1e-6, 1, bf16, y_f.ptr))
+
+
+def test_fused_and_unfused_chains_agree(gpu):
+    from ingot_b200.chain import QWEN3_8B, DecodeChain
+    h0 = np.random.default_rng(1).normal(0, 1, (1, QWEN3_8B.hidden)).astype(np.float32)
+    logits = []
+    for fused in (False, True):
+        chain = DecodeChain(gpu, QWEN3_8B, batch=1, x_kind=BF16, seed=3, layers=2, fused_norm=fused)
+        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.h_in.ptr, h0.ctypes.data, h0.nbytes))
+        chain.step()
+        gpu.complete()
+        logits.append(gpu.read_f32(chain.logits))
+        assert chain.fused_norm == fused
+        del chain
+    scale = float(np.sqrt(np.mean(np.square(logits[0]))))
+    assert np.abs(logits[0] - logits[1]).max() <= 2e-2 * scale     # bfloat16 rounding points move with the sum order
