@@ -50,7 +50,7 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while timing."""
+    """nvidia-smi clocks and throttle reasons sampled every 50 ms while timing."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -64,7 +64,7 @@ class ClockSampler:
             os.close(fd)
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.device)], stdout=self.out,
+                                          "-lms", "50", "-i", str(self.device)], stdout=self.out,
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -166,9 +166,11 @@ def main():
     ap.add_argument("--fused-norm", type=int, default=1, help="0: add_rms as separate launches (comparison)")
     ap.add_argument("--no-mma", type=int, default=0, help="1: streaming GEMVs on the fp32 CUDA-core kernel (comparison)")
     ap.add_argument("--tcgen05-gemv", type=int, default=0, help="1: Q4_K one-token GEMVs on the tcgen05 int8 kernel")
-    ap.add_argument("--workload", default="chain", choices=["chain", "gemm"],
-                    help="chain: the dense decode step (the headline line); gemm: the prefill dequant-GEMM table")
-    ap.add_argument("--tokens", type=int, nargs="*", default=[512, 2048, 8192], help="token counts of --workload gemm")
+    ap.add_argument("--workload", default="chain", choices=["chain", "gemma", "moe", "gemm"],
+                    help="chain: the Qwen3-8B dense decode step (the headline line); gemma: the Gemma-3-4B Q4_0 decode "
+                         "step; moe: the Qwen3-30B-A3B expert-routed FFN chain; gemm: the prefill dequant-GEMM table")
+    ap.add_argument("--tokens", type=int, nargs="*", default=None,
+                    help="token counts of --workload gemm (default 512 2048 8192) and moe (default 1 8 32)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -177,7 +179,7 @@ def main():
 
     import torch
     from ingot_b200 import BF16, F32, Gpu, _abi
-    from ingot_b200.chain import QWEN3_8B, DecodeChain, weight_bytes_per_token
+    from ingot_b200.chain import GEMMA3_4B, QWEN3_8B, DecodeChain, weight_bytes_per_token
     from ingot_b200.gpu import Buffer
 
     rank = int(os.environ.get("RANK", "0"))
@@ -196,12 +198,17 @@ def main():
     gpu.set_option(_abi.OPT_NO_MMA, args.no_mma)
     gpu.set_option(_abi.OPT_PDL, args.pdl)
 
-    shape = QWEN3_8B
+    shape = GEMMA3_4B if args.workload == "gemma" else QWEN3_8B
+    metric = METRIC if args.workload == "chain" else "decode tok/s, Gemma-3-4B Q4_0 shape (Q4_0 GEMV chain)"
     x_kind = BF16 if args.activations == "bf16" else F32
     if args.workload == "gemm":
+        args.tokens = args.tokens or [512, 2048, 8192]
         print(json.dumps(run_gemm(torch, gpu, stream, args)), flush=True)
         gpu.close()
         return
+    if args.workload == "moe":
+        args.tokens = args.tokens or [1, 8, 32]
+        return run_moe(torch, gpu, stream, args, rank, world, local)
     if args.profile_kernel:
         chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, layers=args.layers or 4, packed=not args.no_mma)
         peaks, peak_src = measured_peaks()
@@ -253,14 +260,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # clocks are sampled from the warm-up to the end of the end-to-end loop: the timed regions are
+    # tens of milliseconds, shorter than one sampling period
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         one_step()
     gpu.complete()
     launches_per_step = chain.launches_per_step
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
@@ -292,13 +300,12 @@ def main():
         t = torch.tensor([e2e_ms], device=f"cuda:{local}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    clocks = sampler.stop() if rank == 0 else None
-
     # ---- roofline of the dominant kernel, measured here with CUDA events ----
     peaks, peak_src = measured_peaks()
     roof, per_kernel = None, None
     if world == 1:
         roof, per_kernel = kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src)
+    clocks = sampler.stop() if rank == 0 else None
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu and chain.host:
@@ -313,12 +320,12 @@ def main():
     if rank == 0:
         total_bytes = weight_bytes_per_token(shape) if args.layers is None else chain.bytes_streamed
         line = {
-            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "metric": metric, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "qwen3-8b-q4_k_m dense decode GEMV chain (configs[1]), batch %d" % args.batch,
+            "config": {"workload": "%s dense decode GEMV chain (configs[%d]), batch %d" % (shape.name, 2 if args.workload == "gemma" else 1, args.batch),
                        "layers": chain.n_layers, "hidden": shape.hidden, "ffn": shape.ffn, "vocab": shape.vocab,
-                       "weights": "random Q4_K/Q6_K blocks", "activations": "%s in HBM, fp32 accumulate" % args.activations,
+                       "weights": "random Q4_0 blocks" if args.workload == "gemma" else "random Q4_K/Q6_K blocks", "activations": "%s in HBM, fp32 accumulate" % args.activations,
                        "parallelism": "tp%d rows" % world if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (total_bytes * 1.0 / 1e9 / world),
                        "launch": "one recorded command (CUDA graph) per step" + (" incl. NCCL all-gathers" if world > 1 else "")},
@@ -341,6 +348,97 @@ def main():
 
 
 # ---- helpers ------------------------------------------------------------------------
+
+def run_moe(torch, gpu, stream, args, rank, world, local):
+    """Qwen3-30B-A3B-shaped expert-routed FFN chain: 48 layers of route_topk -> routed gate/up + SiLU ->
+    routed down -> moe_sum, Q4_K experts, synthetic N(0,1) router logits, for each token count.
+    With N > 1 ranks the 128 experts are split expert-parallel (rank r owns experts [r*128/N, ...)),
+    every rank sees the same tokens and routing, and one NCCL all-reduce per layer completes the
+    output: weak scaling is not meaningful here, the same step runs on more GPUs (strong)."""
+    from ingot_b200.moe import QWEN3_30B_A3B, MoeChain, expert_bytes
+    from ingot_b200.gpu import Buffer
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+    def all_reduce(buf: Buffer, n: int):
+        dist.all_reduce(_tensor_view(torch, buf.ptr, n, local))
+
+    s = QWEN3_30B_A3B
+    peaks, peak_src = measured_peaks()
+    results = []
+    chain = MoeChain(gpu, s, tokens=max(args.tokens), seed=0, rank=rank, world=world, all_reduce=all_reduce if world > 1 else None,
+                     layers=args.layers, local_weights_only=True)
+    for tokens in args.tokens:
+        chain.tokens = tokens               # the buffers are sized for the largest count
+        rng = np.random.default_rng(100 + tokens)
+        logits = rng.normal(0, 1, (tokens, s.experts)).astype(np.float32)
+        x = rng.normal(0, 1, (tokens, s.hidden)).astype(np.float32)
+        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.logits.ptr, logits.ctypes.data, logits.nbytes))
+        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.x.ptr, x.ctypes.data, x.nbytes))
+        gpu.complete()
+        graph, tgraph = None, None
+        if world == 1:
+            chain.step()
+            gpu.complete()
+            graph = chain.record()
+        else:
+            for _ in range(2):
+                chain.step()
+            torch.cuda.synchronize()
+            dist.barrier()
+            tgraph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(tgraph, stream=stream, capture_error_mode="thread_local"):
+                chain.step()
+
+        def one_step():
+            if graph is not None:
+                graph.submit()
+            else:
+                tgraph.replay()
+
+        for _ in range(args.warmup):
+            one_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            one_step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        if world > 1:
+            t = torch.tensor([ms], device=f"cuda:{local}")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        ids = gpu.read_bytes(chain.ids).view(np.uint32)[:tokens * s.top]
+        unique = int(len(np.unique(ids)))
+        algo = chain.n_layers * unique * expert_bytes(s)        # every layer routes the same synthetic logits
+        results.append({"tokens": tokens, "ms_per_step": ms, "tok_per_s": tokens * 1000.0 / ms, "unique_experts": unique,
+                        "expert_bytes_per_step": algo, "gbs": algo / (ms * 1e-3) / 1e9,
+                        "frac_of_hbm_peak": algo / (ms * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world),
+                        "launches_per_step": chain.launches_per_step})
+        del graph, tgraph
+    if rank == 0:
+        head = results[0]
+        print(json.dumps({"metric": "decode tok/s, Qwen3-30B-A3B shape (expert-routed Q4_K GEMV chain)", "value": head["tok_per_s"],
+                          "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": "qwen3-30b-a3b expert-routed FFN chain (configs[3]), tokens %s" % args.tokens,
+                                     "layers": args.layers or s.layers, "experts": s.experts, "top": s.top,
+                                     "parallelism": "ep%d" % world if world > 1 else "single GPU",
+                                     "peak_source": peak_src},
+                          "by_tokens": results}), flush=True)
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
+    gpu.close()
+
 
 def run_gemm(torch, gpu, stream, args):
     """The batched prefill dequant-GEMM: Q4_K 4096 -> 12288 and Q6_K 12288 -> 4096 against bf16
@@ -448,6 +546,11 @@ def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e-3 / (reps * len(chain.weights))
 
+    if chain.packed:        # the packed rows the timed launches read (the fused step does not write them)
+        chain._norm(chain.h_in, None, None, chain.xn, s.hidden)
+        chain._norm(chain.q, None, None, chain.a, s.q)
+        chain._norm(chain.act, None, None, chain.actn, s.ffn)
+        gpu.complete()
     xd = None
     if digits:      # the tcgen05 int8 GEMV reads activations as digit rows (Q4_K weights)
         from ingot_b200 import X_DIGITS
@@ -458,10 +561,18 @@ def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps
             return xd.ptr, X_DIGITS
         return chain._x(x)
 
+    # with the norms fused, a projection reads the fp32 vector its norm would read
+    fp32_of = {id(chain.xn): chain.h_in, id(chain.a): chain.q, id(chain.actn): chain.act}
+    rb = int(chain.x_kind != 0)
+
     def proj(role, x, y):
         def fn(i):
             w = chain.weights[i][role]
             t = w.t
+            if chain.fused_norm and xd is None:
+                gpu._check(lib.ingot_matmul_normed(h, w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, fp32_of[id(x)].ptr,
+                                                   None, None, None, 1e-6, 0, rb, y.ptr))
+                return
             xp, xk = x_of(x, t.kind)
             gpu._check(lib.ingot_matmul(h, w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, xp, xk, b, y.ptr))
         return fn
@@ -469,28 +580,39 @@ def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps
     def gate_up(i):
         g, u = chain.weights[i]["gate"], chain.weights[i]["up"]
         t = g.t
+        if chain.fused_norm and xd is None:
+            gpu._check(lib.ingot_gate_up_normed(h, g.buffer.ptr, u.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind,
+                                                chain.h_in.ptr, None, None, None, 1e-6, 0, rb, int(s.gelu), chain.act.ptr))
+            return
         xp, xk = x_of(chain.xn, t.kind)
-        gpu._check(lib.ingot_gate_up(h, g.buffer.ptr, u.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, xp, xk, b, 0,
+        gpu._check(lib.ingot_gate_up(h, g.buffer.ptr, u.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, xp, xk, b, int(s.gelu),
                                      chain.act.ptr))
 
     out = {}
     reps = reps or max(1, 144 // max(len(chain.weights), 1))
-    cases = [("gate_up_q4k", gate_up, 2 * s.ffn * synth.stride_of(s.kinds["gate"], s.hidden), s.hidden, s.ffn),
-             ("down_q6k", proj("down", chain.actn, chain.d), s.hidden * synth.stride_of(s.kinds["down"], s.ffn), s.ffn, s.hidden),
-             ("q_q4k", proj("q", chain.xn, chain.q), s.q * synth.stride_of(s.kinds["q"], s.hidden), s.hidden, s.q),
-             ("k_q4k", proj("k", chain.xn, chain.k), s.kv * synth.stride_of(s.kinds["k"], s.hidden), s.hidden, s.kv),
-             ("v_q6k", proj("v", chain.xn, chain.v), s.kv * synth.stride_of(s.kinds["v"], s.hidden), s.hidden, s.kv)]
+    kn = {synth.Q4_K: "q4k", synth.Q6_K: "q6k", synth.Q4_0: "q4_0", synth.Q8_0: "q8_0"}
+    k = s.kinds
+    cases = [("gate_up_" + kn[k["gate"]], gate_up, 2 * s.ffn * synth.stride_of(k["gate"], s.hidden), s.hidden, s.ffn),
+             ("down_" + kn[k["down"]], proj("down", chain.actn, chain.d), s.hidden * synth.stride_of(k["down"], s.ffn), s.ffn, s.hidden),
+             ("q_" + kn[k["q"]], proj("q", chain.xn, chain.q), s.q * synth.stride_of(k["q"], s.hidden), s.hidden, s.q),
+             ("k_" + kn[k["k"]], proj("k", chain.xn, chain.k), s.kv * synth.stride_of(k["k"], s.hidden), s.hidden, s.kv),
+             ("v_" + kn[k["v"]], proj("v", chain.xn, chain.v), s.kv * synth.stride_of(k["v"], s.hidden), s.hidden, s.kv)]
+    head_name = "head_" + kn[k["head"]]
     for name, fn, wbytes, cols, rows in cases:
         if only and name != only:
             continue
         sec = timed(fn, reps)
         algo = wbytes + b * cols * xb + b * rows * 4
         out[name] = {"us": sec * 1e6, "bytes": algo, "gbs": algo / sec / 1e9, "frac": algo / sec / 1e9 / peaks["hbm_gbs"]}
-    if only and only != "head_q6k":
+    if only and only != head_name:
         return None, out
     # the head: one matrix of 510 MB, far larger than L2 on its own
     t = chain.head.t
     def head(i):
+        if chain.fused_norm and xd is None:
+            gpu._check(lib.ingot_matmul_normed(h, chain.head.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, chain.h_in.ptr,
+                                               None, None, None, 1e-6, 0, rb, chain.logits.ptr))
+            return
         xp, xk = chain._x(chain.xn)
         gpu._check(lib.ingot_matmul(h, chain.head.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, xp, xk, b,
                                     chain.logits.ptr))
@@ -505,13 +627,14 @@ def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps
     torch.cuda.synchronize()
     sec = e0.elapsed_time(e1) * 1e-3 / 8
     algo = t.dims[1] * t.stride + b * t.dims[0] * xb + b * t.dims[1] * 4
-    out["head_q6k"] = {"us": sec * 1e6, "bytes": algo, "gbs": algo / sec / 1e9, "frac": algo / sec / 1e9 / peaks["hbm_gbs"]}
+    out[head_name] = {"us": sec * 1e6, "bytes": algo, "gbs": algo / sec / 1e9, "frac": algo / sec / 1e9 / peaks["hbm_gbs"]}
     if only:
         return None, out
-    g = out["gate_up_q4k"]
-    roof = {"bound": "hbm", "kernel": "gemv_stream_kernel<Q4_K, 1 token, gate+up fused> 4096 -> 2 x 12288",
+    gname = "gate_up_" + kn[k["gate"]]
+    g = out[gname]
+    roof = {"bound": "hbm", "kernel": "gemv_mma_kernel<%s, 1 token, gate+up fused> %d -> 2 x %d" % (kn[k["gate"]], s.hidden, s.ffn),
             "achieved": g["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": g["frac"], "peak_source": peak_src,
-            "bytes_per_launch": g["bytes"], "us_per_launch": g["us"], "traffic": ncu_traffic("gate_up_q4k")}
+            "bytes_per_launch": g["bytes"], "us_per_launch": g["us"], "traffic": ncu_traffic(gname)}
     return roof, out
 
 

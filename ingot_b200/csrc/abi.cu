@@ -25,6 +25,7 @@ struct ingot_gpu {
     size_t workspace_bytes = 0;
     void *tc_scratch = nullptr;       // tile counters and partial rows of the tcgen05 GEMV
     bool use_tc = false;
+    uint32_t ep_world = 1;
     uint32_t sm_count = 0;
     bool failed = false;              // sticky device failure
     bool pdl = true;
@@ -97,6 +98,7 @@ LaunchCtx ctx_of(ingot_gpu *g) {
     c.workspace = g->workspace;
     c.workspace_bytes = g->workspace_bytes;
     c.use_tc = g->use_tc;
+    c.ep_world = g->ep_world;
     c.tc_scratch = g->tc_scratch;
     c.tc_scratch_bytes = TC_SCRATCH_BYTES;
     if (g->in_scope) {            // concurrent launches must not share the handle's scratch areas
@@ -216,6 +218,7 @@ ingot_status ingot_gpu_set_option(ingot_gpu *g, int32_t option, int32_t value) {
     case INGOT_OPT_FORCE_PLAIN: g->force_plain = value != 0; return INGOT_OK;
     case INGOT_OPT_NO_MMA: g->no_mma = value != 0; return INGOT_OK;
     case INGOT_OPT_TCGEN05_GEMV: g->use_tc = value != 0; return INGOT_OK;
+    case INGOT_OPT_EP_WORLD: g->ep_world = value > 1 ? (uint32_t)value : 1u; return INGOT_OK;
     default: return fail(g, INGOT_INVALID, "unknown option");
     }
 }

@@ -7,15 +7,16 @@
 // to the same expectation (f64 dot of F16-rounded operands, src/expert_bench.rs:734-749).
 //
 // One CTA computes a 128 (weight rows) x 256 (tokens) tile of Y^T.  Per 64-column K step:
-//   * four warps decode one weight row each — the fp32 value d*sc*q - dmin*m (Q4_K) or
-//     d*scale*(q-32) (Q6_K) exactly as weight_at forms it, rounded to binary16 — and store
-//     the 128 x 64 tile K-major with the 128-byte swizzle the tensor core expects;
+//   * eight warps decode half a weight row each (32 columns) — the fp32 value d*sc*q - dmin*m
+//     (Q4_K) or d*scale*(q-32) (Q6_K) exactly as weight_at forms it, rounded to binary16 — and
+//     store the 128 x 64 tile K-major with the 128-byte swizzle the tensor core expects;
 //   * two warps bring the 256 x 64 activation tile (already binary16) with 16-byte
 //     cp.async into the same swizzled layout;
 //   * one thread issues four tcgen05.mma (M 128, N 256, K 16) accumulating in tensor
 //     memory (256 columns x 128 lanes of fp32), and a tcgen05.commit frees the stage.
-// After the last step the four decode warps read the accumulator with tcgen05.ld and write
-// Y (token-major) with coalesced stores.  Every wait is bounded.
+// After the last step the eight decode warps read the accumulator with tcgen05.ld (each warp
+// its 32 lanes and half of the token columns) and write Y (token-major) with coalesced stores.
+// Every wait is bounded.
 #include <cuda_fp16.h>
 
 #include "dev_common.cuh"
@@ -32,7 +33,8 @@ static constexpr uint32_t GEMM_STAGES = 4;
 static constexpr uint32_t GEMM_A_BYTES = GEMM_M * GEMM_K * 2;       // 16 KB
 static constexpr uint32_t GEMM_B_BYTES = GEMM_N * GEMM_K * 2;       // 32 KB
 static constexpr uint32_t GEMM_STAGE_BYTES = GEMM_A_BYTES + GEMM_B_BYTES;
-static constexpr uint32_t GEMM_THREADS = 224;    // 4 decode/epilogue warps, 2 activation warps, 1 MMA warp
+static constexpr uint32_t GEMM_DECODE_THREADS = 256;    // 8 decode/epilogue warps
+static constexpr uint32_t GEMM_THREADS = 352;    // + 2 activation warps, 1 MMA warp
 static constexpr uint32_t GEMM_SMEM = 1024 + GEMM_STAGES * GEMM_STAGE_BYTES + 1024;   // + alignment slack
 
 struct GemmArgs {
@@ -108,66 +110,96 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-// ---- decoding 64 consecutive weights of one row into a swizzled tile row ------------------
+// ---- decoding 32 consecutive weights of one row into half a swizzled tile row ----------------
+// Split in two: `load` brings the raw bytes of a step into registers (issued one step ahead, so the
+// global-memory latency overlaps the previous step's arithmetic), `emit` decodes and stores.
 
-// Q4_K: K step ks covers group j = ks % 4 of block ks / 4: 32 bytes, low nibbles = sub-block 2j
-// (columns 0..31 of the step), high nibbles = sub-block 2j+1 (columns 32..63).
-__device__ __forceinline__ void decode64_q4k(const uint8_t *row, uint32_t ks, uint8_t *dst_row_base, uint32_t r) {
+struct GemmRaw {
+    uint32_t w[18];
+};
+
+// Q4_K: K step ks covers group j = ks % 4 of block ks / 4: 32 bytes whose low nibbles are sub-block
+// 2j (columns 0..31 of the step, half 0) and whose high nibbles are sub-block 2j+1 (columns 32..63,
+// half 1).  Raw: header (4 words), quants (8 words).
+__device__ __forceinline__ void load32_q4k(const uint8_t *row, uint32_t ks, GemmRaw &raw) {
     const uint8_t *b = row + (size_t)(ks >> 2) * 144u;
     const uint32_t j = ks & 3u;
     const uint4 hdr = *reinterpret_cast<const uint4 *>(b);
-    uint32_t sc0, m0, sc1, m1;
-    const uint8_t *s = reinterpret_cast<const uint8_t *>(&hdr) + 4;
-    q4k_scale_min(s, 2 * j, sc0, m0);
-    q4k_scale_min(s, 2 * j + 1, sc1, m1);
-    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-    const float ds0 = __fmul_rn(dd.x, (float)sc0), ds1 = __fmul_rn(dd.x, (float)sc1);
-    const float c0 = __fmul_rn(dd.y, (float)m0), c1 = __fmul_rn(dd.y, (float)m1);
     const uint4 q0 = *reinterpret_cast<const uint4 *>(b + 16u + 32u * j);
     const uint4 q1 = *reinterpret_cast<const uint4 *>(b + 32u + 32u * j);
-    const uint32_t qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    raw.w[0] = hdr.x; raw.w[1] = hdr.y; raw.w[2] = hdr.z; raw.w[3] = hdr.w;
+    raw.w[4] = q0.x; raw.w[5] = q0.y; raw.w[6] = q0.z; raw.w[7] = q0.w;
+    raw.w[8] = q1.x; raw.w[9] = q1.y; raw.w[10] = q1.z; raw.w[11] = q1.w;
+}
+__device__ __forceinline__ void emit32_q4k(const GemmRaw &raw, uint32_t ks, uint32_t half, uint8_t *dst_row_base, uint32_t r) {
+    const uint32_t sb = 2u * (ks & 3u) + half;
+    // six-bit (scale, min) of sub-block sb (get_scale_min_k4): words 1, 2, 3 = scale bytes 0..3, 4..7, 8..11
+    uint32_t sc, mn;
+    if (sb < 4u) {
+        sc = (raw.w[1] >> (8u * sb)) & 63u;
+        mn = (raw.w[2] >> (8u * sb)) & 63u;
+    } else {
+        const uint32_t hi = (raw.w[3] >> (8u * (sb - 4u))) & 0xffu;
+        sc = (hi & 15u) | ((((raw.w[1] >> (8u * (sb - 4u))) >> 6) & 3u) << 4);
+        mn = (hi >> 4) | ((((raw.w[2] >> (8u * (sb - 4u))) >> 6) & 3u) << 4);
+    }
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&raw.w[0]));
+    const float ds = __fmul_rn(dd.x, (float)sc), c = __fmul_rn(dd.y, (float)mn);
+    const uint32_t sh = 4u * half;
 #pragma unroll
-    for (uint32_t c = 0; c < 4; ++c) {           // 16-byte chunk c: columns 8c..8c+7 (low), 32+8c.. (high)
-        uint32_t lo[4], hi[4];
+    for (uint32_t ch = 0; ch < 4; ++ch) {           // 16-byte chunk: 8 columns = bytes 8 ch .. 8 ch + 7 of the group
+        uint32_t out[4];
 #pragma unroll
         for (uint32_t i = 0; i < 2; ++i) {
-            const uint32_t wq = qs[2 * c + i];
-#pragma unroll
-            for (uint32_t e = 0; e < 2; ++e) {
-                const float a0 = (float)((wq >> (16 * e)) & 15u), a1 = (float)((wq >> (16 * e + 8)) & 15u);
-                const float b0 = (float)((wq >> (16 * e + 4)) & 15u), b1 = (float)((wq >> (16 * e + 12)) & 15u);
-                lo[2 * i + e] = pack_h2(__fsub_rn(__fmul_rn(ds0, a0), c0), __fsub_rn(__fmul_rn(ds0, a1), c0));
-                hi[2 * i + e] = pack_h2(__fsub_rn(__fmul_rn(ds1, b0), c1), __fsub_rn(__fmul_rn(ds1, b1), c1));
-            }
+            const uint32_t wq = raw.w[4 + 2 * ch + i] >> sh;
+            const float a0 = (float)(wq & 15u), a1 = (float)((wq >> 8) & 15u), a2 = (float)((wq >> 16) & 15u), a3 = (float)((wq >> 24) & 15u);
+            out[2 * i] = pack_h2(__fsub_rn(__fmul_rn(ds, a0), c), __fsub_rn(__fmul_rn(ds, a1), c));
+            out[2 * i + 1] = pack_h2(__fsub_rn(__fmul_rn(ds, a2), c), __fsub_rn(__fmul_rn(ds, a3), c));
         }
-        *reinterpret_cast<uint4 *>(dst_row_base + swz_off(r, c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4 *>(dst_row_base + swz_off(r, 4u + c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4 *>(dst_row_base + swz_off(r, 4u * half + ch)) = make_uint4(out[0], out[1], out[2], out[3]);
     }
 }
 
-// Q6_K: K step ks covers half n = (ks % 4) / 2 of block ks / 4 and quarters q0 = 2 * (ks % 2), q0 + 1.
-__device__ __forceinline__ void decode64_q6k(const uint8_t *row, uint32_t ks, uint8_t *dst_row_base, uint32_t r) {
+// 32-bit word at a 2-byte aligned global address
+__device__ __forceinline__ uint32_t ldg32_u2(const uint8_t *p) {
+    const unsigned short *h = reinterpret_cast<const unsigned short *>(p);
+    return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+}
+
+// Q6_K: K step ks covers half n = (ks % 4) / 2 of block ks / 4 and quarters 2 (ks % 2) and 2 (ks % 2) + 1;
+// this thread takes quarter q = 2 (ks % 2) + half: 32 columns, two runs of 16 with their own scale.
+// Raw: 8 words of ql, 8 words of qh, the two scale bytes, d.
+__device__ __forceinline__ void load32_q6k(const uint8_t *row, uint32_t ks, uint32_t half, GemmRaw &raw) {
     const uint8_t *b = row + (size_t)(ks >> 2) * 210u;
-    const uint32_t n = (ks >> 1) & 1u, q0 = 2u * (ks & 1u);
-    const float d = __half2float(*reinterpret_cast<const __half *>(b + 208));
+    const uint32_t n = (ks >> 1) & 1u, q = 2u * (ks & 1u) + half;
+    const uint8_t *ql = b + 64u * n + 32u * (q & 1u), *qh = b + 128u + 32u * n;
 #pragma unroll
-    for (uint32_t qq = 0; qq < 2; ++qq) {
-        const uint32_t q = q0 + qq;
-        const uint8_t *ql = b + 64u * n + 32u * (q & 1u), *qh = b + 128u + 32u * n;
+    for (uint32_t i = 0; i < 8; ++i) {
+        raw.w[i] = ldg32_u2(ql + 4u * i);
+        raw.w[8 + i] = ldg32_u2(qh + 4u * i);
+    }
+    raw.w[16] = *reinterpret_cast<const unsigned short *>(b + 192u + 8u * n + 2u * q);
+    raw.w[17] = *reinterpret_cast<const unsigned short *>(b + 208u);
+}
+__device__ __forceinline__ void emit32_q6k(const GemmRaw &raw, uint32_t ks, uint32_t half, uint8_t *dst_row_base, uint32_t r) {
+    const uint32_t q = 2u * (ks & 1u) + half;
+    const float d = __half2float(__ushort_as_half((unsigned short)raw.w[17]));
+    const uint32_t lsh = q >= 2u ? 4u : 0u, hsh = 2u * q;
+    const float ds0 = __fmul_rn(d, (float)(int)(int8_t)(raw.w[16] & 0xffu)), ds1 = __fmul_rn(d, (float)(int)(int8_t)(raw.w[16] >> 8));
 #pragma unroll
-        for (uint32_t c = 0; c < 4; ++c) {       // columns 32 qq + 8c .. + 7  (l = 8c .. 8c + 7)
-            const int scale = (int)(int8_t)b[192u + 8u * n + 2u * q + (c >> 1)];
-            const float ds = __fmul_rn(d, (float)scale);
-            uint32_t out[4];
+    for (uint32_t ch = 0; ch < 4; ++ch) {           // columns 8 ch .. 8 ch + 7 of the quarter
+        const float ds = ch < 2 ? ds0 : ds1;
+        uint32_t out[4];
 #pragma unroll
-            for (uint32_t e = 0; e < 4; ++e) {
-                const uint32_t l = 8u * c + 2u * e;
-                const uint32_t v0 = (((uint32_t)ql[l] >> (q >= 2 ? 4 : 0)) & 15u) | ((((uint32_t)qh[l] >> (2 * q)) & 3u) << 4);
-                const uint32_t v1 = (((uint32_t)ql[l + 1] >> (q >= 2 ? 4 : 0)) & 15u) | ((((uint32_t)qh[l + 1] >> (2 * q)) & 3u) << 4);
-                out[e] = pack_h2(__fmul_rn(ds, (float)((int)v0 - 32)), __fmul_rn(ds, (float)((int)v1 - 32)));
-            }
-            *reinterpret_cast<uint4 *>(dst_row_base + swz_off(r, 4u * qq + c)) = make_uint4(out[0], out[1], out[2], out[3]);
+        for (uint32_t i = 0; i < 2; ++i) {
+            const uint32_t lw = raw.w[2 * ch + i], hw = raw.w[8 + 2 * ch + i];
+            const uint32_t v = ((lw >> lsh) & 0x0f0f0f0fu) | (((hw >> hsh) & 0x03030303u) << 4);     // four 6-bit values
+            const float a0 = __fsub_rn((float)(v & 0xffu), 32.0f), a1 = __fsub_rn((float)((v >> 8) & 0xffu), 32.0f);
+            const float a2 = __fsub_rn((float)((v >> 16) & 0xffu), 32.0f), a3 = __fsub_rn((float)(v >> 24), 32.0f);
+            out[2 * i] = pack_h2(__fmul_rn(ds, a0), __fmul_rn(ds, a1));
+            out[2 * i + 1] = pack_h2(__fmul_rn(ds, a2), __fmul_rn(ds, a3));
         }
+        *reinterpret_cast<uint4 *>(dst_row_base + swz_off(r, 4u * half + ch)) = make_uint4(out[0], out[1], out[2], out[3]);
     }
 }
 
@@ -188,14 +220,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < GEMM_STAGES; ++s) {
-            ptx::mbar_init(&full_a[s], 128);
+            ptx::mbar_init(&full_a[s], GEMM_DECODE_THREADS);
             ptx::mbar_init(&full_b[s], 64);
             ptx::mbar_init(&empty[s], 1);
         }
         ptx::mbar_init(acc_full, 1);
         ptx::mbar_init_fence();
     }
-    if (warp == 6) tmem_alloc(tmem_slot, GEMM_N);
+    if (warp == 10) tmem_alloc(tmem_slot, GEMM_N);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -204,34 +236,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
     ptx::pdl_wait();
 
     bool failed = false;
-    if (warp < 4) {
-        // ---- decode warps: one weight row per thread ----
-        const uint32_t r = threadIdx.x;                               // row inside the tile = TMEM lane
+    if (warp < 8) {
+        // ---- decode warps: half a weight row (32 columns of the step) per thread ----
+        const uint32_t r = threadIdx.x & 127u, half = threadIdx.x >> 7;   // row inside the tile = TMEM lane
         const bool live = n0 + r < a.rows;
         const uint8_t *row = a.w + (size_t)(live ? n0 + r : 0) * a.stride;
+        const bool q4k = a.kind == KIND_Q4_K;
+        GemmRaw cur = {}, nxt = {};
+        if (live) { if (q4k) load32_q4k(row, 0, cur); else load32_q6k(row, 0, half, cur); }
         for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
             const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
+            if (live && ks + 1 < ksteps) { if (q4k) load32_q4k(row, ks + 1, nxt); else load32_q6k(row, ks + 1, half, nxt); }
             if (!ptx::mbar_wait_sleep<20>(&empty[s], ph ^ 1u)) { failed = true; break; }
             uint8_t *dst = tiles + (size_t)s * GEMM_STAGE_BYTES;
             if (live) {
-                if (a.kind == KIND_Q4_K) decode64_q4k(row, ks, dst, r);
-                else decode64_q6k(row, ks, dst, r);
+                if (q4k) emit32_q4k(cur, ks, half, dst, r);
+                else emit32_q6k(cur, ks, half, dst, r);
             } else {
 #pragma unroll
-                for (uint32_t c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(dst + swz_off(r, c)) = make_uint4(0, 0, 0, 0);
+                for (uint32_t c = 0; c < 4; ++c) *reinterpret_cast<uint4 *>(dst + swz_off(r, 4u * half + c)) = make_uint4(0, 0, 0, 0);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> tensor core reads
             ptx::mbar_arrive(&full_a[s]);
+            cur = nxt;
         }
-        // ---- epilogue: this warp reads TMEM lanes 32 * warp .. + 31 ----
+        // ---- epilogue: this warp reads TMEM lanes 32 * (warp % 4) .. + 31 and half of the token columns ----
         if (!failed && !ptx::mbar_wait_sleep<64>(acc_full, 0)) failed = true;
         if (!failed) {
             tc_fence_after();
             const uint32_t rowg = n0 + r;
 #pragma unroll 1
-            for (uint32_t c0 = 0; c0 < GEMM_N; c0 += 32) {
+            for (uint32_t c0 = half * (GEMM_N / 2u); c0 < (half + 1u) * (GEMM_N / 2u); c0 += 32) {
                 float v[32];
-                tmem_ld32(tmem_base + ((warp * 32u) << 16) + c0, v);
+                tmem_ld32(tmem_base + (((warp & 3u) * 32u) << 16) + c0, v);
                 if (rowg < a.rows) {
 #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) {
@@ -241,9 +278,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
                 }
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 10) {
         // ---- activation warps: 256 tokens x 64 columns of binary16 per stage, 16 bytes per cp.async ----
-        const uint32_t tid = threadIdx.x - 128u;                       // 0..63
+        const uint32_t tid = threadIdx.x - GEMM_DECODE_THREADS;        // 0..63
         for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
             const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
             if (!ptx::mbar_wait_sleep<20>(&empty[s], ph ^ 1u)) { failed = true; break; }
@@ -281,7 +318,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
     if (failed && lane == 0) set_status_word(a.status, KERNEL_ERR_GEMM_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == 6) tmem_dealloc(tmem_base, GEMM_N);
+    if (warp == 10) tmem_dealloc(tmem_base, GEMM_N);
 }
 
 // ---- activations -> binary16 ------------------------------------------------------------

@@ -161,6 +161,8 @@ IG_HD void consume_chunk(const uint8_t *stage, const F4 *xs, const GemvPlan &p, 
 // pairs in B-operand order, fp32 sums of each 16 columns, and 16 bytes holding
 // 1/scale.  cols must be a multiple of 64.
 IG_HD uint32_t packed_x_bytes(uint32_t cols) { return cols * 4u + cols / 4u + 16u; }
+// The same holding only the high binary16 part (bfloat16 activations).
+IG_HD uint32_t packed_hi_bytes(uint32_t cols) { return cols * 2u + cols / 4u + 16u; }
 
 // Bytes of one activation row as base-256 digits for the int8 tensor-core GEMV: the
 // N = 8 operand image (8 bytes per column), fp32 sums of each 16 columns, 16 bytes

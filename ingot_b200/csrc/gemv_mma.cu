@@ -69,6 +69,7 @@ struct MmaPlan {
     uint32_t red_bytes, smem_bytes;
     uint32_t ctas;
     uint32_t red_slots;      // ring of partial-sum buffers, > stages
+    uint32_t hi_only;        // the packed row holds only the high binary16 part (bfloat16 activations are exact in it)
 };
 
 struct MmaArgs {
@@ -101,7 +102,7 @@ static void step_geometry(uint32_t kind, uint32_t &cols, uint32_t &bytes) {
 static uint32_t pitch_of(uint32_t chunk_bytes) { return chunk_bytes + ((16u + 128u - (chunk_bytes % 128u)) % 128u); }
 
 static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t nmat, uint32_t max_ctas,
-                     uint32_t budget, MmaPlan &p) {
+                     uint32_t budget, bool hi_only, MmaPlan &p) {
     if (!mma_kind(kind)) return false;
     uint32_t block, bytes;
     geometry(kind, block, bytes);
@@ -115,7 +116,8 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     p.kw_log2 = kw;
     p.row_tiles = (uint32_t)MMA_WARPS >> kw;
     const uint32_t per_warp = p.nsteps >> kw;                 // steps each warp owns per row
-    p.x_bytes = packed_x_bytes(cols);
+    p.hi_only = hi_only;
+    p.x_bytes = hi_only ? packed_hi_bytes(cols) : packed_x_bytes(cols);
     p.red_slots = budget <= MMA_SMEM_SMALL ? 4u : MMA_RED_SLOTS;
     p.red_bytes = p.red_slots * MMA_WARPS * 2u * 16u * 4u + MMA_ZERO_BYTES;   // [slot][warp][mat][row] + zeros
     const uint32_t fixed = MMA_BAR_BYTES + ((p.x_bytes + 127u) & ~127u) + p.red_bytes;
@@ -254,7 +256,7 @@ __device__ __forceinline__ uint32_t lds16(const uint8_t *p) { return *reinterpre
 // zeros.  A group's MMAs therefore add to the accumulator only in the lane that owns
 // it, so all groups of a step chain into the same accumulator registers and each lane
 // applies its own group's scale once, without selects.
-#define IG_BFRAG(grp, mi) (*reinterpret_cast<const uint2 *>(xb[grp] + (mi) * 64u))
+#define IG_BFRAG(grp, mi) (*reinterpret_cast<const uint2 *>(xb[grp] + (mi) * XS))
 // A binary16 whose exponent field is zero is subnormal: its value is mantissa * 2^-24,
 // exactly, with no implicit one.  So the masked quant bits ARE the operand (times
 // 2^-24, undone in the scale); no bias to subtract.  The tensor cores take binary16
@@ -283,6 +285,7 @@ template <> struct MmaStep<KIND_Q4_K> {
         dm0 = mul_rn(dd.y, (float)(m & 0xffu));
         dm1 = mul_rn(dd.y, (float)(m >> 8));
     }
+    template <uint32_t XS>      // bytes of packed activations per MMA: 64 (high and low parts) or 32 (high part only)
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
                                                uint32_t t, float &acc0, float &acc1) {
         float s00, s01, m00, m01, s10, s11, m10, m11;
@@ -333,6 +336,7 @@ template <> struct MmaStep<KIND_Q6_K> {
         if (FIRST) mma16816_first(c, six<Q>(la, ha), six<Q>(lb, hb), six<Q>(la >> 8, ha >> 8), six<Q>(lb >> 8, hb >> 8), bf.x, bf.y);
         else mma16816(c, six<Q>(la, ha), six<Q>(lb, hb), six<Q>(la >> 8, ha >> 8), six<Q>(lb >> 8, hb >> 8), bf.x, bf.y);
     }
+    template <uint32_t XS>      // bytes of packed activations per MMA: 64 (high and low parts) or 32 (high part only)
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
                                                uint32_t t, float &acc0, float &acc1) {
         const float d0 = lds_half(r0 + 208u), d1 = lds_half(r1 + 208u);
@@ -368,6 +372,7 @@ template <> struct MmaStep<KIND_Q6_K> {
 // low nibbles (elements 0..15), MMA 2b+1 its high nibbles (16..31).  Lane t owns
 // block b = t.
 template <> struct MmaStep<KIND_Q4_0> {
+    template <uint32_t XS>      // bytes of packed activations per MMA: 64 (high and low parts) or 32 (high part only)
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
                                                uint32_t t, float &acc0, float &acc1) {
         const float d0 = lds_half(r0 + 18u * t), d1 = lds_half(r1 + 18u * t);
@@ -398,6 +403,7 @@ template <> struct MmaStep<KIND_Q4_0> {
 // through the block's activation sum.
 template <> struct MmaStep<KIND_Q8_0> {
     static __device__ __forceinline__ uint32_t s8(uint32_t w) { return (w & 0x00ff00ffu) ^ 0x00800080u; }
+    template <uint32_t XS>      // bytes of packed activations per MMA: 64 (high and low parts) or 32 (high part only)
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
                                                uint32_t t, float &acc0, float &acc1) {
         const float d0 = lds_half(r0 + 34u * t), d1 = lds_half(r1 + 34u * t);
@@ -425,7 +431,7 @@ template <> struct MmaStep<KIND_Q8_0> {
 // kernel
 // ---------------------------------------------------------------------------
 
-template <uint32_t KIND, int NMAT, int OCC>
+template <uint32_t KIND, int NMAT, int OCC, bool HI>
 __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const MmaPlan &p = a.plan;
@@ -434,7 +440,8 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
     uint64_t *xbar = empty + MMA_MAX_STAGES;
     uint64_t *tbar = xbar + 1;                                   // [MMA_RED_SLOTS]
     uint8_t *xrow = smem + MMA_BAR_BYTES;
-    const float *sx = reinterpret_cast<const float *>(xrow + (size_t)p.cols * 4u);
+    constexpr uint32_t XB = HI ? 2u : 4u;                 // packed bytes per activation
+    const float *sx = reinterpret_cast<const float *>(xrow + (size_t)p.cols * XB);
     float *red = reinterpret_cast<float *>(xrow + ((p.x_bytes + 127u) & ~127u));
     uint8_t *zeros = reinterpret_cast<uint8_t *>(red) + p.red_bytes - MMA_ZERO_BYTES;
     uint8_t *stages = reinterpret_cast<uint8_t *>(red) + p.red_bytes;
@@ -591,9 +598,10 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
                 if (i * NT >= n4) break;                               // uniform: the quad shuffles keep all lanes
                 const uint32_t j = tid + i * NT;
                 float u[4] = {v[i].x * scale, v[i].y * scale, v[i].z * scale, v[i].w * scale};
-                pack_store_quad(xrow, p.cols, j, u, j < n4);
+                if (HI) pack_hi_store_quad(xrow, p.cols, j, u, j < n4);
+                else pack_store_quad(xrow, p.cols, j, u, j < n4);
             }
-            if (tid == 0) pack_store_unscale(xrow, p.cols, scale);
+            if (tid == 0) { if (HI) pack_hi_store_unscale(xrow, p.cols, scale); else pack_store_unscale(xrow, p.cols, scale); }
         } else {
             float sum = 0.f;
             for (uint32_t j = tid; j < n4; j += NT) {
@@ -621,9 +629,10 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
 #pragma unroll
                     for (int k = 0; k < 4; ++k) u[k] *= scale;
                 }
-                pack_store_quad(xrow, p.cols, j, u, live);
+                if (HI) pack_hi_store_quad(xrow, p.cols, j, u, live);
+                else pack_store_quad(xrow, p.cols, j, u, live);
             }
-            if (tid == 0) pack_store_unscale(xrow, p.cols, scale);
+            if (tid == 0) { if (HI) pack_hi_store_unscale(xrow, p.cols, scale); else pack_store_unscale(xrow, p.cols, scale); }
         }
         ptx::named_bar_sync(1, MMA_WARPS * 32);
     } else if (!ptx::mbar_wait(xbar, 0)) {
@@ -631,19 +640,21 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
         return;
     }
     ptx::pdl_wait();          // outputs may be read by the previous kernel until it ends
-    const float unscale = *reinterpret_cast<const float *>(xrow + (size_t)p.cols * 4u + p.cols / 4u);
+    const float unscale = *reinterpret_cast<const float *>(xrow + (size_t)p.cols * XB + p.cols / 4u);
 
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t kw = warp & ((1u << p.kw_log2) - 1u), rt = warp >> p.kw_log2;
     constexpr uint32_t STEP_BYTES = KIND == KIND_Q4_K ? 144u : KIND == KIND_Q6_K ? 210u : KIND == KIND_Q4_0 ? 72u : 136u;
     constexpr uint32_t MMAS = (KIND == KIND_Q4_K || KIND == KIND_Q6_K) ? 16u : 8u;     // MMAs per step
+    constexpr uint32_t XS = HI ? 32u : 64u;                                             // packed bytes per MMA
     const uint32_t step_stride = STEP_BYTES << p.kw_log2;                               // this warp's next step
-    const uint32_t x_stride = (MMAS * 64u) << p.kw_log2, s_stride = MMAS << p.kw_log2;     // bytes, floats
+    const uint32_t x_stride = (MMAS * XS) << p.kw_log2, s_stride = MMAS << p.kw_log2;     // bytes, floats
     // B operands: column n = g of the MMA belongs to lane g; columns 2j, 2j+1 carry (xh, xl)
     // for group j only, so this lane reads the real activations for group own = g / 2 and
     // zeros for the others
-    const uint32_t own = g >> 1;
-    const uint8_t *xlane = xrow + ((g & 1u) * 4u + t) * 8u;
+    // (with only the high part packed, the low-part columns — odd g — always read zeros)
+    const uint32_t own = (HI && (g & 1u)) ? 4u : (g >> 1);
+    const uint8_t *xlane = xrow + (HI ? t : (g & 1u) * 4u + t) * 8u;
     const uint8_t *zlane = zeros + ((g & 1u) * 4u + t) * 8u;
     float *y = a.y + (a.ids ? (size_t)pair * p.rows : 0);
     const uint32_t kmask = (1u << p.kw_log2) - 1u;
@@ -696,12 +707,12 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
                 if (rt * 16u < nrows) {
                     const uint8_t *b0 = st + (size_t)ur0 * p.row_pitch + kw * STEP_BYTES;
                     const uint8_t *b1 = st + (size_t)ur1 * p.row_pitch + kw * STEP_BYTES;
-                    const uint8_t *xs = xlane + (size_t)gs0 * MMAS * 64u;
+                    const uint8_t *xs = xlane + (size_t)gs0 * MMAS * XS;
                     const float *ss = sx + gs0 * MMAS;
                     for (uint32_t i = 0; i < p.spw; ++i) {
                         const uint8_t *const xb[4] = {own == 0 ? xs : zlane, own == 1 ? xs : zlane, own == 2 ? xs : zlane,
                                                       own == 3 ? xs : zlane};
-                        MmaStep<KIND>::run(b0, b1, xb, ss, t, acc[m][0], acc[m][1]);
+                        MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1]);
                         b0 += step_stride; b1 += step_stride;
                         xs += x_stride; ss += s_stride;
                     }
@@ -733,9 +744,9 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
 // launch
 // ---------------------------------------------------------------------------
 
-template <uint32_t KIND, int NMAT, int OCC>
+template <uint32_t KIND, int NMAT, int OCC, bool HI>
 static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
-    auto kernel = gemv_mma_kernel<KIND, NMAT, OCC>;
+    auto kernel = gemv_mma_kernel<KIND, NMAT, OCC, HI>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -756,11 +767,15 @@ static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream
     return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
+template <uint32_t KIND, bool HI>
+static cudaError_t launch_mma_h(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl, int occ) {
+    if (occ == 3)
+        return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 3, HI>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 3, HI>(a, grid, stream, pdl);
+    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 2, HI>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 2, HI>(a, grid, stream, pdl);
+}
 template <uint32_t KIND>
 static cudaError_t launch_mma_k(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl, int occ) {
-    if (occ == 3)
-        return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 3>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 3>(a, grid, stream, pdl);
-    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 2>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 2>(a, grid, stream, pdl);
+    return a.plan.hi_only ? launch_mma_h<KIND, true>(a, grid, stream, pdl, occ) : launch_mma_h<KIND, false>(a, grid, stream, pdl, occ);
 }
 
 // True when this call was taken (launched or failed); false to let the caller use
@@ -771,19 +786,25 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     if (!routed && c.count != 1) return false;
     if (c.cols % 64u) return false;
     const uint32_t gy = routed ? c.pairs : 1u;
+    // CTAs per pair are sized for the pairs that are live on this device
+    const uint32_t ep = routed && ctx.ep_world > 1 ? ctx.ep_world : 1u;
+    const uint32_t gy_live = (gy + ep - 1) / ep;
+    // bfloat16 activations are exact in the high binary16 part alone: the fused norm with bfloat16
+    // rounding, and rows packed that way, carry no low part
+    const bool hi_only = c.norm_a ? c.norm_round_bf16 != 0 : c.x_packed == 4u;
     MmaPlan plan;
     int occ = 3;
-    uint32_t max_ctas = (3u * ctx.sm_count + gy - 1) / gy;
-    bool ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, plan);
+    uint32_t max_ctas = (3u * ctx.sm_count + gy_live - 1) / gy_live;
+    bool ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, hi_only, plan);
     if (!ok) {
         occ = 2;
-        max_ctas = (2u * ctx.sm_count + gy - 1) / gy;
+        max_ctas = (2u * ctx.sm_count + gy_live - 1) / gy_live;
         if (max_ctas < 1) max_ctas = 1;
-        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_BUDGET, plan);
+        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_BUDGET, hi_only, plan);
     }
     if (!ok) {
-        max_ctas = (ctx.sm_count + gy - 1) / gy;
-        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas ? max_ctas : 1, MMA_SMEM_MAX, plan);
+        max_ctas = (ctx.sm_count + gy_live - 1) / gy_live;
+        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas ? max_ctas : 1, MMA_SMEM_MAX, hi_only, plan);
     }
     if (!ok) return false;
     const uint8_t *xp = static_cast<const uint8_t *>(c.x);

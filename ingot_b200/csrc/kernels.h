@@ -24,6 +24,7 @@ struct LaunchCtx {
     bool no_mma;          // test hook: use the fp32 CUDA-core streaming kernel instead of the MMA one
     void *workspace;      // device scratch of the handle (packed activations)
     size_t workspace_bytes;
+    uint32_t ep_world;    // experts are split over this many devices: about pairs / ep_world routed pairs are live
     bool use_tc;          // one-token Q4_K GEMVs go to the tcgen05 int8 kernel
     void *tc_scratch;     // its tile counters (TC_COUNTER_BYTES, zero between launches) and partial rows
     size_t tc_scratch_bytes;

@@ -84,6 +84,24 @@ __device__ __forceinline__ void digits_store_unscale(uint8_t *row, uint32_t cols
     *reinterpret_cast<float *>(row + (size_t)cols * 8u + cols / 4u) = 1.0f / scale;
 }
 
+// The same without the low part (bfloat16 activations are exact in binary16): [cols/16 MMAs][4 lanes][4 halves],
+// then the sums and 1/scale: 2 * cols + cols / 4 + 16 bytes.
+__device__ __forceinline__ void pack_hi_store_quad(uint8_t *row, uint32_t cols, uint32_t q, const float (&v)[4], bool live) {
+    const uint32_t mi = q >> 2, t = q & 3u;
+    if (live) {
+        __half2 *dh = reinterpret_cast<__half2 *>(reinterpret_cast<__half *>(row) + (mi * 4u + t) * 4u);
+        dh[0] = __halves2half2(__float2half_rn(v[0]), __float2half_rn(v[2]));
+        dh[1] = __halves2half2(__float2half_rn(v[1]), __float2half_rn(v[3]));
+    }
+    float s = (v[0] + v[1]) + (v[2] + v[3]);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (live && t == 0) reinterpret_cast<float *>(row + (size_t)cols * 2u)[mi] = s;
+}
+__device__ __forceinline__ void pack_hi_store_unscale(uint8_t *row, uint32_t cols, float scale) {
+    *reinterpret_cast<float *>(row + (size_t)cols * 2u + cols / 4u) = 1.0f / scale;
+}
+
 __device__ __forceinline__ void pack_store_unscale(uint8_t *row, uint32_t cols, float scale) {
     *reinterpret_cast<float *>(row + (size_t)cols * 4u + cols / 4u) = 1.0f / scale;
 }

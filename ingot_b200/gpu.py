@@ -458,6 +458,53 @@ class Gpu:
                                                  m.kind, m.stride, out.ctypes.data))
         return out[: m.cols * m.rows * m.count]
 
+    def _ffn(self, matrices, x: Buffer) -> Buffer:
+        """Gpu::ffn (src/metal.rs:1634-1661): every stacked expert's SwiGLU FFN of the same input;
+        returns `count` rows of `down.rows` values."""
+        gate, up, down = matrices
+        if (gate.cols, gate.rows, gate.count) != (up.cols, up.rows, up.count) or \
+                (down.cols, down.rows, down.count) != (gate.rows, gate.cols, gate.count):
+            raise InvalidData("FFN matrix shapes do not match")
+        n = gate.rows * gate.count
+        bufs = [self.bytes(_as_u8(m.data)) for m in matrices]
+        # the stacked experts of gate and up are one tall matrix over the same input
+        g = self.matmul(None, bufs[0], gate.cols, n, gate.stride, gate.kind, 0, x, 1)
+        u = self.matmul(None, bufs[1], up.cols, n, up.stride, up.kind, 0, x, 1)
+        act = self.activation(None, g, u, n)
+        # down: expert e multiplies its own slice of the activation (one input row per pair)
+        ids = self.bytes(np.arange(gate.count, dtype=np.uint32).view(np.uint8))
+        out = self.output(down.rows * down.count)
+        self._check(self._lib.ingot_routed(self._h, bufs[2].ptr, down.cols, down.rows, down.stride, down.kind, down.count,
+                                           act.ptr, F32, ids.ptr, 1, 1, down.count, out.ptr))
+        return out
+
+    def moe(self, routed, shared, shared_gate: Matrix, x, weights) -> np.ndarray:
+        """Gpu::moe (src/metal.rs:1663-1713): the FFNs of the selected experts (stacked in `routed`, one
+        weight each) and of the shared expert, merged as sum_e w_e * routed_e + sigmoid(shared_gate . x) * shared."""
+        xv = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+        wv = np.ascontiguousarray(weights, dtype=np.float32).reshape(-1)
+        for m in list(routed) + list(shared) + [shared_gate]:
+            self._validate(m)
+        width = xv.size
+        if not (np.isfinite(xv).all() and np.isfinite(wv).all()) or routed[0].cols != width or shared[0].cols != width \
+                or shared[0].count != 1 or routed[0].count != wv.size \
+                or (shared_gate.cols, shared_gate.rows, shared_gate.count) != (width, 1, 1):
+            raise InvalidData("MoE input shape mismatch")
+        xb = self.floats(xv)
+        routed_out = self._ffn(routed, xb)
+        shared_out = self._ffn(shared, xb)
+        logit = self.matmul(None, self.bytes(_as_u8(shared_gate.data)), width, 1, shared_gate.stride, shared_gate.kind, 0, xb, 1)
+        y = self.merge(None, routed_out, shared_out, self.floats(wv), logit, width, routed[0].count)
+        return self.finish(None, y)
+
+    def _validate(self, m: Matrix) -> None:
+        """validate_matrix (src/metal.rs:1602-1621) through the library's own layout check."""
+        raw = _as_u8(m.data)
+        stride, total = C.c_uint64(), C.c_uint64()
+        st = self._lib.ingot_tensor_layout(m.kind, m.cols, m.rows, m.count, C.byref(stride), C.byref(total))
+        if st != _abi.OK or stride.value != m.stride or total.value != raw.size:
+            raise InvalidData("matrix layout does not match its data")
+
     def project(self, m: Matrix, x) -> np.ndarray:
         raw = _as_u8(m.data)
         xv = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)

@@ -51,10 +51,11 @@ class MoeChain:
     decode step for `tokens` tokens."""
 
     def __init__(self, gpu: Gpu, shape: MoeShape, tokens: int = 1, seed: int = 0, rank: int = 0, world: int = 1,
-                 all_reduce=None, layers: int | None = None, keep_host: bool = False):
+                 all_reduce=None, layers: int | None = None, keep_host: bool = False, local_weights_only: bool = False):
         self.gpu, self.shape, self.tokens = gpu, shape, tokens
         self.rank, self.world, self.all_reduce = rank, world, all_reduce
         self.n_layers = shape.layers if layers is None else layers
+        gpu.set_option(5, world)                  # INGOT_OPT_EP_WORLD: routed launches expect pairs / world live pairs
         self.first, end = expert_range(shape.experts, rank, world)
         self.local = end - self.first
         self.host = []
@@ -64,9 +65,14 @@ class MoeChain:
             mats = {}
             for i, (role, cols, rows) in enumerate((("gate", s.hidden, s.ffn), ("up", s.hidden, s.ffn),
                                                     ("down", s.ffn, s.hidden))):
-                raw = synth.random_matrix(s.kind, cols, rows, s.experts, seed=(seed * 7919 + layer * 8 + i) & 0x7FFFFFFF)
                 per = synth.stride_of(s.kind, cols) * rows
-                mine = raw[self.first * per:end * per]
+                if local_weights_only:      # throughput runs: draw only this rank's experts (not the same values for every world size)
+                    raw = None
+                    mine = synth.random_matrix(s.kind, cols, rows, self.local,
+                                               seed=(seed * 7919 + layer * 8 + i + 1000003 * rank) & 0x7FFFFFFF)
+                else:
+                    raw = synth.random_matrix(s.kind, cols, rows, s.experts, seed=(seed * 7919 + layer * 8 + i) & 0x7FFFFFFF)
+                    mine = raw[self.first * per:end * per]
                 t = Tensor.of([cols, rows, self.local], s.kind)
                 mats[role] = Weight(gpu.load_weight(mine, t), t)
                 if keep_host:

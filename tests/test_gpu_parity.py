@@ -617,3 +617,32 @@ def test_fused_and_unfused_chains_agree(gpu):
         del chain
     scale = float(np.sqrt(np.mean(np.square(logits[0]))))
     assert np.abs(logits[0] - logits[1]).max() <= 2e-2 * scale     # bfloat16 rounding points move with the sum order
+
+
+# ---- Gpu::moe (host-vector convenience) -------------------------------------------------------
+
+def test_moe_host_wrapper_matches_oracle(gpu):
+    # src/metal.rs:1663-1713: selected experts' FFNs + shared expert, merged with a sigmoid gate
+    width, ffn, top = 512, 256, 4
+    rng = np.random.default_rng(9)
+    mk = lambda kind, cols, rows, count, seed: Matrix.of(synth.random_matrix(kind, cols, rows, count, seed=seed), cols, rows, kind, count)
+    routed = [mk(Q4_K, width, ffn, top, 1), mk(Q4_K, width, ffn, top, 2), mk(Q4_K, ffn, width, top, 3)]
+    shared = [mk(Q4_K, width, ffn, 1, 4), mk(Q4_K, width, ffn, 1, 5), mk(Q4_K, ffn, width, 1, 6)]
+    gate = Matrix.of(rng.normal(0, 0.05, width).astype(np.float32).view(np.uint8), width, 1, F32)
+    x = (rng.normal(0, 1, width) / 64).astype(np.float32)
+    weights = np.array([0.4, 0.3, 0.2, 0.1], np.float32)
+    y = gpu.moe(routed, shared, gate, x, weights)
+
+    def expert_ffn(ms, e):
+        g = O.matvec_f64(ms[0].data, width, ffn, Q4_K, x.reshape(1, -1), expert=e)[0]
+        u = O.matvec_f64(ms[1].data, width, ffn, Q4_K, x.reshape(1, -1), expert=e)[0]
+        act = O.glu(g.astype(np.float32), u.astype(np.float32))
+        return O.matvec_f64(ms[2].data, ffn, width, Q4_K, act.reshape(1, -1), expert=e)[0]
+
+    routed_e = np.stack([expert_ffn(routed, e) for e in range(top)]).astype(np.float32)
+    shared_e = expert_ffn(shared, 0).astype(np.float32)
+    logit = float(np.dot(gate.data.view(np.float32).astype(np.float64), x.astype(np.float64)))
+    e = O.combine(routed_e, shared_e, weights, logit, width).astype(np.float64)
+    assert (np.abs(y - e) <= 4 * tol_ref_scaled(e)).all(), float(np.abs(y - e).max())
+    with pytest.raises(InvalidData):
+        gpu.moe(routed, shared, gate, x, weights[:3])
