@@ -10,8 +10,8 @@
 //   * eight warps decode half a weight row each (32 columns) — the fp32 value d*sc*q - dmin*m
 //     (Q4_K) or d*scale*(q-32) (Q6_K) exactly as weight_at forms it, rounded to binary16 — and
 //     store the 128 x 64 tile K-major with the 128-byte swizzle the tensor core expects;
-//   * two warps bring the 256 x 64 activation tile (already binary16) with 16-byte
-//     cp.async into the same swizzled layout;
+//   * one thread brings the 256 x 64 activation tile (already binary16) with one 2-D TMA
+//     copy whose tensor map applies the same 128-byte swizzle;
 //   * one thread issues four tcgen05.mma (M 128, N 256, K 16) accumulating in tensor
 //     memory (256 columns x 128 lanes of fp32), and a tcgen05.commit frees the stage.
 // After the last step the eight decode warps read the accumulator with tcgen05.ld (each warp
@@ -23,6 +23,7 @@
 #include "gemv_core.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
+#include "tensor_map.h"
 
 namespace ingot {
 
@@ -34,7 +35,7 @@ static constexpr uint32_t GEMM_A_BYTES = GEMM_M * GEMM_K * 2;       // 16 KB
 static constexpr uint32_t GEMM_B_BYTES = GEMM_N * GEMM_K * 2;       // 32 KB
 static constexpr uint32_t GEMM_STAGE_BYTES = GEMM_A_BYTES + GEMM_B_BYTES;
 static constexpr uint32_t GEMM_DECODE_THREADS = 256;    // 8 decode/epilogue warps
-static constexpr uint32_t GEMM_THREADS = 352;    // + 2 activation warps, 1 MMA warp
+static constexpr uint32_t GEMM_THREADS = 320;    // + 1 copy warp, 1 MMA warp
 static constexpr uint32_t GEMM_SMEM = 1024 + GEMM_STAGES * GEMM_STAGE_BYTES + 1024;   // + alignment slack
 
 struct GemmArgs {
@@ -203,7 +204,8 @@ __device__ __forceinline__ void emit32_q6k(const GemmRaw &raw, uint32_t ks, uint
     }
 }
 
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(const __grid_constant__ GemmArgs a) {
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                                               const __grid_constant__ GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern repeats every 1024 bytes)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
@@ -221,13 +223,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < GEMM_STAGES; ++s) {
             ptx::mbar_init(&full_a[s], GEMM_DECODE_THREADS);
-            ptx::mbar_init(&full_b[s], 64);
+            ptx::mbar_init(&full_b[s], 1);
             ptx::mbar_init(&empty[s], 1);
         }
         ptx::mbar_init(acc_full, 1);
         ptx::mbar_init_fence();
     }
-    if (warp == 10) tmem_alloc(tmem_slot, GEMM_N);
+    if (warp == 9) tmem_alloc(tmem_slot, GEMM_N);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -278,27 +280,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
                 }
             }
         }
-    } else if (warp < 10) {
-        // ---- activation warps: 256 tokens x 64 columns of binary16 per stage, 16 bytes per cp.async ----
-        const uint32_t tid = threadIdx.x - GEMM_DECODE_THREADS;        // 0..63
-        for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
-            const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
-            if (!ptx::mbar_wait_sleep<20>(&empty[s], ph ^ 1u)) { failed = true; break; }
-            uint8_t *dst = tiles + (size_t)s * GEMM_STAGE_BYTES + GEMM_A_BYTES;
-#pragma unroll 4
-            for (uint32_t i = tid; i < GEMM_N * 8u; i += 64u) {
-                const uint32_t tok = i >> 3, chunk = i & 7u;
-                const uint32_t t = t0 + tok;
-                const __half *src = a.x + (size_t)(t < a.tokens ? t : 0) * a.cols + (size_t)ks * GEMM_K + chunk * 8u;
-                const uint32_t bytes = t < a.tokens ? 16u : 0u;        // rows past the end are zero-filled
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ptx::smem_addr(dst + swz_off(tok, chunk))), "l"(src),
-                             "r"(bytes)
-                             : "memory");
+    } else if (warp == 8) {
+        // ---- copy thread: 256 tokens x 64 columns of binary16 per stage, one TMA copy (rows past the last
+        // token read as zero) ----
+        if (lane == 0) {
+            for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
+                const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
+                if (!ptx::mbar_wait_sleep<20>(&empty[s], ph ^ 1u)) { failed = true; break; }
+                uint8_t *dst = tiles + (size_t)s * GEMM_STAGE_BYTES + GEMM_A_BYTES;
+                ptx::mbar_expect_tx(&full_b[s], GEMM_B_BYTES);
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                    ::"r"(ptx::smem_addr(dst)), "l"(&xmap), "r"(ks * GEMM_K), "r"(t0), "r"(ptx::smem_addr(&full_b[s]))
+                    : "memory");
             }
-            // the barrier gets this thread's arrival when its copies above have landed
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(ptx::smem_addr(&full_b[s])) : "memory");
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (lane == 0) {
         // ---- MMA thread ----
         const uint32_t idesc = idesc_f16(GEMM_M, GEMM_N);
@@ -318,7 +314,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
     if (failed && lane == 0) set_status_word(a.status, KERNEL_ERR_GEMM_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == 10) tmem_dealloc(tmem_base, GEMM_N);
+    if (warp == 9) tmem_dealloc(tmem_base, GEMM_N);
 }
 
 // ---- activations -> binary16 ------------------------------------------------------------
@@ -357,8 +353,13 @@ cudaError_t launch_gemm_dequant(const uint8_t *w, uint32_t cols, uint32_t rows, 
     }
     GemmArgs a = {w + (size_t)expert * rows * stride, static_cast<const __half *>(x_half_scratch), y, cols, rows, stride, kind, tokens,
                   ctx.status};
+    CUtensorMap xmap;
+    if (((uintptr_t)x_half_scratch % 16u) ||
+        !make_tensor_map_2d(xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_half_scratch, cols, tokens, (uint64_t)cols * 2u, GEMM_K, GEMM_N,
+                            CU_TENSOR_MAP_SWIZZLE_128B))
+        return cudaErrorNotSupported;
     dim3 grid((rows + GEMM_M - 1) / GEMM_M, (tokens + GEMM_N - 1) / GEMM_N);
-    gemm_dequant_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, ctx.stream>>>(a);
+    gemm_dequant_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, ctx.stream>>>(xmap, a);
     return cudaGetLastError();
 }
 

@@ -45,6 +45,7 @@
 #include "kernels.h"
 #include "pack.cuh"
 #include "ptx.cuh"
+#include "tensor_map.h"
 
 namespace ingot {
 
@@ -560,33 +561,9 @@ gemv_tc_q4k_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
 
 // ---- host: tensor maps and launch ----------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // rows x stride bytes, boxes of 128 rows x box_bytes
 static bool make_row_map(CUtensorMap &map, const uint8_t *w, uint32_t rows, uint32_t stride, uint32_t box_bytes) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[2] = {stride, rows};
-    const cuuint64_t strides[1] = {stride};
-    const cuuint32_t box[2] = {box_bytes, TC_TILE};
-    const cuuint32_t estr[2] = {1, 1};
-    return fn(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return make_tensor_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, stride, rows, stride, box_bytes, TC_TILE, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 template <int NMAT>
