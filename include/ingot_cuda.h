@@ -63,7 +63,7 @@ enum {
 };
 
 /* x_kind of activation rows already packed by ingot_pack_x / ingot_pack_digits */
-enum { INGOT_X_PACKED = 256, INGOT_X_DIGITS = 258 };
+enum { INGOT_X_PACKED = 256, INGOT_X_DIGITS = 258, INGOT_X_PACKED_HI = 259 };
 
 typedef struct ingot_gpu ingot_gpu;      /* opaque; the reference's `Gpu` */
 typedef struct ingot_graph ingot_graph;  /* opaque; a recorded `Command` */
@@ -225,7 +225,8 @@ INGOT_API ingot_status ingot_add_rms(ingot_gpu *gpu, const float *a, const float
 /* add_rms that also writes y in the packed order of ingot_pack_x (`y_packed`, rows of
  * ingot_packed_x_bytes(width); width a multiple of 64), so the projections that
  * follow need no separate packing pass.  pack_from_bf16 != 0 packs the bfloat16
- * rounding of y (what packing `y_bf16` would give). */
+ * rounding of y (what packing `y_bf16` would give); pack_from_bf16 = 3 packs that
+ * rounding as high-part rows (ingot_pack_x_hi; rows of ingot_packed_hi_bytes). */
 INGOT_API ingot_status ingot_add_rms_packed(ingot_gpu *gpu, const float *a, const float *b, const float *w, float *s,
                                             float *y, void *y_bf16, void *y_packed, uint32_t pack_from_bf16,
                                             uint32_t width, uint32_t rows, float eps, uint32_t add);
@@ -284,6 +285,18 @@ INGOT_API ingot_status ingot_convert_bf16(ingot_gpu *gpu, const float *x, uint64
 INGOT_API ingot_status ingot_packed_x_bytes(uint32_t cols, uint64_t *bytes);
 INGOT_API ingot_status ingot_pack_x(ingot_gpu *gpu, const void *x, uint32_t x_kind, uint32_t rows, uint32_t cols,
                                     void *packed);
+
+/* High-part rows, for bfloat16 activations only: a bfloat16 value is exact in binary16
+ * (up to underflow below 2^-24 of the row's scale), so the low parts of ingot_pack_x are
+ * all zero and are left out: half the bytes, and with one part per token the eight
+ * columns of the tensor-core operand hold EIGHT TOKENS.  Pass `count` rows (1 to any
+ * number; they go through eight, or as many as fit in shared memory, at a time) with
+ * x_kind = INGOT_X_PACKED_HI to ingot_matmul / ingot_gate_up: the weights are streamed
+ * once per group of tokens (Q4_K, Q6_K with cols a multiple of 2048; one token: every
+ * tensor-core GEMV type).  Rows of ingot_packed_hi_bytes(cols).  No counterpart in the
+ * reference. */
+INGOT_API ingot_status ingot_packed_hi_bytes(uint32_t cols, uint64_t *bytes);
+INGOT_API ingot_status ingot_pack_x_hi(ingot_gpu *gpu, const void *x_bf16, uint32_t rows, uint32_t cols, void *packed);
 
 /* Activations as the operand of the tcgen05 int8 GEMV (INGOT_OPT_TCGEN05_GEMV): every
  * value is round(x * S), S the power of two that puts the row's largest magnitude in

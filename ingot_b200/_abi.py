@@ -15,6 +15,7 @@ OK, INVALID, UNSUPPORTED, DEVICE, EOF, INTERRUPTED, TIMEOUT = range(7)
 OPT_PDL, OPT_FORCE_PLAIN, OPT_NO_MMA, OPT_TCGEN05_GEMV, OPT_EP_WORLD = 1, 2, 3, 4, 5
 X_PACKED = 256
 X_DIGITS = 258
+X_PACKED_HI = 259
 
 vp, u32, u64, i32, f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_float
 sz = C.c_size_t
@@ -57,6 +58,8 @@ SIGNATURES = {
     "ingot_gate_up_normed": [vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, vp, C.c_float, u32, u32, u32, vp],
     "ingot_independent_begin": [vp],
     "ingot_independent_end": [vp],
+    "ingot_packed_hi_bytes": [u32, C.POINTER(u64)],
+    "ingot_pack_x_hi": [vp, vp, u32, u32, vp],
     "ingot_packed_digits_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_digits": [vp, vp, u32, u32, u32, vp],
     "ingot_matvec_static": [vp, u32, u32, u32, u32, u32, vp, vp, vp, i32],

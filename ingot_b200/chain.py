@@ -21,7 +21,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import synth
-from .gpu import BF16, F32, X_PACKED, Buffer, Gpu, Tensor, Weight
+from .gpu import BF16, F32, X_PACKED, X_PACKED_HI, Buffer, Gpu, Tensor, Weight
 
 
 @dataclass
@@ -104,6 +104,10 @@ class DecodeChain:
         self.part = gpu.zeros(b * max(shape.ffn, shape.vocab) // world + b * 8) if world > 1 else None
         # activations packed once per distinct GEMV input (one token: the tensor-core GEMV)
         self.packed = batch == 1 and packed
+        # several tokens: bfloat16 activations as high-part rows, eight tokens per pass over the weights
+        self.packed_hi = (batch > 1 and packed and x_kind == BF16 and world == 1
+                          and all(k in (synth.Q4_K, synth.Q6_K) for k in shape.kinds.values())
+                          and all(c % 2048 == 0 for _, c, _ in layer_roles(shape)))
         # q, k and v read the same activations and write different buffers: issue them concurrently
         # (the reference's independent_projections scope) when nothing has to be gathered between them
         self.independent_qkv = independent_qkv and world == 1 and self.packed
@@ -112,10 +116,11 @@ class DecodeChain:
         self.fused_norm = (fused_norm and self.packed and world == 1 and all(k in tc_kinds for k in shape.kinds.values())
                            and all(synth.stride_of(shape.kinds[r], c) % 16 == 0 for r, c, _ in layer_roles(shape)))
         self.h2 = gpu.zeros(b * h) if self.fused_norm else None        # the residual stream alternates between h and h2
-        if self.packed:
-            self.xn_p = gpu.empty_bytes(gpu.packed_x_bytes(h))
-            self.a_p = gpu.empty_bytes(gpu.packed_x_bytes(shape.q))
-            self.actn_p = gpu.empty_bytes(gpu.packed_x_bytes(shape.ffn))
+        if self.packed or self.packed_hi:
+            size = (lambda c: batch * gpu.packed_hi_bytes(c)) if self.packed_hi else gpu.packed_x_bytes
+            self.xn_p = gpu.empty_bytes(size(h))
+            self.a_p = gpu.empty_bytes(size(shape.q))
+            self.actn_p = gpu.empty_bytes(size(shape.ffn))
         self.launches_per_step = 0
 
     def _make(self, layer, role, cols, rows, kind, seed, keep) -> Weight:
@@ -138,16 +143,18 @@ class DecodeChain:
         y32 = out.ptr if self.x_kind == F32 else None
         y16 = out.ptr if self.x_kind == BF16 else None
         packed = None
-        if self.packed:
+        if self.packed or self.packed_hi:
             packed = {self.xn.ptr: self.xn_p, self.a.ptr: self.a_p, self.actn.ptr: self.actn_p}[out.ptr].ptr
+        mode = 3 if self.packed_hi else int(self.x_kind == BF16)
         g._check(g._lib.ingot_add_rms_packed(g._h, a.ptr, b.ptr if b else None, None, s.ptr if s else None, y32, y16,
-                                             packed, int(self.x_kind == BF16), width, self.batch, 1e-6, 1 if b else 0))
+                                             packed, mode, width, self.batch, 1e-6, 1 if b else 0))
         self.launches_per_step += 1
 
     def _x(self, x: Buffer):
         """(pointer, x_kind) of a GEMV input: the packed copy when there is one."""
-        if self.packed:
-            return {self.xn.ptr: self.xn_p, self.a.ptr: self.a_p, self.actn.ptr: self.actn_p}[x.ptr].ptr, X_PACKED
+        if self.packed or self.packed_hi:
+            p = {self.xn.ptr: self.xn_p, self.a.ptr: self.a_p, self.actn.ptr: self.actn_p}[x.ptr].ptr
+            return p, (X_PACKED_HI if self.packed_hi else X_PACKED)
         return x.ptr, self.x_kind
 
     def _project(self, w: Weight, x: Buffer, y: Buffer) -> None:

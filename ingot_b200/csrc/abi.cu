@@ -116,7 +116,9 @@ ingot_status after_launch(ingot_gpu *g, cudaError_t e, const char *what) {
     return INGOT_OK;
 }
 
-bool x_kind_ok(uint32_t k) { return k == INGOT_KIND_F32 || k == INGOT_KIND_BF16 || k == INGOT_X_PACKED || k == INGOT_X_DIGITS; }
+bool x_kind_ok(uint32_t k) {
+    return k == INGOT_KIND_F32 || k == INGOT_KIND_BF16 || k == INGOT_X_PACKED || k == INGOT_X_DIGITS || k == INGOT_X_PACKED_HI;
+}
 
 constexpr size_t WORKSPACE_BYTES = 16u << 20;
 
@@ -346,7 +348,16 @@ static ingot_status gemv_common(ingot_gpu *g, GemvCall &c, uint32_t x_kind, cons
     if (!x_kind_ok(x_kind)) return fail(g, INGOT_UNSUPPORTED, "activations must be F32 (0), BF16 (30) or packed");
     if (!c.w[0] || (c.nmat == 2 && !c.w[1]) || !c.x || !c.y) return fail(g, INGOT_INVALID, "null pointer");
     c.x_bf16 = x_kind == INGOT_KIND_BF16;
-    c.x_packed = x_kind == INGOT_X_PACKED ? 1u : x_kind == INGOT_X_DIGITS ? 3u : 0u;
+    c.x_packed = x_kind == INGOT_X_PACKED ? 1u : x_kind == INGOT_X_DIGITS ? 3u : x_kind == INGOT_X_PACKED_HI ? 4u : 0u;
+    if (c.x_packed == 4u) {
+        // high-part rows: one token takes the one-token kernel, more take the multi-token one
+        cudaError_t e = cudaSuccess;
+        const bool routed = c.ids != nullptr;
+        const bool taken = ((uintptr_t)c.x % 16u) == 0 && !g->no_mma && !g->force_plain &&
+                           ((routed || c.count == 1) ? try_launch_gemv_mma(c, ctx_of(g), e) : try_launch_gemv_mt(c, ctx_of(g), e));
+        if (!taken) return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": no tensor-core GEMV for these high-part rows and this weight");
+        return after_launch(g, e, what);
+    }
     if (c.x_packed == 3u) {
         cudaError_t e = cudaSuccess;
         if (!try_launch_gemv_tc(c, ctx_of(g), e))
@@ -418,6 +429,28 @@ ingot_status ingot_gate_up(ingot_gpu *g, const void *gate, const void *up, uint3
     c.w[1] = static_cast<const uint8_t *>(up);
     c.x = x; c.y = y; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
     c.count = count; c.nmat = 2; c.glu = gelu ? 2 : 1;
+    // more than four tokens: two tensor-core GEMMs and the activation, as the reference's generic_gate_up
+    // falls back to separate projections + glu for wide batches (src/metal_generic.rs:231-261)
+    if (g && !g->no_mma && !g->force_plain && !g->in_scope && count > 4 && (kind == INGOT_KIND_Q4_K || kind == INGOT_KIND_Q6_K) &&
+        cols % 256u == 0 && ((uintptr_t)gate % 16u) == 0 && ((uintptr_t)up % 16u) == 0 &&
+        (x_kind == INGOT_KIND_F32 || x_kind == INGOT_KIND_BF16) && gate && up && x && y) {
+        ingot_status st = enter(g);
+        if (st) return st;
+        if ((st = check_matrix(g, kind, cols, rows, stride))) return st;
+        // scratch: binary16 activations, then the two projection outputs
+        const size_t xh = ((size_t)count * cols * 2u + 255u) & ~(size_t)255u, out = (size_t)count * rows * 4u;
+        if ((st = ensure_workspace(g, xh + 2u * out))) return st;
+        uint8_t *ws = static_cast<uint8_t *>(g->workspace);
+        float *yg = reinterpret_cast<float *>(ws + xh), *yu = reinterpret_cast<float *>(ws + xh + out);
+        cudaError_t e = launch_gemm_dequant(static_cast<const uint8_t *>(gate), cols, rows, stride, kind, 0, x,
+                                            x_kind == INGOT_KIND_BF16, count, yg, ws, ctx_of(g));
+        if (e == cudaSuccess)
+            e = launch_gemm_dequant(static_cast<const uint8_t *>(up), cols, rows, stride, kind, 0, x, x_kind == INGOT_KIND_BF16, count,
+                                    yu, ws, ctx_of(g));
+        if (e == cudaSuccess) e = launch_activation(yg, yu, (uint64_t)count * rows, gelu, y, ctx_of(g));
+        if (e != cudaErrorNotSupported) return after_launch(g, e, "gate_up");
+        cudaGetLastError();
+    }
     return gemv_common(g, c, x_kind, "gate_up");
 }
 
@@ -525,7 +558,7 @@ ingot_status ingot_add_rms_packed(ingot_gpu *g, const float *a, const float *b, 
                                   float eps, uint32_t add) {
     ingot_status st = enter(g);
     if (st) return st;
-    if (!a || (add && !b) || width % 4u || width == 0 || (y_packed && (width % 64u || ((uintptr_t)y_packed % 16u))))
+    if (!a || (add && !b) || width % 4u || width == 0 || pack_from_bf16 > 3u || (y_packed && (width % 64u || ((uintptr_t)y_packed % 16u))))
         return fail(g, INGOT_INVALID, "add_rms: bad arguments");
     return after_launch(g, launch_add_rms(a, b, w, s, y, width, rows, eps, add, y_bf16, y_packed, pack_from_bf16, ctx_of(g)),
                         "add_rms");
@@ -578,6 +611,19 @@ ingot_status ingot_pack_x(ingot_gpu *g, const void *x, uint32_t x_kind, uint32_t
     if (!x || !packed || cols == 0 || cols % 64u || ((uintptr_t)packed % 16u)) return fail(g, INGOT_INVALID, "pack_x: bad arguments");
     if (x_kind != INGOT_KIND_F32 && x_kind != INGOT_KIND_BF16) return fail(g, INGOT_UNSUPPORTED, "pack_x: activations must be F32 or BF16");
     return after_launch(g, launch_pack_x(x, x_kind == INGOT_KIND_BF16, rows, cols, packed, ctx_of(g)), "pack_x");
+}
+
+ingot_status ingot_packed_hi_bytes(uint32_t cols, uint64_t *bytes) {
+    if (!bytes || cols == 0 || cols % 64u) return INGOT_INVALID;
+    *bytes = packed_hi_bytes(cols);
+    return INGOT_OK;
+}
+
+ingot_status ingot_pack_x_hi(ingot_gpu *g, const void *x_bf16, uint32_t rows, uint32_t cols, void *packed) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!x_bf16 || !packed || cols == 0 || cols % 64u || ((uintptr_t)packed % 16u)) return fail(g, INGOT_INVALID, "pack_x_hi: bad arguments");
+    return after_launch(g, launch_pack_x_hi(x_bf16, rows, cols, packed, ctx_of(g)), "pack_x_hi");
 }
 
 ingot_status ingot_packed_digits_bytes(uint32_t cols, uint64_t *bytes) {

@@ -43,7 +43,7 @@ struct GemvCall {
     uint32_t count;        // dense tokens
     uint32_t pairs, top, per_pair, n_experts;   // routed
     uint32_t x_bf16;
-    uint32_t x_packed;     // x is already packed: 1 = packed_x_bytes(cols) rows (launch_pack_x), 3 = digit rows (launch_pack_digits)
+    uint32_t x_packed;     // x is already packed: 1 = packed_x_bytes(cols) rows (launch_pack_x), 3 = digit rows (launch_pack_digits), 4 = high-part rows (launch_pack_x_hi)
     uint32_t nmat, glu;    // glu: 1 silu, 2 tanh-gelu
     // fused input normalisation (tensor-core GEMV, dense, one token): x = rms_norm(norm_a + norm_b) * norm_w,
     // optionally rounded to bfloat16; norm_s receives norm_a + norm_b.  x is ignored when norm_a is set.
@@ -59,6 +59,10 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
 bool try_launch_gemv_tc(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
 // Packs `rows` activation rows (f32 or bf16) as base-256 digits for it.
 cudaError_t launch_pack_digits(const void *x, uint32_t bf16, uint32_t rows, uint32_t cols, void *packed, const LaunchCtx &ctx);
+// The tensor-core GEMV for 2..8 tokens whose activations are high-part rows (x_packed == 4); false when not handled.
+bool try_launch_gemv_mt(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
+// Packs `rows` bfloat16 activation rows as high-part rows (packed_hi_bytes(cols) each).
+cudaError_t launch_pack_x_hi(const void *x_bf16, uint32_t rows, uint32_t cols, void *packed, const LaunchCtx &ctx);
 // Packs `rows` activation rows (f32 or bf16) for the tensor-core GEMV.
 cudaError_t launch_pack_x(const void *x, uint32_t bf16, uint32_t rows, uint32_t cols, void *packed, const LaunchCtx &ctx);
 

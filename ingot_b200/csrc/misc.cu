@@ -426,7 +426,8 @@ __global__ void __launch_bounds__(256) add_rms_kernel(const __grid_constant__ Rm
 #pragma unroll
     for (int i = 0; i < 8; ++i) mx = fmaxf(mx, partial[i]);
     const float scale = pack_scale(mx);
-    uint8_t *prow = a.y_packed + (size_t)row * packed_x_bytes(a.width);
+    const bool hi = a.pack_bf16 == 3u;
+    uint8_t *prow = a.y_packed + (size_t)row * (hi ? packed_hi_bytes(a.width) : packed_x_bytes(a.width));
     for (uint32_t j0 = 0; j0 < n4; j0 += 256) {
         const uint32_t j = j0 + tid;
         const bool live = j < n4;
@@ -447,9 +448,10 @@ __global__ void __launch_bounds__(256) add_rms_kernel(const __grid_constant__ Rm
 #pragma unroll
             for (int i = 0; i < 4; ++i) v[i] *= scale;
         }
-        pack_store_quad(prow, a.width, j, v, live);
+        if (hi) pack_hi_store_quad(prow, a.width, j, v, live);
+        else pack_store_quad(prow, a.width, j, v, live);
     }
-    if (tid == 0) pack_store_unscale(prow, a.width, scale);
+    if (tid == 0) { if (hi) pack_hi_store_unscale(prow, a.width, scale); else pack_store_unscale(prow, a.width, scale); }
 }
 
 // The same with every element held in registers between the passes: one read of the inputs,
@@ -517,7 +519,8 @@ __global__ void __launch_bounds__(RMS_FAST_THREADS) add_rms_fast_kernel(const __
     if (!a.y_packed) return;
     mx = block_reduce_512(mx, partial, true);
     const float scale = pack_scale(mx);
-    uint8_t *prow = a.y_packed + (size_t)row * packed_x_bytes(a.width);
+    const bool hi = a.pack_bf16 == 3u;
+    uint8_t *prow = a.y_packed + (size_t)row * (hi ? packed_hi_bytes(a.width) : packed_x_bytes(a.width));
 #pragma unroll
     for (uint32_t i = 0; i < RMS_FAST_VEC; ++i) {
         const uint32_t j = tid + i * RMS_FAST_THREADS;
@@ -530,9 +533,10 @@ __global__ void __launch_bounds__(RMS_FAST_THREADS) add_rms_fast_kernel(const __
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) u[k] *= scale;
-        pack_store_quad(prow, a.width, j, u, live);
+        if (hi) pack_hi_store_quad(prow, a.width, j, u, live);
+        else pack_store_quad(prow, a.width, j, u, live);
     }
-    if (tid == 0) pack_store_unscale(prow, a.width, scale);
+    if (tid == 0) { if (hi) pack_hi_store_unscale(prow, a.width, scale); else pack_store_unscale(prow, a.width, scale); }
 }
 
 cudaError_t launch_add_rms(const float *a, const float *b, const float *w, float *s, float *y, uint32_t width,

@@ -26,6 +26,7 @@ from .synth import geometry, stride_of
 
 F32, F16, Q4_0, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 2, 8, 12, 14, 30
 X_PACKED = _abi.X_PACKED     # x_kind of rows produced by Gpu.pack_x
+X_PACKED_HI = _abi.X_PACKED_HI   # x_kind of rows produced by Gpu.pack_x_hi (bfloat16 activations, up to eight tokens per pass)
 X_DIGITS = _abi.X_DIGITS     # x_kind of rows produced by Gpu.pack_digits (tcgen05 int8 GEMV)
 
 
@@ -410,6 +411,17 @@ class Gpu:
         """Packs activation rows for the tensor-core GEMV; pass the result with x_kind=X_PACKED."""
         p = out or self.empty_bytes(rows * self.packed_x_bytes(cols))
         self._check(self._lib.ingot_pack_x(self._h, x.ptr, x_kind, rows, cols, p.ptr))
+        return p
+
+    def packed_hi_bytes(self, cols: int) -> int:
+        n = C.c_uint64()
+        self._check(self._lib.ingot_packed_hi_bytes(cols, C.byref(n)))
+        return n.value
+
+    def pack_x_hi(self, x_bf16: Buffer, rows: int, cols: int, out: Buffer | None = None) -> Buffer:
+        """Packs bfloat16 activation rows as high-part rows; pass the result with x_kind=X_PACKED_HI."""
+        p = out or self.empty_bytes(rows * self.packed_hi_bytes(cols))
+        self._check(self._lib.ingot_pack_x_hi(self._h, x_bf16.ptr, rows, cols, p.ptr))
         return p
 
     def packed_digits_bytes(self, cols: int) -> int:

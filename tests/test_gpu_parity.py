@@ -646,3 +646,69 @@ def test_moe_host_wrapper_matches_oracle(gpu):
     assert (np.abs(y - e) <= 4 * tol_ref_scaled(e)).all(), float(np.abs(y - e).max())
     with pytest.raises(InvalidData):
         gpu.moe(routed, shared, gate, x, weights[:3])
+
+
+def test_gate_up_wide_batch_takes_the_gemm(gpu):
+    cols, rows, tokens = 1024, 300, 9
+    g_raw, u_raw = synth.random_matrix(Q4_K, cols, rows, seed=81), synth.random_matrix(Q4_K, cols, rows, seed=82)
+    x = standard_x(cols * tokens).reshape(tokens, cols) * np.float32(0.5)
+    t = Tensor.of([cols, rows], Q4_K)
+    wg, wu = Weight(gpu.bytes(g_raw), t), Weight(gpu.bytes(u_raw), t)
+    y = gpu.finish(None, gpu.generic_gate_up(None, [wg, wu], gpu.floats(x), tokens, False)).reshape(tokens, rows)
+    eg, eu = O.gemm_f16_f64(g_raw, cols, rows, Q4_K, x), O.gemm_f16_f64(u_raw, cols, rows, Q4_K, x)
+    e = O.glu(eg.astype(np.float32), eu.astype(np.float32)).reshape(tokens, rows).astype(np.float64)
+    assert (np.abs(y - e) <= 4 * tol_contract(e)).all(), float(np.abs(y - e).max())
+
+
+# ---- several tokens per pass over the weights (high-part rows) ---------------------------------
+
+@pytest.mark.parametrize("kind,cols,rows", [(Q4_K, 4096, 300), (Q6_K, 4096, 130), (Q4_K, 2048, 16), (Q6_K, 12288, 40)])
+@pytest.mark.parametrize("tokens", [1, 2, 5, 8, 11])
+def test_multi_token_gemv_on_high_part_rows(gpu, kind, cols, rows, tokens):
+    from ingot_b200 import X_PACKED_HI
+    raw = synth.random_matrix(kind, cols, rows, 2, seed=91)
+    x = synth.activations(tokens, cols, seed=92) / 256.0
+    xr = synth.from_bf16_bits(synth.to_bf16_bits(x))
+    w = gpu.bytes(raw)
+    stride = synth.stride_of(kind, cols)
+    packed = gpu.pack_x_hi(gpu.bf16(x), tokens, cols)
+    y = gpu.finish(None, gpu.matmul(None, w, cols, rows, stride, kind, 1, packed, tokens, X_PACKED_HI)).reshape(tokens, rows)
+    e = O.matvec_f64(raw, cols, rows, kind, xr, expert=1)
+    assert (np.abs(y - e) <= tol_ref(e)).all(), float(np.abs(y - e).max())
+    if tokens > 1:       # each token agrees with the one-token kernel on the same row to summation-order noise
+        one = gpu.finish(None, gpu.matmul(None, w, cols, rows, stride, kind, 1, packed, 1, X_PACKED_HI))
+        assert (np.abs(one - y[0]) <= 2 * tol_ref(e[0])).all()
+
+
+def test_multi_token_gate_up_and_chain(gpu):
+    from ingot_b200 import X_PACKED_HI
+    from ingot_b200.chain import QWEN3_8B, DecodeChain
+    cols, rows, tokens = 4096, 200, 8
+    g_raw, u_raw = synth.random_matrix(Q4_K, cols, rows, seed=93), synth.random_matrix(Q4_K, cols, rows, seed=94)
+    x = synth.activations(tokens, cols, seed=95) * np.float32(0.02)
+    xr = synth.from_bf16_bits(synth.to_bf16_bits(x))
+    packed = gpu.pack_x_hi(gpu.bf16(x), tokens, cols)
+    y = gpu.output(tokens * rows)
+    wg, wu = gpu.bytes(g_raw), gpu.bytes(u_raw)
+    gpu._check(gpu._lib.ingot_gate_up(gpu._h, wg.ptr, wu.ptr, cols, rows, synth.stride_of(Q4_K, cols), Q4_K,
+                                      packed.ptr, X_PACKED_HI, tokens, 0, y.ptr))
+    got = gpu.finish(None, y).reshape(tokens, rows)
+    eg, eu = O.matvec_f64(g_raw, cols, rows, Q4_K, xr), O.matvec_f64(u_raw, cols, rows, Q4_K, xr)
+    e = O.glu(eg.astype(np.float32), eu.astype(np.float32)).reshape(tokens, rows).astype(np.float64)
+    assert (np.abs(got - e) <= tol_contract(e)).all(), float(np.abs(got - e).max())
+    # the batch-8 chain: every token's logits equal the batch-1 chain's on the same input, to bfloat16 noise
+    h0 = np.random.default_rng(1).normal(0, 1, (8, QWEN3_8B.hidden)).astype(np.float32)
+    c8 = DecodeChain(gpu, QWEN3_8B, batch=8, x_kind=BF16, seed=3, layers=2)
+    assert c8.packed_hi
+    gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, c8.h_in.ptr, h0.ctypes.data, h0.nbytes))
+    c8.step()
+    gpu.complete()
+    l8 = gpu.read_f32(c8.logits).reshape(8, -1)
+    del c8
+    c1 = DecodeChain(gpu, QWEN3_8B, batch=1, x_kind=BF16, seed=3, layers=2, fused_norm=False)
+    gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, c1.h_in.ptr, h0[3].ctypes.data, h0[3].nbytes))
+    c1.step()
+    gpu.complete()
+    l1 = gpu.read_f32(c1.logits)
+    scale = float(np.sqrt(np.mean(np.square(l1))))
+    assert np.abs(l8[3] - l1).max() <= 2e-2 * scale
