@@ -250,11 +250,13 @@ __device__ __forceinline__ uint32_t unmagic(uint32_t h2) {
     return *reinterpret_cast<const uint32_t *>(&r);
 }
 
-// 32-bit word at a 2-byte aligned shared address
-__device__ __forceinline__ uint32_t lds32_u2(const uint8_t *p) {
-    const uint32_t a = (uint32_t)(uintptr_t)p;
-    const uint32_t *q = reinterpret_cast<const uint32_t *>(p - (a & 2u));
-    return __funnelshift_r(q[0], q[1], (a & 2u) * 8u);
+// 32-bit word at a shared address that is known to be 4-byte aligned (`mis` false) or 2 bytes past
+// such an address (`mis` true).  With `mis` a compile-time constant after inlining this is one
+// load, or two loads and a funnel shift, with no address arithmetic.
+__device__ __forceinline__ uint32_t lds32_known(const uint8_t *p, bool mis) {
+    if (!mis) return *reinterpret_cast<const uint32_t *>(p);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(p - 2);
+    return __funnelshift_r(q[0], q[1], 16u);
 }
 __device__ __forceinline__ uint32_t lds32(const uint8_t *p) { return *reinterpret_cast<const uint32_t *>(p); }
 __device__ __forceinline__ float lds_half(const uint8_t *p) { return __half2float(*reinterpret_cast<const __half *>(p)); }
@@ -302,7 +304,7 @@ template <> struct MmaStep<KIND_Q4_K> {
     }
     template <uint32_t XS>      // bytes of packed activations per MMA: 64 (high and low parts) or 32 (high part only)
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
-                                               uint32_t t, float &acc0, float &acc1) {
+                                               uint32_t t, float &acc0, float &acc1, bool) {
         float s00, s01, m00, m01, s10, s11, m10, m11;
         scales(r0, t, s00, s01, m00, m01);
         scales(r1, t, s10, s11, m10, m11);
@@ -351,9 +353,10 @@ template <> struct MmaStep<KIND_Q6_K> {
         if (FIRST) mma16816_first(c, six<Q>(la, ha), six<Q>(lb, hb), six<Q>(la >> 8, ha >> 8), six<Q>(lb >> 8, hb >> 8), bf.x, bf.y);
         else mma16816(c, six<Q>(la, ha), six<Q>(lb, hb), six<Q>(la >> 8, ha >> 8), six<Q>(lb >> 8, hb >> 8), bf.x, bf.y);
     }
+    // mis: the block starts 2 bytes past a 4-byte boundary (odd blocks of a 16-byte aligned row)
     template <uint32_t XS>      // bytes of packed activations per MMA: 64 (high and low parts) or 32 (high part only)
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
-                                               uint32_t t, float &acc0, float &acc1) {
+                                               uint32_t t, float &acc0, float &acc1, bool mis) {
         const float d0 = lds_half(r0 + 208u), d1 = lds_half(r1 + 208u);
         const float up = t < 2 ? SUBNORMAL_SCALE : SUBNORMAL_SCALE * 0.0625f;       // x16 of the in-place high nibble undone
         float t0 = 0.f, t1 = 0.f;
@@ -364,8 +367,9 @@ template <> struct MmaStep<KIND_Q6_K> {
 #pragma unroll
             for (uint32_t h = 0; h < 2; ++h) {
                 const uint32_t o = 64u * n + 16u * h + 4u * t;
-                const uint32_t a_lo = lds32_u2(r0 + o), a_hi = lds32_u2(r0 + o + 32u), a_h = lds32_u2(r0 + 128u + 32u * n + 16u * h + 4u * t);
-                const uint32_t b_lo = lds32_u2(r1 + o), b_hi = lds32_u2(r1 + o + 32u), b_h = lds32_u2(r1 + 128u + 32u * n + 16u * h + 4u * t);
+                const uint32_t oh = 128u + 32u * n + 16u * h + 4u * t;
+                const uint32_t a_lo = lds32_known(r0 + o, mis), a_hi = lds32_known(r0 + o + 32u, mis), a_h = lds32_known(r0 + oh, mis);
+                const uint32_t b_lo = lds32_known(r1 + o, mis), b_hi = lds32_known(r1 + o + 32u, mis), b_h = lds32_known(r1 + oh, mis);
                 float c[4];
                 quarter<0, true>(a_lo, b_lo, a_h, b_h, IG_BFRAG(0, 8u * n + 0u + h), c);
                 quarter<1, false>(a_hi, b_hi, a_h, b_h, IG_BFRAG(1, 8u * n + 2u + h), c);
@@ -389,13 +393,14 @@ template <> struct MmaStep<KIND_Q6_K> {
 template <> struct MmaStep<KIND_Q4_0> {
     template <uint32_t XS>      // bytes of packed activations per MMA: 64 (high and low parts) or 32 (high part only)
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
-                                               uint32_t t, float &acc0, float &acc1) {
+                                               uint32_t t, float &acc0, float &acc1, bool) {
         const float d0 = lds_half(r0 + 18u * t), d1 = lds_half(r1 + 18u * t);
         const float sxv = mul_rn(add_rn(sx[2u * t], sx[2u * t + 1u]), -8.0f);
         float lo[4], hi[4];
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
-            const uint32_t wa = lds32_u2(r0 + 18u * b + 2u + 4u * t), wb = lds32_u2(r1 + 18u * b + 2u + 4u * t);
+            // a step (72 bytes) starts on a 4-byte boundary: the quants of even blocks lie 2 bytes past one
+            const uint32_t wa = lds32_known(r0 + 18u * b + 2u + 4u * t, (b & 1u) == 0u), wb = lds32_known(r1 + 18u * b + 2u + 4u * t, (b & 1u) == 0u);
             const uint32_t as = wa >> 8, bs = wb >> 8;
             const uint2 bl = IG_BFRAG(b, 2u * b), bh = IG_BFRAG(b, 2u * b + 1u);
             if (b == 0) {
@@ -420,7 +425,7 @@ template <> struct MmaStep<KIND_Q8_0> {
     static __device__ __forceinline__ uint32_t s8(uint32_t w) { return (w & 0x00ff00ffu) ^ 0x00800080u; }
     template <uint32_t XS>      // bytes of packed activations per MMA: 64 (high and low parts) or 32 (high part only)
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&xb)[4], const float *sx,
-                                               uint32_t t, float &acc0, float &acc1) {
+                                               uint32_t t, float &acc0, float &acc1, bool) {
         const float d0 = lds_half(r0 + 34u * t), d1 = lds_half(r1 + 34u * t);
         const float sxv = mul_rn(add_rn(sx[2u * t], sx[2u * t + 1u]), -128.0f);
         float c[4];
@@ -428,7 +433,9 @@ template <> struct MmaStep<KIND_Q8_0> {
         for (uint32_t b = 0; b < 4; ++b)
 #pragma unroll
             for (uint32_t h = 0; h < 2; ++h) {
-                const uint32_t wa = lds32_u2(r0 + 34u * b + 2u + 16u * h + 4u * t), wb = lds32_u2(r1 + 34u * b + 2u + 16u * h + 4u * t);
+                // a step (136 bytes) starts on a 4-byte boundary: the quants of even blocks lie 2 bytes past one
+                const uint32_t wa = lds32_known(r0 + 34u * b + 2u + 16u * h + 4u * t, (b & 1u) == 0u);
+                const uint32_t wb = lds32_known(r1 + 34u * b + 2u + 16u * h + 4u * t, (b & 1u) == 0u);
                 const uint2 bf = IG_BFRAG(b, 2u * b + h);
                 if (b == 0 && h == 0) mma16816_first(c, s8(wa), s8(wb), s8(wa >> 8), s8(wb >> 8), bf.x, bf.y);
                 else mma16816(c, s8(wa), s8(wb), s8(wa >> 8), s8(wb >> 8), bf.x, bf.y);
@@ -729,7 +736,12 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
                     for (uint32_t i = 0; i < p.spw; ++i) {
                         const uint8_t *const xb[4] = {own == 0 ? xs : zlane, own == 1 ? xs : zlane, own == 2 ? xs : zlane,
                                                       own == 3 ? xs : zlane};
-                        MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1]);
+                        // rows start on 16-byte boundaries in the stage: an odd Q6_K block (210 bytes) starts
+                        // 2 bytes past a 4-byte boundary (warp-uniform; the other formats ignore it)
+                        if (KIND == KIND_Q6_K && (((kw + (i << p.kw_log2)) & 1u) != 0u))
+                            MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1], true);
+                        else
+                            MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1], false);
                         b0 += step_stride; b1 += step_stride;
                         xs += x_stride; ss += s_stride;
                     }
@@ -843,7 +855,7 @@ template <uint32_t KIND> struct MtStep;
 // tokens 2t and 2t+1 at the step; acc: rows g, g+8 x tokens 2t, 2t+1
 template <> struct MtStep<KIND_Q4_K> {
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *xs, const float *s0, const float *s1,
-                                               uint32_t t, float (&acc)[4]) {
+                                               uint32_t t, float (&acc)[4], bool) {
         const U4 h0 = *reinterpret_cast<const U4 *>(r0), h1 = *reinterpret_cast<const U4 *>(r1);
         const float2 d0 = __half22float2(*reinterpret_cast<const __half2 *>(&h0.x)), d1 = __half22float2(*reinterpret_cast<const __half2 *>(&h1.x));
         // six-bit scales and mins of sub-blocks 0..3 (lo words) and 4..7 (hi words), one per byte
@@ -909,8 +921,9 @@ template <> struct MtStep<KIND_Q6_K> {
         p[2] = fma_rn(sb, fma_rn(c[2], up, x0), p[2]);
         p[3] = fma_rn(sb, fma_rn(c[3], up, x1), p[3]);
     }
+    // mis: the block starts 2 bytes past a 4-byte boundary
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *xs, const float *s0, const float *s1,
-                                               uint32_t t, float (&acc)[4]) {
+                                               uint32_t t, float (&acc)[4], bool mis) {
         const float d0 = lds_half(r0 + 208u), d1 = lds_half(r1 + 208u);
         float p[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -918,8 +931,9 @@ template <> struct MtStep<KIND_Q6_K> {
 #pragma unroll
             for (uint32_t h = 0; h < 2; ++h) {
                 const uint32_t o = 64u * n + 16u * h + 4u * t;
-                const uint32_t a_lo = lds32_u2(r0 + o), a_hi = lds32_u2(r0 + o + 32u), a_h = lds32_u2(r0 + 128u + 32u * n + 16u * h + 4u * t);
-                const uint32_t b_lo = lds32_u2(r1 + o), b_hi = lds32_u2(r1 + o + 32u), b_h = lds32_u2(r1 + 128u + 32u * n + 16u * h + 4u * t);
+                const uint32_t oh = 128u + 32u * n + 16u * h + 4u * t;
+                const uint32_t a_lo = lds32_known(r0 + o, mis), a_hi = lds32_known(r0 + o + 32u, mis), a_h = lds32_known(r0 + oh, mis);
+                const uint32_t b_lo = lds32_known(r1 + o, mis), b_hi = lds32_known(r1 + o + 32u, mis), b_h = lds32_known(r1 + oh, mis);
 #pragma unroll
                 for (uint32_t q = 0; q < 4; ++q) {
                     // run (n, q, h): 16 columns, MMA index 8n + 2q + h, its own int8 scale and activation sum
@@ -1074,7 +1088,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mt_kernel(const __grid_co
                 const uint8_t *b1 = st + (size_t)ur1 * p.row_pitch + kw * p.step_bytes;
                 for (uint32_t i = 0; i < p.spw; ++i) {
                     const uint32_t step = gs0 + i * MMA_WARPS;                 // 256 columns: 16 MMAs of 32 packed bytes, 16 sums
-                    MtStep<KIND>::run(b0, b1, xlane + (size_t)step * 512u, sum0 + step * 16u, sum1 + step * 16u, t, acc[m]);
+                    // rows start on 16-byte boundaries in the stage and this warp's steps are kw, kw + 8, ...:
+                    // its Q6_K blocks (210 bytes) all start 2 bytes past a 4-byte boundary when kw is odd
+                    if (KIND == KIND_Q6_K && (kw & 1u))
+                        MtStep<KIND>::run(b0, b1, xlane + (size_t)step * 512u, sum0 + step * 16u, sum1 + step * 16u, t, acc[m], true);
+                    else
+                        MtStep<KIND>::run(b0, b1, xlane + (size_t)step * 512u, sum0 + step * 16u, sum1 + step * 16u, t, acc[m], false);
                     b0 += step_stride; b1 += step_stride;
                 }
                 __syncwarp();
@@ -1206,6 +1225,18 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
         ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas ? max_ctas : 1, MMA_SMEM_MAX, hi_only, plan);
     }
     if (!ok) return false;
+    if (gy_live == 1) {
+        // A one-wave grid that leaves every CTA with part of a 16-row tile pays the whole tile's
+        // arithmetic in each of them.  When one full tile per CTA puts fewer tiles on the busiest
+        // SM, take that grid instead (4096 rows: 256 CTAs, two per SM at most, instead of 444
+        // CTAs of 9 or 10 rows, three per SM).
+        const uint32_t tile_rows = 16u * plan.row_tiles;
+        const uint32_t tiles = (c.rows + tile_rows - 1) / tile_rows;
+        const uint32_t rows_per_cta = (c.rows + plan.ctas - 1) / plan.ctas;
+        const uint32_t load_now = ((plan.ctas + ctx.sm_count - 1) / ctx.sm_count) * ((rows_per_cta + tile_rows - 1) / tile_rows);
+        const uint32_t load_full = (tiles + ctx.sm_count - 1) / ctx.sm_count;
+        if (tiles <= plan.ctas && load_full < load_now) plan.ctas = tiles;
+    }
     const uint8_t *xp = static_cast<const uint8_t *>(c.x);
     if (c.norm_a) {
         if (routed || c.cols % 64u) return false;
