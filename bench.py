@@ -164,6 +164,8 @@ def main():
     ap.add_argument("--pdl", type=int, default=1, help="0: launch without programmatic dependent launch (comparison)")
     ap.add_argument("--graph", type=int, default=1, help="0: issue every step's launches instead of replaying a recorded command")
     ap.add_argument("--fused-norm", type=int, default=1, help="0: add_rms as separate launches (comparison)")
+    ap.add_argument("--group-scope", type=int, default=1,
+                    help="0: the projections of an independent scope on their own streams instead of one grid (comparison)")
     ap.add_argument("--no-mma", type=int, default=0, help="1: streaming GEMVs on the fp32 CUDA-core kernel (comparison)")
     ap.add_argument("--tcgen05-gemv", type=int, default=0, help="1: Q4_K one-token GEMVs on the tcgen05 int8 kernel")
     ap.add_argument("--workload", default="chain", choices=["chain", "gemma", "moe", "gemm"],
@@ -197,6 +199,7 @@ def main():
     gpu.set_option(_abi.OPT_TCGEN05_GEMV, args.tcgen05_gemv)
     gpu.set_option(_abi.OPT_NO_MMA, args.no_mma)
     gpu.set_option(_abi.OPT_PDL, args.pdl)
+    gpu.set_option(_abi.OPT_GROUP_SCOPE, args.group_scope)
 
     shape = GEMMA3_4B if args.workload == "gemma" else QWEN3_8B
     metric = METRIC if args.workload == "chain" else "decode tok/s, Gemma-3-4B Q4_0 shape (Q4_0 GEMV chain)"
@@ -597,6 +600,12 @@ def kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src, only=None, reps
              ("q_" + kn[k["q"]], proj("q", chain.xn, chain.q), s.q * synth.stride_of(k["q"], s.hidden), s.hidden, s.q),
              ("k_" + kn[k["k"]], proj("k", chain.xn, chain.k), s.kv * synth.stride_of(k["k"], s.hidden), s.hidden, s.kv),
              ("v_" + kn[k["v"]], proj("v", chain.xn, chain.v), s.kv * synth.stride_of(k["v"], s.hidden), s.hidden, s.kv)]
+    if chain.independent_qkv:       # the three projections of one layer inside the independent scope (one grid)
+        fq, fk, fv = proj("q", chain.xn, chain.q), proj("k", chain.xn, chain.k), proj("v", chain.xn, chain.v)
+        def qkv(i):
+            with gpu.independent():
+                fk(i); fv(i); fq(i)
+        cases.append(("qkv_scope", qkv, sum(c[2] for c in cases[2:5]), s.hidden, s.q + 2 * s.kv))
     head_name = "head_" + kn[k["head"]]
     for name, fn, wbytes, cols, rows in cases:
         if only and name != only:

@@ -115,8 +115,11 @@ INGOT_API ingot_status ingot_independent_end(ingot_gpu *gpu);
  * that multiplies on the tcgen05 int8 tensor cores (rows unpacked into tensor
  * memory, activations as base-256 digits); INGOT_OPT_EP_WORLD (default 1) is the
  * number of devices the experts are split over (ingot_ep_localize): routed launches
- * then expect about pairs / value live pairs and give each more CTAs. */
-enum { INGOT_OPT_PDL = 1, INGOT_OPT_FORCE_PLAIN = 2, INGOT_OPT_NO_MMA = 3, INGOT_OPT_TCGEN05_GEMV = 4, INGOT_OPT_EP_WORLD = 5 };
+ * then expect about pairs / value live pairs and give each more CTAs;
+ * INGOT_OPT_GROUP_SCOPE (default 1) launches the one-token projections of an
+ * independent scope as one grid at the scope's end (0: each on its own stream). */
+enum { INGOT_OPT_PDL = 1, INGOT_OPT_FORCE_PLAIN = 2, INGOT_OPT_NO_MMA = 3, INGOT_OPT_TCGEN05_GEMV = 4, INGOT_OPT_EP_WORLD = 5,
+       INGOT_OPT_GROUP_SCOPE = 6 };
 INGOT_API ingot_status ingot_gpu_set_option(ingot_gpu *gpu, int32_t option, int32_t value);
 
 /* Command::wait / Gpu::complete (src/metal.rs:1224-1235): blocks until the

@@ -111,6 +111,10 @@ class DecodeChain:
         # q, k and v read the same activations and write different buffers: issue them concurrently
         # (the reference's independent_projections scope) when nothing has to be gathered between them
         self.independent_qkv = independent_qkv and world == 1 and self.packed
+        # ... and the scope launches them as one grid when all three take the tensor-core GEMV
+        self.grouped_qkv = self.independent_qkv and all(
+            shape.kinds[r] in (synth.Q4_0, synth.Q8_0, synth.Q4_K, synth.Q6_K) and shape.hidden % 64 == 0
+            and synth.stride_of(shape.kinds[r], shape.hidden) % 16 == 0 for r in ("q", "k", "v"))
         # add_rms fused into the projections that consume it (one token, tensor-core GEMV kinds only)
         tc_kinds = (synth.Q4_0, synth.Q8_0, synth.Q4_K, synth.Q6_K)
         self.fused_norm = (fused_norm and self.packed and world == 1 and all(k in tc_kinds for k in shape.kinds.values())
@@ -199,6 +203,8 @@ class DecodeChain:
                 self._normed(ws["k"], cur, delta, None, self.k)
                 self._normed(ws["v"], cur, delta, None, self.v)
                 self._normed(ws["q"], cur, delta, summed, self.q)
+            if self.independent_qkv:
+                self.launches_per_step -= 2          # the scope issues its three projections as one grid
             if delta:
                 cur, nxt = summed, nxt ^ 1
             self._normed(ws["o"], self.q, None, None, self.o)                 # stands in for attention: o(rms_norm(q))
@@ -232,6 +238,8 @@ class DecodeChain:
                     self._project(ws["q"], self.xn, self.q)
                     self._project(ws["k"], self.xn, self.k)
                     self._project(ws["v"], self.xn, self.v)
+                if self.grouped_qkv:
+                    self.launches_per_step -= 2      # the scope issues its three projections as one grid
             else:
                 self._project(ws["q"], self.xn, self.q)
                 self._project(ws["k"], self.xn, self.k)

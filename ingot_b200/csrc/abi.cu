@@ -31,6 +31,7 @@ struct ingot_gpu {
     bool pdl = true;
     bool force_plain = false;
     bool no_mma = false;
+    bool group_scope = true;
     bool capturing = false;
     // independent-projection scope: launches rotate over the main stream and side streams
     static constexpr int SIDE_STREAMS = 3;
@@ -39,6 +40,7 @@ struct ingot_gpu {
     bool in_scope = false;
     int scope_next = 0;               // stream of the next launch inside the scope: 0 = main, i > 0 = side[i - 1]
     int scope_used = 0;               // side streams touched in this scope (bit mask)
+    std::vector<GemvCall> pending;    // one-token tensor-core projections of the open scope: they share one launch at its end
     std::string error;
 };
 
@@ -87,9 +89,12 @@ cudaStream_t next_stream(ingot_gpu *g) {
     return g->side[i - 1];
 }
 
-LaunchCtx ctx_of(ingot_gpu *g) {
+LaunchCtx ctx_on(ingot_gpu *g, cudaStream_t stream);
+LaunchCtx ctx_of(ingot_gpu *g) { return ctx_on(g, next_stream(g)); }
+
+LaunchCtx ctx_on(ingot_gpu *g, cudaStream_t stream) {
     LaunchCtx c;
-    c.stream = next_stream(g);
+    c.stream = stream;
     c.status = g->status;
     c.sm_count = g->sm_count;
     c.pdl = g->pdl;
@@ -221,6 +226,7 @@ ingot_status ingot_gpu_set_option(ingot_gpu *g, int32_t option, int32_t value) {
     case INGOT_OPT_NO_MMA: g->no_mma = value != 0; return INGOT_OK;
     case INGOT_OPT_TCGEN05_GEMV: g->use_tc = value != 0; return INGOT_OK;
     case INGOT_OPT_EP_WORLD: g->ep_world = value > 1 ? (uint32_t)value : 1u; return INGOT_OK;
+    case INGOT_OPT_GROUP_SCOPE: g->group_scope = value != 0; return INGOT_OK;
     default: return fail(g, INGOT_INVALID, "unknown option");
     }
 }
@@ -341,6 +347,35 @@ ingot_status ingot_dequant_rows(ingot_gpu *g, const void *w, uint32_t cols, uint
     return after_launch(g, launch_dequant(static_cast<const uint8_t *>(w), cols, rows, stride, kind, y, ctx_of(g)), "dequant_rows");
 }
 
+// Inside an independent scope a one-token tensor-core projection is not launched at once: the
+// scope's projections are launched together, as one grid, when it closes.
+static bool defer_in_scope(ingot_gpu *g, const GemvCall &c) {
+    if (!g->in_scope || !g->group_scope || g->no_mma || g->force_plain) return false;
+    if (!gemv_mma_group_eligible(c, ctx_on(g, g->stream))) return false;
+    g->pending.push_back(c);
+    return true;
+}
+
+static ingot_status flush_pending(ingot_gpu *g) {
+    std::vector<GemvCall> calls;
+    calls.swap(g->pending);
+    const LaunchCtx ctx = ctx_on(g, g->stream);
+    for (size_t i = 0; i < calls.size();) {
+        const uint32_t n = (uint32_t)(calls.size() - i < 4 ? calls.size() - i : 4);
+        cudaError_t e = cudaSuccess;
+        if (n >= 2 && try_launch_gemv_mma_group(&calls[i], n, ctx, e)) {
+            if (e != cudaSuccess) return cuda_fail(g, e, "independent projections");
+        } else {
+            for (uint32_t k = 0; k < n; ++k) {
+                if (!try_launch_gemv_mma(calls[i + k], ctx, e)) return fail(g, INGOT_UNSUPPORTED, "independent projections: no kernel for a deferred call");
+                if (e != cudaSuccess) return cuda_fail(g, e, "independent projections");
+            }
+        }
+        i += n;
+    }
+    return INGOT_OK;
+}
+
 static ingot_status gemv_common(ingot_gpu *g, GemvCall &c, uint32_t x_kind, const char *what) {
     ingot_status st = enter(g);
     if (st) return st;
@@ -353,6 +388,7 @@ static ingot_status gemv_common(ingot_gpu *g, GemvCall &c, uint32_t x_kind, cons
         // high-part rows: one token takes the one-token kernel, more take the multi-token one
         cudaError_t e = cudaSuccess;
         const bool routed = c.ids != nullptr;
+        if (((uintptr_t)c.x % 16u) == 0 && defer_in_scope(g, c)) return INGOT_OK;
         const bool taken = ((uintptr_t)c.x % 16u) == 0 && !g->no_mma && !g->force_plain &&
                            ((routed || c.count == 1) ? try_launch_gemv_mma(c, ctx_of(g), e) : try_launch_gemv_mt(c, ctx_of(g), e));
         if (!taken) return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": no tensor-core GEMV for these high-part rows and this weight");
@@ -367,6 +403,7 @@ static ingot_status gemv_common(ingot_gpu *g, GemvCall &c, uint32_t x_kind, cons
     if (c.x_packed) {
         // packed rows only feed the tensor-core GEMV: one token, a block-quantised type, 16-byte aligned rows
         cudaError_t e = cudaSuccess;
+        if (((uintptr_t)c.x % 16u) == 0 && defer_in_scope(g, c)) return INGOT_OK;
         if (((uintptr_t)c.x % 16u) || !try_launch_gemv_mma(c, ctx_of(g), e))
             return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": packed activations need one token and a quantised weight");
         return after_launch(g, e, what);
@@ -469,6 +506,7 @@ static ingot_status normed_common(ingot_gpu *g, GemvCall &c, const float *a, con
     c.count = 1;
     cudaError_t e = cudaSuccess;
     const bool aligned = ((uintptr_t)c.w[0] % 16u) == 0 && (c.nmat < 2 || ((uintptr_t)c.w[1] % 16u) == 0) && ((size_t)c.rows * c.stride) % 16u == 0;
+    if (aligned && defer_in_scope(g, c)) return INGOT_OK;
     if (g->no_mma || g->force_plain || !aligned || !try_launch_gemv_mma(c, ctx_of(g), e))
         return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": no fused kernel for this weight; use add_rms and the plain projection");
     return after_launch(g, e, what);
@@ -657,6 +695,7 @@ ingot_status ingot_independent_begin(ingot_gpu *g) {
     cudaError_t e = cudaEventRecord(g->fork_event, g->stream);
     if (e != cudaSuccess) return cuda_fail(g, e, "independent scope fork");
     g->in_scope = true;
+    g->pending.clear();
     g->scope_next = 0;
     g->scope_used = 0;
     return INGOT_OK;
@@ -666,13 +705,14 @@ ingot_status ingot_independent_end(ingot_gpu *g) {
     if (!g) return INGOT_INVALID;
     if (!g->in_scope) return fail(g, INGOT_INVALID, "no independent scope open");
     g->in_scope = false;
+    ingot_status st = g->pending.empty() ? INGOT_OK : flush_pending(g);
     for (int i = 0; i < ingot_gpu::SIDE_STREAMS; ++i) {
         if (!(g->scope_used & (1 << i))) continue;
         cudaError_t e = cudaEventRecord(g->join_event[i], g->side[i]);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(g->stream, g->join_event[i], 0);
         if (e != cudaSuccess) return cuda_fail(g, e, "independent scope join");
     }
-    return INGOT_OK;
+    return st;
 }
 
 // ---- command recording --------------------------------------------------------

@@ -34,6 +34,7 @@
 // and odd ones xl, replicated over the quads, so every lane ends with (sum q xh,
 // sum q xl) in (c0, c1) and the four lanes of a quad share the scale work.
 #include <cuda_fp16.h>
+#include <type_traits>
 
 #include "dev_common.cuh"
 #include "gemv_core.cuh"
@@ -453,9 +454,10 @@ template <> struct MmaStep<KIND_Q8_0> {
 // kernel
 // ---------------------------------------------------------------------------
 
-template <uint32_t KIND, int NMAT, int OCC, bool HI>
-__global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[];
+// The whole CTA's work on one projection: CTA `cta` of `nctas` (its share of the rows), pair `pair`.
+template <uint32_t KIND, int NMAT, bool HI>
+__device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, const uint32_t cta, const uint32_t nctas, const uint32_t pair,
+                                              const bool whole_tiles) {
     const MmaPlan &p = a.plan;
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MMA_MAX_STAGES;
@@ -483,10 +485,21 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
     ptx::pdl_launch_dependents();
 
     uint32_t r_begin, r_end;
-    cta_rows(p.rows, blockIdx.x, gridDim.x, r_begin, r_end);
     const uint32_t stage_rows = 16u * p.row_tiles;
+    {
+        // An even split of the rows keeps every CTA's bytes equal (long launches are bound by the
+        // CTA that streams the most).  The grouped launch asks for whole tiles per CTA instead:
+        // its parts are short and a tile costs its arithmetic whether or not all its rows are live.
+        const uint32_t tiles = (p.rows + stage_rows - 1) / stage_rows;
+        if (whole_tiles && nctas < tiles) {
+            r_begin = (uint32_t)((uint64_t)tiles * cta / nctas) * stage_rows;
+            r_end = (uint32_t)((uint64_t)tiles * (cta + 1) / nctas) * stage_rows;
+            if (r_end > p.rows) r_end = p.rows;
+        } else {
+            cta_rows(p.rows, cta, nctas, r_begin, r_end);
+        }
+    }
     const uint32_t n_tiles = (r_end - r_begin + stage_rows - 1) / stage_rows;
-    const uint32_t pair = blockIdx.y;
 
     if (warp == MMA_WARPS) {
         // ---- producer warp: weights first (they do not depend on the previous kernel),
@@ -576,7 +589,7 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
             for (int i = 1; i < MMA_WARPS; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
             return r;
         };
-        constexpr uint32_t NV = 12, NT = MMA_WARPS * 32;           // rows of up to 12288 columns stay in registers
+        constexpr uint32_t NT = MMA_WARPS * 32;
         auto finish = [&](float (&u)[4], uint32_t j, float inv) {
             const float4 wv = a.nw ? reinterpret_cast<const float4 *>(a.nw)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
             u[0] = u[0] * inv * wv.x; u[1] = u[1] * inv * wv.y; u[2] = u[2] * inv * wv.z; u[3] = u[3] * inv * wv.w;
@@ -589,7 +602,10 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
                 }
             }
         };
-        if (n4 <= NV * NT) {
+        // the row stays in registers, NV float4 per thread (the unrolled loops issue their instructions
+        // for dead slots too, so narrow rows take the short form)
+        auto in_registers = [&](auto nv_const) {
+            constexpr uint32_t NV = decltype(nv_const)::value;
             float4 v[NV];
             float sum = 0.f;
 #pragma unroll
@@ -598,7 +614,7 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
                 v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (j < n4) {
                     v[i] = load(j);
-                    if (a.ns && blockIdx.x == 0) reinterpret_cast<float4 *>(a.ns)[j] = v[i];
+                    if (a.ns && cta == 0) reinterpret_cast<float4 *>(a.ns)[j] = v[i];
                     sum += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
                 }
             }
@@ -625,11 +641,14 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
                 else pack_store_quad(xrow, p.cols, j, u, j < n4);
             }
             if (tid == 0) { if (HI) pack_hi_store_unscale(xrow, p.cols, scale); else pack_store_unscale(xrow, p.cols, scale); }
-        } else {
+        };
+        if (n4 <= 4u * NT) in_registers(std::integral_constant<uint32_t, 4>{});            // up to 4096 columns
+        else if (n4 <= 12u * NT) in_registers(std::integral_constant<uint32_t, 12>{});     // up to 12288
+        else {
             float sum = 0.f;
             for (uint32_t j = tid; j < n4; j += NT) {
                 const float4 v = load(j);
-                if (a.ns && blockIdx.x == 0) reinterpret_cast<float4 *>(a.ns)[j] = v;
+                if (a.ns && cta == 0) reinterpret_cast<float4 *>(a.ns)[j] = v;
                 sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             }
             const float inv = 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
@@ -767,6 +786,40 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
         if (tile > 0 && !sum_tile(tile - 1)) return;
     }
     if (n_tiles > 0) sum_tile(n_tiles - 1);
+}
+
+template <uint32_t KIND, int NMAT, int OCC, bool HI>
+__global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    gemv_mma_body<KIND, NMAT, HI>(a, smem, blockIdx.x, gridDim.x, blockIdx.y, false);
+}
+
+// Several independent one-token projections in one launch (what the reference's
+// independent_projections scope expresses, e.g. q, k and v of one layer): CTAs
+// [first[i], first[i + 1]) work on part i, each part with its own weight type, shape,
+// inputs and plan.  Parts are ordered by size so that the long ones start first.
+static constexpr uint32_t MMA_GROUP_MAX = 4;
+struct MmaGroupArgs {
+    MmaArgs part[MMA_GROUP_MAX];
+    uint32_t first[MMA_GROUP_MAX + 1];
+    uint32_t n;
+};
+
+// Two CTAs per SM: the Q6_K step needs the registers, and a three-per-SM form without it (smaller
+// rings, a few spills) measured slower on an all-Q4_0 group (11.2 us against 6.7 us).
+template <bool HI>
+__global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_group_kernel(const __grid_constant__ MmaGroupArgs ga) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint32_t i = 0;
+    while (i + 1 < ga.n && blockIdx.x >= ga.first[i + 1]) ++i;
+    const MmaArgs &a = ga.part[i];
+    const uint32_t cta = blockIdx.x - ga.first[i], nctas = ga.first[i + 1] - ga.first[i];
+    switch (a.plan.kind) {
+    case KIND_Q4_K: gemv_mma_body<KIND_Q4_K, 1, HI>(a, smem, cta, nctas, 0u, true); break;
+    case KIND_Q6_K: gemv_mma_body<KIND_Q6_K, 1, HI>(a, smem, cta, nctas, 0u, true); break;
+    case KIND_Q4_0: gemv_mma_body<KIND_Q4_0, 1, HI>(a, smem, cta, nctas, 0u, true); break;
+    default: gemv_mma_body<KIND_Q8_0, 1, HI>(a, smem, cta, nctas, 0u, true); break;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -1213,7 +1266,11 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     MmaPlan plan;
     int occ = 3;
     uint32_t max_ctas = (3u * ctx.sm_count + gy_live - 1) / gy_live;
-    bool ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, hi_only, plan);
+    // a matrix whose 16-row tiles all fit in one wave of two CTAs per SM takes that form: its
+    // deeper ring holds a CTA's whole share, so the copies of one launch run under the tail of
+    // the launch before it (4096 x 4096 Q4_K: 6.3 us against 7.6 us back to back)
+    bool ok = !(gy_live == 1 && (c.rows + 15u) / 16u <= 2u * ctx.sm_count) &&
+              plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, hi_only, plan);
     if (!ok) {
         occ = 2;
         max_ctas = (2u * ctx.sm_count + gy_live - 1) / gy_live;
@@ -1263,6 +1320,94 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     case KIND_Q4_0: err = launch_mma_k<KIND_Q4_0>(a, grid, ctx.stream, ctx.pdl, occ); break;
     default: err = launch_mma_k<KIND_Q8_0>(a, grid, ctx.stream, ctx.pdl, occ); break;
     }
+    return true;
+}
+
+// One-token dense projections that can share a launch: the checks of try_launch_gemv_mma for a
+// call whose activations need no packing pass (packed rows, or the fused norm).
+bool gemv_mma_group_eligible(const GemvCall &c, const LaunchCtx &ctx) {
+    if (c.ids || c.count != 1 || c.nmat != 1 || !mma_kind(c.kind) || c.cols % 64u) return false;
+    if (!c.norm_a && c.x_packed != 1u && c.x_packed != 4u) return false;
+    const bool hi_only = c.norm_a ? c.norm_round_bf16 != 0 : c.x_packed == 4u;
+    MmaPlan plan;
+    return plan_mma(c.kind, c.cols, c.rows, c.stride, 1, 2u * ctx.sm_count, MMA_SMEM_BUDGET, hi_only, plan);
+}
+
+template <bool HI>
+static cudaError_t launch_mma_group_t(const MmaGroupArgs &ga, uint32_t smem_bytes, cudaStream_t stream, bool pdl) {
+    auto kernel = gemv_mma_group_kernel<HI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_BUDGET);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ga.first[ga.n]);
+    cfg.blockDim = dim3(MMA_THREADS);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, ga);
+}
+
+// Launches 2..MMA_GROUP_MAX eligible calls as one grid.  False (nothing launched) when they
+// cannot share one: different activation row forms, or a part that does not plan.
+bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx, cudaError_t &err) {
+    if (n < 2 || n > MMA_GROUP_MAX) return false;
+    bool hi0 = false;
+    uint32_t order[MMA_GROUP_MAX];
+    size_t bytes[MMA_GROUP_MAX];
+    for (uint32_t i = 0; i < n; ++i) {
+        const GemvCall &c = calls[i];
+        if (!gemv_mma_group_eligible(c, ctx)) return false;
+        const bool hi = c.norm_a ? c.norm_round_bf16 != 0 : c.x_packed == 4u;
+        if (i == 0) hi0 = hi;
+        else if (hi != hi0) return false;
+        bytes[i] = (size_t)c.rows * c.stride;
+        order[i] = i;
+    }
+    for (uint32_t i = 1; i < n; ++i)                     // largest part first
+        for (uint32_t j = i; j > 0 && bytes[order[j]] > bytes[order[j - 1]]; --j) { const uint32_t t = order[j]; order[j] = order[j - 1]; order[j - 1] = t; }
+    // one tile per CTA while all of them are resident at once (two CTAs per SM); beyond that every
+    // part gets its share of one wave, in whole tiles: a CTA's latency, not its arithmetic, sets
+    // the time of these short launches, so a second wave would double it
+    MmaGroupArgs ga = {};
+    ga.n = n;
+    uint32_t smem_bytes = 0, tiles_total = 0;
+    MmaPlan plans[MMA_GROUP_MAX];
+    const uint32_t slots = 2u * ctx.sm_count;
+    for (uint32_t k = 0; k < n; ++k) {
+        const GemvCall &c = calls[order[k]];
+        if (!plan_mma(c.kind, c.cols, c.rows, c.stride, 1, slots, MMA_SMEM_BUDGET, hi0, plans[k])) return false;
+        tiles_total += (c.rows + 16u * plans[k].row_tiles - 1) / (16u * plans[k].row_tiles);
+    }
+    for (uint32_t k = 0; k < n; ++k) {
+        const GemvCall &c = calls[order[k]];
+        MmaPlan &plan = plans[k];
+        const uint32_t tiles = (c.rows + 16u * plan.row_tiles - 1) / (16u * plan.row_tiles);
+        uint32_t ctas = tiles;
+        if (tiles_total > slots) {
+            ctas = (uint32_t)((uint64_t)slots * tiles / tiles_total);
+            if (ctas < 1) ctas = 1;
+        }
+        plan.ctas = ctas;
+        MmaArgs &a = ga.part[k];
+        a.plan = plan;
+        a.w[0] = c.w[0]; a.w[1] = nullptr;
+        a.xp = c.norm_a ? nullptr : static_cast<const uint8_t *>(c.x);
+        a.y = c.y;
+        a.ids = nullptr; a.expert = c.expert; a.n_experts = c.n_experts; a.per_pair = 0; a.top = 1; a.glu = 0;
+        a.status = ctx.status;
+        a.na = c.norm_a; a.nb = c.norm_b; a.nw = c.norm_w; a.ns = c.norm_s; a.neps = c.norm_eps; a.nround_bf16 = c.norm_round_bf16;
+        ga.first[k + 1] = ga.first[k] + ctas;
+        if (plan.smem_bytes > smem_bytes) smem_bytes = plan.smem_bytes;
+    }
+    err = hi0 ? launch_mma_group_t<true>(ga, smem_bytes, ctx.stream, ctx.pdl) : launch_mma_group_t<false>(ga, smem_bytes, ctx.stream, ctx.pdl);
     return true;
 }
 

@@ -55,6 +55,9 @@ struct GemvCall {
 cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);
 // The tensor-core-assisted streaming GEMV; false when the call is not one it handles.
 bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
+// Several independent one-token projections as one grid (2..4 calls that gemv_mma_group_eligible accepts).
+bool gemv_mma_group_eligible(const GemvCall &c, const LaunchCtx &ctx);
+bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx, cudaError_t &err);
 // The tcgen05 int8 GEMV (one token, Q4_K); false when the call is not one it handles.
 bool try_launch_gemv_tc(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
 // Packs `rows` activation rows (f32 or bf16) as base-256 digits for it.

@@ -572,6 +572,29 @@ def test_independent_scope_matches_serial_issue_and_records(gpu):
                 pass
 
 
+def test_independent_scope_groups_mixed_types_and_shapes(gpu):
+    # five projections, four weight types, two activation widths: the scope launches them as
+    # grids of up to four parts; every part must equal the same call issued alone
+    from ingot_b200 import X_PACKED
+    parts = [(Q4_K, 4096, 520), (Q6_K, 4096, 136), (Q4_0, 2560, 77), (Q8_0, 2560, 40), (Q4_K, 4096, 16)]
+    raws = [synth.random_matrix(k, c, r, seed=160 + i) for i, (k, c, r) in enumerate(parts)]
+    ws = [gpu.bytes(r) for r in raws]
+    xs = {c: synth.activations(1, c, seed=170 + c) / 128.0 for c in (4096, 2560)}
+    packed = {c: gpu.pack_x(gpu.floats(x), 1, c) for c, x in xs.items()}
+
+    def issue():
+        return [gpu.matmul(None, w, c, r, synth.stride_of(k, c), k, 0, packed[c], 1, X_PACKED) for w, (k, c, r) in zip(ws, parts)]
+
+    alone = [gpu.finish(None, y) for y in issue()]
+    with gpu.independent():
+        ys = issue()
+    grouped = [gpu.finish(None, y) for y in ys]
+    for a, b, raw, (k, c, r) in zip(alone, grouped, raws, parts):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        e = O.matvec_f64(raw, c, r, k, xs[c])[0]
+        assert (np.abs(b - e) <= tol_ref(e)).all()
+
+
 # ---- add_rms fused into the projection ------------------------------------------------------
 
 @pytest.mark.parametrize("kind,cols,rows", [(Q4_K, 4096, 300), (Q6_K, 4096, 130), (Q4_0, 2560, 77), (Q4_K, 12288, 64)])
