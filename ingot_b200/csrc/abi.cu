@@ -451,7 +451,7 @@ ingot_status ingot_gemm(ingot_gpu *g, const void *w, uint32_t cols, uint32_t row
     if (!w || !x || !y || count == 0) return fail(g, INGOT_INVALID, "gemm: bad arguments");
     if ((kind != INGOT_KIND_Q4_K && kind != INGOT_KIND_Q6_K) || cols % 256u || ((uintptr_t)w % 16u))
         return fail(g, INGOT_UNSUPPORTED, "gemm: no tensor-core kernel for this type or shape");
-    if ((st = ensure_workspace(g, (size_t)count * cols * 2u))) return st;
+    if ((st = ensure_workspace(g, gemm_scratch_bytes(cols, rows, count, g->sm_count)))) return st;
     cudaError_t e = launch_gemm_dequant(static_cast<const uint8_t *>(w), cols, rows, stride, kind, expert, x,
                                         x_kind == INGOT_KIND_BF16, count, y, g->workspace, ctx_of(g));
     if (e == cudaErrorNotSupported) { cudaGetLastError(); return fail(g, INGOT_UNSUPPORTED, "gemm: no tensor-core kernel for this type or shape"); }
@@ -475,7 +475,7 @@ ingot_status ingot_gate_up(ingot_gpu *g, const void *gate, const void *up, uint3
         if (st) return st;
         if ((st = check_matrix(g, kind, cols, rows, stride))) return st;
         // scratch: binary16 activations, then the two projection outputs
-        const size_t xh = ((size_t)count * cols * 2u + 255u) & ~(size_t)255u, out = (size_t)count * rows * 4u;
+        const size_t xh = (gemm_scratch_bytes(cols, rows, count, g->sm_count) + 255u) & ~(size_t)255u, out = (size_t)count * rows * 4u;
         if ((st = ensure_workspace(g, xh + 2u * out))) return st;
         uint8_t *ws = static_cast<uint8_t *>(g->workspace);
         float *yg = reinterpret_cast<float *>(ws + xh), *yu = reinterpret_cast<float *>(ws + xh + out);

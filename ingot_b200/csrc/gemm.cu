@@ -6,14 +6,16 @@
 // accumulation is fp32 (its simdgroup_half8x8 staging, :343,355-361), so results are held
 // to the same expectation (f64 dot of F16-rounded operands, src/expert_bench.rs:734-749).
 //
-// One CTA computes a 128 (weight rows) x 256 (tokens) tile of Y^T.  Per 64-column K step:
+// One CTA computes a 128 (weight rows) x 256 (tokens) tile of Y^T — or, for more than 256 tokens,
+// two such tiles side by side (512 tokens, two accumulators) so that every decoded weight tile is
+// used twice: the decode, not the tensor pipe, bounds this kernel.  Per 64-column K step:
 //   * eight warps decode half a weight row each (32 columns) — the fp32 value d*sc*q - dmin*m
 //     (Q4_K) or d*scale*(q-32) (Q6_K) exactly as weight_at forms it, rounded to binary16 — and
 //     store the 128 x 64 tile K-major with the 128-byte swizzle the tensor core expects;
-//   * one thread brings the 256 x 64 activation tile (already binary16) with one 2-D TMA
+//   * one thread brings each 256 x 64 activation tile (already binary16) with one 2-D TMA
 //     copy whose tensor map applies the same 128-byte swizzle;
-//   * one thread issues four tcgen05.mma (M 128, N 256, K 16) accumulating in tensor
-//     memory (256 columns x 128 lanes of fp32), and a tcgen05.commit frees the stage.
+//   * one thread issues four tcgen05.mma (M 128, N 256, K 16) per accumulator, accumulating in
+//     tensor memory (256 columns x 128 lanes of fp32 each), and a tcgen05.commit frees the stage.
 // After the last step the eight decode warps read the accumulator with tcgen05.ld (each warp
 // its 32 lanes and half of the token columns) and write Y (token-major) with coalesced stores.
 // Every wait is bounded.
@@ -30,13 +32,19 @@ namespace ingot {
 static constexpr uint32_t GEMM_M = 128;          // weight rows per CTA (MMA M)
 static constexpr uint32_t GEMM_N = 256;          // tokens per CTA (MMA N)
 static constexpr uint32_t GEMM_K = 64;           // columns per stage (4 MMAs of K 16)
-static constexpr uint32_t GEMM_STAGES = 4;
+static constexpr uint32_t GEMM_MAX_STAGES = 4;
 static constexpr uint32_t GEMM_A_BYTES = GEMM_M * GEMM_K * 2;       // 16 KB
-static constexpr uint32_t GEMM_B_BYTES = GEMM_N * GEMM_K * 2;       // 32 KB
-static constexpr uint32_t GEMM_STAGE_BYTES = GEMM_A_BYTES + GEMM_B_BYTES;
+static constexpr uint32_t GEMM_B_BYTES = GEMM_N * GEMM_K * 2;       // 32 KB per block of 256 tokens
+// NB = blocks of 256 tokens per CTA, each with its own 256-column accumulator: with two, a decoded
+// weight tile is multiplied with 512 tokens (the decode, not the tensor pipe, bounds the kernel),
+// at the price of a two-stage ring (80 KB per stage).
+template <uint32_t NB> struct GemmShape {
+    static constexpr uint32_t STAGES = NB == 1 ? 4u : 2u;
+    static constexpr uint32_t STAGE_BYTES = GEMM_A_BYTES + NB * GEMM_B_BYTES;
+    static constexpr uint32_t SMEM = 1024 + STAGES * STAGE_BYTES + 1024;   // + alignment slack
+};
 static constexpr uint32_t GEMM_DECODE_THREADS = 256;    // 8 decode/epilogue warps
 static constexpr uint32_t GEMM_THREADS = 320;    // + 1 copy warp, 1 MMA warp
-static constexpr uint32_t GEMM_SMEM = 1024 + GEMM_STAGES * GEMM_STAGE_BYTES + 1024;   // + alignment slack
 
 struct GemmArgs {
     const uint8_t *w;          // [rows][stride] of expert `expert`
@@ -44,6 +52,9 @@ struct GemmArgs {
     float *y;                  // [tokens][rows]
     uint32_t cols, rows, stride, kind, tokens;
     int *status;
+    // K split over gridDim.z CTAs when the tiles alone do not fill the GPU: split z writes its partial
+    // products to partial[z][tokens][rows] and a second kernel adds them in order
+    float *partial;
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
@@ -111,6 +122,13 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 
+// Byte i of `v` as a float, through the bits of 2^23 + byte (exact; no integer-to-float conversion,
+// which runs on a slower pipe than the fp32 arithmetic that follows).
+__device__ __forceinline__ float magic_byte(uint32_t v, uint32_t i) {
+    return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650u | i));      // 8388608 + byte
+}
+static constexpr float MAGIC = 8388608.0f;
+
 // ---- decoding 32 consecutive weights of one row into half a swizzled tile row ----------------
 // Split in two: `load` brings the raw bytes of a step into registers (issued one step ahead, so the
 // global-memory latency overlaps the previous step's arithmetic), `emit` decodes and stores.
@@ -146,16 +164,20 @@ __device__ __forceinline__ void emit32_q4k(const GemmRaw &raw, uint32_t ks, uint
     }
     const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&raw.w[0]));
     const float ds = __fmul_rn(dd.x, (float)sc), c = __fmul_rn(dd.y, (float)mn);
+    // ds * q with one rounding, as fmul would give: fma(ds, 2^23 + q, -(ds * 2^23)); the product with
+    // 2^23 is exact
+    const float nds = -__fmul_rn(ds, MAGIC);
     const uint32_t sh = 4u * half;
 #pragma unroll
     for (uint32_t ch = 0; ch < 4; ++ch) {           // 16-byte chunk: 8 columns = bytes 8 ch .. 8 ch + 7 of the group
         uint32_t out[4];
 #pragma unroll
         for (uint32_t i = 0; i < 2; ++i) {
-            const uint32_t wq = raw.w[4 + 2 * ch + i] >> sh;
-            const float a0 = (float)(wq & 15u), a1 = (float)((wq >> 8) & 15u), a2 = (float)((wq >> 16) & 15u), a3 = (float)((wq >> 24) & 15u);
-            out[2 * i] = pack_h2(__fsub_rn(__fmul_rn(ds, a0), c), __fsub_rn(__fmul_rn(ds, a1), c));
-            out[2 * i + 1] = pack_h2(__fsub_rn(__fmul_rn(ds, a2), c), __fsub_rn(__fmul_rn(ds, a3), c));
+            const uint32_t wq = (raw.w[4 + 2 * ch + i] >> sh) & 0x0f0f0f0fu;
+            const float p0 = __fmaf_rn(ds, magic_byte(wq, 0), nds), p1 = __fmaf_rn(ds, magic_byte(wq, 1), nds);
+            const float p2 = __fmaf_rn(ds, magic_byte(wq, 2), nds), p3 = __fmaf_rn(ds, magic_byte(wq, 3), nds);
+            out[2 * i] = pack_h2(__fsub_rn(p0, c), __fsub_rn(p1, c));
+            out[2 * i + 1] = pack_h2(__fsub_rn(p2, c), __fsub_rn(p3, c));
         }
         *reinterpret_cast<uint4 *>(dst_row_base + swz_off(r, 4u * half + ch)) = make_uint4(out[0], out[1], out[2], out[3]);
     }
@@ -170,14 +192,33 @@ __device__ __forceinline__ uint32_t ldg32_u2(const uint8_t *p) {
 // Q6_K: K step ks covers half n = (ks % 4) / 2 of block ks / 4 and quarters 2 (ks % 2) and 2 (ks % 2) + 1;
 // this thread takes quarter q = 2 (ks % 2) + half: 32 columns, two runs of 16 with their own scale.
 // Raw: 8 words of ql, 8 words of qh, the two scale bytes, d.
-__device__ __forceinline__ void load32_q6k(const uint8_t *row, uint32_t ks, uint32_t half, GemmRaw &raw) {
+// rows4: every row starts on a 4-byte boundary (the stride is a multiple of 4).  A block is 210 bytes,
+// so the words of even blocks are then aligned and those of odd blocks lie 2 bytes past a boundary —
+// the same for every thread of the CTA: whole-word loads (and a funnel shift) instead of 16-bit ones.
+__device__ __forceinline__ void load32_q6k(const uint8_t *row, uint32_t ks, uint32_t half, bool rows4, GemmRaw &raw) {
     const uint8_t *b = row + (size_t)(ks >> 2) * 210u;
     const uint32_t n = (ks >> 1) & 1u, q = 2u * (ks & 1u) + half;
     const uint8_t *ql = b + 64u * n + 32u * (q & 1u), *qh = b + 128u + 32u * n;
+    if (!rows4) {
 #pragma unroll
-    for (uint32_t i = 0; i < 8; ++i) {
-        raw.w[i] = ldg32_u2(ql + 4u * i);
-        raw.w[8 + i] = ldg32_u2(qh + 4u * i);
+        for (uint32_t i = 0; i < 8; ++i) {
+            raw.w[i] = ldg32_u2(ql + 4u * i);
+            raw.w[8 + i] = ldg32_u2(qh + 4u * i);
+        }
+    } else if (((ks >> 2) & 1u) == 0u) {
+        const uint32_t *l = reinterpret_cast<const uint32_t *>(ql), *h = reinterpret_cast<const uint32_t *>(qh);
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) { raw.w[i] = l[i]; raw.w[8 + i] = h[i]; }
+    } else {
+        const uint32_t *l = reinterpret_cast<const uint32_t *>(ql - 2), *h = reinterpret_cast<const uint32_t *>(qh - 2);
+        uint32_t tl[9], th[9];
+#pragma unroll
+        for (uint32_t i = 0; i < 9; ++i) { tl[i] = l[i]; th[i] = h[i]; }
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {
+            raw.w[i] = __funnelshift_r(tl[i], tl[i + 1], 16u);
+            raw.w[8 + i] = __funnelshift_r(th[i], th[i + 1], 16u);
+        }
     }
     raw.w[16] = *reinterpret_cast<const unsigned short *>(b + 192u + 8u * n + 2u * q);
     raw.w[17] = *reinterpret_cast<const unsigned short *>(b + 208u);
@@ -195,8 +236,8 @@ __device__ __forceinline__ void emit32_q6k(const GemmRaw &raw, uint32_t ks, uint
         for (uint32_t i = 0; i < 2; ++i) {
             const uint32_t lw = raw.w[2 * ch + i], hw = raw.w[8 + 2 * ch + i];
             const uint32_t v = ((lw >> lsh) & 0x0f0f0f0fu) | (((hw >> hsh) & 0x03030303u) << 4);     // four 6-bit values
-            const float a0 = __fsub_rn((float)(v & 0xffu), 32.0f), a1 = __fsub_rn((float)((v >> 8) & 0xffu), 32.0f);
-            const float a2 = __fsub_rn((float)((v >> 16) & 0xffu), 32.0f), a3 = __fsub_rn((float)(v >> 24), 32.0f);
+            const float a0 = __fsub_rn(magic_byte(v, 0), MAGIC + 32.0f), a1 = __fsub_rn(magic_byte(v, 1), MAGIC + 32.0f);     // q - 32, exact
+            const float a2 = __fsub_rn(magic_byte(v, 2), MAGIC + 32.0f), a3 = __fsub_rn(magic_byte(v, 3), MAGIC + 32.0f);
             out[2 * i] = pack_h2(__fmul_rn(ds, a0), __fmul_rn(ds, a1));
             out[2 * i + 1] = pack_h2(__fmul_rn(ds, a2), __fmul_rn(ds, a3));
         }
@@ -204,21 +245,26 @@ __device__ __forceinline__ void emit32_q6k(const GemmRaw &raw, uint32_t ks, uint
     }
 }
 
+template <uint32_t NB>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                                const __grid_constant__ GemmArgs a) {
+    constexpr uint32_t GEMM_STAGES = GemmShape<NB>::STAGES, GEMM_STAGE_BYTES = GemmShape<NB>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern repeats every 1024 bytes)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
     uint64_t *full_a = reinterpret_cast<uint64_t *>(smem);          // [STAGES] decode warps -> MMA
-    uint64_t *full_b = full_a + GEMM_STAGES;                          // [STAGES] activation warps -> MMA
-    uint64_t *empty = full_b + GEMM_STAGES;                           // [STAGES] MMA -> producers
-    uint64_t *acc_full = empty + GEMM_STAGES;                         // accumulator complete
+    uint64_t *full_b = full_a + GEMM_MAX_STAGES;                      // [STAGES] activation warps -> MMA
+    uint64_t *empty = full_b + GEMM_MAX_STAGES;                       // [STAGES] MMA -> producers
+    uint64_t *acc_full = empty + GEMM_MAX_STAGES;                     // accumulator complete
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     uint8_t *tiles = smem + 1024;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t n0 = blockIdx.x * GEMM_M, t0 = blockIdx.y * GEMM_N;
-    const uint32_t ksteps = a.cols / GEMM_K;
+    const uint32_t n0 = blockIdx.x * GEMM_M, t0 = blockIdx.y * GEMM_N * NB;
+    const uint32_t all_steps = a.cols / GEMM_K;
+    const uint32_t ks0 = (uint32_t)((uint64_t)all_steps * blockIdx.z / gridDim.z);
+    const uint32_t ksteps = (uint32_t)((uint64_t)all_steps * (blockIdx.z + 1) / gridDim.z) - ks0;      // this CTA's K steps
+    float *const out = a.partial ? a.partial + (size_t)blockIdx.z * a.tokens * a.rows : a.y;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < GEMM_STAGES; ++s) {
@@ -229,7 +275,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
         ptx::mbar_init(acc_full, 1);
         ptx::mbar_init_fence();
     }
-    if (warp == 9) tmem_alloc(tmem_slot, GEMM_N);
+    if (warp == 9) tmem_alloc(tmem_slot, GEMM_N * NB);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -244,16 +290,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
         const bool live = n0 + r < a.rows;
         const uint8_t *row = a.w + (size_t)(live ? n0 + r : 0) * a.stride;
         const bool q4k = a.kind == KIND_Q4_K;
+        const bool rows4 = (a.stride % 4u) == 0u;           // the weight base is 16-byte aligned
         GemmRaw cur = {}, nxt = {};
-        if (live) { if (q4k) load32_q4k(row, 0, cur); else load32_q6k(row, 0, half, cur); }
+        if (live) { if (q4k) load32_q4k(row, ks0, cur); else load32_q6k(row, ks0, half, rows4, cur); }
         for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
             const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
-            if (live && ks + 1 < ksteps) { if (q4k) load32_q4k(row, ks + 1, nxt); else load32_q6k(row, ks + 1, half, nxt); }
+            if (live && ks + 1 < ksteps) { if (q4k) load32_q4k(row, ks0 + ks + 1, nxt); else load32_q6k(row, ks0 + ks + 1, half, rows4, nxt); }
             if (!ptx::mbar_wait_sleep<20>(&empty[s], ph ^ 1u)) { failed = true; break; }
             uint8_t *dst = tiles + (size_t)s * GEMM_STAGE_BYTES;
             if (live) {
-                if (q4k) emit32_q4k(cur, ks, half, dst, r);
-                else emit32_q6k(cur, ks, half, dst, r);
+                if (q4k) emit32_q4k(cur, ks0 + ks, half, dst, r);
+                else emit32_q6k(cur, ks0 + ks, half, dst, r);
             } else {
 #pragma unroll
                 for (uint32_t c = 0; c < 4; ++c) *reinterpret_cast<uint4 *>(dst + swz_off(r, 4u * half + c)) = make_uint4(0, 0, 0, 0);
@@ -262,20 +309,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
             ptx::mbar_arrive(&full_a[s]);
             cur = nxt;
         }
-        // ---- epilogue: this warp reads TMEM lanes 32 * (warp % 4) .. + 31 and half of the token columns ----
+        // ---- epilogue: this warp reads TMEM lanes 32 * (warp % 4) .. + 31 and half of the token columns
+        // (with two accumulators: all of accumulator `half`) ----
         if (!failed && !ptx::mbar_wait_sleep<64>(acc_full, 0)) failed = true;
         if (!failed) {
             tc_fence_after();
             const uint32_t rowg = n0 + r;
 #pragma unroll 1
-            for (uint32_t c0 = half * (GEMM_N / 2u); c0 < (half + 1u) * (GEMM_N / 2u); c0 += 32) {
+            for (uint32_t c0 = half * (GEMM_N * NB / 2u); c0 < (half + 1u) * (GEMM_N * NB / 2u); c0 += 32) {
+                if (t0 + c0 >= a.tokens) break;
                 float v[32];
                 tmem_ld32(tmem_base + (((warp & 3u) * 32u) << 16) + c0, v);
                 if (rowg < a.rows) {
 #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) {
                         const uint32_t t = t0 + c0 + i;
-                        if (t < a.tokens) a.y[(size_t)t * a.rows + rowg] = v[i];
+                        if (t < a.tokens) out[(size_t)t * a.rows + rowg] = v[i];
                     }
                 }
             }
@@ -288,11 +337,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
                 const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
                 if (!ptx::mbar_wait_sleep<20>(&empty[s], ph ^ 1u)) { failed = true; break; }
                 uint8_t *dst = tiles + (size_t)s * GEMM_STAGE_BYTES + GEMM_A_BYTES;
-                ptx::mbar_expect_tx(&full_b[s], GEMM_B_BYTES);
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                    ::"r"(ptx::smem_addr(dst)), "l"(&xmap), "r"(ks * GEMM_K), "r"(t0), "r"(ptx::smem_addr(&full_b[s]))
-                    : "memory");
+                ptx::mbar_expect_tx(&full_b[s], NB * GEMM_B_BYTES);
+#pragma unroll
+                for (uint32_t nb = 0; nb < NB; ++nb)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                        ::"r"(ptx::smem_addr(dst + nb * GEMM_B_BYTES)), "l"(&xmap), "r"((ks0 + ks) * GEMM_K), "r"(t0 + nb * GEMM_N),
+                          "r"(ptx::smem_addr(&full_b[s]))
+                        : "memory");
             }
         }
     } else if (lane == 0) {
@@ -306,7 +358,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
             const uint32_t a_addr = ptx::smem_addr(tiles + (size_t)s * GEMM_STAGE_BYTES), b_addr = a_addr + GEMM_A_BYTES;
 #pragma unroll
             for (uint32_t k = 0; k < GEMM_K / 16u; ++k)
-                tc_mma_f16(tmem_base, smem_desc_k128(a_addr + k * 32u), smem_desc_k128(b_addr + k * 32u), idesc, (ks | k) != 0u);
+#pragma unroll
+                for (uint32_t nb = 0; nb < NB; ++nb)
+                    tc_mma_f16(tmem_base + nb * GEMM_N, smem_desc_k128(a_addr + k * 32u), smem_desc_k128(b_addr + nb * GEMM_B_BYTES + k * 32u),
+                               idesc, (ks | k) != 0u);
             tc_commit(&empty[s]);                                     // frees the stage when these MMAs are done
         }
         if (!failed) tc_commit(acc_full);
@@ -314,7 +369,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
     if (failed && lane == 0) set_status_word(a.status, KERNEL_ERR_GEMM_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem_base, GEMM_N);
+    if (warp == 9) tmem_dealloc(tmem_base, GEMM_N * NB);
 }
 
 // ---- activations -> binary16 ------------------------------------------------------------
@@ -333,6 +388,40 @@ __global__ void __launch_bounds__(256) to_half_kernel(const __grid_constant__ To
         a.y[i] = __float2half_rn(load_x(a.x, i, a.bf16));
 }
 
+// ---- sum of the K splits ------------------------------------------------------------------
+
+struct SplitSumArgs {
+    const float *partial;      // [splits][n]
+    float *y;
+    uint64_t n;                // tokens * rows (a multiple of 4 is not required)
+    uint32_t splits;
+};
+
+__global__ void __launch_bounds__(256) split_sum_kernel(const __grid_constant__ SplitSumArgs a) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
+        float s = a.partial[i];
+        for (uint32_t z = 1; z < a.splits; ++z) s = __fadd_rn(s, a.partial[(uint64_t)z * a.n + i]);
+        a.y[i] = s;
+    }
+}
+
+// K splits for a grid of `ctas` tiles: whole extra waves only, at least 1024 columns per split.
+static uint32_t gemm_splits(uint32_t cols, uint32_t rows, uint32_t tokens, uint32_t sm_count) {
+    const uint32_t tok_tile = tokens > GEMM_N ? 2u * GEMM_N : GEMM_N;
+    const uint32_t ctas = ((rows + GEMM_M - 1) / GEMM_M) * ((tokens + tok_tile - 1) / tok_tile);
+    uint32_t splits = sm_count / (ctas ? ctas : 1u);
+    const uint32_t by_k = cols / GEMM_K / 16u;
+    if (splits > by_k) splits = by_k;
+    if (splits > 8u) splits = 8u;
+    return splits < 2u ? 1u : splits;
+}
+
+size_t gemm_scratch_bytes(uint32_t cols, uint32_t rows, uint32_t tokens, uint32_t sm_count) {
+    const size_t xh = ((size_t)tokens * cols * 2u + 255u) & ~(size_t)255u;
+    const uint32_t splits = gemm_splits(cols, rows, tokens, sm_count);
+    return xh + (splits > 1 ? (size_t)splits * tokens * rows * 4u : 0u);
+}
+
 cudaError_t launch_gemm_dequant(const uint8_t *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind, uint32_t expert,
                                 const void *x, uint32_t x_bf16, uint32_t tokens, float *y, void *x_half_scratch,
                                 const LaunchCtx &ctx) {
@@ -347,19 +436,35 @@ cudaError_t launch_gemm_dequant(const uint8_t *w, uint32_t cols, uint32_t rows, 
     if (e != cudaSuccess) return e;
     static bool configured = false;
     if (!configured) {
-        e = cudaFuncSetAttribute(gemm_dequant_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+        e = cudaFuncSetAttribute(gemm_dequant_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmShape<1>::SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_dequant_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmShape<2>::SMEM);
         if (e != cudaSuccess) return e;
         configured = true;
     }
+    const uint32_t splits = gemm_splits(cols, rows, tokens, ctx.sm_count);
+    float *partial = splits > 1 ? reinterpret_cast<float *>(static_cast<uint8_t *>(x_half_scratch) + (((size_t)tokens * cols * 2u + 255u) & ~(size_t)255u))
+                                : nullptr;
     GemmArgs a = {w + (size_t)expert * rows * stride, static_cast<const __half *>(x_half_scratch), y, cols, rows, stride, kind, tokens,
-                  ctx.status};
+                  ctx.status, partial};
     CUtensorMap xmap;
     if (((uintptr_t)x_half_scratch % 16u) ||
         !make_tensor_map_2d(xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_half_scratch, cols, tokens, (uint64_t)cols * 2u, GEMM_K, GEMM_N,
                             CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorNotSupported;
-    dim3 grid((rows + GEMM_M - 1) / GEMM_M, (tokens + GEMM_N - 1) / GEMM_N);
-    gemm_dequant_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, ctx.stream>>>(xmap, a);
+    if (tokens > GEMM_N) {          // 512 tokens per decoded weight tile
+        dim3 grid((rows + GEMM_M - 1) / GEMM_M, (tokens + 2u * GEMM_N - 1) / (2u * GEMM_N), splits);
+        gemm_dequant_tcgen05_kernel<2><<<grid, GEMM_THREADS, GemmShape<2>::SMEM, ctx.stream>>>(xmap, a);
+    } else {
+        dim3 grid((rows + GEMM_M - 1) / GEMM_M, 1, splits);
+        gemm_dequant_tcgen05_kernel<1><<<grid, GEMM_THREADS, GemmShape<1>::SMEM, ctx.stream>>>(xmap, a);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess || splits == 1) return e;
+    SplitSumArgs sa = {partial, y, (uint64_t)tokens * rows, splits};
+    uint64_t sblocks = (sa.n + 255) / 256;
+    if (sblocks > cap) sblocks = cap;
+    split_sum_kernel<<<(uint32_t)sblocks, 256, 0, ctx.stream>>>(sa);
     return cudaGetLastError();
 }
 

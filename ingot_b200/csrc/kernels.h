@@ -89,7 +89,9 @@ cudaError_t launch_expert_layout(const uint32_t *ids, uint32_t n_pairs, uint32_t
                                  const LaunchCtx &ctx);
 cudaError_t launch_combine_packed(const float *routed, const float *w, const uint32_t *inverse, uint32_t width,
                                   uint32_t top, uint32_t tokens, float *y, const LaunchCtx &ctx);
-// Y[T][N] = X[T][K] W^T with binary16 operand staging on tcgen05 (Q4_K, Q6_K).  x_half_scratch: tokens*cols*2 bytes.
+// Y[T][N] = X[T][K] W^T with binary16 operand staging on tcgen05 (Q4_K, Q6_K).  x_half_scratch:
+// gemm_scratch_bytes(...) bytes (the binary16 activations, then the partial products of a K split).
+size_t gemm_scratch_bytes(uint32_t cols, uint32_t rows, uint32_t tokens, uint32_t sm_count);
 cudaError_t launch_gemm_dequant(const uint8_t *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind, uint32_t expert,
                                 const void *x, uint32_t x_bf16, uint32_t tokens, float *y, void *x_half_scratch,
                                 const LaunchCtx &ctx);

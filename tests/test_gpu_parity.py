@@ -471,7 +471,8 @@ def test_moe_layer_matches_oracle_and_expert_shards_sum_to_it(gpu):
 # ---- prefill GEMM on the tensor cores ------------------------------------------------------
 
 @pytest.mark.parametrize("kind", [Q4_K, Q6_K])
-@pytest.mark.parametrize("cols,rows,tokens", [(256, 128, 16), (512, 200, 70), (1024, 128, 256), (2560, 37, 32), (4096, 300, 513)])
+@pytest.mark.parametrize("cols,rows,tokens", [(256, 128, 16), (512, 200, 70), (1024, 128, 256), (2560, 37, 32), (4096, 300, 513),
+                                              (512, 128, 300), (768, 140, 600)])
 def test_gemm_matches_f16_staged_expectation(gpu, kind, cols, rows, tokens):
     # src/expert_bench.rs:734-749: wide GEMM against an f64 dot of F16-rounded weights (and activations)
     raw = synth.random_matrix(kind, cols, rows, 2, seed=cols + rows)
