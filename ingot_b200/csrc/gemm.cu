@@ -9,15 +9,16 @@
 // One CTA computes a 128 (weight rows) x 256 (tokens) tile of Y^T — or, for more than 256 tokens,
 // two such tiles side by side (512 tokens, two accumulators) so that every decoded weight tile is
 // used twice: the decode, not the tensor pipe, bounds this kernel.  Per 64-column K step:
-//   * eight warps decode half a weight row each (32 columns) — the fp32 value d*sc*q - dmin*m
+//   * eight warps (two groups of eight take alternate steps) decode half a weight row each (32
+//     columns) — the fp32 value d*sc*q - dmin*m
 //     (Q4_K) or d*scale*(q-32) (Q6_K) exactly as weight_at forms it, rounded to binary16 — and
 //     store the 128 x 64 tile K-major with the 128-byte swizzle the tensor core expects;
 //   * one thread brings each 256 x 64 activation tile (already binary16) with one 2-D TMA
 //     copy whose tensor map applies the same 128-byte swizzle;
 //   * one thread issues four tcgen05.mma (M 128, N 256, K 16) per accumulator, accumulating in
 //     tensor memory (256 columns x 128 lanes of fp32 each), and a tcgen05.commit frees the stage.
-// After the last step the eight decode warps read the accumulator with tcgen05.ld (each warp
-// its 32 lanes and half of the token columns) and write Y (token-major) with coalesced stores.
+// After the last step the sixteen decode warps read the accumulator with tcgen05.ld (each warp
+// its 32 lanes and a quarter of the token columns) and write Y (token-major) with coalesced stores.
 // Every wait is bounded.
 #include <cuda_fp16.h>
 
@@ -36,15 +37,20 @@ static constexpr uint32_t GEMM_MAX_STAGES = 4;
 static constexpr uint32_t GEMM_A_BYTES = GEMM_M * GEMM_K * 2;       // 16 KB
 static constexpr uint32_t GEMM_B_BYTES = GEMM_N * GEMM_K * 2;       // 32 KB per block of 256 tokens
 // NB = blocks of 256 tokens per CTA, each with its own 256-column accumulator: with two, a decoded
-// weight tile is multiplied with 512 tokens (the decode, not the tensor pipe, bounds the kernel),
-// at the price of a two-stage ring (80 KB per stage).
+// weight tile is multiplied with 512 tokens.  The weight tiles and the activation tiles have rings
+// of their own.  Two stages each with two accumulators (162 KB): a third activation stage (231 KB)
+// left the decode loads 25 KB of L1 and ran Q6_K 25 % slower, Q4_K no faster.
 template <uint32_t NB> struct GemmShape {
-    static constexpr uint32_t STAGES = NB == 1 ? 4u : 2u;
-    static constexpr uint32_t STAGE_BYTES = GEMM_A_BYTES + NB * GEMM_B_BYTES;
-    static constexpr uint32_t SMEM = 1024 + STAGES * STAGE_BYTES + 1024;   // + alignment slack
+    static constexpr uint32_t A_STAGES = NB == 1 ? 4u : 2u;
+    static constexpr uint32_t B_STAGES = NB == 1 ? 4u : 2u;
+    static constexpr uint32_t B_STAGE_BYTES = NB * GEMM_B_BYTES;
+    static constexpr uint32_t SMEM = 1024 + A_STAGES * GEMM_A_BYTES + B_STAGES * B_STAGE_BYTES + 1024;   // + alignment slack
 };
-static constexpr uint32_t GEMM_DECODE_THREADS = 256;    // 8 decode/epilogue warps
-static constexpr uint32_t GEMM_THREADS = 320;    // + 1 copy warp, 1 MMA warp
+static constexpr uint32_t GEMM_DECODE_THREADS = 256;    // 8 warps decode one K step (half a weight row per thread) ...
+static constexpr uint32_t GEMM_DECODE_GROUPS = 2;       // ... and two such groups take alternate steps: the decode is a long
+                                                        // dependent chain per thread, and more warps hide its latency
+static constexpr uint32_t GEMM_DECODE_WARPS = GEMM_DECODE_GROUPS * GEMM_DECODE_THREADS / 32u;
+static constexpr uint32_t GEMM_THREADS = (GEMM_DECODE_WARPS + 2u) * 32u;    // + 1 copy warp, 1 MMA warp
 
 struct GemmArgs {
     const uint8_t *w;          // [rows][stride] of expert `expert`
@@ -248,16 +254,17 @@ __device__ __forceinline__ void emit32_q6k(const GemmRaw &raw, uint32_t ks, uint
 template <uint32_t NB>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                                const __grid_constant__ GemmArgs a) {
-    constexpr uint32_t GEMM_STAGES = GemmShape<NB>::STAGES, GEMM_STAGE_BYTES = GemmShape<NB>::STAGE_BYTES;
+    constexpr uint32_t A_STAGES = GemmShape<NB>::A_STAGES, B_STAGES = GemmShape<NB>::B_STAGES, B_STAGE_BYTES = GemmShape<NB>::B_STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern repeats every 1024 bytes)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
-    uint64_t *full_a = reinterpret_cast<uint64_t *>(smem);          // [STAGES] decode warps -> MMA
-    uint64_t *full_b = full_a + GEMM_MAX_STAGES;                      // [STAGES] activation warps -> MMA
-    uint64_t *empty = full_b + GEMM_MAX_STAGES;                       // [STAGES] MMA -> producers
-    uint64_t *acc_full = empty + GEMM_MAX_STAGES;                     // accumulator complete
+    uint64_t *full_a = reinterpret_cast<uint64_t *>(smem);          // [A_STAGES] decode warps -> MMA
+    uint64_t *full_b = full_a + GEMM_MAX_STAGES;                      // [B_STAGES] copy thread -> MMA
+    uint64_t *empty_a = full_b + GEMM_MAX_STAGES;                     // [A_STAGES] MMA -> decode warps
+    uint64_t *empty_b = empty_a + GEMM_MAX_STAGES;                    // [B_STAGES] MMA -> copy thread
+    uint64_t *acc_full = empty_b + GEMM_MAX_STAGES;                   // accumulator complete
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
-    uint8_t *tiles = smem + 1024;
+    uint8_t *tiles_a = smem + 1024, *tiles_b = tiles_a + A_STAGES * GEMM_A_BYTES;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t n0 = blockIdx.x * GEMM_M, t0 = blockIdx.y * GEMM_N * NB;
@@ -267,15 +274,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
     float *const out = a.partial ? a.partial + (size_t)blockIdx.z * a.tokens * a.rows : a.y;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < GEMM_STAGES; ++s) {
+        for (uint32_t s = 0; s < GEMM_MAX_STAGES; ++s) {
             ptx::mbar_init(&full_a[s], GEMM_DECODE_THREADS);
             ptx::mbar_init(&full_b[s], 1);
-            ptx::mbar_init(&empty[s], 1);
+            ptx::mbar_init(&empty_a[s], 1);
+            ptx::mbar_init(&empty_b[s], 1);
         }
         ptx::mbar_init(acc_full, 1);
         ptx::mbar_init_fence();
     }
-    if (warp == 9) tmem_alloc(tmem_slot, GEMM_N * NB);
+    if (warp == GEMM_DECODE_WARPS + 1u) tmem_alloc(tmem_slot, GEMM_N * NB);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -284,20 +292,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
     ptx::pdl_wait();
 
     bool failed = false;
-    if (warp < 8) {
-        // ---- decode warps: half a weight row (32 columns of the step) per thread ----
-        const uint32_t r = threadIdx.x & 127u, half = threadIdx.x >> 7;   // row inside the tile = TMEM lane
+    if (warp < GEMM_DECODE_WARPS) {
+        // ---- decode warps: half a weight row (32 columns of the step) per thread; group `grp` takes
+        // steps grp, grp + 2, ... ----
+        const uint32_t r = threadIdx.x & 127u, half = (threadIdx.x >> 7) & 1u;   // row inside the tile = TMEM lane
+        const uint32_t grp = threadIdx.x >> 8;
         const bool live = n0 + r < a.rows;
         const uint8_t *row = a.w + (size_t)(live ? n0 + r : 0) * a.stride;
         const bool q4k = a.kind == KIND_Q4_K;
         const bool rows4 = (a.stride % 4u) == 0u;           // the weight base is 16-byte aligned
         GemmRaw cur = {}, nxt = {};
-        if (live) { if (q4k) load32_q4k(row, ks0, cur); else load32_q6k(row, ks0, half, rows4, cur); }
-        for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
-            const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
-            if (live && ks + 1 < ksteps) { if (q4k) load32_q4k(row, ks0 + ks + 1, nxt); else load32_q6k(row, ks0 + ks + 1, half, rows4, nxt); }
-            if (!ptx::mbar_wait_sleep<20>(&empty[s], ph ^ 1u)) { failed = true; break; }
-            uint8_t *dst = tiles + (size_t)s * GEMM_STAGE_BYTES;
+        if (live && grp < ksteps) { if (q4k) load32_q4k(row, ks0 + grp, cur); else load32_q6k(row, ks0 + grp, half, rows4, cur); }
+        for (uint32_t ks = grp; ks < ksteps && !failed; ks += GEMM_DECODE_GROUPS) {
+            const uint32_t s = ks % A_STAGES, ph = (ks / A_STAGES) & 1u;
+            if (live && ks + GEMM_DECODE_GROUPS < ksteps) {
+                if (q4k) load32_q4k(row, ks0 + ks + GEMM_DECODE_GROUPS, nxt);
+                else load32_q6k(row, ks0 + ks + GEMM_DECODE_GROUPS, half, rows4, nxt);
+            }
+            if (!ptx::mbar_wait_sleep<20>(&empty_a[s], ph ^ 1u)) { failed = true; break; }
+            uint8_t *dst = tiles_a + (size_t)s * GEMM_A_BYTES;
             if (live) {
                 if (q4k) emit32_q4k(cur, ks0 + ks, half, dst, r);
                 else emit32_q6k(cur, ks0 + ks, half, dst, r);
@@ -309,14 +322,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
             ptx::mbar_arrive(&full_a[s]);
             cur = nxt;
         }
-        // ---- epilogue: this warp reads TMEM lanes 32 * (warp % 4) .. + 31 and half of the token columns
-        // (with two accumulators: all of accumulator `half`) ----
+        // ---- epilogue: this warp reads TMEM lanes 32 * (warp % 4) .. + 31 and a quarter of the token columns ----
         if (!failed && !ptx::mbar_wait_sleep<64>(acc_full, 0)) failed = true;
         if (!failed) {
             tc_fence_after();
             const uint32_t rowg = n0 + r;
 #pragma unroll 1
-            for (uint32_t c0 = half * (GEMM_N * NB / 2u); c0 < (half + 1u) * (GEMM_N * NB / 2u); c0 += 32) {
+            constexpr uint32_t SLICE = GEMM_N * NB / (GEMM_DECODE_WARPS / 4u);
+            for (uint32_t c0 = (warp >> 2) * SLICE; c0 < ((warp >> 2) + 1u) * SLICE; c0 += 32) {
                 if (t0 + c0 >= a.tokens) break;
                 float v[32];
                 tmem_ld32(tmem_base + (((warp & 3u) * 32u) << 16) + c0, v);
@@ -329,14 +342,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
                 }
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == GEMM_DECODE_WARPS) {
         // ---- copy thread: 256 tokens x 64 columns of binary16 per stage, one TMA copy (rows past the last
         // token read as zero) ----
         if (lane == 0) {
             for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
-                const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
-                if (!ptx::mbar_wait_sleep<20>(&empty[s], ph ^ 1u)) { failed = true; break; }
-                uint8_t *dst = tiles + (size_t)s * GEMM_STAGE_BYTES + GEMM_A_BYTES;
+                const uint32_t s = ks % B_STAGES, ph = (ks / B_STAGES) & 1u;
+                if (!ptx::mbar_wait_sleep<20>(&empty_b[s], ph ^ 1u)) { failed = true; break; }
+                uint8_t *dst = tiles_b + (size_t)s * B_STAGE_BYTES;
                 ptx::mbar_expect_tx(&full_b[s], NB * GEMM_B_BYTES);
 #pragma unroll
                 for (uint32_t nb = 0; nb < NB; ++nb)
@@ -351,25 +364,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
         // ---- MMA thread ----
         const uint32_t idesc = idesc_f16(GEMM_M, GEMM_N);
         for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
-            const uint32_t s = ks % GEMM_STAGES, ph = (ks / GEMM_STAGES) & 1u;
-            if (!ptx::mbar_wait_sleep<0>(&full_a[s], ph) || !ptx::mbar_wait_sleep<0>(&full_b[s], ph)) { failed = true; break; }
+            const uint32_t sa = ks % A_STAGES, sb = ks % B_STAGES;
+            if (!ptx::mbar_wait_sleep<0>(&full_a[sa], (ks / A_STAGES) & 1u) || !ptx::mbar_wait_sleep<0>(&full_b[sb], (ks / B_STAGES) & 1u)) {
+                failed = true;
+                break;
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // tiles were written through the generic proxy
             tc_fence_after();
-            const uint32_t a_addr = ptx::smem_addr(tiles + (size_t)s * GEMM_STAGE_BYTES), b_addr = a_addr + GEMM_A_BYTES;
+            const uint32_t a_addr = ptx::smem_addr(tiles_a + (size_t)sa * GEMM_A_BYTES), b_addr = ptx::smem_addr(tiles_b + (size_t)sb * B_STAGE_BYTES);
 #pragma unroll
             for (uint32_t k = 0; k < GEMM_K / 16u; ++k)
 #pragma unroll
                 for (uint32_t nb = 0; nb < NB; ++nb)
                     tc_mma_f16(tmem_base + nb * GEMM_N, smem_desc_k128(a_addr + k * 32u), smem_desc_k128(b_addr + nb * GEMM_B_BYTES + k * 32u),
                                idesc, (ks | k) != 0u);
-            tc_commit(&empty[s]);                                     // frees the stage when these MMAs are done
+            tc_commit(&empty_a[sa]);                                  // frees the stages when these MMAs are done
+            tc_commit(&empty_b[sb]);
         }
         if (!failed) tc_commit(acc_full);
     }
     if (failed && lane == 0) set_status_word(a.status, KERNEL_ERR_GEMM_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem_base, GEMM_N * NB);
+    if (warp == GEMM_DECODE_WARPS + 1u) tmem_dealloc(tmem_base, GEMM_N * NB);
 }
 
 // ---- activations -> binary16 ------------------------------------------------------------
