@@ -87,6 +87,9 @@ struct MmaArgs {
     float *ns;
     float neps;
     uint32_t nround_bf16;
+    // npack: na holds plain float32 activation rows (row `pair / top` or `pair` of a routed call) that
+    // the CTA only packs — no sum, no norm, no rounding: the packing launch folded into the GEMV
+    uint32_t npack;
 };
 
 static bool mma_kind(uint32_t kind) { return kind == KIND_Q4_K || kind == KIND_Q6_K || kind == KIND_Q4_0 || kind == KIND_Q8_0; }
@@ -569,7 +572,8 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         // kernels/generic.metal:390-404): the 256 consumer threads of every CTA build the packed row ----
         ptx::pdl_wait();
         const uint32_t tid = threadIdx.x, n4 = p.cols >> 2;
-        const float4 *a4 = reinterpret_cast<const float4 *>(a.na), *b4 = reinterpret_cast<const float4 *>(a.nb);
+        const uint32_t in_row = a.ids ? (a.per_pair ? pair : pair / a.top) : 0u;
+        const float4 *a4 = reinterpret_cast<const float4 *>(a.na) + (size_t)in_row * n4, *b4 = reinterpret_cast<const float4 *>(a.nb);
         float *scratch = red;                          // the partial-sum area is idle until the first tile ends
         auto load = [&](uint32_t j) {
             float4 v = a4[j];
@@ -618,7 +622,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                     sum += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
                 }
             }
-            const float inv = 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
+            const float inv = a.npack ? 1.0f : 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
             float mx = 0.f;
 #pragma unroll
             for (uint32_t i = 0; i < NV; ++i) {
@@ -631,7 +635,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 }
             }
             // without a norm weight |x_i| * inv <= sqrt(cols) < 2^14: the packing scale is 1 and the second reduction is not needed
-            const float scale = a.nw ? pack_scale(reduce(mx, true)) : 1.0f;
+            const float scale = (a.nw || a.npack) ? pack_scale(reduce(mx, true)) : 1.0f;
 #pragma unroll
             for (uint32_t i = 0; i < NV; ++i) {
                 if (i * NT >= n4) break;                               // uniform: the quad shuffles keep all lanes
@@ -651,7 +655,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 if (a.ns && cta == 0) reinterpret_cast<float4 *>(a.ns)[j] = v;
                 sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             }
-            const float inv = 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
+            const float inv = a.npack ? 1.0f : 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
             float mx = 0.f;
             for (uint32_t j = tid; j < n4; j += NT) {
                 const float4 v = load(j);
@@ -660,7 +664,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 mx = fmaxf(mx, fmaxf(fmaxf(fabsf(u[0]), fabsf(u[1])), fmaxf(fabsf(u[2]), fabsf(u[3]))));
             }
             // without a norm weight |x_i| * inv <= sqrt(cols) < 2^14: the packing scale is 1 and the second reduction is not needed
-            const float scale = a.nw ? pack_scale(reduce(mx, true)) : 1.0f;
+            const float scale = (a.nw || a.npack) ? pack_scale(reduce(mx, true)) : 1.0f;
             for (uint32_t j0 = 0; j0 < n4; j0 += NT) {                 // uniform trip count: the quad shuffles keep all lanes
                 const uint32_t j = j0 + tid;
                 const bool live = j < n4;
@@ -1295,8 +1299,12 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
         if (tiles <= plan.ctas && load_full < load_now) plan.ctas = tiles;
     }
     const uint8_t *xp = static_cast<const uint8_t *>(c.x);
+    // plain float32 rows are packed by the CTAs themselves (one launch, as the reference's matmul is)
+    const bool pack_inside = !c.norm_a && !c.x_packed && !c.x_bf16 && ((uintptr_t)c.x % 16u) == 0;
     if (c.norm_a) {
         if (routed || c.cols % 64u) return false;
+        xp = nullptr;
+    } else if (pack_inside) {
         xp = nullptr;
     } else if (!c.x_packed) {
         const uint32_t x_rows = routed ? (c.per_pair ? c.pairs : (c.pairs + (c.top ? c.top : 1u) - 1) / (c.top ? c.top : 1u)) : 1u;
@@ -1313,6 +1321,7 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     a.per_pair = c.per_pair; a.top = c.top ? c.top : 1u; a.glu = c.glu;
     a.status = ctx.status;
     a.na = c.norm_a; a.nb = c.norm_b; a.nw = c.norm_w; a.ns = c.norm_s; a.neps = c.norm_eps; a.nround_bf16 = c.norm_round_bf16;
+    if (pack_inside) { a.na = static_cast<const float *>(c.x); a.npack = 1u; }
     const dim3 grid(plan.ctas, gy);
     switch (c.kind) {
     case KIND_Q4_K: err = launch_mma_k<KIND_Q4_K>(a, grid, ctx.stream, ctx.pdl, occ); break;
