@@ -108,17 +108,17 @@ class DecodeChain:
         self.packed_hi = (batch > 1 and packed and x_kind == BF16 and world == 1
                           and all(k in (synth.Q4_K, synth.Q6_K) for k in shape.kinds.values())
                           and all(c % 2048 == 0 for _, c, _ in layer_roles(shape)))
+        # add_rms fused into the projections that consume it (one token, tensor-core GEMV kinds only)
+        tc_kinds = (synth.Q4_0, synth.Q8_0, synth.Q4_K, synth.Q6_K)
+        self.fused_norm = (fused_norm and self.packed and all(k in tc_kinds for k in shape.kinds.values())
+                           and all(synth.stride_of(shape.kinds[r], c) % 16 == 0 for r, c, _ in layer_roles(shape)))
         # q, k and v read the same activations and write different buffers: issue them concurrently
-        # (the reference's independent_projections scope) when nothing has to be gathered between them
-        self.independent_qkv = independent_qkv and world == 1 and self.packed
+        # (the reference's independent_projections scope); row shards: only the fused step, which gathers q after the scope
+        self.independent_qkv = independent_qkv and self.packed and (world == 1 or self.fused_norm)
         # ... and the scope launches them as one grid when all three take the tensor-core GEMV
         self.grouped_qkv = self.independent_qkv and all(
             shape.kinds[r] in (synth.Q4_0, synth.Q8_0, synth.Q4_K, synth.Q6_K) and shape.hidden % 64 == 0
             and synth.stride_of(shape.kinds[r], shape.hidden) % 16 == 0 for r in ("q", "k", "v"))
-        # add_rms fused into the projections that consume it (one token, tensor-core GEMV kinds only)
-        tc_kinds = (synth.Q4_0, synth.Q8_0, synth.Q4_K, synth.Q6_K)
-        self.fused_norm = (fused_norm and self.packed and world == 1 and all(k in tc_kinds for k in shape.kinds.values())
-                           and all(synth.stride_of(shape.kinds[r], c) % 16 == 0 for r, c, _ in layer_roles(shape)))
         self.h2 = gpu.zeros(b * h) if self.fused_norm else None        # the residual stream alternates between h and h2
         if self.packed or self.packed_hi:
             size = (lambda c: batch * gpu.packed_hi_bytes(c)) if self.packed_hi else gpu.packed_x_bytes
@@ -182,12 +182,19 @@ class DecodeChain:
             self.all_gather(dst, y, self.batch, t.dims[1])
 
     # ---- the same step with every add_rms fused into its consumers ------------------------
-    def _normed(self, w: Weight, a: Buffer, b: Buffer | None, s: Buffer | None, y: Buffer) -> None:
+    def _normed(self, w: Weight, a: Buffer, b: Buffer | None, s: Buffer | None, y: Buffer, gather: bool = True,
+                shard_only: bool = False) -> None:
+        """y = w . rms_norm(a + b).  Row shards: the result goes to the scratch shard and is gathered into y,
+        unless `shard_only` (nobody reads the whole vector: the shard stays at the front of y) or
+        `gather` is False (the caller gathers later, e.g. after an independent scope)."""
         g, t = self.gpu, w.t
+        dst = y if (self.world == 1 or shard_only) else self.part      # every rank norms the whole input itself
         g._check(g._lib.ingot_matmul_normed(g._h, w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, a.ptr,
                                             b.ptr if b else None, None, s.ptr if s else None, 1e-6, 1 if b else 0,
-                                            int(self.x_kind == BF16), y.ptr))
+                                            int(self.x_kind == BF16), dst.ptr))
         self.launches_per_step += 1
+        if self.world > 1 and gather and not shard_only:
+            self.all_gather(dst, y, self.batch, t.dims[1])
 
     def _step_fused(self) -> None:
         s, g = self.shape, self.gpu
@@ -200,9 +207,12 @@ class DecodeChain:
             summed = bufs[nxt] if delta else None
             with g.independent() if self.independent_qkv else _null_scope():
                 # the two small projections first: their CTAs leave room for q's to start beside them
-                self._normed(ws["k"], cur, delta, None, self.k)
-                self._normed(ws["v"], cur, delta, None, self.v)
-                self._normed(ws["q"], cur, delta, summed, self.q)
+                # (attention over row-sharded k and v is local to a rank's heads: they are never gathered)
+                self._normed(ws["k"], cur, delta, None, self.k, shard_only=True)
+                self._normed(ws["v"], cur, delta, None, self.v, shard_only=True)
+                self._normed(ws["q"], cur, delta, summed, self.q, gather=False)
+            if self.world > 1:
+                self.all_gather(self.part, self.q, self.batch, ws["q"].t.dims[1])
             if self.independent_qkv:
                 self.launches_per_step -= 2          # the scope issues its three projections as one grid
             if delta:
@@ -210,10 +220,13 @@ class DecodeChain:
             self._normed(ws["o"], self.q, None, None, self.o)                 # stands in for attention: o(rms_norm(q))
             t = ws["gate"].t
             after = bufs[nxt]
+            act = self.act if self.world == 1 else self.part
             g._check(g._lib.ingot_gate_up_normed(g._h, ws["gate"].buffer.ptr, ws["up"].buffer.ptr, t.dims[0], t.dims[1],
                                                  t.stride, t.kind, cur.ptr, self.o.ptr, None, after.ptr, 1e-6, 1,
-                                                 int(self.x_kind == BF16), int(s.gelu), self.act.ptr))
+                                                 int(self.x_kind == BF16), int(s.gelu), act.ptr))
             self.launches_per_step += 1
+            if self.world > 1:
+                self.all_gather(act, self.act, self.batch, t.dims[1])
             cur, nxt = after, nxt ^ 1
             self._normed(ws["down"], self.act, None, None, self.d)
             delta = self.d

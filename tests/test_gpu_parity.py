@@ -643,6 +643,60 @@ def test_fused_and_unfused_chains_agree(gpu):
     assert np.abs(logits[0] - logits[1]).max() <= 2e-2 * scale     # bfloat16 rounding points move with the sum order
 
 
+def test_row_sharded_chain_matches_the_unsharded_chain(gpu):
+    # two ranks of the row-sharded (tensor-parallel) step in lock step on one device, the all-gather done
+    # through the host: every rank's logits equal the unsharded chain's bit for bit (a row's arithmetic
+    # does not depend on which rank or CTA owns it)
+    import threading
+    from ingot_b200 import Gpu
+    from ingot_b200.chain import QWEN3_8B, DecodeChain
+    h0 = np.random.default_rng(1).normal(0, 1, (1, QWEN3_8B.hidden)).astype(np.float32)
+    ref = DecodeChain(gpu, QWEN3_8B, batch=1, x_kind=BF16, seed=3, layers=2)
+    gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, ref.h_in.ptr, h0.ctypes.data, h0.nbytes))
+    ref.step()
+    gpu.complete()
+    want = gpu.read_f32(ref.logits).copy()
+    del ref
+    world = 2
+    handles = [Gpu(0) for _ in range(world)]
+    slots, bar, errors, got = [None] * world, threading.Barrier(world, timeout=120), [], [None] * world
+
+    def gather_for(r):
+        def all_gather(part, full, batch, rows_local):
+            g = handles[r]
+            g.complete()
+            slots[r] = g.read_f32(part, batch * rows_local).copy()
+            bar.wait()
+            whole = np.concatenate(slots)
+            bar.wait()
+            g._check(g._lib.ingot_buffer_upload(g._h, full.ptr, whole.ctypes.data, whole.nbytes))
+        return all_gather
+
+    def run(r):
+        try:
+            g = handles[r]
+            c = DecodeChain(g, QWEN3_8B, batch=1, x_kind=BF16, seed=3, layers=2, rank=r, world=world, all_gather=gather_for(r))
+            assert c.fused_norm
+            g._check(g._lib.ingot_buffer_upload(g._h, c.h_in.ptr, h0.ctypes.data, h0.nbytes))
+            c.step()
+            g.complete()
+            got[r] = g.read_f32(c.logits).copy()
+        except Exception as e:          # a failed rank must not leave the other one waiting
+            errors.append(e)
+            bar.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for g in handles:
+        g.close()
+    assert not errors, errors
+    for r in range(world):
+        assert np.array_equal(got[r].view(np.uint32), want.view(np.uint32))
+
+
 # ---- Gpu::moe (host-vector convenience) -------------------------------------------------------
 
 def test_moe_host_wrapper_matches_oracle(gpu):
