@@ -346,7 +346,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
         // ---- copy thread: 256 tokens x 64 columns of binary16 per stage, one TMA copy (rows past the last
         // token read as zero) ----
         if (lane == 0) {
-            for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
+            uint32_t issued = 0;
+            for (uint32_t ks = 0; ks < ksteps && !failed; ++ks, ++issued) {
                 const uint32_t s = ks % B_STAGES, ph = (ks / B_STAGES) & 1u;
                 if (!ptx::mbar_wait_sleep<20>(&empty_b[s], ph ^ 1u)) { failed = true; break; }
                 uint8_t *dst = tiles_b + (size_t)s * B_STAGE_BYTES;
@@ -359,6 +360,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
                           "r"(ptx::smem_addr(&full_b[s]))
                         : "memory");
             }
+            // no copy of this CTA may still be in flight when it leaves (the MMA thread has waited for
+            // all of them unless a wait ran out): wait for the last copies of every stage, bounded
+            for (uint32_t j = issued > B_STAGES ? issued - B_STAGES : 0u; j < issued; ++j)
+                if (!ptx::mbar_wait_sleep<20>(&full_b[j % B_STAGES], (j / B_STAGES) & 1u)) failed = true;
         }
     } else if (lane == 0) {
         // ---- MMA thread ----
@@ -381,7 +386,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
             tc_commit(&empty_a[sa]);                                  // frees the stages when these MMAs are done
             tc_commit(&empty_b[sb]);
         }
-        if (!failed) tc_commit(acc_full);
+        tc_commit(acc_full);
+        // after a wait that ran out nobody reads the accumulator: let the issued MMAs finish (bounded)
+        // before tensor memory is freed
+        if (failed) ptx::mbar_wait_sleep<64>(acc_full, 0);
     }
     if (failed && lane == 0) set_status_word(a.status, KERNEL_ERR_GEMM_TIMEOUT);
     tc_fence_before();
