@@ -15,7 +15,7 @@
 //     store the 128 x 64 tile K-major with the 128-byte swizzle the tensor core expects;
 //   * one thread brings each 256 x 64 activation tile (already binary16) with one 2-D TMA
 //     copy whose tensor map applies the same 128-byte swizzle;
-//   * one thread issues four tcgen05.mma (M 128, N 256, K 16) per accumulator, accumulating in
+//   * one thread per accumulator issues four tcgen05.mma (M 128, N 256, K 16), accumulating in
 //     tensor memory (256 columns x 128 lanes of fp32 each), and a tcgen05.commit frees the stage.
 // After the last step the sixteen decode warps read the accumulator with tcgen05.ld (each warp
 // its 32 lanes and a quarter of the token columns) and write Y (token-major) with coalesced stores.
@@ -50,7 +50,9 @@ static constexpr uint32_t GEMM_DECODE_THREADS = 256;    // 8 warps decode one K 
 static constexpr uint32_t GEMM_DECODE_GROUPS = 2;       // ... and two such groups take alternate steps: the decode is a long
                                                         // dependent chain per thread, and more warps hide its latency
 static constexpr uint32_t GEMM_DECODE_WARPS = GEMM_DECODE_GROUPS * GEMM_DECODE_THREADS / 32u;
-static constexpr uint32_t GEMM_THREADS = (GEMM_DECODE_WARPS + 2u) * 32u;    // + 1 copy warp, 1 MMA warp
+// + 1 copy warp and one MMA warp per accumulator: issuing a tcgen05.mma costs its thread about 100 cycles,
+// so one thread issuing the eight MMAs of a step (two accumulators) would take most of the step's tensor time
+static constexpr uint32_t GEMM_THREADS = (GEMM_DECODE_WARPS + 3u) * 32u;
 
 struct GemmArgs {
     const uint8_t *w;          // [rows][stride] of expert `expert`
@@ -277,10 +279,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
         for (uint32_t s = 0; s < GEMM_MAX_STAGES; ++s) {
             ptx::mbar_init(&full_a[s], GEMM_DECODE_THREADS);
             ptx::mbar_init(&full_b[s], 1);
-            ptx::mbar_init(&empty_a[s], 1);
-            ptx::mbar_init(&empty_b[s], 1);
+            ptx::mbar_init(&empty_a[s], NB);          // one commit per MMA thread
+            ptx::mbar_init(&empty_b[s], NB);
         }
-        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_full, NB);
         ptx::mbar_init_fence();
     }
     if (warp == GEMM_DECODE_WARPS + 1u) tmem_alloc(tmem_slot, GEMM_N * NB);
@@ -365,8 +367,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
             for (uint32_t j = issued > B_STAGES ? issued - B_STAGES : 0u; j < issued; ++j)
                 if (!ptx::mbar_wait_sleep<20>(&full_b[j % B_STAGES], (j / B_STAGES) & 1u)) failed = true;
         }
-    } else if (lane == 0) {
-        // ---- MMA thread ----
+    } else if (lane == 0 && warp - (GEMM_DECODE_WARPS + 1u) < NB) {
+        // ---- MMA thread of accumulator nb ----
+        const uint32_t nb = warp - (GEMM_DECODE_WARPS + 1u);
         const uint32_t idesc = idesc_f16(GEMM_M, GEMM_N);
         for (uint32_t ks = 0; ks < ksteps && !failed; ++ks) {
             const uint32_t sa = ks % A_STAGES, sb = ks % B_STAGES;
@@ -379,10 +382,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
             const uint32_t a_addr = ptx::smem_addr(tiles_a + (size_t)sa * GEMM_A_BYTES), b_addr = ptx::smem_addr(tiles_b + (size_t)sb * B_STAGE_BYTES);
 #pragma unroll
             for (uint32_t k = 0; k < GEMM_K / 16u; ++k)
-#pragma unroll
-                for (uint32_t nb = 0; nb < NB; ++nb)
-                    tc_mma_f16(tmem_base + nb * GEMM_N, smem_desc_k128(a_addr + k * 32u), smem_desc_k128(b_addr + nb * GEMM_B_BYTES + k * 32u),
-                               idesc, (ks | k) != 0u);
+                tc_mma_f16(tmem_base + nb * GEMM_N, smem_desc_k128(a_addr + k * 32u), smem_desc_k128(b_addr + nb * GEMM_B_BYTES + k * 32u),
+                           idesc, (ks | k) != 0u);
             tc_commit(&empty_a[sa]);                                  // frees the stages when these MMAs are done
             tc_commit(&empty_b[sb]);
         }
