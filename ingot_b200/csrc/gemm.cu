@@ -197,17 +197,46 @@ __device__ __forceinline__ uint32_t ldg32_u2(const uint8_t *p) {
     return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
 }
 
+// 32 bytes at p, where p is CLS bytes (0, 2, 4 or 6) past an 8-byte boundary: four or five 64-bit loads and,
+// for the odd classes, funnel shifts.  The decode of Q6_K is bound by the number of its global loads.
+template <uint32_t CLS>
+__device__ __forceinline__ void ldg_span32(const uint8_t *p, uint32_t *out) {
+    const uint2 *q = reinterpret_cast<const uint2 *>(p - CLS);
+    if (CLS == 0) {
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) { const uint2 v = q[i]; out[2 * i] = v.x; out[2 * i + 1] = v.y; }
+        return;
+    }
+    uint32_t t[10];
+#pragma unroll
+    for (uint32_t i = 0; i < 5; ++i) { const uint2 v = q[i]; t[2 * i] = v.x; t[2 * i + 1] = v.y; }
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        if (CLS == 4) out[i] = t[i + 1];
+        else if (CLS == 2) out[i] = __funnelshift_r(t[i], t[i + 1], 16u);
+        else out[i] = __funnelshift_r(t[i + 1], t[i + 2], 16u);
+    }
+}
+
 // Q6_K: K step ks covers half n = (ks % 4) / 2 of block ks / 4 and quarters 2 (ks % 2) and 2 (ks % 2) + 1;
 // this thread takes quarter q = 2 (ks % 2) + half: 32 columns, two runs of 16 with their own scale.
 // Raw: 8 words of ql, 8 words of qh, the two scale bytes, d.
 // rows4: every row starts on a 4-byte boundary (the stride is a multiple of 4).  A block is 210 bytes,
 // so the words of even blocks are then aligned and those of odd blocks lie 2 bytes past a boundary —
 // the same for every thread of the CTA: whole-word loads (and a funnel shift) instead of 16-bit ones.
-__device__ __forceinline__ void load32_q6k(const uint8_t *row, uint32_t ks, uint32_t half, bool rows4, GemmRaw &raw) {
+// rows8: every row starts on an 8-byte boundary: block b then starts 2 b mod 8 bytes past one.
+__device__ __forceinline__ void load32_q6k(const uint8_t *row, uint32_t ks, uint32_t half, bool rows4, bool rows8, GemmRaw &raw) {
     const uint8_t *b = row + (size_t)(ks >> 2) * 210u;
     const uint32_t n = (ks >> 1) & 1u, q = 2u * (ks & 1u) + half;
     const uint8_t *ql = b + 64u * n + 32u * (q & 1u), *qh = b + 128u + 32u * n;
-    if (!rows4) {
+    if (rows8) {
+        switch ((ks >> 2) & 3u) {
+        case 0: ldg_span32<0>(ql, raw.w); ldg_span32<0>(qh, raw.w + 8); break;
+        case 1: ldg_span32<2>(ql, raw.w); ldg_span32<2>(qh, raw.w + 8); break;
+        case 2: ldg_span32<4>(ql, raw.w); ldg_span32<4>(qh, raw.w + 8); break;
+        default: ldg_span32<6>(ql, raw.w); ldg_span32<6>(qh, raw.w + 8); break;
+        }
+    } else if (!rows4) {
 #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) {
             raw.w[i] = ldg32_u2(ql + 4u * i);
@@ -302,14 +331,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
         const bool live = n0 + r < a.rows;
         const uint8_t *row = a.w + (size_t)(live ? n0 + r : 0) * a.stride;
         const bool q4k = a.kind == KIND_Q4_K;
-        const bool rows4 = (a.stride % 4u) == 0u;           // the weight base is 16-byte aligned
+        const bool rows4 = (a.stride % 4u) == 0u, rows8 = (a.stride % 8u) == 0u;           // the weight base is 16-byte aligned
         GemmRaw cur = {}, nxt = {};
-        if (live && grp < ksteps) { if (q4k) load32_q4k(row, ks0 + grp, cur); else load32_q6k(row, ks0 + grp, half, rows4, cur); }
+        if (live && grp < ksteps) { if (q4k) load32_q4k(row, ks0 + grp, cur); else load32_q6k(row, ks0 + grp, half, rows4, rows8, cur); }
         for (uint32_t ks = grp; ks < ksteps && !failed; ks += GEMM_DECODE_GROUPS) {
             const uint32_t s = ks % A_STAGES, ph = (ks / A_STAGES) & 1u;
             if (live && ks + GEMM_DECODE_GROUPS < ksteps) {
                 if (q4k) load32_q4k(row, ks0 + ks + GEMM_DECODE_GROUPS, nxt);
-                else load32_q6k(row, ks0 + ks + GEMM_DECODE_GROUPS, half, rows4, nxt);
+                else load32_q6k(row, ks0 + ks + GEMM_DECODE_GROUPS, half, rows4, rows8, nxt);
             }
             if (!ptx::mbar_wait_sleep<20>(&empty_a[s], ph ^ 1u)) { failed = true; break; }
             uint8_t *dst = tiles_a + (size_t)s * GEMM_A_BYTES;
