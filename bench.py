@@ -49,8 +49,49 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
 
 
+class _NvmlPoller:
+    """SM clock and clock-event reasons read through NVML every 10 ms on a thread (read-only queries): the
+    timed region of a short run is over before nvidia-smi's 100 ms loop has sampled it twice."""
+    BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+
+    def __init__(self, device: int):
+        self.sm, self.reasons, self.max_mhz, self.thread = [], set(), None, None
+        try:
+            import threading
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv, self.h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(device)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.stop_flag = threading.Event()
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.thread = None
+
+    def _run(self):
+        nv = self.nv
+        read = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self.stop_flag.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(read(self.h))
+                for bit, name in self.BITS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            self.stop_flag.wait(0.01)
+
+    def stop(self):
+        if self.thread:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+        return self.sm, self.reasons, self.max_mhz
+
+
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 100 ms while timing."""
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms while timing, and the same through NVML
+    every 10 ms."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -59,6 +100,7 @@ class ClockSampler:
         self.device, self.proc, self.path = device, None, None
 
     def start(self):
+        self.nvml = _NvmlPoller(self.device)
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -70,7 +112,11 @@ class ClockSampler:
             self.proc = None
 
     def stop(self) -> dict:
+        nv_sm, nv_reasons, nv_max = self.nvml.stop() if getattr(self, "nvml", None) else ([], set(), None)
         if not self.proc:
+            if nv_sm:
+                return {"sm_mhz": statistics.median(nv_sm), "sm_max_mhz": nv_max, "samples": len(nv_sm),
+                        "reasons": sorted(nv_reasons), "source": "nvml every 10 ms"}
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
@@ -94,6 +140,10 @@ class ClockSampler:
                     if val.lower().startswith("active"):
                         reasons.add(name)
         os.unlink(self.path)
+        if nv_sm:       # the denser record; nvidia-smi's samples and reasons are merged in
+            return {"sm_mhz": statistics.median(nv_sm + sm), "sm_max_mhz": max(smax + [nv_max]) if nv_max else (max(smax) if smax else None),
+                    "samples": len(nv_sm) + len(sm), "reasons": sorted(reasons | nv_reasons),
+                    "source": "nvml every 10 ms + nvidia-smi every 100 ms"}
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
 
