@@ -37,6 +37,23 @@ class DenseShape:
     gelu: bool = False
 
 
+@dataclass
+class FusedOp:
+    """One projection of the fused step together with the add_rms it consumes."""
+    name: str
+    layer: int
+    w: Weight
+    w2: Weight | None      # the up matrix of a fused gate/up
+    a: Buffer
+    b: Buffer | None
+    s: Buffer | None
+    y: Buffer
+    scope: int | None = None
+    shard_only: bool = False      # row shards: nobody reads the whole vector, the shard stays at the front of y
+    gather_late: bool = False     # row shards: gathered after the operator's scope has closed
+    gelu: bool = False
+
+
 QWEN3_8B = DenseShape("qwen3-8b-q4_k_m", 36, 4096, 4096, 1024, 12288, 151936,
                       {"q": synth.Q4_K, "k": synth.Q4_K, "v": synth.Q6_K, "o": synth.Q4_K, "gate": synth.Q4_K,
                        "up": synth.Q4_K, "down": synth.Q6_K, "head": synth.Q6_K})
@@ -53,6 +70,12 @@ def layer_roles(s: DenseShape):
 def weight_bytes_per_token(s: DenseShape) -> int:
     per_layer = sum(synth.stride_of(s.kinds[r], c) * n for r, c, n in layer_roles(s))
     return s.layers * per_layer + synth.stride_of(s.kinds["head"], s.hidden) * s.vocab
+
+
+def weight_seed(seed: int, layer: int, role: str) -> int:
+    """Seed of the synthetic matrix of `role` in `layer` (the head counts as layer `n_layers`)."""
+    role_id = ["q", "k", "v", "o", "gate", "up", "down", "head"].index(role)
+    return (seed * 1000003 + layer * 64 + role_id) & 0x7FFFFFFF
 
 
 def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
@@ -130,8 +153,7 @@ class DecodeChain:
     def _make(self, layer, role, cols, rows, kind, seed, keep) -> Weight:
         r0, r1 = shard_rows(rows, self.rank, self.world)
         stride = synth.stride_of(kind, cols)
-        role_id = ["q", "k", "v", "o", "gate", "up", "down", "head"].index(role)
-        full_seed = (seed * 1000003 + layer * 64 + role_id) & 0x7FFFFFFF
+        full_seed = weight_seed(seed, layer, role)
         if self.world == 1:
             raw = synth.random_matrix(kind, cols, rows, seed=full_seed)
         else:   # every rank draws the same full matrix stream and keeps its rows
@@ -182,55 +204,71 @@ class DecodeChain:
             self.all_gather(dst, y, self.batch, t.dims[1])
 
     # ---- the same step with every add_rms fused into its consumers ------------------------
-    def _normed(self, w: Weight, a: Buffer, b: Buffer | None, s: Buffer | None, y: Buffer, gather: bool = True,
-                shard_only: bool = False) -> None:
-        """y = w . rms_norm(a + b).  Row shards: the result goes to the scratch shard and is gathered into y,
-        unless `shard_only` (nobody reads the whole vector: the shard stays at the front of y) or
-        `gather` is False (the caller gathers later, e.g. after an independent scope)."""
-        g, t = self.gpu, w.t
-        dst = y if (self.world == 1 or shard_only) else self.part      # every rank norms the whole input itself
-        g._check(g._lib.ingot_matmul_normed(g._h, w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, a.ptr,
-                                            b.ptr if b else None, None, s.ptr if s else None, 1e-6, 1 if b else 0,
-                                            int(self.x_kind == BF16), dst.ptr))
-        self.launches_per_step += 1
-        if self.world > 1 and gather and not shard_only:
-            self.all_gather(dst, y, self.batch, t.dims[1])
-
-    def _step_fused(self) -> None:
-        s, g = self.shape, self.gpu
-        self.launches_per_step = 0
+    def fused_ops(self) -> list["FusedOp"]:
+        """The fused step as a list of operators in issue order: every projection with the add_rms it
+        consumes (`y = w . rms_norm(a + b)`, the sum stored to `s`).  Operators that share a `scope`
+        number are independent of each other and are issued inside one independent scope."""
+        s = self.shape
+        ops: list[FusedOp] = []
         cur, delta = self.h_in, None            # residual stream so far and the update not yet added to it
         bufs = [self.h, self.h2]
         nxt = 0
-        for ws in self.weights:
+        for li, ws in enumerate(self.weights):
             # q, k, v read rms_norm(cur + delta); q also stores the sum
             summed = bufs[nxt] if delta else None
-            with g.independent() if self.independent_qkv else _null_scope():
-                # the two small projections first: their CTAs leave room for q's to start beside them
-                # (attention over row-sharded k and v is local to a rank's heads: they are never gathered)
-                self._normed(ws["k"], cur, delta, None, self.k, shard_only=True)
-                self._normed(ws["v"], cur, delta, None, self.v, shard_only=True)
-                self._normed(ws["q"], cur, delta, summed, self.q, gather=False)
-            if self.world > 1:
-                self.all_gather(self.part, self.q, self.batch, ws["q"].t.dims[1])
-            if self.independent_qkv:
-                self.launches_per_step -= 2          # the scope issues its three projections as one grid
+            scope = li if self.independent_qkv else None
+            # the two small projections first: their CTAs leave room for q's to start beside them
+            # (attention over row-sharded k and v is local to a rank's heads: they are never gathered)
+            ops.append(FusedOp("k", li, ws["k"], None, cur, delta, None, self.k, scope=scope, shard_only=True))
+            ops.append(FusedOp("v", li, ws["v"], None, cur, delta, None, self.v, scope=scope, shard_only=True))
+            ops.append(FusedOp("q", li, ws["q"], None, cur, delta, summed, self.q, scope=scope, gather_late=True))
             if delta:
                 cur, nxt = summed, nxt ^ 1
-            self._normed(ws["o"], self.q, None, None, self.o)                 # stands in for attention: o(rms_norm(q))
-            t = ws["gate"].t
+            ops.append(FusedOp("o", li, ws["o"], None, self.q, None, None, self.o))      # stands in for attention: o(rms_norm(q))
             after = bufs[nxt]
-            act = self.act if self.world == 1 else self.part
-            g._check(g._lib.ingot_gate_up_normed(g._h, ws["gate"].buffer.ptr, ws["up"].buffer.ptr, t.dims[0], t.dims[1],
-                                                 t.stride, t.kind, cur.ptr, self.o.ptr, None, after.ptr, 1e-6, 1,
-                                                 int(self.x_kind == BF16), int(s.gelu), act.ptr))
-            self.launches_per_step += 1
-            if self.world > 1:
-                self.all_gather(act, self.act, self.batch, t.dims[1])
+            ops.append(FusedOp("gate_up", li, ws["gate"], ws["up"], cur, self.o, after, self.act, gelu=s.gelu))
             cur, nxt = after, nxt ^ 1
-            self._normed(ws["down"], self.act, None, None, self.d)
+            ops.append(FusedOp("down", li, ws["down"], None, self.act, None, None, self.d))
             delta = self.d
-        self._normed(self.head, cur, delta, None, self.logits)
+        ops.append(FusedOp("head", self.n_layers, self.head, None, cur, delta, None, self.logits))
+        return ops
+
+    def issue(self, op: "FusedOp") -> None:
+        """Issues one fused operator (and, on a row shard, the gather of its result)."""
+        g, t = self.gpu, op.w.t
+        sharded = self.world > 1 and not op.shard_only
+        dst = self.part if sharded else op.y           # every rank norms the whole input itself
+        a, b, sm = op.a.ptr, op.b.ptr if op.b else None, op.s.ptr if op.s else None
+        rb = int(self.x_kind == BF16)
+        if op.w2 is None:
+            g._check(g._lib.ingot_matmul_normed(g._h, op.w.buffer.ptr, t.dims[0], t.dims[1], t.stride, t.kind, 0, a, b, None,
+                                                sm, 1e-6, 1 if op.b else 0, rb, dst.ptr))
+        else:
+            g._check(g._lib.ingot_gate_up_normed(g._h, op.w.buffer.ptr, op.w2.buffer.ptr, t.dims[0], t.dims[1], t.stride,
+                                                 t.kind, a, b, None, sm, 1e-6, 1 if op.b else 0, rb, int(op.gelu), dst.ptr))
+        self.launches_per_step += 1
+        if sharded and not op.gather_late:
+            self.all_gather(dst, op.y, self.batch, t.dims[1])
+
+    def _step_fused(self) -> None:
+        g = self.gpu
+        self.launches_per_step = 0
+        ops = self.fused_ops()
+        i = 0
+        while i < len(ops):
+            j = i + 1
+            if ops[i].scope is not None:
+                while j < len(ops) and ops[j].scope == ops[i].scope:
+                    j += 1
+            with g.independent() if j - i > 1 else _null_scope():
+                for op in ops[i:j]:
+                    self.issue(op)
+            for op in ops[i:j]:
+                if self.world > 1 and op.gather_late and not op.shard_only:
+                    self.all_gather(self.part, op.y, self.batch, op.w.t.dims[1])
+            if j - i > 1:
+                self.launches_per_step -= j - i - 1      # the scope issues its projections as one grid
+            i = j
 
     def step(self) -> None:
         """Issues one token step on the handle's stream (asynchronous)."""

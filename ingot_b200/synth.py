@@ -38,7 +38,9 @@ def random_blocks(kind: int, n_blocks: int, rng: np.random.Generator) -> np.ndar
     """uint8 [n_blocks, block_bytes] drawn like the benchmark configurations:
     quant bytes and packed scale bytes uniform; f16 super-scales |N(0, s)|."""
     _, size = geometry(kind)
-    raw = rng.integers(0, 256, size=(n_blocks, size), dtype=np.uint8)
+    # uniform bytes, drawn four at a time (full-range 32-bit draws are the generator's fast path)
+    n = n_blocks * size
+    raw = rng.integers(0, 1 << 32, size=(n + 3) // 4, dtype=np.uint32).view(np.uint8)[:n].reshape(n_blocks, size)
     if kind == Q4_K:      # [f16 d][f16 dmin][12 scales][128 qs]
         raw[:, 0:2] = _f16_bits(np.abs(rng.normal(0.0, 0.02, n_blocks))).reshape(-1, 1).view(np.uint8)
         raw[:, 2:4] = _f16_bits(np.abs(rng.normal(0.0, 0.01, n_blocks))).reshape(-1, 1).view(np.uint8)
