@@ -164,6 +164,10 @@ IG_HD uint32_t packed_x_bytes(uint32_t cols) { return cols * 4u + cols / 4u + 16
 // The same holding only the high binary16 part (bfloat16 activations).
 IG_HD uint32_t packed_hi_bytes(uint32_t cols) { return cols * 2u + cols / 4u + 16u; }
 
+// Bytes of one activation row in fixed point for the int8 mma.sync GEMV: `nd` digit planes per
+// sub-block of 32 and two float2 of scale and run sum per sub-block (pack.cuh: fx_store).
+IG_HD uint32_t fx_row_bytes(uint32_t cols, uint32_t nd) { return cols * nd + cols / 2u; }
+
 // Bytes of one activation row as base-256 digits for the int8 tensor-core GEMV: the
 // N = 8 operand image (8 bytes per column), fp32 sums of each 16 columns, 16 bytes
 // holding 1/scale.  cols must be a multiple of 256.

@@ -70,8 +70,20 @@ struct MmaPlan {
     uint32_t red_bytes, smem_bytes;
     uint32_t ctas;
     uint32_t red_slots;      // ring of partial-sum buffers, > stages
-    uint32_t hi_only;        // the packed row holds only the high binary16 part (bfloat16 activations are exact in it)
+    uint32_t xm;             // form of the activation row in shared memory (XM_*)
 };
+
+// Activation row forms.  The binary16 forms are what ingot_pack_x / ingot_pack_x_hi write; the
+// fixed-point forms are built by the CTA itself (fused norm, or plain float32 rows) and feed the int8 MMA.
+enum : uint32_t {
+    XM_F16 = 0,      // binary16 (high, low) parts
+    XM_F16_HI = 1,   // binary16 high part only (bfloat16 activations are exact in it)
+    XM_FX2 = 2,      // fixed point, two base-256 digits per activation (bfloat16-rounded activations)
+    XM_FX4 = 3       // fixed point, four digits (float32 activations)
+};
+static uint32_t x_row_bytes(uint32_t xm, uint32_t cols) {
+    return xm == XM_F16 ? packed_x_bytes(cols) : xm == XM_F16_HI ? packed_hi_bytes(cols) : fx_row_bytes(cols, xm == XM_FX2 ? 2u : 4u);
+}
 
 struct MmaArgs {
     MmaPlan plan;
@@ -103,10 +115,12 @@ static void step_geometry(uint32_t kind, uint32_t &cols, uint32_t &bytes) {
     }
 }
 
-static uint32_t pitch_of(uint32_t chunk_bytes) { return chunk_bytes + ((16u + 128u - (chunk_bytes % 128u)) % 128u); }
+// Row pitch inside a stage: `lead` mod 128, so that the loads of one instruction hit different banks
+// (16: eight rows x 4 lanes x 4 bytes; 32: four rows x 4 lanes x 8 bytes per half-warp of a 64-bit load).
+static uint32_t pitch_of(uint32_t chunk_bytes, uint32_t lead = 16u) { return chunk_bytes + ((lead + 128u - (chunk_bytes % 128u)) % 128u); }
 
 static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t nmat, uint32_t max_ctas,
-                     uint32_t budget, bool hi_only, MmaPlan &p) {
+                     uint32_t budget, uint32_t xm, MmaPlan &p) {
     if (!mma_kind(kind)) return false;
     uint32_t block, bytes;
     geometry(kind, block, bytes);
@@ -120,8 +134,10 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     p.kw_log2 = kw;
     p.row_tiles = (uint32_t)MMA_WARPS >> kw;
     const uint32_t per_warp = p.nsteps >> kw;                 // steps each warp owns per row
-    p.hi_only = hi_only;
-    p.x_bytes = hi_only ? packed_hi_bytes(cols) : packed_x_bytes(cols);
+    p.xm = xm;
+    p.x_bytes = x_row_bytes(xm, cols);
+    // the int8 steps of the K-quants read 8 bytes per lane
+    const uint32_t lead = (xm >= XM_FX2 && (kind == KIND_Q4_K || kind == KIND_Q6_K)) ? 32u : 16u;
     p.red_slots = budget <= MMA_SMEM_SMALL ? 4u : MMA_RED_SLOTS;
     p.red_bytes = p.red_slots * MMA_WARPS * 2u * 16u * 4u + MMA_ZERO_BYTES;   // [slot][warp][mat][row] + zeros
     const uint32_t fixed = MMA_BAR_BYTES + ((p.x_bytes + 127u) & ~127u) + p.red_bytes;
@@ -134,7 +150,7 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
         if (per_warp % spw) continue;
         const uint32_t cb = spw * (1u << kw) * p.step_bytes;
         if (cb % 16u) continue;
-        const uint32_t sb = (pitch_of(cb) * 16u * p.row_tiles + 64u + 127u) & ~127u;      // one matrix per stage
+        const uint32_t sb = (pitch_of(cb, lead) * 16u * p.row_tiles + 64u + 127u) & ~127u;      // one matrix per stage
         if (room / sb < 2) break;
         if (pick == 0 || sb <= MMA_STAGE_TARGET) pick = spw;
     }
@@ -142,7 +158,7 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     p.spw = pick;
     p.chunks = per_warp / pick;
     p.chunk_bytes = pick * (1u << kw) * p.step_bytes;
-    p.row_pitch = pitch_of(p.chunk_bytes);
+    p.row_pitch = pitch_of(p.chunk_bytes, lead);
     p.stage_bytes = (p.row_pitch * 16u * p.row_tiles + 64u + 127u) & ~127u;
     p.stages = room / p.stage_bytes;
     if (p.stages > (uint32_t)MMA_MAX_STAGES) p.stages = MMA_MAX_STAGES;
@@ -454,11 +470,251 @@ template <> struct MmaStep<KIND_Q8_0> {
 #undef IG_HI
 
 // ---------------------------------------------------------------------------
+// int8 steps: mma.sync m16n8k32 (u8 or s8 weights x s8 activation digits -> s32) on fixed-point
+// activation rows (pack.cuh: fx_store).  One MMA covers one sub-block of 32 columns of 16 rows:
+//   A (rows x k): a0 = row g, k 4t..4t+3;  a1 = row g+8, same k;  a2 = row g, k 16+4t..;  a3 = row g+8
+//   B (k x n):    b0 = k 4t..4t+3, n = g;  b1 = k 16+4t.., n = g
+//   C (rows x n): c0, c1 = row g, n 2t, 2t+1;  c2, c3 = row g+8, same n
+// A nibble mask turns four packed quants into four operand bytes with one logic op, twice as many
+// weights per operand register as binary16 takes and half as many MMAs.  The eight B columns are
+// (position in the chain, digit) pairs: a lane supplies digits only at the chain position it owns
+// and zeros elsewhere, so the MMAs of a chain add into the same accumulator registers and lane t
+// ends with the exact integer sums of the sub-block it owns, one per digit.  Digits recombine in
+// integers (256 c0 + c1), the sub-block's power-of-two scale and the format's scales apply in fp32.
+// Two digits make one pass; float32 activations take a second pass over the same A registers with
+// digits 2 and 3.
+// ---------------------------------------------------------------------------
+
+template <bool SIGNED_A, bool FIRST>
+__device__ __forceinline__ void imma16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    if (FIRST) {
+        if (SIGNED_A)
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+        else
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    } else {
+        if (SIGNED_A)
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        else
+            asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// The exact digit sums of one row as a float: element i (row g) or i + 2 (row g+8) of the accumulators.
+template <int NP>
+__device__ __forceinline__ float fx_sum(const int (&c)[NP][4], int i) {
+    const float hi = (float)(c[0][i] * 256 + c[0][i + 1]);
+    if (NP == 1) return hi;
+    return fma_rn(hi, 65536.0f, (float)(c[NP - 1][i] * 256 + c[NP - 1][i + 1]));
+}
+
+#define IG_B8(ptr) (*reinterpret_cast<const uint2 *>(ptr))
+static constexpr uint32_t NIB = 0x0f0f0f0fu;
+
+template <uint32_t KIND> struct ImmaStep;
+
+// Q4_K.  Chain X = sub-blocks 0..3 of the block, chain Y = sub-blocks 4..7; the 32 quant bytes of
+// chunk c hold sub-block 2c in their low nibbles and 2c+1 in their high nibbles (kept in place as
+// 16 q; the factor comes off in the scale of the lanes that own odd sub-blocks).  Lane t owns
+// sub-blocks t and t+4: their six-bit scales and mins are bytes t, t+4 and t+8 of the 12 scale bytes.
+template <> struct ImmaStep<KIND_Q4_K> {
+    static constexpr uint32_t POS_STRIDE = 1;        // chain position p reads sub-block p (+ 4 in chain Y)
+    static __device__ __forceinline__ void scales(const uint8_t *r, uint32_t sel, float &d, float &dmin, float &sa, float &sb, float &ma,
+                                                  float &mb) {
+        const U4 hdr = *reinterpret_cast<const U4 *>(r);
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+        d = dd.x; dmin = dd.y;
+        const uint32_t a = __byte_perm(hdr.y, 0u, sel), b = __byte_perm(hdr.z, 0u, sel), c = __byte_perm(hdr.w, 0u, sel);
+        sa = (float)(a & 63u);
+        ma = (float)(b & 63u);
+        sb = (float)((c & 15u) | ((a >> 2) & 0x30u));
+        mb = (float)((c >> 4) | ((b >> 2) & 0x30u));
+    }
+    template <int ND>
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&bx)[4], const uint8_t *meta,
+                                               uint32_t t, float nibf, float &acc0, float &acc1, uint32_t) {
+        constexpr uint32_t SBS = ND * 32u;
+        constexpr int NP = ND / 2;
+        int cx[NP][4], cy[NP][4];
+        const uint8_t *q0 = r0 + 16u + 8u * t, *q1 = r1 + 16u + 8u * t;
+#pragma unroll
+        for (uint32_t c = 0; c < 4; ++c) {
+            const uint2 wa = IG_B8(q0 + 32u * c), wb = IG_B8(q1 + 32u * c);
+            const uint32_t p = 2u * (c & 1u), off = (c >> 1) * 4u * SBS;
+#pragma unroll
+            for (int ps = 0; ps < NP; ++ps) {
+                const uint2 bl = IG_B8(bx[p] + off + ps * 64), bh = IG_B8(bx[p + 1u] + off + ps * 64);
+                if (c == 0) imma16832<false, true>(cx[ps], wa.x & NIB, wb.x & NIB, wa.y & NIB, wb.y & NIB, bl.x, bl.y);
+                else if (c == 1) imma16832<false, false>(cx[ps], wa.x & NIB, wb.x & NIB, wa.y & NIB, wb.y & NIB, bl.x, bl.y);
+                else if (c == 2) imma16832<false, true>(cy[ps], wa.x & NIB, wb.x & NIB, wa.y & NIB, wb.y & NIB, bl.x, bl.y);
+                else imma16832<false, false>(cy[ps], wa.x & NIB, wb.x & NIB, wa.y & NIB, wb.y & NIB, bl.x, bl.y);
+                if (c < 2) imma16832<false, false>(cx[ps], wa.x & ~NIB, wb.x & ~NIB, wa.y & ~NIB, wb.y & ~NIB, bh.x, bh.y);
+                else imma16832<false, false>(cy[ps], wa.x & ~NIB, wb.x & ~NIB, wa.y & ~NIB, wb.y & ~NIB, bh.x, bh.y);
+            }
+        }
+        const uint32_t sel = 0x4440u + t;
+        float d0, n0, sa0, sb0, ma0, mb0, d1, n1, sa1, sb1, ma1, mb1;
+        scales(r0, sel, d0, n0, sa0, sb0, ma0, mb0);
+        scales(r1, sel, d1, n1, sa1, sb1, ma1, mb1);
+        // {1/S, sum of run 0, 1/S, sum of run 1} of sub-blocks t and t+4
+        const float4 mx = *reinterpret_cast<const float4 *>(meta + 16u * t), my = *reinterpret_cast<const float4 *>(meta + 16u * t + 64u);
+        const float ex = mul_rn(mx.x, nibf), ey = mul_rn(my.x, nibf);
+        const float sxx = add_rn(mx.y, mx.w), sxy = add_rn(my.y, my.w);
+        const float zx0 = mul_rn(fx_sum<NP>(cx, 0), ex), zy0 = mul_rn(fx_sum<NP>(cy, 0), ey);
+        const float zx1 = mul_rn(fx_sum<NP>(cx, 2), ex), zy1 = mul_rn(fx_sum<NP>(cy, 2), ey);
+        acc0 = add_rn(acc0, sub_rn(mul_rn(d0, fma_rn(sb0, zy0, mul_rn(sa0, zx0))), mul_rn(n0, fma_rn(mb0, sxy, mul_rn(ma0, sxx)))));
+        acc1 = add_rn(acc1, sub_rn(mul_rn(d1, fma_rn(sb1, zy1, mul_rn(sa1, zx1))), mul_rn(n1, fma_rn(mb1, sxy, mul_rn(ma1, sxx)))));
+    }
+};
+
+// Q6_K.  A quarter (n, q) is 32 columns: two runs of 16, each with its own int8 scale.  The eight B
+// columns are (position, run, digit): the lanes with t < 2 hold the k slots of run 0 and supply the
+// run-0 columns, the lanes with t >= 2 the run-1 columns, so lane t ends with the sums of quarter
+// position t / 2, run t % 2.  Chains: (n, 0) + (n, 2), which share their ql bytes (low and high
+// nibbles), and (n, 1) + (n, 3).  Blocks are only 2-byte aligned: CLS = (block start mod 8) / 2.
+template <> struct ImmaStep<KIND_Q6_K> {
+    static constexpr uint32_t POS_STRIDE = 2;        // chain position p reads quarter q0 + 2 p
+    template <int CLS>
+    static __device__ __forceinline__ uint2 ld8(const uint8_t *p) {      // 8 bytes at an address that is 2 CLS mod 8
+        if (CLS == 0) return *reinterpret_cast<const uint2 *>(p);
+        if (CLS == 2) return make_uint2(*reinterpret_cast<const uint32_t *>(p), *reinterpret_cast<const uint32_t *>(p + 4));
+        if (CLS == 1) {
+            const uint2 a = *reinterpret_cast<const uint2 *>(p - 2);
+            const uint32_t b = *reinterpret_cast<const uint32_t *>(p + 6);
+            return make_uint2(__funnelshift_r(a.x, a.y, 16u), __funnelshift_r(a.y, b, 16u));
+        }
+        const uint32_t a = *reinterpret_cast<const uint32_t *>(p - 2);
+        const uint2 b = *reinterpret_cast<const uint2 *>(p + 2);
+        return make_uint2(__funnelshift_r(a, b.x, 16u), __funnelshift_r(b.x, b.y, 16u));
+    }
+    // four six-bit values of quarter Q from a word of ql (L) and a word of qh (H)
+    template <int Q>
+    static __device__ __forceinline__ uint32_t six(uint32_t L, uint32_t H) {
+        const uint32_t lo = (Q < 2 ? L : (L >> 4)) & NIB;
+        const uint32_t hi = (Q == 0 ? (H << 4) : Q == 1 ? (H << 2) : Q == 2 ? H : (H >> 2)) & 0x30303030u;
+        return lo | hi;
+    }
+    template <int ND, int CLS>
+    static __device__ __forceinline__ void run_cls(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&bx)[4], const uint8_t *meta,
+                                                   uint32_t t, float &acc0, float &acc1) {
+        constexpr uint32_t SBS = ND * 32u;
+        constexpr int NP = ND / 2;
+        const float d0 = lds_half(r0 + 208u), d1 = lds_half(r1 + 208u);
+        const uint32_t run = t & 1u, pos = t >> 1;
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (uint32_t n = 0; n < 2; ++n) {
+            const uint2 la0 = ld8<CLS>(r0 + 64u * n + 8u * t), lb0 = ld8<CLS>(r0 + 64u * n + 32u + 8u * t), h0 = ld8<CLS>(r0 + 128u + 32u * n + 8u * t);
+            const uint2 la1 = ld8<CLS>(r1 + 64u * n + 8u * t), lb1 = ld8<CLS>(r1 + 64u * n + 32u + 8u * t), h1 = ld8<CLS>(r1 + 128u + 32u * n + 8u * t);
+#pragma unroll
+            for (uint32_t ch = 0; ch < 2; ++ch) {
+                int c[NP][4];
+#pragma unroll
+                for (int ps = 0; ps < NP; ++ps) {
+                    const uint2 b_lo = IG_B8(bx[0] + (4u * n + ch) * SBS + ps * 64), b_hi = IG_B8(bx[1] + (4u * n + ch) * SBS + ps * 64);
+                    if (ch == 0) {
+                        imma16832<false, true>(c[ps], six<0>(la0.x, h0.x), six<0>(la1.x, h1.x), six<0>(la0.y, h0.y), six<0>(la1.y, h1.y), b_lo.x, b_lo.y);
+                        imma16832<false, false>(c[ps], six<2>(la0.x, h0.x), six<2>(la1.x, h1.x), six<2>(la0.y, h0.y), six<2>(la1.y, h1.y), b_hi.x, b_hi.y);
+                    } else {
+                        imma16832<false, true>(c[ps], six<1>(lb0.x, h0.x), six<1>(lb1.x, h1.x), six<1>(lb0.y, h0.y), six<1>(lb1.y, h1.y), b_lo.x, b_lo.y);
+                        imma16832<false, false>(c[ps], six<3>(lb0.x, h0.x), six<3>(lb1.x, h1.x), six<3>(lb0.y, h0.y), six<3>(lb1.y, h1.y), b_hi.x, b_hi.y);
+                    }
+                }
+                // this lane: quarter q = ch + 2 pos, run `run`; value - 32 through the run's activation sum
+                const uint32_t q = ch + 2u * pos, idx = 8u * n + 2u * q + run;
+                const float s0 = (float)(int)*reinterpret_cast<const int8_t *>(r0 + 192u + idx);
+                const float s1 = (float)(int)*reinterpret_cast<const int8_t *>(r1 + 192u + idx);
+                const float2 mt = *reinterpret_cast<const float2 *>(meta + (4u * n + q) * 16u + run * 8u);      // {1/S, run sum}
+                const float off = mul_rn(mt.y, -32.0f);
+                t0 = fma_rn(s0, fma_rn(fx_sum<NP>(c, 0), mt.x, off), t0);
+                t1 = fma_rn(s1, fma_rn(fx_sum<NP>(c, 2), mt.x, off), t1);
+            }
+        }
+        acc0 = fma_rn(d0, t0, acc0);
+        acc1 = fma_rn(d1, t1, acc1);
+    }
+    template <int ND>
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&bx)[4], const uint8_t *meta,
+                                               uint32_t t, float, float &acc0, float &acc1, uint32_t cls) {
+        switch (cls) {          // warp-uniform
+        case 0: run_cls<ND, 0>(r0, r1, bx, meta, t, acc0, acc1); break;
+        case 1: run_cls<ND, 1>(r0, r1, bx, meta, t, acc0, acc1); break;
+        case 2: run_cls<ND, 2>(r0, r1, bx, meta, t, acc0, acc1); break;
+        default: run_cls<ND, 3>(r0, r1, bx, meta, t, acc0, acc1); break;
+        }
+    }
+};
+
+// Q4_0: step = 4 blocks of 32 (18 bytes each, 2-byte aligned), one MMA per block: the low nibbles of
+// a word are columns 4t..4t+3, its high nibbles columns 16+4t...  Lane t owns block t.
+template <> struct ImmaStep<KIND_Q4_0> {
+    static constexpr uint32_t POS_STRIDE = 1;
+    template <int ND>
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&bx)[4], const uint8_t *meta,
+                                               uint32_t t, float, float &acc0, float &acc1, uint32_t) {
+        constexpr int NP = ND / 2;
+        int c[NP][4];
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            // a step (72 bytes) starts on a 4-byte boundary: the quants of even blocks lie 2 bytes past one
+            const uint32_t wa = lds32_known(r0 + 18u * b + 2u + 4u * t, (b & 1u) == 0u), wb = lds32_known(r1 + 18u * b + 2u + 4u * t, (b & 1u) == 0u);
+#pragma unroll
+            for (int ps = 0; ps < NP; ++ps) {
+                const uint8_t *xb = bx[b] + ps * 64;
+                const uint32_t b0 = lds32(xb), b1 = lds32(xb + 16);
+                if (b == 0) imma16832<false, true>(c[ps], wa & NIB, wb & NIB, (wa >> 4) & NIB, (wb >> 4) & NIB, b0, b1);
+                else imma16832<false, false>(c[ps], wa & NIB, wb & NIB, (wa >> 4) & NIB, (wb >> 4) & NIB, b0, b1);
+            }
+        }
+        const float d0 = lds_half(r0 + 18u * t), d1 = lds_half(r1 + 18u * t);
+        const float4 mt = *reinterpret_cast<const float4 *>(meta + 16u * t);
+        const float off = mul_rn(add_rn(mt.y, mt.w), -8.0f);
+        acc0 = fma_rn(d0, fma_rn(fx_sum<NP>(c, 0), mt.x, off), acc0);
+        acc1 = fma_rn(d1, fma_rn(fx_sum<NP>(c, 2), mt.x, off), acc1);
+    }
+};
+
+// Q8_0: step = 4 blocks of 32 int8 (34 bytes each, 2-byte aligned), one MMA per block with signed
+// weights.  Lane t owns block t.
+template <> struct ImmaStep<KIND_Q8_0> {
+    static constexpr uint32_t POS_STRIDE = 1;
+    template <int ND>
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&bx)[4], const uint8_t *meta,
+                                               uint32_t t, float, float &acc0, float &acc1, uint32_t) {
+        constexpr int NP = ND / 2;
+        int c[NP][4];
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            // a step (136 bytes) starts on a 4-byte boundary: the quants of even blocks lie 2 bytes past one
+            const bool mis = (b & 1u) == 0u;
+            const uint32_t wa0 = lds32_known(r0 + 34u * b + 2u + 4u * t, mis), wa1 = lds32_known(r0 + 34u * b + 18u + 4u * t, mis);
+            const uint32_t wb0 = lds32_known(r1 + 34u * b + 2u + 4u * t, mis), wb1 = lds32_known(r1 + 34u * b + 18u + 4u * t, mis);
+#pragma unroll
+            for (int ps = 0; ps < NP; ++ps) {
+                const uint8_t *xb = bx[b] + ps * 64;
+                const uint32_t b0 = lds32(xb), b1 = lds32(xb + 16);
+                if (b == 0) imma16832<true, true>(c[ps], wa0, wb0, wa1, wb1, b0, b1);
+                else imma16832<true, false>(c[ps], wa0, wb0, wa1, wb1, b0, b1);
+            }
+        }
+        const float d0 = lds_half(r0 + 34u * t), d1 = lds_half(r1 + 34u * t);
+        const float inv = *reinterpret_cast<const float *>(meta + 16u * t);
+        acc0 = fma_rn(d0, mul_rn(fx_sum<NP>(c, 0), inv), acc0);
+        acc1 = fma_rn(d1, mul_rn(fx_sum<NP>(c, 2), inv), acc1);
+    }
+};
+#undef IG_B8
+
+// ---------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------
 
 // The whole CTA's work on one projection: CTA `cta` of `nctas` (its share of the rows), pair `pair`.
-template <uint32_t KIND, int NMAT, bool HI>
+template <uint32_t KIND, int NMAT, int XM>
 __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, const uint32_t cta, const uint32_t nctas, const uint32_t pair,
                                               const bool whole_tiles) {
     const MmaPlan &p = a.plan;
@@ -467,8 +723,11 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     uint64_t *xbar = empty + MMA_MAX_STAGES;
     uint64_t *tbar = xbar + 1;                                   // [MMA_RED_SLOTS]
     uint8_t *xrow = smem + MMA_BAR_BYTES;
-    constexpr uint32_t XB = HI ? 2u : 4u;                 // packed bytes per activation
-    const float *sx = reinterpret_cast<const float *>(xrow + (size_t)p.cols * XB);
+    constexpr bool HI = XM == XM_F16_HI;
+    constexpr bool FX = XM >= XM_FX2;                     // fixed-point rows, int8 MMA
+    constexpr int ND = XM == XM_FX4 ? 4 : 2;              // digits per activation (fixed point)
+    constexpr uint32_t XB = FX ? (uint32_t)ND : HI ? 2u : 4u;       // packed bytes per activation
+    const float *sx = reinterpret_cast<const float *>(xrow + (size_t)p.cols * XB);     // binary16 rows: 16-column sums; fixed point: {1/S, run sum} pairs
     float *red = reinterpret_cast<float *>(xrow + ((p.x_bytes + 127u) & ~127u));
     uint8_t *zeros = reinterpret_cast<uint8_t *>(red) + p.red_bytes - MMA_ZERO_BYTES;
     uint8_t *stages = reinterpret_cast<uint8_t *>(red) + p.red_bytes;
@@ -567,7 +826,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             return;
         }
     }
-    if (a.na) {
+    if constexpr (FX) {
         // ---- fused add + RMS normalisation + packing (what add_rms with a packed output computes,
         // kernels/generic.metal:390-404): the 256 consumer threads of every CTA build the packed row ----
         ptx::pdl_wait();
@@ -623,28 +882,14 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 }
             }
             const float inv = a.npack ? 1.0f : 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
-            float mx = 0.f;
 #pragma unroll
             for (uint32_t i = 0; i < NV; ++i) {
+                if (i * NT >= n4) break;                               // uniform: the shuffles of a sub-block keep all its lanes
                 const uint32_t j = tid + i * NT;
-                if (j < n4) {
-                    float u[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-                    finish(u, j, inv);
-                    v[i] = make_float4(u[0], u[1], u[2], u[3]);
-                    mx = fmaxf(mx, fmaxf(fmaxf(fabsf(u[0]), fabsf(u[1])), fmaxf(fabsf(u[2]), fabsf(u[3]))));
-                }
+                float u[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+                if (j < n4) finish(u, j, inv);
+                fx_store<ND>(xrow, p.cols, j, u, j < n4);
             }
-            // without a norm weight |x_i| * inv <= sqrt(cols) < 2^14: the packing scale is 1 and the second reduction is not needed
-            const float scale = (a.nw || a.npack) ? pack_scale(reduce(mx, true)) : 1.0f;
-#pragma unroll
-            for (uint32_t i = 0; i < NV; ++i) {
-                if (i * NT >= n4) break;                               // uniform: the quad shuffles keep all lanes
-                const uint32_t j = tid + i * NT;
-                float u[4] = {v[i].x * scale, v[i].y * scale, v[i].z * scale, v[i].w * scale};
-                if (HI) pack_hi_store_quad(xrow, p.cols, j, u, j < n4);
-                else pack_store_quad(xrow, p.cols, j, u, j < n4);
-            }
-            if (tid == 0) { if (HI) pack_hi_store_unscale(xrow, p.cols, scale); else pack_store_unscale(xrow, p.cols, scale); }
         };
         if (n4 <= 4u * NT) in_registers(std::integral_constant<uint32_t, 4>{});            // up to 4096 columns
         else if (n4 <= 12u * NT) in_registers(std::integral_constant<uint32_t, 12>{});     // up to 12288
@@ -656,16 +901,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             }
             const float inv = a.npack ? 1.0f : 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
-            float mx = 0.f;
-            for (uint32_t j = tid; j < n4; j += NT) {
-                const float4 v = load(j);
-                float u[4] = {v.x, v.y, v.z, v.w};
-                finish(u, j, inv);
-                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(u[0]), fabsf(u[1])), fmaxf(fabsf(u[2]), fabsf(u[3]))));
-            }
-            // without a norm weight |x_i| * inv <= sqrt(cols) < 2^14: the packing scale is 1 and the second reduction is not needed
-            const float scale = (a.nw || a.npack) ? pack_scale(reduce(mx, true)) : 1.0f;
-            for (uint32_t j0 = 0; j0 < n4; j0 += NT) {                 // uniform trip count: the quad shuffles keep all lanes
+            for (uint32_t j0 = 0; j0 < n4; j0 += NT) {                 // uniform trip count: the shuffles of a sub-block keep all its lanes
                 const uint32_t j = j0 + tid;
                 const bool live = j < n4;
                 float u[4] = {0.f, 0.f, 0.f, 0.f};
@@ -673,36 +909,40 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                     const float4 v = load(j);
                     u[0] = v.x; u[1] = v.y; u[2] = v.z; u[3] = v.w;
                     finish(u, j, inv);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) u[k] *= scale;
                 }
-                if (HI) pack_hi_store_quad(xrow, p.cols, j, u, live);
-                else pack_store_quad(xrow, p.cols, j, u, live);
+                fx_store<ND>(xrow, p.cols, j, u, live);
             }
-            if (tid == 0) { if (HI) pack_hi_store_unscale(xrow, p.cols, scale); else pack_store_unscale(xrow, p.cols, scale); }
         }
         ptx::named_bar_sync(1, MMA_WARPS * 32);
-    } else if (!ptx::mbar_wait(xbar, 0)) {
-        if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
-        return;
+    } else {
+        if (!ptx::mbar_wait(xbar, 0)) {
+            if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
+            return;
+        }
     }
     ptx::pdl_wait();          // outputs may be read by the previous kernel until it ends
-    const float unscale = *reinterpret_cast<const float *>(xrow + (size_t)p.cols * XB + p.cols / 4u);
+    // binary16 rows carry one power-of-two scale for the whole row; fixed-point rows one per sub-block, applied in the steps
+    const float unscale = FX ? 1.0f : *reinterpret_cast<const float *>(xrow + (size_t)p.cols * XB + p.cols / 4u);
 
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t kw = warp & ((1u << p.kw_log2) - 1u), rt = warp >> p.kw_log2;
     constexpr uint32_t STEP_BYTES = KIND == KIND_Q4_K ? 144u : KIND == KIND_Q6_K ? 210u : KIND == KIND_Q4_0 ? 72u : 136u;
-    constexpr uint32_t MMAS = (KIND == KIND_Q4_K || KIND == KIND_Q6_K) ? 16u : 8u;     // MMAs per step
-    constexpr uint32_t XS = HI ? 32u : 64u;                                             // packed bytes per MMA
+    constexpr uint32_t MMAS = (KIND == KIND_Q4_K || KIND == KIND_Q6_K) ? 16u : 8u;     // binary16 MMAs (16 columns each) per step
+    constexpr uint32_t XS = FX ? (uint32_t)ND * 16u : HI ? 32u : 64u;                   // packed bytes per 16 columns
     const uint32_t step_stride = STEP_BYTES << p.kw_log2;                               // this warp's next step
-    const uint32_t x_stride = (MMAS * XS) << p.kw_log2, s_stride = MMAS << p.kw_log2;     // bytes, floats
+    const uint32_t x_stride = (MMAS * XS) << p.kw_log2, s_stride = MMAS << p.kw_log2;     // bytes, floats (fixed point: 8 bytes of scale and sum per 16 columns = 2 floats)
     // B operands: column n = g of the MMA belongs to lane g; columns 2j, 2j+1 carry (xh, xl)
     // for group j only, so this lane reads the real activations for group own = g / 2 and
     // zeros for the others
     // (with only the high part packed, the low-part columns — odd g — always read zeros)
-    const uint32_t own = (HI && (g & 1u)) ? 4u : (g >> 1);
-    const uint8_t *xlane = xrow + (HI ? t : (g & 1u) * 4u + t) * 8u;
-    const uint8_t *zlane = zeros + ((g & 1u) * 4u + t) * 8u;
+    // (fixed point: column g is digit g % 2 of chain position g / 2; Q6_K splits a position's columns
+    // over the two runs of 16, and the run-0 columns belong to the lanes with t < 2)
+    const uint32_t own = FX ? (KIND == KIND_Q6_K ? (((t >> 1) == ((g >> 1) & 1u)) ? (g >> 2) : 9u) : (g >> 1))
+                            : (HI && (g & 1u)) ? 4u : (g >> 1);
+    const uint8_t *xlane = FX ? xrow + (g & 1u) * 32u + t * ((KIND == KIND_Q4_K || KIND == KIND_Q6_K) ? 8u : 4u)
+                              : xrow + (HI ? t : (g & 1u) * 4u + t) * 8u;
+    const uint8_t *zlane = FX ? zeros + lane * 8u : zeros + ((g & 1u) * 4u + t) * 8u;
+    const float nibf = (t & 1u) ? 0.0625f : 1.0f;                  // Q4_K int8 steps: odd sub-blocks keep their nibbles in place (16 q)
     float *y = a.y + (a.ids ? (size_t)pair * p.rows : 0);
     const uint32_t kmask = (1u << p.kw_log2) - 1u;
 
@@ -755,18 +995,29 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                     const uint8_t *b0 = st + (size_t)ur0 * p.row_pitch + kw * STEP_BYTES;
                     const uint8_t *b1 = st + (size_t)ur1 * p.row_pitch + kw * STEP_BYTES;
                     const uint8_t *xs = xlane + (size_t)gs0 * MMAS * XS;
-                    const float *ss = sx + gs0 * MMAS;
+                    const float *ss = sx + gs0 * MMAS * (FX ? 2u : 1u);
                     for (uint32_t i = 0; i < p.spw; ++i) {
-                        const uint8_t *const xb[4] = {own == 0 ? xs : zlane, own == 1 ? xs : zlane, own == 2 ? xs : zlane,
-                                                      own == 3 ? xs : zlane};
-                        // rows start on 16-byte boundaries in the stage: an odd Q6_K block (210 bytes) starts
-                        // 2 bytes past a 4-byte boundary (warp-uniform; the other formats ignore it)
-                        if (KIND == KIND_Q6_K && (((kw + (i << p.kw_log2)) & 1u) != 0u))
-                            MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1], true);
-                        else
-                            MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1], false);
+                        if constexpr (FX) {
+                            // chain position p of this lane: its own digits at the sub-block of that position, zeros elsewhere
+                            constexpr uint32_t PS = ImmaStep<KIND>::POS_STRIDE * ND * 32u;
+                            const uint8_t *const xb[4] = {own == 0 ? xs : zlane, own == 1 ? xs + PS : zlane, own == 2 ? xs + 2u * PS : zlane,
+                                                          own == 3 ? xs + 3u * PS : zlane};
+                            // rows start on 16-byte boundaries in the stage: a Q6_K block (210 bytes) starts 2 (block mod 4)
+                            // bytes past an 8-byte boundary (warp-uniform; the other formats ignore it)
+                            ImmaStep<KIND>::template run<ND>(b0, b1, xb, reinterpret_cast<const uint8_t *>(ss), t, nibf, acc[m][0], acc[m][1],
+                                                             (kw + (i << p.kw_log2)) & 3u);
+                        } else {
+                            const uint8_t *const xb[4] = {own == 0 ? xs : zlane, own == 1 ? xs : zlane, own == 2 ? xs : zlane,
+                                                          own == 3 ? xs : zlane};
+                            // rows start on 16-byte boundaries in the stage: an odd Q6_K block (210 bytes) starts
+                            // 2 bytes past a 4-byte boundary (warp-uniform; the other formats ignore it)
+                            if (KIND == KIND_Q6_K && (((kw + (i << p.kw_log2)) & 1u) != 0u))
+                                MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1], true);
+                            else
+                                MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1], false);
+                        }
                         b0 += step_stride; b1 += step_stride;
-                        xs += x_stride; ss += s_stride;
+                        xs += x_stride; ss += s_stride * (FX ? 2u : 1u);
                     }
                 }
                 __syncwarp();
@@ -792,10 +1043,10 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     if (n_tiles > 0) sum_tile(n_tiles - 1);
 }
 
-template <uint32_t KIND, int NMAT, int OCC, bool HI>
+template <uint32_t KIND, int NMAT, int OCC, int XM>
 __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    gemv_mma_body<KIND, NMAT, HI>(a, smem, blockIdx.x, gridDim.x, blockIdx.y, false);
+    gemv_mma_body<KIND, NMAT, XM>(a, smem, blockIdx.x, gridDim.x, blockIdx.y, false);
 }
 
 // Several independent one-token projections in one launch (what the reference's
@@ -811,7 +1062,7 @@ struct MmaGroupArgs {
 
 // Two CTAs per SM: the Q6_K step needs the registers, and a three-per-SM form without it (smaller
 // rings, a few spills) measured slower on an all-Q4_0 group (11.2 us against 6.7 us).
-template <bool HI>
+template <int XM>
 __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_group_kernel(const __grid_constant__ MmaGroupArgs ga) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint32_t i = 0;
@@ -819,10 +1070,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_group_kernel(const __
     const MmaArgs &a = ga.part[i];
     const uint32_t cta = blockIdx.x - ga.first[i], nctas = ga.first[i + 1] - ga.first[i];
     switch (a.plan.kind) {
-    case KIND_Q4_K: gemv_mma_body<KIND_Q4_K, 1, HI>(a, smem, cta, nctas, 0u, true); break;
-    case KIND_Q6_K: gemv_mma_body<KIND_Q6_K, 1, HI>(a, smem, cta, nctas, 0u, true); break;
-    case KIND_Q4_0: gemv_mma_body<KIND_Q4_0, 1, HI>(a, smem, cta, nctas, 0u, true); break;
-    default: gemv_mma_body<KIND_Q8_0, 1, HI>(a, smem, cta, nctas, 0u, true); break;
+    case KIND_Q4_K: gemv_mma_body<KIND_Q4_K, 1, XM>(a, smem, cta, nctas, 0u, true); break;
+    case KIND_Q6_K: gemv_mma_body<KIND_Q6_K, 1, XM>(a, smem, cta, nctas, 0u, true); break;
+    case KIND_Q4_0: gemv_mma_body<KIND_Q4_0, 1, XM>(a, smem, cta, nctas, 0u, true); break;
+    default: gemv_mma_body<KIND_Q8_0, 1, XM>(a, smem, cta, nctas, 0u, true); break;
     }
 }
 
@@ -1219,9 +1470,9 @@ bool try_launch_gemv_mt(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &er
 // launch
 // ---------------------------------------------------------------------------
 
-template <uint32_t KIND, int NMAT, int OCC, bool HI>
+template <uint32_t KIND, int NMAT, int OCC, int XM>
 static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
-    auto kernel = gemv_mma_kernel<KIND, NMAT, OCC, HI>;
+    auto kernel = gemv_mma_kernel<KIND, NMAT, OCC, XM>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1242,15 +1493,28 @@ static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream
     return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
-template <uint32_t KIND, bool HI>
+template <uint32_t KIND, int XM>
 static cudaError_t launch_mma_h(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl, int occ) {
     if (occ == 3)
-        return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 3, HI>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 3, HI>(a, grid, stream, pdl);
-    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 2, HI>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 2, HI>(a, grid, stream, pdl);
+        return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 3, XM>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 3, XM>(a, grid, stream, pdl);
+    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 2, XM>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 2, XM>(a, grid, stream, pdl);
 }
 template <uint32_t KIND>
 static cudaError_t launch_mma_k(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl, int occ) {
-    return a.plan.hi_only ? launch_mma_h<KIND, true>(a, grid, stream, pdl, occ) : launch_mma_h<KIND, false>(a, grid, stream, pdl, occ);
+    switch (a.plan.xm) {
+    case XM_F16: return launch_mma_h<KIND, XM_F16>(a, grid, stream, pdl, occ);
+    case XM_F16_HI: return launch_mma_h<KIND, XM_F16_HI>(a, grid, stream, pdl, occ);
+    case XM_FX2: return launch_mma_h<KIND, XM_FX2>(a, grid, stream, pdl, occ);
+    default: return launch_mma_h<KIND, XM_FX4>(a, grid, stream, pdl, occ);
+    }
+}
+
+// The activation row form of a call: the CTAs build fixed-point rows themselves when they norm or
+// pack the activations; rows packed beforehand are binary16.
+static uint32_t x_mode_of(const GemvCall &c, bool pack_inside) {
+    if (c.norm_a) return c.norm_round_bf16 ? XM_FX2 : XM_FX4;
+    if (pack_inside) return XM_FX4;
+    return c.x_packed == 4u ? XM_F16_HI : XM_F16;
 }
 
 // True when this call was taken (launched or failed); false to let the caller use
@@ -1266,7 +1530,9 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     const uint32_t gy_live = (gy + ep - 1) / ep;
     // bfloat16 activations are exact in the high binary16 part alone: the fused norm with bfloat16
     // rounding, and rows packed that way, carry no low part
-    const bool hi_only = c.norm_a ? c.norm_round_bf16 != 0 : c.x_packed == 4u;
+    // plain float32 rows are packed by the CTAs themselves (one launch, as the reference's matmul is)
+    const bool pack_inside = !c.norm_a && !c.x_packed && !c.x_bf16 && ((uintptr_t)c.x % 16u) == 0;
+    const uint32_t xmode = x_mode_of(c, pack_inside);
     MmaPlan plan;
     int occ = 3;
     uint32_t max_ctas = (3u * ctx.sm_count + gy_live - 1) / gy_live;
@@ -1274,16 +1540,16 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     // deeper ring holds a CTA's whole share, so the copies of one launch run under the tail of
     // the launch before it (4096 x 4096 Q4_K: 6.3 us against 7.6 us back to back)
     bool ok = !(gy_live == 1 && (c.rows + 15u) / 16u <= 2u * ctx.sm_count) &&
-              plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, hi_only, plan);
+              plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, xmode, plan);
     if (!ok) {
         occ = 2;
         max_ctas = (2u * ctx.sm_count + gy_live - 1) / gy_live;
         if (max_ctas < 1) max_ctas = 1;
-        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_BUDGET, hi_only, plan);
+        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_BUDGET, xmode, plan);
     }
     if (!ok) {
         max_ctas = (ctx.sm_count + gy_live - 1) / gy_live;
-        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas ? max_ctas : 1, MMA_SMEM_MAX, hi_only, plan);
+        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas ? max_ctas : 1, MMA_SMEM_MAX, xmode, plan);
     }
     if (!ok) return false;
     if (gy_live == 1) {
@@ -1299,8 +1565,6 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
         if (tiles <= plan.ctas && load_full < load_now) plan.ctas = tiles;
     }
     const uint8_t *xp = static_cast<const uint8_t *>(c.x);
-    // plain float32 rows are packed by the CTAs themselves (one launch, as the reference's matmul is)
-    const bool pack_inside = !c.norm_a && !c.x_packed && !c.x_bf16 && ((uintptr_t)c.x % 16u) == 0;
     if (c.norm_a) {
         if (routed || c.cols % 64u) return false;
         xp = nullptr;
@@ -1337,14 +1601,13 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
 bool gemv_mma_group_eligible(const GemvCall &c, const LaunchCtx &ctx) {
     if (c.ids || c.count != 1 || c.nmat != 1 || !mma_kind(c.kind) || c.cols % 64u) return false;
     if (!c.norm_a && c.x_packed != 1u && c.x_packed != 4u) return false;
-    const bool hi_only = c.norm_a ? c.norm_round_bf16 != 0 : c.x_packed == 4u;
     MmaPlan plan;
-    return plan_mma(c.kind, c.cols, c.rows, c.stride, 1, 2u * ctx.sm_count, MMA_SMEM_BUDGET, hi_only, plan);
+    return plan_mma(c.kind, c.cols, c.rows, c.stride, 1, 2u * ctx.sm_count, MMA_SMEM_BUDGET, x_mode_of(c, false), plan);
 }
 
-template <bool HI>
+template <int XM>
 static cudaError_t launch_mma_group_t(const MmaGroupArgs &ga, uint32_t smem_bytes, cudaStream_t stream, bool pdl) {
-    auto kernel = gemv_mma_group_kernel<HI>;
+    auto kernel = gemv_mma_group_kernel<XM>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_BUDGET);
@@ -1368,15 +1631,15 @@ static cudaError_t launch_mma_group_t(const MmaGroupArgs &ga, uint32_t smem_byte
 // cannot share one: different activation row forms, or a part that does not plan.
 bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx, cudaError_t &err) {
     if (n < 2 || n > MMA_GROUP_MAX) return false;
-    bool hi0 = false;
+    uint32_t xm0 = 0;
     uint32_t order[MMA_GROUP_MAX];
     size_t bytes[MMA_GROUP_MAX];
     for (uint32_t i = 0; i < n; ++i) {
         const GemvCall &c = calls[i];
         if (!gemv_mma_group_eligible(c, ctx)) return false;
-        const bool hi = c.norm_a ? c.norm_round_bf16 != 0 : c.x_packed == 4u;
-        if (i == 0) hi0 = hi;
-        else if (hi != hi0) return false;
+        const uint32_t hi = x_mode_of(c, false);
+        if (i == 0) xm0 = hi;
+        else if (hi != xm0) return false;
         bytes[i] = (size_t)c.rows * c.stride;
         order[i] = i;
     }
@@ -1392,7 +1655,7 @@ bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCt
     const uint32_t slots = 2u * ctx.sm_count;
     for (uint32_t k = 0; k < n; ++k) {
         const GemvCall &c = calls[order[k]];
-        if (!plan_mma(c.kind, c.cols, c.rows, c.stride, 1, slots, MMA_SMEM_BUDGET, hi0, plans[k])) return false;
+        if (!plan_mma(c.kind, c.cols, c.rows, c.stride, 1, slots, MMA_SMEM_BUDGET, xm0, plans[k])) return false;
         tiles_total += (c.rows + 16u * plans[k].row_tiles - 1) / (16u * plans[k].row_tiles);
     }
     for (uint32_t k = 0; k < n; ++k) {
@@ -1416,7 +1679,12 @@ bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCt
         ga.first[k + 1] = ga.first[k] + ctas;
         if (plan.smem_bytes > smem_bytes) smem_bytes = plan.smem_bytes;
     }
-    err = hi0 ? launch_mma_group_t<true>(ga, smem_bytes, ctx.stream, ctx.pdl) : launch_mma_group_t<false>(ga, smem_bytes, ctx.stream, ctx.pdl);
+    switch (xm0) {
+    case XM_F16: err = launch_mma_group_t<XM_F16>(ga, smem_bytes, ctx.stream, ctx.pdl); break;
+    case XM_F16_HI: err = launch_mma_group_t<XM_F16_HI>(ga, smem_bytes, ctx.stream, ctx.pdl); break;
+    case XM_FX2: err = launch_mma_group_t<XM_FX2>(ga, smem_bytes, ctx.stream, ctx.pdl); break;
+    default: err = launch_mma_group_t<XM_FX4>(ga, smem_bytes, ctx.stream, ctx.pdl); break;
+    }
     return true;
 }
 

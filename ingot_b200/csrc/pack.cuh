@@ -84,6 +84,74 @@ __device__ __forceinline__ void digits_store_unscale(uint8_t *row, uint32_t cols
     *reinterpret_cast<float *>(row + (size_t)cols * 8u + cols / 4u) = 1.0f / scale;
 }
 
+// ---- fixed-point rows for the int8 mma.sync GEMV ----
+// Every sub-block of 32 activations has its own power-of-two scale S: x is held as the integer
+// round(x S), split into ND signed base-256 digits (most significant first; 2 digits = 16 bits for
+// activations that carry a bfloat16's eight significant bits, 4 digits = 31 bits for float32).  Row:
+//   [cols/32 sub-blocks][ND digit planes][32 bytes]     digit d of the sub-block's 32 activations
+//   [cols/32 sub-blocks][2 runs of 16]{1/S, sum of the run's quantised activations / S}   (float2)
+// = cols * ND + cols / 2 bytes.  An all-zero (or denormal) sub-block has S = 1 and zero digits; a
+// sub-block with a non-finite activation stores that value as its 1/S, which makes every result that
+// touches it non-finite as well.
+// One thread stores four consecutive activations v[0..3] = columns 4j..4j+3.  The eight threads of a
+// sub-block (consecutive j, the first a multiple of 8, in one warp) must call this together: the scale
+// and the run sums use shuffles among them.
+template <int ND>
+__device__ __forceinline__ void fx_store(uint8_t *row, uint32_t cols, uint32_t j, const float (&v)[4], bool live) {
+    static_assert(ND == 2 || ND == 4, "two or four digits");
+    constexpr uint32_t LB = ND == 2 ? 15u : 30u;             // max |x| S lands in [2^(LB-1), 2^LB)
+    float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+    const uint32_t e = __float_as_uint(m) >> 23;             // biased exponent (m >= 0); NaN compares through fmaxf as the other operand
+    float s = 1.0f, inv = 1.0f;
+    if (e >= 32u && e < 255u) {
+        uint32_t se = 253u + LB - e;                         // S = 2^(LB - 1 - (e - 127))
+        if (ND == 2 && m * __uint_as_float(se << 23) > 32512.0f) --se;      // keep the high digit inside int8 after rounding
+        s = __uint_as_float(se << 23);
+        inv = __uint_as_float((254u - se) << 23);
+    } else if (e == 255u) {
+        inv = m;                                             // infinity: poisons the sub-block's results
+    }
+    bool nan = false;
+    float xq[4];
+    int xi[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        nan = nan || (v[i] != v[i]);
+        xq[i] = rintf(v[i] * s);
+        xi[i] = __float2int_rn(xq[i]);
+    }
+    if (__any_sync(0xffffffffu, nan)) {                      // rare: find the sub-blocks that hold a NaN
+        unsigned mask = __ballot_sync(0xffffffffu, nan);
+        if ((mask >> ((threadIdx.x & 24u))) & 0xffu) inv = __uint_as_float(0x7fc00000u);
+    }
+    float rs = (xq[0] + xq[1]) + (xq[2] + xq[3]);
+    rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+    rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+    uint32_t w[ND];
+#pragma unroll
+    for (int d = 0; d < ND; ++d) w[d] = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int r = xi[i];
+#pragma unroll
+        for (int d = ND - 1; d >= 0; --d) {
+            w[d] |= (uint32_t)(r & 0xff) << (8 * i);
+            r = (r + 128) >> 8;
+        }
+    }
+    if (live) {
+        const uint32_t sb = j >> 3, jj = j & 7u;
+        uint8_t *dst = row + (size_t)sb * (ND * 32u) + 4u * jj;
+#pragma unroll
+        for (int d = 0; d < ND; ++d) *reinterpret_cast<uint32_t *>(dst + 32 * d) = w[d];
+        if ((jj & 3u) == 0u)
+            *reinterpret_cast<float2 *>(row + (size_t)cols * ND + (size_t)sb * 16u + (jj >> 2) * 8u) = make_float2(inv, rs * inv);
+    }
+}
+
 // The same without the low part (bfloat16 activations are exact in binary16): [cols/16 MMAs][4 lanes][4 halves],
 // then the sums and 1/scale: 2 * cols + cols / 4 + 16 bytes.
 __device__ __forceinline__ void pack_hi_store_quad(uint8_t *row, uint32_t cols, uint32_t q, const float (&v)[4], bool live) {

@@ -164,7 +164,7 @@ def test_token_counts_agree_bitwise_and_with_oracle(gpu, kind, cols):
 
 
 @pytest.mark.parametrize("kind,cols,rows", [(Q4_K, 4096, 77), (Q6_K, 4096, 50), (Q4_0, 2560, 33), (Q8_0, 1024, 19)])
-def test_packed_activations_match_the_automatic_path(gpu, kind, cols, rows):
+def test_packed_and_plain_activation_rows_meet_the_oracle(gpu, kind, cols, rows):
     from ingot_b200 import X_PACKED
     raw = synth.random_matrix(kind, cols, rows, seed=11)
     x = synth.activations(1, cols, seed=12)
@@ -173,9 +173,11 @@ def test_packed_activations_match_the_automatic_path(gpu, kind, cols, rows):
     auto = gpu.finish(None, gpu.matmul(None, w, cols, rows, synth.stride_of(kind, cols), kind, 0, xb, 1))
     packed = gpu.pack_x(xb, 1, cols)
     y = gpu.finish(None, gpu.matmul(None, w, cols, rows, synth.stride_of(kind, cols), kind, 0, packed, 1, X_PACKED))
-    assert np.array_equal(y.view(np.uint32), auto.view(np.uint32))
+    # rows packed beforehand are binary16 with one scale per row; plain float32 rows become fixed point inside the
+    # kernel with one scale per 32 columns, which the outlier cannot coarsen: both meet the oracle, the second tighter
     e = O.matvec_f64(raw, cols, rows, kind, x)[0]
     assert (np.abs(y - e) <= tol_contract(e)).all()
+    assert (np.abs(auto - e) <= tol_ref_scaled(e)).all(), float(np.abs(auto - e).max())
     with pytest.raises(InvalidData):       # packed rows carry one token
         gpu.matmul(None, w, cols, rows, synth.stride_of(kind, cols), kind, 0, packed, 2, X_PACKED)
 
