@@ -214,6 +214,8 @@ def main():
     ap.add_argument("--pdl", type=int, default=1, help="0: launch without programmatic dependent launch (comparison)")
     ap.add_argument("--graph", type=int, default=1, help="0: issue every step's launches instead of replaying a recorded command")
     ap.add_argument("--fused-norm", type=int, default=1, help="0: add_rms as separate launches (comparison)")
+    ap.add_argument("--chain", type=int, default=1,
+                    help="1: the one-token step of a single GPU runs as one persistent kernel (ingot_chain_*); 0: one launch per projection, replayed as a CUDA graph (comparison)")
     ap.add_argument("--group-scope", type=int, default=1,
                     help="0: the projections of an independent scope on their own streams instead of one grid (comparison)")
     ap.add_argument("--no-mma", type=int, default=0, help="1: streaming GEMVs on the fp32 CUDA-core kernel (comparison)")
@@ -286,7 +288,13 @@ def main():
 
     use_graph = True
     tgraph = None
-    if world == 1:
+    fused = None
+    if world == 1 and args.chain and chain.fused_norm:
+        chain.step()                      # once through the one-by-one path (also sizes every buffer)
+        gpu.complete()
+        fused = chain.record_chain()
+        graph = None
+    elif world == 1:
         graph = chain.record() if args.graph else None
     else:
         # the step contains NCCL all-gathers: let torch record it (its NCCL bindings join the
@@ -301,7 +309,9 @@ def main():
             chain.step()
 
     def one_step():
-        if graph is not None:
+        if fused is not None:
+            fused.submit()
+        elif graph is not None:
             graph.submit()
         elif tgraph is not None:
             tgraph.replay()
@@ -381,7 +391,8 @@ def main():
                        "weights": "random Q4_0 blocks" if args.workload == "gemma" else "random Q4_K/Q6_K blocks", "activations": "%s in HBM, fp32 accumulate" % args.activations,
                        "parallelism": "tp%d rows" % world if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (total_bytes * 1.0 / 1e9 / world),
-                       "launch": "one recorded command (CUDA graph) per step" + (" incl. NCCL all-gathers" if world > 1 else "")},
+                       "launch": ("one persistent kernel per step (chain of %(projections)d projections, %(waits)d grid-wide waits, %(stages)d stages of %(stage_bytes)d bytes per SM)" % fused.info())
+                                 if fused is not None else "one recorded command (CUDA graph) per step" + (" incl. NCCL all-gathers" if world > 1 else "")},
             "hbm_gbs_effective": total_bytes / world / (ms_per_step * 1e-3) / 1e9,
             "hbm_frac_of_peak_chain": total_bytes / world / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "e2e": {"value": args.batch * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,

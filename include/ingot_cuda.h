@@ -313,16 +313,20 @@ INGOT_API ingot_status ingot_pack_digits(ingot_gpu *gpu, const void *x, uint32_t
 
 /* No counterpart in the reference.  y = W[expert] x for ONE float32 activation row, for
  * callers that must not allocate: it takes no handle and calls neither cudaMalloc nor
- * cudaFree nor any allocating routine.  The scratch of the tensor-core GEMV (the packed
- * copy of x) and its error word live in file-scope __device__ arrays of the library
- * (about 70 KB per GPU, held until the process exits), so cols is limited to 16384
- * (INGOT_INVALID beyond that; ingot_matvec_static_error() gives the text).  Served:
+ * cudaFree nor any allocating routine.  The scratch of the tensor-core GEMV and its error
+ * word live in file-scope __device__ arrays of the library (about 70 KB per GPU, held
+ * until the process exits), so cols is limited to 16384 (INGOT_INVALID beyond that;
+ * ingot_matvec_static_error() gives the text).  The scratch array receives the packed copy
+ * of x when x is only 4-byte aligned; a 16-byte aligned x is packed inside the kernel, in
+ * shared memory, and only the error word is touched.  Served:
  * kinds 2, 8, 12, 14 with cols % 64 == 0 and 16-byte aligned rows (INGOT_UNSUPPORTED
  * otherwise).  The first call on a device looks up the arrays' device addresses
  * (cudaGetSymbolAddress) — make that first call outside any stream capture.  Work is
  * enqueued on `cuda_stream` of the CURRENT device; wait != 0 also waits for it and
  * reports a device-side time-out.  Every call uses the same scratch: two calls that
- * overlap on the GPU (different streams, no ordering) race — serialise them. */
+ * overlap on the GPU (different streams, no ordering) race — serialise them.  First calls
+ * on a device from several host threads are serialised by the library (a lock around the
+ * address look-up). */
 INGOT_API ingot_status ingot_matvec_static(const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
                                            uint32_t kind, uint32_t expert, const float *x, float *y,
                                            void *cuda_stream, int32_t wait);
@@ -337,6 +341,32 @@ INGOT_API ingot_status ingot_command_begin(ingot_gpu *gpu);
 INGOT_API ingot_status ingot_command_end(ingot_gpu *gpu, ingot_graph **out);
 INGOT_API ingot_status ingot_command_submit(ingot_gpu *gpu, ingot_graph *graph);
 INGOT_API void ingot_command_destroy(ingot_graph *graph);
+
+/* ---- chains: a whole decode step as ONE kernel -----------------------------
+ * The reference encodes a token's operators into one command buffer
+ * (src/generic.rs:701-704) and Metal runs them back to back.  On B200 a chain of short,
+ * dependent GEMV launches leaves HBM idle between them, so the projections of a step can
+ * be recorded into a chain instead: between ingot_chain_begin and ingot_chain_end,
+ * ingot_matmul_normed and ingot_gate_up_normed are collected, not launched (independent
+ * scopes may be opened and closed; any other operator is INGOT_INVALID).  ingot_chain_end
+ * works out from the buffer addresses which projection waits for which, lets projections
+ * with the same normalised input (q, k, v) share it, and builds the list on the device.
+ * ingot_chain_submit enqueues ONE cooperative kernel (one CTA per SM, all resident): a
+ * producer warp per CTA streams the weights of projection after projection without
+ * pause, the other warps wait — with a time limit, reported as INGOT_TIMEOUT by
+ * ingot_synchronize — for the projections theirs depends on.  Results are those of the
+ * same calls issued one by one.  INGOT_UNSUPPORTED when a recorded projection has no
+ * fused tensor-core form or the types mix K-quants with Q4_0/Q8_0.  The buffers and
+ * weights of the recorded calls must stay alive and in place while the chain is used. */
+typedef struct ingot_chain ingot_chain;
+INGOT_API ingot_status ingot_chain_begin(ingot_gpu *gpu);
+INGOT_API ingot_status ingot_chain_end(ingot_gpu *gpu, ingot_chain **out);
+INGOT_API ingot_status ingot_chain_submit(ingot_gpu *gpu, ingot_chain *chain);
+/* Counts of a built chain (any pointer may be NULL): recorded projections, projections that
+ * wait for another one, and the shared-memory ring (stages, bytes per stage). */
+INGOT_API ingot_status ingot_chain_info(const ingot_chain *chain, uint32_t *projections, uint32_t *waits,
+                                        uint32_t *stages, uint32_t *stage_bytes);
+INGOT_API void ingot_chain_destroy(ingot_chain *chain);
 
 /* ---- host-vector conveniences (the reference's public parity hooks) ------ */
 

@@ -63,6 +63,10 @@ SIGNATURES = {
     "ingot_packed_digits_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_digits": [vp, vp, u32, u32, u32, vp],
     "ingot_matvec_static": [vp, u32, u32, u32, u32, u32, vp, vp, vp, i32],
+    "ingot_chain_begin": [vp],
+    "ingot_chain_end": [vp, C.POINTER(vp)],
+    "ingot_chain_submit": [vp, vp],
+    "ingot_chain_info": [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)],
     "ingot_command_begin": [vp],
     "ingot_command_end": [vp, C.POINTER(vp)],
     "ingot_command_submit": [vp, vp],
@@ -74,6 +78,7 @@ OTHER = {
     "ingot_gpu_destroy": (None, [vp]),
     "ingot_last_error": (C.c_char_p, [vp]),
     "ingot_command_destroy": (None, [vp]),
+    "ingot_chain_destroy": (None, [vp]),
     "ingot_matvec_static_error": (C.c_char_p, []),
 }
 

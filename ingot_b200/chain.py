@@ -305,6 +305,22 @@ class DecodeChain:
         self._norm(src, delta, self.h if delta else None, self.xn, s.hidden)
         self._project(self.head, self.xn, self.logits)
 
+    def record_chain(self):
+        """Records the fused step as a chain: one persistent kernel per token step."""
+        if not self.fused_norm or self.world != 1:
+            raise ValueError("only the fused one-token step of a single device can be recorded as a chain")
+        self.gpu.chain_begin()
+        try:
+            self.step()
+        except Exception:
+            try:
+                self.gpu.chain_end()
+            except Exception:
+                pass
+            raise
+        self.launches_per_step = 1
+        return self.gpu.chain_end()
+
     def record(self):
         """Records one step as a replayable command (a CUDA graph)."""
         self.gpu.record()

@@ -23,6 +23,7 @@ struct ingot_gpu {
     int *status_host = nullptr;       // pinned mirror
     void *workspace = nullptr;        // scratch for packed activations
     size_t workspace_bytes = 0;
+    std::vector<void *> retired;      // outgrown scratch blocks: recorded commands may still hold their addresses
     void *tc_scratch = nullptr;       // tile counters and partial rows of the tcgen05 GEMV
     bool use_tc = false;
     uint32_t ep_world = 1;
@@ -41,7 +42,14 @@ struct ingot_gpu {
     int scope_next = 0;               // stream of the next launch inside the scope: 0 = main, i > 0 = side[i - 1]
     int scope_used = 0;               // side streams touched in this scope (bit mask)
     std::vector<GemvCall> pending;    // one-token tensor-core projections of the open scope: they share one launch at its end
+    bool chain_recording = false;     // fused-norm projections are being collected for one persistent kernel
+    std::vector<GemvCall> chain_calls;
     std::string error;
+};
+
+struct ingot_chain {
+    ChainLaunch launch;
+    int device = 0;
 };
 
 struct ingot_graph {
@@ -204,6 +212,7 @@ void ingot_gpu_destroy(ingot_gpu *g) {
     if (g->fork_event) cudaEventDestroy(g->fork_event);
     if (g->status) cudaFree(g->status);
     if (g->workspace) cudaFree(g->workspace);
+    for (void *p : g->retired) cudaFree(p);
     if (g->tc_scratch) cudaFree(g->tc_scratch);
     if (g->status_host) cudaFreeHost(g->status_host);
     delete g;
@@ -250,6 +259,7 @@ ingot_status ingot_synchronize(ingot_gpu *g) {
     case KERNEL_ERR_PRODUCER_TIMEOUT: return fail(g, INGOT_TIMEOUT, "GEMV producer wait ran out");
     case KERNEL_ERR_CONSUMER_TIMEOUT: return fail(g, INGOT_TIMEOUT, "GEMV consumer wait ran out");
     case KERNEL_ERR_GEMM_TIMEOUT: return fail(g, INGOT_TIMEOUT, "GEMM pipeline wait ran out");
+    case KERNEL_ERR_CHAIN_TIMEOUT: return fail(g, INGOT_TIMEOUT, "chain kernel: a projection never saw the one it depends on finish");
     default: return fail(g, INGOT_DEVICE, "unknown device status " + std::to_string(code));
     }
 }
@@ -379,6 +389,7 @@ static ingot_status flush_pending(ingot_gpu *g) {
 static ingot_status gemv_common(ingot_gpu *g, GemvCall &c, uint32_t x_kind, const char *what) {
     ingot_status st = enter(g);
     if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, std::string(what) + ": only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
     if ((st = check_matrix(g, c.kind, c.cols, c.rows, c.stride))) return st;
     if (!x_kind_ok(x_kind)) return fail(g, INGOT_UNSUPPORTED, "activations must be F32 (0), BF16 (30) or packed");
     if (!c.w[0] || (c.nmat == 2 && !c.w[1]) || !c.x || !c.y) return fail(g, INGOT_INVALID, "null pointer");
@@ -418,7 +429,10 @@ ingot_status ingot_matmul(ingot_gpu *g, const void *w, uint32_t cols, uint32_t r
     c.x = x; c.y = y; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
     c.expert = expert; c.count = count; c.nmat = 1;
     // more than four tokens: the reference switches to its GEMM (src/metal_generic.rs:182-206)
-    if (g && !g->no_mma && !g->force_plain && count > 4 && (kind == INGOT_KIND_Q4_K || kind == INGOT_KIND_Q6_K) && cols % 256u == 0 &&
+    // (inside an independent scope the projections run concurrently and the GEMM's scratch is the handle's
+    // one workspace: such calls take the GEMV in groups of four tokens, as the reference's project() does
+    // for any count inside independent_projections, src/qwen.rs:822)
+    if (g && !g->no_mma && !g->force_plain && !g->in_scope && count > 4 && (kind == INGOT_KIND_Q4_K || kind == INGOT_KIND_Q6_K) && cols % 256u == 0 &&
         ((uintptr_t)w % 16u) == 0 && (x_kind == INGOT_KIND_F32 || x_kind == INGOT_KIND_BF16))
         return ingot_gemm(g, w, cols, rows, stride, kind, expert, x, x_kind, count, y);
     return gemv_common(g, c, x_kind, "matmul");
@@ -434,7 +448,9 @@ static ingot_status ensure_workspace(ingot_gpu *g, size_t bytes) {
     e = cudaMalloc(&p, bytes);
     if (e == cudaErrorMemoryAllocation) { cudaGetLastError(); return fail(g, INGOT_INVALID, "out of device memory"); }
     if (e != cudaSuccess) return cuda_fail(g, e, "cudaMalloc");
-    cudaFree(g->workspace);
+    // the old block is kept until the handle goes: a command recorded earlier has its address in its
+    // kernel arguments and must stay replayable
+    g->retired.push_back(g->workspace);
     g->workspace = p;
     g->workspace_bytes = bytes;
     return INGOT_OK;
@@ -504,6 +520,12 @@ static ingot_status normed_common(ingot_gpu *g, GemvCall &c, const float *a, con
     c.norm_a = a; c.norm_b = add ? b : nullptr; c.norm_w = norm_w; c.norm_s = add ? s : nullptr;
     c.norm_eps = eps; c.norm_round_bf16 = round_bf16;
     c.count = 1;
+    if (g->chain_recording) {
+        if (g->no_mma || g->force_plain || !chain_call_eligible(c))
+            return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": this projection cannot be part of a chain (weight type, alignment or shape)");
+        g->chain_calls.push_back(c);
+        return INGOT_OK;
+    }
     cudaError_t e = cudaSuccess;
     const bool aligned = ((uintptr_t)c.w[0] % 16u) == 0 && (c.nmat < 2 || ((uintptr_t)c.w[1] % 16u) == 0) && ((size_t)c.rows * c.stride) % 16u == 0;
     if (aligned && defer_in_scope(g, c)) return INGOT_OK;
@@ -713,6 +735,71 @@ ingot_status ingot_independent_end(ingot_gpu *g) {
         if (e != cudaSuccess) return cuda_fail(g, e, "independent scope join");
     }
     return st;
+}
+
+// ---- chains: a sequence of fused-norm projections as one persistent kernel ------------
+
+ingot_status ingot_chain_begin(ingot_gpu *g) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, "already recording a chain");
+    if (g->capturing || g->in_scope) return fail(g, INGOT_INVALID, "a chain cannot start inside a command recording or an independent scope");
+    g->chain_recording = true;
+    g->chain_calls.clear();
+    return INGOT_OK;
+}
+
+ingot_status ingot_chain_end(ingot_gpu *g, ingot_chain **out) {
+    if (!g || !out) return INGOT_INVALID;
+    *out = nullptr;
+    if (!g->chain_recording) return fail(g, INGOT_INVALID, "not recording a chain");
+    g->chain_recording = false;
+    std::vector<GemvCall> calls;
+    calls.swap(g->chain_calls);
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->in_scope) return fail(g, INGOT_INVALID, "independent scope still open");
+    ingot_chain *ch = new (std::nothrow) ingot_chain();
+    if (!ch) return fail(g, INGOT_DEVICE, "out of host memory");
+    ch->device = g->device;
+    const char *why = "";
+    cudaError_t e = chain_build(calls.data(), (uint32_t)calls.size(), ctx_on(g, g->stream), ch->launch, why);
+    if (e != cudaSuccess) {
+        delete ch;
+        if (e == cudaErrorNotSupported || e == cudaErrorInvalidValue) {
+            cudaGetLastError();
+            return fail(g, e == cudaErrorNotSupported ? INGOT_UNSUPPORTED : INGOT_INVALID, std::string("chain: ") + why);
+        }
+        if (e == cudaErrorMemoryAllocation) { cudaGetLastError(); return fail(g, INGOT_INVALID, "out of device memory"); }
+        return cuda_fail(g, e, "chain build");
+    }
+    *out = ch;
+    return INGOT_OK;
+}
+
+ingot_status ingot_chain_submit(ingot_gpu *g, ingot_chain *ch) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!ch || !ch->launch.ops_dev) return fail(g, INGOT_INVALID, "null chain");
+    if (ch->device != g->device) return fail(g, INGOT_INVALID, "chain was built on another device");
+    if (g->chain_recording || g->in_scope) return fail(g, INGOT_INVALID, "chain: cannot submit inside a chain recording or an independent scope");
+    return after_launch(g, chain_launch(ch->launch, ctx_on(g, g->stream)), "chain");
+}
+
+ingot_status ingot_chain_info(const ingot_chain *ch, uint32_t *projections, uint32_t *waits, uint32_t *stages, uint32_t *stage_bytes) {
+    if (!ch) return INGOT_INVALID;
+    if (projections) *projections = ch->launch.n_ops;
+    if (waits) *waits = ch->launch.waits;
+    if (stages) *stages = ch->launch.slots;
+    if (stage_bytes) *stage_bytes = ch->launch.slot_bytes;
+    return INGOT_OK;
+}
+
+void ingot_chain_destroy(ingot_chain *ch) {
+    if (!ch) return;
+    cudaSetDevice(ch->device);
+    chain_free(ch->launch);
+    delete ch;
 }
 
 // ---- command recording --------------------------------------------------------

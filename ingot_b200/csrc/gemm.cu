@@ -489,14 +489,10 @@ cudaError_t launch_gemm_dequant(const uint8_t *w, uint32_t cols, uint32_t rows, 
     to_half_kernel<<<(uint32_t)blocks, 256, 0, ctx.stream>>>(h);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    static bool configured = false;
-    if (!configured) {
-        e = cudaFuncSetAttribute(gemm_dequant_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmShape<1>::SMEM);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemm_dequant_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmShape<2>::SMEM);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static DeviceOnce once1, once2;
+    e = once1.smem(gemm_dequant_tcgen05_kernel<1>, (int)GemmShape<1>::SMEM);
+    if (e == cudaSuccess) e = once2.smem(gemm_dequant_tcgen05_kernel<2>, (int)GemmShape<2>::SMEM);
+    if (e != cudaSuccess) return e;
     const uint32_t splits = gemm_splits(cols, rows, tokens, ctx.sm_count);
     float *partial = splits > 1 ? reinterpret_cast<float *>(static_cast<uint8_t *>(x_half_scratch) + (((size_t)tokens * cols * 2u + 255u) & ~(size_t)255u))
                                 : nullptr;

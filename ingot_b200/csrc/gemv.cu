@@ -229,11 +229,10 @@ __global__ void __launch_bounds__(128) gemv_plain_kernel(const __grid_constant__
 template <uint32_t KIND, int NTOK, int NMAT>
 static cudaError_t launch_stream_t(const GemvArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
     auto kernel = gemv_stream_kernel<KIND, NTOK, NMAT>;
-    static bool configured = false;          // per instantiation; the attribute is per device function
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_MAX);
+    static DeviceOnce once;
+    {
+        const cudaError_t e = once.smem(kernel, (int)GEMV_SMEM_MAX);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

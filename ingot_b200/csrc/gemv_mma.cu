@@ -34,13 +34,18 @@
 // and odd ones xl, replicated over the quads, so every lane ends with (sum q xh,
 // sum q xl) in (c0, c1) and the four lanes of a quad share the scale work.
 #include <cuda_fp16.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
 #include <type_traits>
+#include <vector>
 
 #include "dev_common.cuh"
 #include "gemv_core.cuh"
 #include "kernels.h"
 #include "pack.cuh"
 #include "ptx.cuh"
+#include "tensor_map.h"
 
 namespace ingot {
 
@@ -102,6 +107,9 @@ struct MmaArgs {
     // npack: na holds plain float32 activation rows (row `pair / top` or `pair` of a routed call) that
     // the CTA only packs — no sum, no norm, no rounding: the packing launch folded into the GEMV
     uint32_t npack;
+    // optional tensor maps (device memory) of the matrices as rows of 8-byte elements, in boxes of
+    // (row_pitch / 8) x (16 row_tiles): a stage then arrives by one tiled copy instead of one copy per row
+    const void *tmap[2];
 };
 
 static bool mma_kind(uint32_t kind) { return kind == KIND_Q4_K || kind == KIND_Q6_K || kind == KIND_Q4_0 || kind == KIND_Q8_0; }
@@ -119,8 +127,15 @@ static void step_geometry(uint32_t kind, uint32_t &cols, uint32_t &bytes) {
 // (16: eight rows x 4 lanes x 4 bytes; 32: four rows x 4 lanes x 8 bytes per half-warp of a 64-bit load).
 static uint32_t pitch_of(uint32_t chunk_bytes, uint32_t lead = 16u) { return chunk_bytes + ((lead + 128u - (chunk_bytes % 128u)) % 128u); }
 
+// Shared-memory geometry that several projections of one kernel have in common: the region of the
+// activation row, and a ring of `slots` stages of `slot_bytes` each.
+struct MmaFixed {
+    uint32_t x_bytes, slot_bytes, slots;
+    uint32_t warps;          // consumer warps of the kernel (8 or 16)
+};
+
 static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t nmat, uint32_t max_ctas,
-                     uint32_t budget, uint32_t xm, MmaPlan &p) {
+                     uint32_t budget, uint32_t xm, MmaPlan &p, const MmaFixed *common = nullptr) {
     if (!mma_kind(kind)) return false;
     uint32_t block, bytes;
     geometry(kind, block, bytes);
@@ -135,7 +150,8 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     p.row_tiles = (uint32_t)MMA_WARPS >> kw;
     const uint32_t per_warp = p.nsteps >> kw;                 // steps each warp owns per row
     p.xm = xm;
-    p.x_bytes = x_row_bytes(xm, cols);
+    p.x_bytes = common ? common->x_bytes : x_row_bytes(xm, cols);
+    if (common && x_row_bytes(xm, cols) > common->x_bytes) return false;
     // the int8 steps of the K-quants read 8 bytes per lane
     const uint32_t lead = (xm >= XM_FX2 && (kind == KIND_Q4_K || kind == KIND_Q6_K)) ? 32u : 16u;
     p.red_slots = budget <= MMA_SMEM_SMALL ? 4u : MMA_RED_SLOTS;
@@ -151,6 +167,10 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
         const uint32_t cb = spw * (1u << kw) * p.step_bytes;
         if (cb % 16u) continue;
         const uint32_t sb = (pitch_of(cb, lead) * 16u * p.row_tiles + 64u + 127u) & ~127u;      // one matrix per stage
+        if (common) {                                 // the most steps whose stage fits a slot
+            if (sb <= common->slot_bytes) pick = spw;
+            continue;
+        }
         if (room / sb < 2) break;
         if (pick == 0 || sb <= MMA_STAGE_TARGET) pick = spw;
     }
@@ -161,6 +181,11 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     p.row_pitch = pitch_of(p.chunk_bytes, lead);
     p.stage_bytes = (p.row_pitch * 16u * p.row_tiles + 64u + 127u) & ~127u;
     p.stages = room / p.stage_bytes;
+    if (common) {
+        p.stage_bytes = common->slot_bytes;
+        p.stages = common->slots;
+        if ((uint64_t)p.stages * p.stage_bytes > room) return false;
+    }
     if (p.stages > (uint32_t)MMA_MAX_STAGES) p.stages = MMA_MAX_STAGES;
     if (p.stages > p.red_slots - 2u) p.stages = p.red_slots - 2u;
     if (p.stages < 2) return false;
@@ -591,12 +616,20 @@ template <> struct ImmaStep<KIND_Q6_K> {
         const uint2 b = *reinterpret_cast<const uint2 *>(p + 2);
         return make_uint2(__funnelshift_r(a, b.x, 16u), __funnelshift_r(b.x, b.y, 16u));
     }
-    // four six-bit values of quarter Q from a word of ql (L) and a word of qh (H)
-    template <int Q>
-    static __device__ __forceinline__ uint32_t six(uint32_t L, uint32_t H) {
-        const uint32_t lo = (Q < 2 ? L : (L >> 4)) & NIB;
-        const uint32_t hi = (Q == 0 ? (H << 4) : Q == 1 ? (H << 2) : Q == 2 ? H : (H >> 2)) & 0x30303030u;
-        return lo | hi;
+    // The six-bit values of the four quarters of a half block, four columns at a time: la / lb = a word of
+    // ql (low nibbles: quarter 0 / 1, high nibbles: quarter 2 / 3), h = the word of qh (two bits per
+    // quarter).  The qh fields are masked in pairs (0x33: quarters 0 and 2, or 1 and 3 after a shift by
+    // two), so that one select per quarter puts a nibble of ql under a two-bit field of qh.
+    struct Six4 { uint32_t q[4]; };
+    static __device__ __forceinline__ uint32_t under(uint32_t nib, uint32_t top) { return (nib & NIB) | (top & ~NIB); }
+    static __device__ __forceinline__ Six4 six4(uint32_t la, uint32_t lb, uint32_t h) {
+        const uint32_t ha = h & 0x33333333u, hb = (h >> 2) & 0x33333333u;
+        Six4 r;
+        r.q[0] = under(la, ha << 4);
+        r.q[1] = under(lb, hb << 4);
+        r.q[2] = under(la >> 4, ha);
+        r.q[3] = under(lb >> 4, hb);
+        return r;
     }
     template <int ND, int CLS>
     static __device__ __forceinline__ void run_cls(const uint8_t *r0, const uint8_t *r1, const uint8_t *const (&bx)[4], const uint8_t *meta,
@@ -610,19 +643,16 @@ template <> struct ImmaStep<KIND_Q6_K> {
         for (uint32_t n = 0; n < 2; ++n) {
             const uint2 la0 = ld8<CLS>(r0 + 64u * n + 8u * t), lb0 = ld8<CLS>(r0 + 64u * n + 32u + 8u * t), h0 = ld8<CLS>(r0 + 128u + 32u * n + 8u * t);
             const uint2 la1 = ld8<CLS>(r1 + 64u * n + 8u * t), lb1 = ld8<CLS>(r1 + 64u * n + 32u + 8u * t), h1 = ld8<CLS>(r1 + 128u + 32u * n + 8u * t);
+            const Six4 x0 = six4(la0.x, lb0.x, h0.x), y0 = six4(la0.y, lb0.y, h0.y);      // row g: k slots 4t.., 16+4t..
+            const Six4 x1 = six4(la1.x, lb1.x, h1.x), y1 = six4(la1.y, lb1.y, h1.y);      // row g+8
 #pragma unroll
             for (uint32_t ch = 0; ch < 2; ++ch) {
                 int c[NP][4];
 #pragma unroll
                 for (int ps = 0; ps < NP; ++ps) {
                     const uint2 b_lo = IG_B8(bx[0] + (4u * n + ch) * SBS + ps * 64), b_hi = IG_B8(bx[1] + (4u * n + ch) * SBS + ps * 64);
-                    if (ch == 0) {
-                        imma16832<false, true>(c[ps], six<0>(la0.x, h0.x), six<0>(la1.x, h1.x), six<0>(la0.y, h0.y), six<0>(la1.y, h1.y), b_lo.x, b_lo.y);
-                        imma16832<false, false>(c[ps], six<2>(la0.x, h0.x), six<2>(la1.x, h1.x), six<2>(la0.y, h0.y), six<2>(la1.y, h1.y), b_hi.x, b_hi.y);
-                    } else {
-                        imma16832<false, true>(c[ps], six<1>(lb0.x, h0.x), six<1>(lb1.x, h1.x), six<1>(lb0.y, h0.y), six<1>(lb1.y, h1.y), b_lo.x, b_lo.y);
-                        imma16832<false, false>(c[ps], six<3>(lb0.x, h0.x), six<3>(lb1.x, h1.x), six<3>(lb0.y, h0.y), six<3>(lb1.y, h1.y), b_hi.x, b_hi.y);
-                    }
+                    imma16832<false, true>(c[ps], x0.q[ch], x1.q[ch], y0.q[ch], y1.q[ch], b_lo.x, b_lo.y);
+                    imma16832<false, false>(c[ps], x0.q[ch + 2u], x1.q[ch + 2u], y0.q[ch + 2u], y1.q[ch + 2u], b_hi.x, b_hi.y);
                 }
                 // this lane: quarter q = ch + 2 pos, run `run`; value - 32 through the run's activation sum
                 const uint32_t q = ch + 2u * pos, idx = 8u * n + 2u * q + run;
@@ -713,10 +743,23 @@ template <> struct ImmaStep<KIND_Q8_0> {
 // kernel
 // ---------------------------------------------------------------------------
 
+// What a thread carries from one projection to the next when a kernel runs several of them
+// back to back over the same ring (the one-projection kernels use a fresh one).
+struct MmaRun {
+    uint32_t itg[2] = {0u, 0u};   // stage fills so far in the ring of each consumer group (a consumer counts its own group's)
+    uint32_t tiles = 0;      // tiles so far: slot and phase of the partial-sum ring
+    bool setup = true;       // initialise the barriers and the zero block (first projection only)
+    bool build_x = true;     // consumers build the activation row; false: the row of the previous projection is still there
+    unsigned long long *trace = nullptr;    // debugging: where thread 0 stores the time at which the activation row was ready
+};
+
 // The whole CTA's work on one projection: CTA `cta` of `nctas` (its share of the rows), pair `pair`.
-template <uint32_t KIND, int NMAT, int XM>
-__device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, const uint32_t cta, const uint32_t nctas, const uint32_t pair,
-                                              const bool whole_tiles) {
+// False when a bounded wait ran out (the status word says which).
+// CW consumer warps in groups of eight: a group splits the columns of a tile among its warps and takes
+// every (CW / 8)-th tile, so with sixteen warps two stages of the ring are in work at once.
+template <uint32_t KIND, int NMAT, int XM, int CW = MMA_WARPS>
+__device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, const uint32_t cta, const uint32_t nctas, const uint32_t pair,
+                                              const bool whole_tiles, MmaRun &run) {
     const MmaPlan &p = a.plan;
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MMA_MAX_STAGES;
@@ -733,18 +776,21 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     uint8_t *stages = reinterpret_cast<uint8_t *>(red) + p.red_bytes;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < p.stages; ++s) {
-            ptx::mbar_init(&full[s], 1);
-            ptx::mbar_init(&empty[s], MMA_WARPS);
+    if (run.setup) {
+        if (threadIdx.x == 0) {
+            for (uint32_t s = 0; s < p.stages; ++s) {
+                ptx::mbar_init(&full[s], 1);
+                ptx::mbar_init(&empty[s], MMA_WARPS);
+            }
+            ptx::mbar_init(xbar, 1);
+            for (uint32_t i = 0; i < p.red_slots; ++i) ptx::mbar_init(&tbar[i], MMA_WARPS);
+            ptx::mbar_init_fence();
         }
-        ptx::mbar_init(xbar, 1);
-        for (uint32_t i = 0; i < p.red_slots; ++i) ptx::mbar_init(&tbar[i], MMA_WARPS);
-        ptx::mbar_init_fence();
+        for (uint32_t i = threadIdx.x; i < MMA_ZERO_BYTES / 4u; i += (CW + 1) * 32) reinterpret_cast<uint32_t *>(zeros)[i] = 0u;
+        __syncthreads();
+        ptx::pdl_launch_dependents();
+        run.setup = false;
     }
-    for (uint32_t i = threadIdx.x; i < MMA_ZERO_BYTES / 4u; i += MMA_THREADS) reinterpret_cast<uint32_t *>(zeros)[i] = 0u;
-    __syncthreads();
-    ptx::pdl_launch_dependents();
 
     uint32_t r_begin, r_end;
     const uint32_t stage_rows = 16u * p.row_tiles;
@@ -763,7 +809,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     }
     const uint32_t n_tiles = (r_end - r_begin + stage_rows - 1) / stage_rows;
 
-    if (warp == MMA_WARPS) {
+    if (warp == (uint32_t)CW) {
         // ---- producer warp: weights first (they do not depend on the previous kernel),
         // then, once the ring is primed, wait for the previous kernel and fetch the
         // packed activations ----
@@ -771,18 +817,31 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         if (a.ids) {                                   // routing comes from the previous kernel
             ptx::pdl_wait();
             expert = a.ids[pair];
-            if (expert >= a.n_experts) return;         // skipped pair, or out of range: consumers handle it
+            if (expert >= a.n_experts) return true;    // skipped pair, or out of range: consumers handle it
             x_row = a.per_pair ? pair : pair / a.top;
         }
         const size_t mat_off = (size_t)expert * p.rows * p.stride;
+        // Each consumer group has its own ring (stages / GROUPS slots) and takes every GROUPS-th tile; the
+        // producer fills the groups' rings in turn, one stage each, so that all groups are fed at once.
         bool x_sent = false;
-        uint32_t it = 0;
-        for (uint32_t tile = 0; tile < n_tiles; ++tile) {
-            const uint32_t row0 = r_begin + tile * stage_rows;
-            const uint32_t nrows = (r_end - row0) < stage_rows ? (r_end - row0) : stage_rows;
-            for (uint32_t cm = 0; cm < p.chunks * NMAT; ++cm, ++it) {
+        constexpr uint32_t GROUPS_P = CW / MMA_WARPS;
+        const uint32_t fpt = p.chunks * NMAT, sg = p.stages / GROUPS_P;
+        uint32_t fills_g[GROUPS_P], tile_g[GROUPS_P], cm_g[GROUPS_P], done_g[GROUPS_P], max_fills = 0, issued = 0;
+#pragma unroll
+        for (uint32_t gq = 0; gq < GROUPS_P; ++gq) {
+            fills_g[gq] = n_tiles > gq ? ((n_tiles - 1u - gq) / GROUPS_P + 1u) * fpt : 0u;
+            tile_g[gq] = gq; cm_g[gq] = 0u; done_g[gq] = 0u;
+            if (fills_g[gq] > max_fills) max_fills = fills_g[gq];
+        }
+        for (uint32_t j = 0; j < max_fills; ++j) {
+#pragma unroll
+            for (uint32_t gq = 0; gq < GROUPS_P; ++gq) {
+                if (done_g[gq] >= fills_g[gq]) continue;
+                const uint32_t tile = tile_g[gq], cm = cm_g[gq];
+                const uint32_t row0 = r_begin + tile * stage_rows;
+                const uint32_t nrows = (r_end - row0) < stage_rows ? (r_end - row0) : stage_rows;
                 const uint32_t c = cm / NMAT, m = cm - c * NMAT;
-                if (!x_sent && it == p.stages && !a.na) {       // ring primed: the next wait needs the consumers
+                if (!x_sent && issued == p.stages && !a.na) {   // ring primed: the next wait needs the consumers
                     if (!a.ids) ptx::pdl_wait();
                     if (lane == 0) {
                         ptx::mbar_expect_tx(xbar, p.x_bytes);
@@ -790,18 +849,31 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                     }
                     x_sent = true;
                 }
-                const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                const uint32_t itl = run.itg[gq] + done_g[gq];
+                const uint32_t s = gq * sg + itl % sg, ph = (itl / sg) & 1u;
                 bool ok = true;
                 if (lane == 0) ok = ptx::mbar_wait_sleep<128>(&empty[s], ph ^ 1u);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) { if (lane == 0) set_status_word(a.status, KERNEL_ERR_PRODUCER_TIMEOUT); return; }
+                if (!ok) { if (lane == 0) set_status_word(a.status, KERNEL_ERR_PRODUCER_TIMEOUT); return false; }
                 uint8_t *dst = stages + (size_t)s * p.stage_bytes;
-                if (lane == 0) ptx::mbar_expect_tx(&full[s], p.chunk_bytes * nrows);
-                __syncwarp();
-                for (uint32_t r = lane; r < nrows; r += 32u)
-                    ptx::bulk_g2s(dst + (size_t)r * p.row_pitch,
-                                  a.w[m] + mat_off + (size_t)(row0 + r) * p.stride + (size_t)c * p.chunk_bytes,
-                                  p.chunk_bytes, &full[s]);
+                if (a.tmap[m]) {
+                    // one tiled copy brings the whole stage: stage_rows rows of row_pitch bytes each (the chunk and the
+                    // first bytes of the next one, which make the pitch; rows past the matrix read as zeros).  A 1-D
+                    // bulk copy per row costs the issuing warp about 150 cycles each, more than the rows take to stream.
+                    if (lane == 0) {
+                        ptx::mbar_expect_tx(&full[s], p.row_pitch * stage_rows);
+                        ptx::tma_load_2d(dst, a.tmap[m], (c * p.chunk_bytes) >> 3, row0, &full[s]);
+                    }
+                } else {
+                    if (lane == 0) ptx::mbar_expect_tx(&full[s], p.chunk_bytes * nrows);
+                    __syncwarp();
+                    for (uint32_t r = lane; r < nrows; r += 32u)
+                        ptx::bulk_g2s(dst + (size_t)r * p.row_pitch,
+                                      a.w[m] + mat_off + (size_t)(row0 + r) * p.stride + (size_t)c * p.chunk_bytes,
+                                      p.chunk_bytes, &full[s]);
+                }
+                ++issued; ++done_g[gq];
+                if (++cm_g[gq] == fpt) { cm_g[gq] = 0u; tile_g[gq] += GROUPS_P; }
             }
         }
         if (!x_sent && !a.na) {                          // fewer stage fills than ring slots
@@ -811,7 +883,9 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 ptx::bulk_g2s(xrow, a.xp + (size_t)x_row * p.x_bytes, p.x_bytes, xbar);
             }
         }
-        return;
+#pragma unroll
+        for (uint32_t gq = 0; gq < GROUPS_P; ++gq) run.itg[gq] += fills_g[gq];
+        return true;
     }
 
     // ---- consumer warps ----
@@ -821,12 +895,13 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         if (e >= a.n_experts) {
             if (e == ROUTE_SKIP) {                      // not this device's expert: the row is zero
                 float *yz = a.y + (size_t)pair * p.rows;
-                for (uint32_t r = r_begin + threadIdx.x; r < r_end; r += MMA_WARPS * 32) yz[r] = 0.f;
+                for (uint32_t r = r_begin + threadIdx.x; r < r_end; r += CW * 32) yz[r] = 0.f;
             } else if (threadIdx.x == 0) set_status_word(a.status, KERNEL_ERR_EXPERT_RANGE);
-            return;
+            return true;
         }
     }
     if constexpr (FX) {
+      if (run.build_x && warp < (uint32_t)MMA_WARPS) {
         // ---- fused add + RMS normalisation + packing (what add_rms with a packed output computes,
         // kernels/generic.metal:390-404): the 256 consumer threads of every CTA build the packed row ----
         ptx::pdl_wait();
@@ -835,8 +910,9 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         const float4 *a4 = reinterpret_cast<const float4 *>(a.na) + (size_t)in_row * n4, *b4 = reinterpret_cast<const float4 *>(a.nb);
         float *scratch = red;                          // the partial-sum area is idle until the first tile ends
         auto load = [&](uint32_t j) {
-            float4 v = a4[j];
-            if (b4) { const float4 o = b4[j]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+            // (read through L2: in a kernel that runs several projections the vectors come from other CTAs)
+            float4 v = __ldcg(a4 + j);
+            if (b4) { const float4 o = __ldcg(b4 + j); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
             return v;
         };
         auto reduce = [&](float v, bool is_max) {
@@ -853,42 +929,49 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             return r;
         };
         constexpr uint32_t NT = MMA_WARPS * 32;
-        auto finish = [&](float (&u)[4], uint32_t j, float inv) {
-            const float4 wv = a.nw ? reinterpret_cast<const float4 *>(a.nw)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
-            u[0] = u[0] * inv * wv.x; u[1] = u[1] * inv * wv.y; u[2] = u[2] * inv * wv.z; u[3] = u[3] * inv * wv.w;
-            if (a.nround_bf16) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    uint32_t x = __float_as_uint(u[k]);
-                    if ((x & 0x7fffffffu) <= 0x7f800000u) x += 0x7fffu + ((x >> 16) & 1u);       // round to nearest even
-                    u[k] = __uint_as_float(x & 0xffff0000u);
-                }
-            }
-        };
         // the row stays in registers, NV float4 per thread (the unrolled loops issue their instructions
         // for dead slots too, so narrow rows take the short form)
         auto in_registers = [&](auto nv_const) {
             constexpr uint32_t NV = decltype(nv_const)::value;
             float4 v[NV];
             float sum = 0.f;
+            // all loads of the row first, nothing that depends on one of them in between: one trip to L2 for the
+            // whole row (a store of the residual sum after each load would make every load wait for the one before)
 #pragma unroll
             for (uint32_t i = 0; i < NV; ++i) {
                 const uint32_t j = tid + i * NT;
-                v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                v[i] = j < n4 ? __ldcg(a4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            if (b4) {                                  // (four at a time: the second vector's loads are in flight together with the first's)
+#pragma unroll
+                for (uint32_t i0 = 0; i0 < NV; i0 += 4u) {
+                    float4 o[4];
+#pragma unroll
+                    for (uint32_t k = 0; k < 4u; ++k) {
+                        const uint32_t j = tid + (i0 + k) * NT;
+                        o[k] = (i0 + k < NV && j < n4) ? __ldcg(b4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (uint32_t k = 0; k < 4u; ++k)
+                        if (i0 + k < NV) { v[i0 + k].x += o[k].x; v[i0 + k].y += o[k].y; v[i0 + k].z += o[k].z; v[i0 + k].w += o[k].w; }
+                }
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < NV; ++i) {
+                const uint32_t j = tid + i * NT;
                 if (j < n4) {
-                    v[i] = load(j);
                     if (a.ns && cta == 0) reinterpret_cast<float4 *>(a.ns)[j] = v[i];
                     sum += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
                 }
             }
+            if (run.trace && threadIdx.x == 0) run.trace[2] = ptx::global_timer_ns() + (unsigned long long)(sum == 12345.678f);
             const float inv = a.npack ? 1.0f : 1.0f / sqrtf(reduce(sum, false) / (float)p.cols + a.neps);
+            if (run.trace && threadIdx.x == 0) run.trace[3] = ptx::global_timer_ns();
 #pragma unroll
             for (uint32_t i = 0; i < NV; ++i) {
                 if (i * NT >= n4) break;                               // uniform: the shuffles of a sub-block keep all its lanes
                 const uint32_t j = tid + i * NT;
-                float u[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-                if (j < n4) finish(u, j, inv);
-                fx_store<ND>(xrow, p.cols, j, u, j < n4);
+                fx_norm_store<ND>(xrow, p.cols, j, v[i], inv, a.nw, a.nround_bf16, j < n4);
             }
         };
         if (n4 <= 4u * NT) in_registers(std::integral_constant<uint32_t, 4>{});            // up to 4096 columns
@@ -904,20 +987,18 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             for (uint32_t j0 = 0; j0 < n4; j0 += NT) {                 // uniform trip count: the shuffles of a sub-block keep all its lanes
                 const uint32_t j = j0 + tid;
                 const bool live = j < n4;
-                float u[4] = {0.f, 0.f, 0.f, 0.f};
-                if (live) {
-                    const float4 v = load(j);
-                    u[0] = v.x; u[1] = v.y; u[2] = v.z; u[3] = v.w;
-                    finish(u, j, inv);
-                }
-                fx_store<ND>(xrow, p.cols, j, u, live);
+                fx_norm_store<ND>(xrow, p.cols, j, live ? load(j) : make_float4(0.f, 0.f, 0.f, 0.f), inv, a.nw, a.nround_bf16, live);
             }
         }
         ptx::named_bar_sync(1, MMA_WARPS * 32);
+      }
+      // (the first eight warps build the row, so its arithmetic does not depend on CW; the others wait here)
+      if (CW > MMA_WARPS && run.build_x) ptx::named_bar_sync(2, CW * 32);
+      if (run.trace && threadIdx.x == 0) *run.trace = ptx::global_timer_ns();
     } else {
         if (!ptx::mbar_wait(xbar, 0)) {
             if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
-            return;
+            return false;
         }
     }
     ptx::pdl_wait();          // outputs may be read by the previous kernel until it ends
@@ -925,7 +1006,9 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     const float unscale = FX ? 1.0f : *reinterpret_cast<const float *>(xrow + (size_t)p.cols * XB + p.cols / 4u);
 
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t kw = warp & ((1u << p.kw_log2) - 1u), rt = warp >> p.kw_log2;
+    constexpr uint32_t GROUPS = CW / MMA_WARPS;
+    const uint32_t grp = warp / MMA_WARPS, wg = warp % MMA_WARPS;         // consumer group and the warp's place in it
+    const uint32_t kw = wg & ((1u << p.kw_log2) - 1u), rt = wg >> p.kw_log2;
     constexpr uint32_t STEP_BYTES = KIND == KIND_Q4_K ? 144u : KIND == KIND_Q6_K ? 210u : KIND == KIND_Q4_0 ? 72u : 136u;
     constexpr uint32_t MMAS = (KIND == KIND_Q4_K || KIND == KIND_Q6_K) ? 16u : 8u;     // binary16 MMAs (16 columns each) per step
     constexpr uint32_t XS = FX ? (uint32_t)ND * 16u : HI ? 32u : 64u;                   // packed bytes per 16 columns
@@ -949,11 +1032,13 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     // Sum of a finished tile's partials over the K warps -> y.  The warp that sums rotates with
     // the tile, and it sums tile T only after its own work on tile T + 1, when the partials are
     // long complete: no warp falls behind the others at a tile boundary.
+    const uint32_t tile_base = run.tiles;          // position of this projection's first tile in the partial-sum ring
     auto sum_tile = [&](uint32_t tile) -> bool {
-        if (((tile ^ kw) & kmask) != 0u) return true;                  // another warp's turn
-        const uint32_t slot_id = tile % p.red_slots;
+        const uint32_t ring = tile_base + tile;
+        if (((ring ^ kw) & kmask) != 0u) return true;                  // another warp's turn
+        const uint32_t slot_id = ring % p.red_slots;
         const float *slot = red + (size_t)slot_id * MMA_WARPS * 2u * 16u;
-        if (!ptx::mbar_wait_sleep<20>(&tbar[slot_id], (tile / p.red_slots) & 1u)) {
+        if (!ptx::mbar_wait_sleep<20>(&tbar[slot_id], (ring / p.red_slots) & 1u)) {
             if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
             return false;
         }
@@ -971,8 +1056,9 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         return true;
     };
 
-    uint32_t it = 0;
-    for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+    const uint32_t sg = p.stages / GROUPS;             // slots of this group's ring
+    uint32_t it = run.itg[grp];
+    for (uint32_t tile = grp; tile < n_tiles; tile += GROUPS) {
         const uint32_t row0 = r_begin + tile * stage_rows;
         const uint32_t nrows = (r_end - row0) < stage_rows ? (r_end - row0) : stage_rows;
         const uint32_t lr0 = rt * 16u + g, lr1 = lr0 + 8u;             // rows of this lane inside the stage
@@ -985,10 +1071,10 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             const uint32_t gs0 = c * (p.spw << p.kw_log2) + kw;                // first step inside the row
 #pragma unroll
             for (int m = 0; m < NMAT; ++m, ++it) {
-                const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                const uint32_t s = grp * sg + it % sg, ph = (it / sg) & 1u;
                 if (!ptx::mbar_wait_sleep<20>(&full[s], ph)) {
                     if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
-                    return;
+                    return false;
                 }
                 const uint8_t *st = stages + (size_t)s * p.stage_bytes;
                 if (rt * 16u < nrows) {
@@ -1025,7 +1111,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             }
         }
         // quad reduce (the four lanes hold different scale groups), then across the K warps
-        const uint32_t slot_id = tile % p.red_slots;
+        const uint32_t slot_id = (tile_base + tile) % p.red_slots;
         float *slot = red + (size_t)slot_id * MMA_WARPS * 2u * 16u;
 #pragma unroll
         for (int m = 0; m < NMAT; ++m)
@@ -1034,19 +1120,26 @@ __device__ __forceinline__ void gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 float v = acc[m][h];
                 v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
                 v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
-                if (t == 0) slot[(warp * 2u + m) * 16u + g + 8u * h] = v;
+                if (t == 0) slot[(wg * 2u + m) * 16u + g + 8u * h] = v;
             }
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&tbar[slot_id]);
-        if (tile > 0 && !sum_tile(tile - 1)) return;
+        if (tile >= GROUPS && !sum_tile(tile - GROUPS)) return false;
     }
-    if (n_tiles > 0) sum_tile(n_tiles - 1);
+    if (n_tiles > grp) {                               // the group's last tile
+        const uint32_t last = grp + (n_tiles - 1u - grp) / GROUPS * GROUPS;
+        if (!sum_tile(last)) return false;
+    }
+    run.itg[grp] = it;
+    run.tiles = tile_base + n_tiles;
+    return true;
 }
 
 template <uint32_t KIND, int NMAT, int OCC, int XM>
 __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    gemv_mma_body<KIND, NMAT, XM>(a, smem, blockIdx.x, gridDim.x, blockIdx.y, false);
+    MmaRun run;
+    gemv_mma_body<KIND, NMAT, XM>(a, smem, blockIdx.x, gridDim.x, blockIdx.y, false, run);
 }
 
 // Several independent one-token projections in one launch (what the reference's
@@ -1069,11 +1162,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_group_kernel(const __
     while (i + 1 < ga.n && blockIdx.x >= ga.first[i + 1]) ++i;
     const MmaArgs &a = ga.part[i];
     const uint32_t cta = blockIdx.x - ga.first[i], nctas = ga.first[i + 1] - ga.first[i];
+    MmaRun run;
     switch (a.plan.kind) {
-    case KIND_Q4_K: gemv_mma_body<KIND_Q4_K, 1, XM>(a, smem, cta, nctas, 0u, true); break;
-    case KIND_Q6_K: gemv_mma_body<KIND_Q6_K, 1, XM>(a, smem, cta, nctas, 0u, true); break;
-    case KIND_Q4_0: gemv_mma_body<KIND_Q4_0, 1, XM>(a, smem, cta, nctas, 0u, true); break;
-    default: gemv_mma_body<KIND_Q8_0, 1, XM>(a, smem, cta, nctas, 0u, true); break;
+    case KIND_Q4_K: gemv_mma_body<KIND_Q4_K, 1, XM>(a, smem, cta, nctas, 0u, true, run); break;
+    case KIND_Q6_K: gemv_mma_body<KIND_Q6_K, 1, XM>(a, smem, cta, nctas, 0u, true, run); break;
+    case KIND_Q4_0: gemv_mma_body<KIND_Q4_0, 1, XM>(a, smem, cta, nctas, 0u, true, run); break;
+    default: gemv_mma_body<KIND_Q8_0, 1, XM>(a, smem, cta, nctas, 0u, true, run); break;
     }
 }
 
@@ -1426,11 +1520,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mt_kernel(const __grid_co
 template <uint32_t KIND, int NMAT>
 static cudaError_t launch_mt_t(const MtArgs &a, cudaStream_t stream, bool pdl) {
     auto kernel = gemv_mt_kernel<KIND, NMAT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_MAX);
+    static DeviceOnce once;
+    {
+        const cudaError_t e = once.smem(kernel, (int)MMA_SMEM_MAX);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.p.ctas);
@@ -1473,12 +1566,10 @@ bool try_launch_gemv_mt(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &er
 template <uint32_t KIND, int NMAT, int OCC, int XM>
 static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
     auto kernel = gemv_mma_kernel<KIND, NMAT, OCC, XM>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(OCC == 3 ? MMA_SMEM_SMALL : MMA_SMEM_MAX));
+    static DeviceOnce once;
+    {
+        const cudaError_t e = once.smem(kernel, (int)(OCC == 3 ? MMA_SMEM_SMALL : MMA_SMEM_MAX));
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -1608,11 +1699,10 @@ bool gemv_mma_group_eligible(const GemvCall &c, const LaunchCtx &ctx) {
 template <int XM>
 static cudaError_t launch_mma_group_t(const MmaGroupArgs &ga, uint32_t smem_bytes, cudaStream_t stream, bool pdl) {
     auto kernel = gemv_mma_group_kernel<XM>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_BUDGET);
+    static DeviceOnce once;
+    {
+        const cudaError_t e = once.smem(kernel, (int)MMA_SMEM_BUDGET);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ga.first[ga.n]);
@@ -1686,6 +1776,385 @@ bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCt
     default: err = launch_mma_group_t<XM_FX4>(ga, smem_bytes, ctx.stream, ctx.pdl); break;
     }
     return true;
+}
+
+// ---------------------------------------------------------------------------
+// A sequence of one-token fused-norm projections run by ONE persistent kernel.
+//
+// A decode step is a chain of short, dependent projections; launched one by one, each pays a launch,
+// a ramp of its copy ring and a tail, and HBM idles in between.  Here every SM keeps one resident CTA
+// for the whole sequence (a cooperative launch: all CTAs are co-resident).  The producer warp of a
+// CTA walks the list of projections and keeps streaming weight rows into the ring — weights depend
+// on nothing, so it runs ahead into the next projection while the consumer warps still finish the
+// current one or wait for its inputs.  The consumer warps take the projections in order: wait until
+// every CTA has finished the projection this one depends on (a counter per projection in global
+// memory, raised with a fence by each CTA and polled, with a time limit, by one thread), build the
+// activation row (add + RMS norm + fixed point, read through L2), multiply their share of the rows,
+// store.  Projections that read the same normalised input (k, v and q of a layer) build it once.
+// ---------------------------------------------------------------------------
+
+static constexpr uint32_t CHAIN_NO_WAIT = 0xffffffffu;
+
+struct ChainOp {
+    MmaArgs a;
+    uint32_t wait_op;        // the projection whose completion (by every CTA) this one waits for, or CHAIN_NO_WAIT
+    uint32_t reuse_x;        // the activation row of the previous projection is this one's as well
+    uint32_t pad[2];
+};
+static_assert(sizeof(ChainOp) % 16 == 0, "copied as 16-byte words");
+
+struct ChainArgs {
+    const ChainOp *ops;
+    uint32_t *done;          // [n_ops] CTAs that have finished each projection (zero at launch)
+    uint32_t n_ops;
+    int *status;
+    unsigned long long *trace;     // debugging (INGOT_CHAIN_TRACE): [n_ops][4] times of CTA 0: start, inputs ready, row built, done
+};
+
+__device__ __forceinline__ bool chain_wait(const uint32_t *counter, uint32_t target) {
+    uint64_t t0 = 0;
+    for (;;) {
+        for (int i = 0; i < 1024; ++i) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+            if (v >= target) return true;
+        }
+        const uint64_t now = ptx::global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > ptx::WAIT_LIMIT_NS) return false;
+    }
+}
+
+// FAMILY 0: Q4_K and Q6_K weights; 1: Q4_0 and Q8_0.  OCC resident CTAs per SM of CW consumer warps each.
+template <int FAMILY, int XM, int OCC, int CW>
+__global__ void __launch_bounds__((CW + 1) * 32, OCC) gemv_chain_kernel(const __grid_constant__ ChainArgs c) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // projection descriptors, two per role (the next one is fetched while the current one runs):
+    // [0], [1] the consumers', [2], [3] the producer's (it runs ahead of them)
+    __shared__ __align__(16) ChainOp op_slot[4];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const bool producer = warp == (uint32_t)CW;
+    constexpr uint32_t WORDS = sizeof(ChainOp) / 16u;
+    static_assert(WORDS <= 32u, "one descriptor word per lane");
+    // the copier of a role: the producer warp's lanes, or the consumers' first warp
+    const bool copier = producer || warp == 0u;
+    ChainOp *slots = &op_slot[producer ? 2 : 0];
+    const uint4 *src = reinterpret_cast<const uint4 *>(c.ops);
+    if (copier && lane < WORDS) {
+        reinterpret_cast<uint4 *>(&slots[0])[lane] = __ldg(src + lane);
+        if (c.n_ops > 1) reinterpret_cast<uint4 *>(&slots[1])[lane] = __ldg(src + WORDS + lane);
+    }
+    // A wait that runs out (the status word says which) must not leave the CTA's other warps at a barrier
+    // for ever: the CTA is marked dead, skips the arithmetic of this and every later projection — all its
+    // warps decide that together, right after a barrier — and still raises its counters, so that the other
+    // CTAs run to their end as well.
+    __shared__ uint32_t cta_dead, wait_ok;
+    if (threadIdx.x == 0) cta_dead = 0u;
+    MmaRun run;
+    uint4 ahead = make_uint4(0u, 0u, 0u, 0u);
+    for (uint32_t i = 0; i < c.n_ops; ++i) {
+        if (producer) {
+            __syncwarp();
+        } else {
+            // every consumer warp is through with the previous projection: its outputs are complete, the
+            // activation row may be rebuilt, and this projection's descriptor is in place
+            ptx::named_bar_sync(3, CW * 32);
+            if (i > 0 && threadIdx.x == 0)             // (a release: the CTA's stores, ordered before it by the barrier, are visible to whoever sees the count)
+                asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(c.done + (i - 1)), "r"(1u) : "memory");
+            if (c.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+                const unsigned long long now = ptx::global_timer_ns();
+                c.trace[8u * i] = now;
+                if (i > 0) c.trace[8u * (i - 1u) + 3u] = now;
+            }
+        }
+        if (copier && lane < WORDS) {
+            // the slot of the projection just finished takes the next one (fetched while that one ran), and
+            // the one after it starts its way from global memory now
+            if (i >= 1 && i + 1 < c.n_ops) reinterpret_cast<uint4 *>(&slots[(i + 1) & 1u])[lane] = ahead;
+            if (i + 2 < c.n_ops) ahead = __ldg(src + (size_t)(i + 2) * WORDS + lane);
+        }
+        const ChainOp *mine = &slots[i & 1u];
+        if (!producer) {
+            if (threadIdx.x == 0) {
+                bool ok = true;
+                const uint32_t dep = mine->wait_op;
+                if (dep != CHAIN_NO_WAIT && !*(volatile uint32_t *)&cta_dead) {
+                    ok = chain_wait(c.done + dep, gridDim.x);
+                    if (!ok) set_status_word(c.status, KERNEL_ERR_CHAIN_TIMEOUT);
+                }
+                if (!ok) cta_dead = 1u;
+                wait_ok = *(volatile uint32_t *)&cta_dead ? 0u : 1u;
+            }
+            ptx::named_bar_sync(4, CW * 32);
+            if (!*(volatile uint32_t *)&wait_ok) continue;             // the whole CTA skips (barriers and counters go on)
+            if (c.trace && blockIdx.x == 0 && threadIdx.x == 0) c.trace[8u * i + 1u] = ptx::global_timer_ns();
+        }
+        run.trace = (c.trace && blockIdx.x == 0) ? c.trace + 8u * i + 2u : nullptr;
+        const MmaArgs &a = mine->a;
+        run.build_x = mine->reuse_x == 0u;
+        const uint32_t kind = a.plan.kind, nmat = a.plan.nmat;
+        bool ok;
+        if (FAMILY == 0) {
+            if (kind == KIND_Q4_K)
+                ok = nmat == 2 ? gemv_mma_body<KIND_Q4_K, 2, XM, CW>(a, smem, blockIdx.x, gridDim.x, 0u, false, run)
+                               : gemv_mma_body<KIND_Q4_K, 1, XM, CW>(a, smem, blockIdx.x, gridDim.x, 0u, false, run);
+            else
+                ok = gemv_mma_body<KIND_Q6_K, 1, XM, CW>(a, smem, blockIdx.x, gridDim.x, 0u, false, run);
+        } else {
+            if (kind == KIND_Q4_0)
+                ok = nmat == 2 ? gemv_mma_body<KIND_Q4_0, 2, XM, CW>(a, smem, blockIdx.x, gridDim.x, 0u, false, run)
+                               : gemv_mma_body<KIND_Q4_0, 1, XM, CW>(a, smem, blockIdx.x, gridDim.x, 0u, false, run);
+            else
+                ok = gemv_mma_body<KIND_Q8_0, 1, XM, CW>(a, smem, blockIdx.x, gridDim.x, 0u, false, run);
+        }
+        if (!ok) {
+            if (producer) return;                  // the producer meets nobody at a barrier; the consumers' waits for its stages run out
+            if (lane == 0) *(volatile uint32_t *)&cta_dead = 1u;
+        }
+    }
+}
+
+static bool ranges_overlap(const void *p, size_t np, const void *q, size_t nq) {
+    if (!p || !q) return false;
+    const uintptr_t a = (uintptr_t)p, b = (uintptr_t)q;
+    return a < b + nq && b < a + np;
+}
+
+bool chain_call_eligible(const GemvCall &c) {
+    if (c.ids || !c.norm_a || !mma_kind(c.kind) || c.cols % 64u || (c.nmat != 1 && c.nmat != 2)) return false;
+    if (c.nmat == 2 && (c.kind == KIND_Q6_K || c.kind == KIND_Q8_0)) return false;
+    if (((uintptr_t)c.w[0] % 16u) || (c.nmat == 2 && ((uintptr_t)c.w[1] % 16u)) || ((size_t)c.rows * c.stride) % 16u) return false;
+    return true;
+}
+
+cudaError_t chain_build(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx, ChainLaunch &out, const char *&why) {
+    out = ChainLaunch();
+    why = "";
+    if (n == 0) { why = "no projections were recorded"; return cudaErrorInvalidValue; }
+    std::vector<GemvCall> cs(calls, calls + n);
+    const bool family1 = cs[0].kind == KIND_Q4_0 || cs[0].kind == KIND_Q8_0;
+    const uint32_t xm = cs[0].norm_round_bf16 ? XM_FX2 : XM_FX4;
+    for (const GemvCall &c : cs) {
+        if (!chain_call_eligible(c)) { why = "a recorded projection has no fused tensor-core form (type, alignment or shape)"; return cudaErrorNotSupported; }
+        if ((c.kind == KIND_Q4_0 || c.kind == KIND_Q8_0) != family1) { why = "K-quant and legacy weight types cannot share one chain"; return cudaErrorNotSupported; }
+        if ((c.norm_round_bf16 ? XM_FX2 : XM_FX4) != xm) { why = "all projections of a chain round their activations the same way"; return cudaErrorNotSupported; }
+    }
+    // projections that read the same normalised input build it once: the first of the group takes the
+    // group's residual-sum store
+    std::vector<uint32_t> reuse(n, 0u);
+    auto same_input = [](const GemvCall &p, const GemvCall &q) {
+        return p.norm_a == q.norm_a && p.norm_b == q.norm_b && p.norm_w == q.norm_w && p.cols == q.cols && p.norm_eps == q.norm_eps;
+    };
+    for (uint32_t j = 1; j < n; ++j) {
+        uint32_t first = j - 1;
+        while (reuse[first]) --first;
+        GemvCall &f = cs[first], &c = cs[j];
+        if (!same_input(f, c)) continue;
+        if (c.norm_s && f.norm_s && c.norm_s != f.norm_s) continue;
+        // nothing the group writes may touch what a slower CTA is still reading to build the row
+        bool clash = false;
+        for (uint32_t k = first; k <= j && !clash; ++k) {
+            const GemvCall &m = cs[k];
+            const void *outs[2] = {m.y, m.norm_s ? (const void *)m.norm_s : (const void *)c.norm_s};
+            const size_t lens[2] = {(size_t)m.rows * 4u, (size_t)m.cols * 4u};
+            for (int o = 0; o < 2; ++o)
+                clash = clash || ranges_overlap(outs[o], lens[o], c.norm_a, (size_t)c.cols * 4u) || ranges_overlap(outs[o], lens[o], c.norm_b, (size_t)c.cols * 4u);
+        }
+        // ... and what this projection writes must not be written by another member (members run unordered across CTAs)
+        for (uint32_t k = first; k < j && !clash; ++k) {
+            const GemvCall &m = cs[k];
+            clash = ranges_overlap(c.y, (size_t)c.rows * 4u, m.y, (size_t)m.rows * 4u) ||
+                    ranges_overlap(c.y, (size_t)c.rows * 4u, m.norm_s, (size_t)m.cols * 4u) ||
+                    ranges_overlap(c.norm_s, (size_t)c.cols * 4u, m.y, (size_t)m.rows * 4u);
+        }
+        if (clash) continue;
+        if (c.norm_s) { f.norm_s = c.norm_s; c.norm_s = nullptr; }
+        reuse[j] = 1u;
+    }
+    // the projection each one waits for: the latest earlier one that wrote what it reads, or that read
+    // or wrote what it writes.  CTAs take the projections in order, so "all CTAs finished i" covers all before i.
+    std::vector<uint32_t> wait(n, CHAIN_NO_WAIT);
+    for (uint32_t j = 0; j < n; ++j) {
+        const GemvCall &c = cs[j];
+        const void *rd[2] = {c.norm_a, c.norm_b};
+        const void *wr[2] = {c.y, c.norm_s};
+        const size_t wl[2] = {(size_t)c.rows * 4u, (size_t)c.cols * 4u};
+        for (uint32_t i = 0; i < j; ++i) {
+            const GemvCall &e = cs[i];
+            const void *er[2] = {e.norm_a, e.norm_b};
+            const void *ew[2] = {e.y, e.norm_s};
+            const size_t el[2] = {(size_t)e.rows * 4u, (size_t)e.cols * 4u};
+            bool dep = false;
+            for (int x = 0; x < 2; ++x)
+                for (int y = 0; y < 2; ++y) {
+                    dep = dep || ranges_overlap(rd[x], (size_t)c.cols * 4u, ew[y], el[y]);      // read after write
+                    dep = dep || ranges_overlap(wr[x], wl[x], er[y], (size_t)e.cols * 4u);      // write after read
+                    dep = dep || ranges_overlap(wr[x], wl[x], ew[y], el[y]);                    // write after write
+                }
+            if (dep) wait[j] = i;
+        }
+    }
+    for (uint32_t j = 0; j < n; ++j) {          // a group waits, at its first projection, for everything any member needs
+        if (!reuse[j]) continue;
+        uint32_t first = j;
+        while (reuse[first]) --first;
+        if (wait[j] != CHAIN_NO_WAIT && wait[j] >= first) { why = "internal: a projection depends on a member of its own group"; return cudaErrorNotSupported; }
+        if (wait[j] != CHAIN_NO_WAIT && (wait[first] == CHAIN_NO_WAIT || wait[j] > wait[first])) wait[first] = wait[j];
+        wait[j] = CHAIN_NO_WAIT;
+    }
+    // common shared-memory geometry: the widest activation row, a ring of equal slots that holds every
+    // projection's smallest stage, one CTA per SM
+    MmaFixed fx = {0u, 0u, 0u, (uint32_t)MMA_WARPS};
+    for (const GemvCall &c : cs) {
+        const uint32_t xb = x_row_bytes(xm, c.cols);
+        if (xb > fx.x_bytes) fx.x_bytes = xb;
+    }
+    const char *occ_env = getenv("INGOT_CHAIN_OCC");                // experiments: resident CTAs per SM (1 or 2)
+    const uint32_t occ = occ_env && atoi(occ_env) == 2 ? 2u : 1u;
+    const char *cw_env = getenv("INGOT_CHAIN_WARPS");               // experiments: consumer warps per CTA (8 or 16)
+    const uint32_t cw = occ == 2 ? 8u : (cw_env && atoi(cw_env) == 8 ? 8u : 16u);
+    fx.warps = cw;
+    const uint32_t budget = occ == 2 ? 113u * 1024u : MMA_SMEM_MAX;
+    const uint32_t red_slots = budget <= MMA_SMEM_SMALL ? 4u : MMA_RED_SLOTS;      // as plan_mma sizes it
+    const uint32_t red_bytes = red_slots * MMA_WARPS * 2u * 16u * 4u + MMA_ZERO_BYTES;
+    const uint32_t fixed_bytes = MMA_BAR_BYTES + ((fx.x_bytes + 127u) & ~127u) + red_bytes;
+    if (fixed_bytes + 2u * 16384u > budget) { why = "activation rows too wide for the chain kernel"; return cudaErrorNotSupported; }
+    for (const GemvCall &c : cs) {              // smallest stage of each projection: one step per warp
+        uint32_t step_cols, step_bytes;
+        step_geometry(c.kind, step_cols, step_bytes);
+        if (c.cols % step_cols) { why = "a recorded projection does not plan"; return cudaErrorNotSupported; }
+        const uint32_t nsteps = c.cols / step_cols;
+        uint32_t kw = 3;
+        while (kw > 0 && (nsteps % (1u << kw))) --kw;
+        const uint32_t per_warp = nsteps >> kw, row_tiles = (uint32_t)MMA_WARPS >> kw;
+        const uint32_t lead = (c.kind == KIND_Q4_K || c.kind == KIND_Q6_K) ? 32u : 16u;
+        uint32_t sb = 0;
+        for (uint32_t spw = 1; spw <= per_warp; ++spw) {
+            const uint32_t cb = spw * (1u << kw) * step_bytes;
+            if (per_warp % spw || cb % 16u) continue;
+            sb = (pitch_of(cb, lead) * 16u * row_tiles + 64u + 127u) & ~127u;
+            break;
+        }
+        if (sb == 0) { why = "a recorded projection does not plan"; return cudaErrorNotSupported; }
+        if (sb > fx.slot_bytes) fx.slot_bytes = sb;
+    }
+    const char *slot_env = getenv("INGOT_CHAIN_SLOT_BYTES");        // experiments: a larger slot lets narrow rows take more steps per stage
+    if (slot_env && (uint32_t)atoi(slot_env) > fx.slot_bytes) fx.slot_bytes = ((uint32_t)atoi(slot_env) + 127u) & ~127u;
+    fx.slots = (budget - fixed_bytes) / fx.slot_bytes;
+    if (fx.slots > (uint32_t)MMA_MAX_STAGES) fx.slots = MMA_MAX_STAGES;
+    const uint32_t groups = cw / (uint32_t)MMA_WARPS;                // every consumer group has a ring of its own
+    fx.slots -= fx.slots % groups;
+    if (fx.slots < 2 * groups) { why = "the chain's stages do not fit in shared memory"; return cudaErrorNotSupported; }
+    const uint32_t ctas = ctx.sm_count * occ;
+    std::vector<ChainOp> ops(n);
+    std::vector<CUtensorMap> maps(2u * n);
+    cudaError_t e = cudaMalloc(&out.maps_dev, sizeof(CUtensorMap) * 2u * n);
+    if (e != cudaSuccess) return e;
+    const bool use_tma = !(getenv("INGOT_CHAIN_TMA") && atoi(getenv("INGOT_CHAIN_TMA")) == 0);      // experiments: 0 = one bulk copy per row
+    uint32_t smem_bytes = 0;
+    for (uint32_t j = 0; j < n; ++j) {
+        const GemvCall &c = cs[j];
+        ChainOp &o = ops[j];
+        memset(&o, 0, sizeof(o));
+        if (!plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, ctas, budget, xm, o.a.plan, &fx)) {
+            why = "a recorded projection does not plan";
+            chain_free(out);
+            return cudaErrorNotSupported;
+        }
+        o.a.plan.ctas = ctas;
+        if (o.a.plan.smem_bytes > smem_bytes) smem_bytes = o.a.plan.smem_bytes;
+        o.a.w[0] = c.w[0]; o.a.w[1] = c.nmat == 2 ? c.w[1] : nullptr;
+        o.a.y = c.y; o.a.expert = c.expert; o.a.n_experts = 0; o.a.top = 1; o.a.glu = c.glu;
+        o.a.status = ctx.status;
+        o.a.na = c.norm_a; o.a.nb = c.norm_b; o.a.nw = c.norm_w; o.a.ns = c.norm_s; o.a.neps = c.norm_eps; o.a.nround_bf16 = c.norm_round_bf16;
+        o.wait_op = wait[j];
+        o.reuse_x = reuse[j];
+        // the stage as one box: rows of 8-byte elements, row_pitch / 8 of them (at most 256) by 16 row_tiles rows
+        const MmaPlan &pl = o.a.plan;
+        for (uint32_t m = 0; m < c.nmat && use_tma; ++m) {
+            const uint8_t *base = c.w[m] + (size_t)c.expert * c.rows * c.stride;
+            if (pl.row_pitch % 16u || pl.row_pitch / 8u > 256u || c.stride % 16u || ((uintptr_t)base % 16u)) break;
+            if (!make_tensor_map_2d(maps[2u * j + m], CU_TENSOR_MAP_DATA_TYPE_UINT64, base, c.stride / 8u, c.rows, c.stride,
+                                    pl.row_pitch / 8u, 16u * pl.row_tiles, CU_TENSOR_MAP_SWIZZLE_NONE))
+                break;
+            o.a.tmap[m] = static_cast<const CUtensorMap *>(out.maps_dev) + (2u * j + m);
+        }
+        if (c.nmat == 2 && !o.a.tmap[1]) o.a.tmap[0] = nullptr;       // both matrices or neither
+        if (o.a.tmap[0]) o.a.expert = 0;                               // the maps start at the expert's first row
+    }
+    e = cudaMemcpy(out.maps_dev, maps.data(), sizeof(CUtensorMap) * 2u * n, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&out.ops_dev, sizeof(ChainOp) * n);
+    if (e == cudaSuccess) e = cudaMalloc(&out.done_dev, sizeof(uint32_t) * n);
+    if (e == cudaSuccess) e = cudaMemcpy(out.ops_dev, ops.data(), sizeof(ChainOp) * n, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { chain_free(out); return e; }
+    out.n_ops = n; out.ctas = ctas; out.smem_bytes = smem_bytes; out.xm = xm; out.family = family1 ? 1u : 0u;
+    out.slots = fx.slots; out.slot_bytes = fx.slot_bytes; out.occ = occ; out.warps = cw;
+    if (getenv("INGOT_CHAIN_TRACE") && atoi(getenv("INGOT_CHAIN_TRACE")) != 0 &&
+        cudaMalloc(&out.trace_dev, 64u * n) == cudaSuccess)
+        cudaMemset(out.trace_dev, 0, 64u * n);
+    uint32_t waits = 0;
+    for (uint32_t j = 0; j < n; ++j) waits += wait[j] != CHAIN_NO_WAIT;
+    out.waits = waits;
+    return cudaSuccess;
+}
+
+void chain_free(ChainLaunch &c) {
+    if (c.ops_dev) cudaFree(c.ops_dev);
+    if (c.done_dev) cudaFree(c.done_dev);
+    if (c.maps_dev) cudaFree(c.maps_dev);
+    if (c.trace_dev) {
+        // debugging: the last launch's times of CTA 0, one line per projection
+        std::vector<unsigned long long> t(8u * c.n_ops);
+        if (cudaDeviceSynchronize() == cudaSuccess && cudaMemcpy(t.data(), c.trace_dev, t.size() * 8u, cudaMemcpyDeviceToHost) == cudaSuccess) {
+            fprintf(stderr, "chain trace (CTA 0, microseconds): projection  start  wait  build (loads, reduce, pack)  rows  total\n");
+            for (uint32_t i = 0; i + 1 < c.n_ops; ++i) {
+                const unsigned long long *q = &t[8u * i];
+                const double t0 = (double)q[0], t1 = (double)q[1], t2 = (double)q[2], t3 = (double)q[3];
+                const bool built = q[2] >= q[1] && q[2] <= q[3];
+                fprintf(stderr, "%4u %10.2f %7.2f %7.2f (%5.2f %5.2f %5.2f) %7.2f %7.2f\n", i, (t0 - (double)t[0]) * 1e-3, (t1 - t0) * 1e-3,
+                        built ? (t2 - t1) * 1e-3 : 0.0, built ? ((double)q[4] - t1) * 1e-3 : 0.0, built ? ((double)q[5] - (double)q[4]) * 1e-3 : 0.0,
+                        built ? (t2 - (double)q[5]) * 1e-3 : 0.0, (t3 - (built ? t2 : t1)) * 1e-3, (t3 - t0) * 1e-3);
+            }
+        }
+        cudaFree(c.trace_dev);
+    }
+    c = ChainLaunch();
+}
+
+template <int FAMILY, int XM, int OCC, int CW>
+static cudaError_t chain_launch_t(const ChainLaunch &c, const ChainArgs &args, cudaStream_t stream) {
+    auto kernel = gemv_chain_kernel<FAMILY, XM, OCC, CW>;
+    static DeviceOnce once;
+    const cudaError_t e = once.smem(kernel, (int)MMA_SMEM_MAX);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(c.ctas);
+    cfg.blockDim = dim3((CW + 1) * 32);
+    cfg.dynamicSmemBytes = c.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;          // every CTA resident at once: they wait for one another
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args);
+}
+
+cudaError_t chain_launch(const ChainLaunch &c, const LaunchCtx &ctx) {
+    cudaError_t e = cudaMemsetAsync(c.done_dev, 0, sizeof(uint32_t) * c.n_ops, ctx.stream);
+    if (e != cudaSuccess) return e;
+    ChainArgs args = {static_cast<const ChainOp *>(c.ops_dev), c.done_dev, c.n_ops, ctx.status, static_cast<unsigned long long *>(c.trace_dev)};
+    const bool fx2 = c.xm == XM_FX2;
+    if (c.occ == 2) {
+        if (c.family == 0) return fx2 ? chain_launch_t<0, XM_FX2, 2, 8>(c, args, ctx.stream) : chain_launch_t<0, XM_FX4, 2, 8>(c, args, ctx.stream);
+        return fx2 ? chain_launch_t<1, XM_FX2, 2, 8>(c, args, ctx.stream) : chain_launch_t<1, XM_FX4, 2, 8>(c, args, ctx.stream);
+    }
+    if (c.warps == 8) {
+        if (c.family == 0) return fx2 ? chain_launch_t<0, XM_FX2, 1, 8>(c, args, ctx.stream) : chain_launch_t<0, XM_FX4, 1, 8>(c, args, ctx.stream);
+        return fx2 ? chain_launch_t<1, XM_FX2, 1, 8>(c, args, ctx.stream) : chain_launch_t<1, XM_FX4, 1, 8>(c, args, ctx.stream);
+    }
+    if (c.family == 0) return fx2 ? chain_launch_t<0, XM_FX2, 1, 16>(c, args, ctx.stream) : chain_launch_t<0, XM_FX4, 1, 16>(c, args, ctx.stream);
+    return fx2 ? chain_launch_t<1, XM_FX2, 1, 16>(c, args, ctx.stream) : chain_launch_t<1, XM_FX4, 1, 16>(c, args, ctx.stream);
 }
 
 }  // namespace ingot

@@ -569,11 +569,10 @@ static bool make_row_map(CUtensorMap &map, const uint8_t *w, uint32_t rows, uint
 template <int NMAT>
 static cudaError_t launch_tc_t(const CUtensorMap &m0, const CUtensorMap &m1, const TcArgs &a, cudaStream_t stream, bool pdl) {
     auto kernel = gemv_tc_q4k_kernel<NMAT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX);
+    static DeviceOnce once;
+    {
+        const cudaError_t e = once.smem(kernel, (int)TC_SMEM_MAX);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.p.ctas);

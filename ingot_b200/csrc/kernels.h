@@ -3,7 +3,27 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace ingot {
+
+// A kernel's dynamic shared-memory limit is a per-device attribute: set it once per (kernel
+// instantiation, device) — one static DeviceOnce per instantiation, a bit per device ordinal — and
+// safely from several host threads (setting it twice is harmless, skipping it is not).
+struct DeviceOnce {
+    std::atomic<uint64_t> mask{0};
+    template <typename K>
+    cudaError_t smem(K kernel, int bytes) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        const uint64_t bit = 1ull << (dev & 63);
+        if (mask.load(std::memory_order_acquire) & bit) return cudaSuccess;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess) mask.fetch_or(bit, std::memory_order_release);
+        return e;
+    }
+};
 
 // Codes kernels write to the device status word (0 = ok).
 enum : int {
@@ -12,7 +32,8 @@ enum : int {
     KERNEL_ERR_CONSUMER_TIMEOUT = 2,   // bulk copy never landed
     KERNEL_ERR_EXPERT_RANGE = 3,       // routed id >= number of experts
     KERNEL_ERR_ROUTER_INPUT = 4,       // non-finite router logit
-    KERNEL_ERR_GEMM_TIMEOUT = 5        // prefill GEMM pipeline wait ran out
+    KERNEL_ERR_GEMM_TIMEOUT = 5,       // prefill GEMM pipeline wait ran out
+    KERNEL_ERR_CHAIN_TIMEOUT = 6       // a projection of a chain kernel never saw the one it depends on finish
 };
 
 struct LaunchCtx {
@@ -58,6 +79,21 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
 // Several independent one-token projections as one grid (2..4 calls that gemv_mma_group_eligible accepts).
 bool gemv_mma_group_eligible(const GemvCall &c, const LaunchCtx &ctx);
 bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx, cudaError_t &err);
+// A recorded sequence of one-token fused-norm projections run by one persistent kernel: built once
+// (device copies of the projection list and its completion counters), launched any number of times.
+struct ChainLaunch {
+    void *ops_dev = nullptr;
+    uint32_t *done_dev = nullptr;
+    void *maps_dev = nullptr;          // tensor maps of the recorded matrices (one tiled copy per stage)
+    void *trace_dev = nullptr;         // debugging (INGOT_CHAIN_TRACE=1): per-projection times of CTA 0, printed when the chain is freed
+    uint32_t n_ops = 0, ctas = 0, smem_bytes = 0, xm = 0, family = 0;
+    uint32_t slots = 0, slot_bytes = 0, waits = 0, occ = 1, warps = 8;
+};
+bool chain_call_eligible(const GemvCall &c);
+// cudaErrorNotSupported (with `why`) when the calls cannot run as one chain.
+cudaError_t chain_build(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx, ChainLaunch &out, const char *&why);
+cudaError_t chain_launch(const ChainLaunch &c, const LaunchCtx &ctx);
+void chain_free(ChainLaunch &c);
 // The tcgen05 int8 GEMV (one token, Q4_K); false when the call is not one it handles.
 bool try_launch_gemv_tc(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
 // Packs `rows` activation rows (f32 or bf16) as base-256 digits for it.

@@ -7,12 +7,15 @@
 // synchronisation and the failure modes of cudaMalloc / cudaFree in the middle of a
 // token step.  The regular entry points need a handle (ingot_gpu_create allocates a
 // status word and a workspace); this one needs nothing but the library itself: the
-// scratch the tensor-core GEMV uses for its packed activations, and the word its
-// kernels report errors through, are file-scope __device__ arrays that every GPU
+// scratch the tensor-core GEMV uses for its packed activations (written when x is not
+// 16-byte aligned; an aligned x is packed in shared memory inside the kernel), and the word
+// its kernels report errors through, are file-scope __device__ arrays that every GPU
 // loading the library carries until the process exits.
 #include "../../include/ingot_cuda.h"
 
 #include <stdio.h>
+
+#include <mutex>
 
 #include "gemv_core.cuh"
 #include "kernels.h"
@@ -36,6 +39,7 @@ struct DeviceState {
 };
 constexpr int MAX_DEVICES = 64;
 DeviceState g_state[MAX_DEVICES];
+std::mutex g_setup_lock;          // first calls from several host threads: one of them fills a device's entry
 thread_local char g_error[256] = "";
 
 ingot_status fail(ingot_status code, const char *msg) {
@@ -48,6 +52,7 @@ ingot_status fail(ingot_status code, const char *msg) {
 // that device current.
 ingot_status setup(int device, DeviceState **out) {
     if (device < 0 || device >= MAX_DEVICES) return fail(INGOT_DEVICE, "device ordinal out of range");
+    std::lock_guard<std::mutex> guard(g_setup_lock);
     DeviceState &s = g_state[device];
     if (!s.ready) {
         void *scratch = nullptr, *status = nullptr;
@@ -101,7 +106,9 @@ ingot_status ingot_matvec_static(const void *w, uint32_t cols, uint32_t rows, ui
     ctx.status = s->status;
     ctx.sm_count = s->sm_count;
     ctx.pdl = false;
-    ctx.workspace = s->scratch;                   // the packed activations land in the static array
+    // an x that is 16-byte aligned is turned into the kernel's operand form inside the kernel (shared
+    // memory only); any other x (4-byte aligned) is packed into the static array by a first small launch
+    ctx.workspace = s->scratch;
     ctx.workspace_bytes = STATIC_SCRATCH_BYTES;
     GemvCall c = {};
     c.w[0] = static_cast<const uint8_t *>(w);

@@ -152,6 +152,30 @@ __device__ __forceinline__ void fx_store(uint8_t *row, uint32_t cols, uint32_t j
     }
 }
 
+// The norm's last step and fx_store for one thread's four columns, as ONE copy of code that a row's
+// unrolled loop calls: x = v * inv * w (w may be null), rounded to bfloat16 when `round_bf16`.  The
+// packing code of a row runs once per projection; inlined into every iteration of an unrolled loop it
+// is kilobytes of straight-line code that the instruction cache has to fetch each time, which costs
+// more than the arithmetic.  All 32 lanes of a warp call it together.
+template <int ND>
+__device__ __noinline__ void fx_norm_store(uint8_t *row, uint32_t cols, uint32_t j, float4 v, float inv, const float *nw, uint32_t round_bf16,
+                                           bool live) {
+    float u[4] = {v.x, v.y, v.z, v.w};
+    if (live) {
+        const float4 wv = nw ? reinterpret_cast<const float4 *>(nw)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
+        u[0] = u[0] * inv * wv.x; u[1] = u[1] * inv * wv.y; u[2] = u[2] * inv * wv.z; u[3] = u[3] * inv * wv.w;
+        if (round_bf16) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t x = __float_as_uint(u[k]);
+                if ((x & 0x7fffffffu) <= 0x7f800000u) x += 0x7fffu + ((x >> 16) & 1u);       // round to nearest even
+                u[k] = __uint_as_float(x & 0xffff0000u);
+            }
+        }
+    }
+    fx_store<ND>(row, cols, j, u, live);
+}
+
 // The same without the low part (bfloat16 activations are exact in binary16): [cols/16 MMAs][4 lanes][4 halves],
 // then the sums and 1/scale: 2 * cols + cols / 4 + 16 bytes.
 __device__ __forceinline__ void pack_hi_store_quad(uint8_t *row, uint32_t cols, uint32_t q, const float (&v)[4], bool live) {

@@ -84,6 +84,16 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
         : "memory");
 }
 
+// Tiled 2-D copy global -> shared through a tensor map (in global or parameter memory): the box at
+// element coordinates (x, y), x the inner one; x times the element size must be a multiple of 16
+// bytes.  Signals `bar` with the bytes of the whole box.  No multicast.
+__device__ __forceinline__ void tma_load_2d(void *dst_smem, const void *tensor_map, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_addr(dst_smem)),
+                 "l"(tensor_map), "r"(x), "r"(y), "r"(smem_addr(bar))
+                 : "memory");
+}
+
 // Programmatic dependent launch: let the next kernel in the stream begin its
 // prologue; wait until the previous kernel's writes are visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -137,6 +137,29 @@ class Graph:
             pass
 
 
+class Chain:
+    """A recorded sequence of fused-norm projections that runs as one persistent kernel."""
+
+    def __init__(self, gpu: "Gpu", handle: int):
+        self.gpu, self._c = gpu, handle
+
+    def submit(self) -> None:
+        self.gpu._check(self.gpu._lib.ingot_chain_submit(self.gpu._h, self._c))
+
+    def info(self) -> dict:
+        v = [C.c_uint32() for _ in range(4)]
+        self.gpu._check(self.gpu._lib.ingot_chain_info(self._c, *[C.byref(x) for x in v]))
+        return dict(zip(("projections", "waits", "stages", "stage_bytes"), (x.value for x in v)))
+
+    def __del__(self):
+        try:
+            if self._c:
+                self.gpu._lib.ingot_chain_destroy(self._c)
+                self._c = 0
+        except Exception:
+            pass
+
+
 @dataclass
 class Weight:
     """A device buffer plus its tensor descriptor (src/weights.rs:10-13)."""
@@ -258,6 +281,14 @@ class Gpu:
         g = C.c_void_p()
         self._check(self._lib.ingot_command_end(self._h, C.byref(g)))
         return Graph(self, g.value)
+
+    def chain_begin(self) -> None:
+        self._check(self._lib.ingot_chain_begin(self._h))
+
+    def chain_end(self) -> Chain:
+        c = C.c_void_p()
+        self._check(self._lib.ingot_chain_end(self._h, C.byref(c)))
+        return Chain(self, c.value)
 
     def complete(self, cmd: Command | None = None) -> None:
         self._check(self._lib.ingot_synchronize(self._h))

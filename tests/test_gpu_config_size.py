@@ -101,6 +101,15 @@ def test_two_layer_chain_operator_by_operator_and_logits(gpu, x_kind):
     graph.submit()
     gpu.complete()
     assert np.array_equal(gpu.read_f32(chain.logits).view(np.uint32), one_by_one.view(np.uint32))
+    # ... and so does the step as ONE persistent kernel (the chain), twice in a row
+    fused = chain.record_chain()
+    info = fused.info()
+    assert info["projections"] == 13 and info["waits"] == 8 and info["stages"] >= 2, info
+    for _ in range(2):
+        gpu._check(gpu._lib.ingot_buffer_zero(gpu._h, chain.logits.ptr, chain.logits.nbytes))
+        fused.submit()
+        gpu.complete()
+        assert np.array_equal(gpu.read_f32(chain.logits).view(np.uint32), one_by_one.view(np.uint32))
     if x_kind == F32:
         # without bfloat16 rounding points the oracle's own chain (f64 dots) reproduces the logits end to end
         e = CK.OracleChain(QWEN3_8B, layers=2, seed=3, bf16=False).step(h0[0]).astype(np.float64)

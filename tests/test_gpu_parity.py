@@ -792,3 +792,46 @@ def test_multi_token_gate_up_and_chain(gpu):
     l1 = gpu.read_f32(c1.logits)
     scale = float(np.sqrt(np.mean(np.square(l1))))
     assert np.abs(l8[3] - l1).max() <= 2e-2 * scale
+
+
+# ---- scratch and scopes around the wide-batch GEMM ------------------------------------------------
+
+def test_wide_batch_projections_inside_an_independent_scope(gpu):
+    # more than four tokens inside a scope: the GEMM's scratch is the handle's one workspace, so the scope takes the
+    # GEMV in groups of four (the reference's project() runs for any count inside independent_projections, src/qwen.rs:822)
+    cols, rows, tokens = 1024, 96, 8
+    raws = [synth.random_matrix(Q4_K, cols, rows, seed=200 + i) for i in range(2)]
+    ws = [gpu.bytes(r) for r in raws]
+    x = standard_x(cols * tokens).reshape(tokens, cols)
+    xb = gpu.floats(x)
+    stride = synth.stride_of(Q4_K, cols)
+    with gpu.independent():
+        ys = [gpu.matmul(None, w, cols, rows, stride, Q4_K, 0, xb, tokens) for w in ws]
+    got = [gpu.finish(None, y).reshape(tokens, rows) for y in ys]
+    for g, raw in zip(got, raws):
+        e = O.matvec_f64(raw, cols, rows, Q4_K, x)
+        assert (np.abs(g - e) <= tol_ref(e)).all(), float(np.abs(g - e).max())
+
+
+def test_recorded_command_survives_growth_of_the_scratch(gpu):
+    # a recorded wide-batch projection has the scratch address in its kernel arguments; a later, larger call makes the
+    # handle take a bigger scratch block, and the old block must stay valid for the replay
+    cols, rows, tokens = 512, 128, 8
+    raw = synth.random_matrix(Q4_K, cols, rows, seed=210)
+    x = standard_x(cols * tokens).reshape(tokens, cols)
+    w, xb, y = gpu.bytes(raw), gpu.floats(x), gpu.zeros(tokens * rows)
+    stride = synth.stride_of(Q4_K, cols)
+    gpu.matmul(None, w, cols, rows, stride, Q4_K, 0, xb, tokens, out=y)
+    first = gpu.finish(None, y).copy()
+    gpu.record()
+    gpu.matmul(None, w, cols, rows, stride, Q4_K, 0, xb, tokens, out=y)
+    graph = gpu.end_record()
+    # a call whose scratch need (binary16 copy of 9000 x 4096 activations: 74 MB) exceeds the initial 16 MB block
+    big_cols, big_rows, big_tokens = 4096, 128, 9000
+    wb = gpu.bytes(synth.random_matrix(Q4_K, big_cols, big_rows, seed=211))
+    xbig = gpu.zeros(big_tokens * big_cols)
+    gpu.finish(None, gpu.gemm(None, wb, big_cols, big_rows, synth.stride_of(Q4_K, big_cols), Q4_K, 0, xbig, big_tokens))
+    for _ in range(2):
+        gpu._check(gpu._lib.ingot_buffer_zero(gpu._h, y.ptr, y.nbytes))
+        graph.submit()
+        assert np.array_equal(gpu.finish(None, y).view(np.uint32), first.view(np.uint32))
