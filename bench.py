@@ -148,49 +148,48 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_layer_baseline(host_layer, threads: int, repeats: int = 2):
-    """Seconds for the oracle to run one layer's seven GEMVs (scalar dequantise + fp32
-    dot, rows over `threads`), best of `repeats`; and that layer's weight bytes."""
-    from oracle import oracle as O
-    best, nbytes = None, 0
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        nbytes = 0
-        for raw, cols, rows, kind in host_layer:
-            x = np.ones(cols, np.float32)
-            O.matvec_f32(raw, cols, rows, kind, x, threads=threads)
-            nbytes += raw.size
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return best, nbytes
+def workload_config(shape, batch: int, layers: int, world: int, step_bytes: int, activations: str = "bf16") -> dict:
+    """The workload description both arms print (identical for the same command line)."""
+    return {"workload": "%s dense decode GEMV chain (configs[%d]), batch %d" % (shape.name, 2 if shape.gelu else 1, batch),
+            "layers": layers, "hidden": shape.hidden, "ffn": shape.ffn, "vocab": shape.vocab,
+            "weights": "random Q4_0 blocks" if shape.gelu else "random Q4_K/Q6_K blocks",
+            "activations": "%s between projections, fp32 accumulate" % activations,
+            "parallelism": "tp%d rows" % world if world > 1 else "single GPU",
+            "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (step_bytes / 1e9 / world)}
+
+
+def cpu_chain_step(oc, h0, threads: int) -> float:
+    """Seconds for the oracle's chain to run one whole token step (every projection of every layer and the
+    head: scalar dequantise + fp32 dot, rows over `threads`)."""
+    t0 = time.perf_counter()
+    oc.step(h0, f64=False, threads=threads)
+    return time.perf_counter() - t0
 
 
 def run_reference(args):
-    """The CPU arm: the oracle on the host cores, one layer per step as the bounded sample."""
-    from ingot_b200 import synth
-    from ingot_b200.chain import QWEN3_8B, layer_roles, weight_bytes_per_token
+    """The CPU arm: the oracle's own chain on the host cores, one WHOLE token step per step (all 36 layers'
+    distinct weights and the head, 4.92 GB), measured, not scaled."""
+    from ingot_b200.chain import QWEN3_8B
+    from oracle import chain_check as CK
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     shape = QWEN3_8B
     threads = os.cpu_count() or 1
-    layer = [(synth.random_matrix(shape.kinds[r], c, n, seed=i), c, n, shape.kinds[r])
-             for i, (r, c, n) in enumerate(layer_roles(shape))]
-    total = weight_bytes_per_token(shape)
-    for _ in range(max(args.warmup, 1)):
-        cpu_layer_baseline(layer, threads, repeats=1)
-    times = []
-    for _ in range(args.steps):
-        dt, nbytes = cpu_layer_baseline(layer, threads, repeats=1)
-        times.append(dt * total / nbytes)             # seconds per full token step
+    oc = CK.OracleChain(shape, layers=args.layers, seed=0, bf16=True)
+    h0 = np.random.default_rng(1).normal(0, 1, shape.hidden).astype(np.float32)
+    for _ in range(max(min(args.warmup, 1), 1)):          # one untimed step pages the weights in; more would only repeat it
+        cpu_chain_step(oc, h0, threads)
+    times = [cpu_chain_step(oc, h0, threads) for _ in range(args.steps)]
     sec = sum(times) / len(times)
     value = args.batch / sec
-    sample = "one decoder layer (7 GEMVs, 122.6 MB of Q4_K/Q6_K blocks) per step, scaled by bytes to the 4.92 GB token step"
+    sample = "measured: %d whole token steps (%d layers + head, %.2f GB of distinct weights each) on %d threads" % (
+        args.steps, oc.n_layers, oc.bytes / 1e9, threads)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "qwen3-8b-q4_k_m dense decode GEMV chain, batch %d" % args.batch,
-                       "note": "CPU oracle: restated reference shader arithmetic; the reference itself has no CPU path"},
+            "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(shape, args.batch, oc.n_layers, max(args.gpus, 1), oc.bytes),
+            "note": "CPU oracle: restated reference shader arithmetic; the reference itself has no CPU path",
             "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -214,8 +213,9 @@ def main():
     ap.add_argument("--pdl", type=int, default=1, help="0: launch without programmatic dependent launch (comparison)")
     ap.add_argument("--graph", type=int, default=1, help="0: issue every step's launches instead of replaying a recorded command")
     ap.add_argument("--fused-norm", type=int, default=1, help="0: add_rms as separate launches (comparison)")
-    ap.add_argument("--chain", type=int, default=1,
-                    help="1: the one-token step of a single GPU runs as one persistent kernel (ingot_chain_*); 0: one launch per projection, replayed as a CUDA graph (comparison)")
+    ap.add_argument("--chain", type=int, default=0,
+                    help="1: the one-token step of a single GPU runs as one persistent kernel (ingot_chain_*); 0: one launch per projection, replayed as a CUDA graph")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of layer 0 and the logits after the timed region")
     ap.add_argument("--group-scope", type=int, default=1,
                     help="0: the projections of an independent scope on their own streams instead of one grid (comparison)")
     ap.add_argument("--no-mma", type=int, default=0, help="1: streaming GEMVs on the fp32 CUDA-core kernel (comparison)")
@@ -281,7 +281,7 @@ def main():
 
     chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, rank=rank, world=world,
                         all_gather=all_gather if world > 1 else None, layers=args.layers, packed=not args.no_mma, fused_norm=bool(args.fused_norm),
-                        keep_host=1 if (rank == 0 and world == 1 and not args.no_cpu) else 0)
+                        keep_host=1 if (rank == 0 and world == 1 and not (args.no_cpu and args.no_parity)) else 0)
     h0 = np.random.default_rng(1).normal(0, 1, (args.batch, shape.hidden)).astype(np.float32)
     gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.h_in.ptr, h0.ctypes.data, h0.nbytes))
     gpu.complete()
@@ -370,15 +370,34 @@ def main():
         roof, per_kernel = kernel_rooflines(torch, gpu, chain, stream, peaks, peak_src)
     clocks = sampler.stop() if rank == 0 else None
 
-    cpu = None
+    cpu, parity = None, None
+    if rank == 0 and world == 1 and not args.no_parity and chain.host and chain.fused_norm and args.batch == 1:
+        # outside the timed region: the head (on the inputs the last step left) and every projection of layer 0, each
+        # against the oracle's f64 dot on the inputs the operator read (oracle/chain_check.py)
+        from oracle import chain_check as CK
+        ops = chain.fused_ops()
+        picked = [ops[-1]] + [op for op in ops if op.layer == 0]
+        records = CK.check_fused_ops(gpu, chain, picked, chain.host)
+        parity = {"parity_checked": True, "operators": len(records),
+                  "worst_error_over_bound": max(r["max_err_over_tol"] for r in records)}
     if rank == 0 and world == 1 and not args.no_cpu and chain.host:
+        # the oracle on the host cores: the same weights' layer 0 and the head, measured (a bounded sample of the step:
+        # 633 MB of its 4.92 GB); tok/s = 1 / (36 x the layer's time + the head's time)
+        from oracle import oracle as O
         threads = os.cpu_count() or 1
-        layer = [chain.host[(0, r)] for r in ("q", "k", "v", "o", "gate", "up", "down")]
-        dt, nbytes = cpu_layer_baseline(layer, threads, repeats=2)
-        total = weight_bytes_per_token(shape)
-        cpu = {"value": args.batch / (dt * total / nbytes), "unit": "tok/s", "cores": threads, "kind": "port",
-               "sample": "layer 0 of the same weights (7 GEMVs, %.1f MB), best of 2, scaled by bytes to the %.2f GB token step"
-                         % (nbytes / 1e6, total / 1e9)}
+        def cpu_time(keys):
+            t0 = time.perf_counter()
+            for key in keys:
+                raw, cols, rows, kind = chain.host[key]
+                O.matvec_f32(raw, cols, rows, kind, np.ones(cols, np.float32), threads=threads)
+            return time.perf_counter() - t0
+        layer_keys = [(0, r) for r in ("q", "k", "v", "o", "gate", "up", "down")]
+        cpu_time(layer_keys)
+        t_layer = min(cpu_time(layer_keys) for _ in range(2))
+        t_head = cpu_time([(chain.n_layers, "head")])
+        cpu = {"value": args.batch / (chain.n_layers * t_layer + t_head), "unit": "tok/s", "cores": threads, "kind": "port",
+               "sample": "measured on layer 0 (%.1f ms) and the head (%.1f ms) of the same weights; the step is %d such layers and the head"
+                         % (t_layer * 1e3, t_head * 1e3, chain.n_layers)}
 
     if rank == 0:
         total_bytes = weight_bytes_per_token(shape) if args.layers is None else chain.bytes_streamed
@@ -386,13 +405,9 @@ def main():
             "metric": metric, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "%s dense decode GEMV chain (configs[%d]), batch %d" % (shape.name, 2 if args.workload == "gemma" else 1, args.batch),
-                       "layers": chain.n_layers, "hidden": shape.hidden, "ffn": shape.ffn, "vocab": shape.vocab,
-                       "weights": "random Q4_0 blocks" if args.workload == "gemma" else "random Q4_K/Q6_K blocks", "activations": "%s in HBM, fp32 accumulate" % args.activations,
-                       "parallelism": "tp%d rows" % world if world > 1 else "single GPU",
-                       "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (total_bytes * 1.0 / 1e9 / world),
-                       "launch": ("one persistent kernel per step (chain of %(projections)d projections, %(waits)d grid-wide waits, %(stages)d stages of %(stage_bytes)d bytes per SM)" % fused.info())
-                                 if fused is not None else "one recorded command (CUDA graph) per step" + (" incl. NCCL all-gathers" if world > 1 else "")},
+            "config": workload_config(shape, args.batch, chain.n_layers, world, total_bytes, args.activations),
+            "launch_mode": ("one persistent kernel per step (chain of %(projections)d projections, %(waits)d grid-wide waits, %(stages)d stages of %(stage_bytes)d bytes per SM)" % fused.info())
+                                 if fused is not None else "one recorded command (CUDA graph) per step" + (" incl. NCCL all-gathers" if world > 1 else ""),
             "hbm_gbs_effective": total_bytes / world / (ms_per_step * 1e-3) / 1e9,
             "hbm_frac_of_peak_chain": total_bytes / world / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "e2e": {"value": args.batch * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
@@ -400,6 +415,8 @@ def main():
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks, "roofline": roof, "kernels": per_kernel, "cpu_baseline": cpu,
         }
+        if parity:
+            line.update(parity)
         print(json.dumps(line), flush=True)
     if world > 1:
         # leave without tearing the communicator down: the recorded step holds NCCL work, and

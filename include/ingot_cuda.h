@@ -368,6 +368,60 @@ INGOT_API ingot_status ingot_chain_info(const ingot_chain *chain, uint32_t *proj
                                         uint32_t *stages, uint32_t *stage_bytes);
 INGOT_API void ingot_chain_destroy(ingot_chain *chain);
 
+/* ---- GGUF v3 files (src/gguf.rs) -------------------------------------------
+ * Gguf::open (src/gguf.rs:205-271) with the directory rules of :121-202: little-endian
+ * version 3; metadata types 0..12, arrays not nested, no duplicate key; general.alignment
+ * (default 32) a power of two; tensors of rank 1..4 with no zero dimension, dims[0] a whole
+ * number of blocks (geometry(): :470-491, every type the reference lists), aligned offsets,
+ * no duplicate, none beyond the file, no overlap; split models through their primary shard.
+ * Any violation is INGOT_INVALID; a positional read the file can no longer satisfy is
+ * INGOT_EOF (io::ErrorKind::UnexpectedEof).  These functions take no GPU handle and keep
+ * their error text per thread (ingot_gguf_last_error). */
+typedef struct ingot_gguf ingot_gguf;
+
+/* Tensor (src/gguf.rs:18-25): dims[0] = cols (contiguous), dims[1] = rows, dims[2] = experts;
+ * offset = absolute byte offset in file `shard`; stride = bytes of one row; bytes = all rows. */
+typedef struct ingot_tensor_info {
+    uint64_t dims[4];
+    uint32_t rank, kind;
+    uint64_t offset;
+    uint32_t shard, reserved;
+    uint64_t stride, bytes;
+} ingot_tensor_info;
+
+INGOT_API ingot_status ingot_gguf_open(const char *path, ingot_gguf **out);
+INGOT_API void ingot_gguf_close(ingot_gguf *gguf);
+INGOT_API const char *ingot_gguf_last_error(void);
+INGOT_API const char *ingot_gguf_architecture(const ingot_gguf *gguf);
+INGOT_API uint64_t ingot_gguf_tensor_count(const ingot_gguf *gguf);
+/* Gguf::bytes_read: bytes delivered by successful positional reads. */
+INGOT_API uint64_t ingot_gguf_bytes_read(const ingot_gguf *gguf);
+INGOT_API ingot_status ingot_gguf_tensor_at(const ingot_gguf *gguf, uint64_t index, const char **name,
+                                            ingot_tensor_info *info);
+/* Gguf::tensor (:338-342): "missing tensor" is INGOT_INVALID. */
+INGOT_API ingot_status ingot_gguf_tensor(const ingot_gguf *gguf, const char *name, ingot_tensor_info *info);
+/* Gguf::integer / float / string / array accessors (:273-337); a missing key or a value of another
+ * type is INGOT_INVALID.  Returned strings live as long as the handle. */
+INGOT_API ingot_status ingot_gguf_integer(const ingot_gguf *gguf, const char *key, uint64_t *value);
+INGOT_API ingot_status ingot_gguf_float(const ingot_gguf *gguf, const char *key, float *value);
+INGOT_API ingot_status ingot_gguf_string(const ingot_gguf *gguf, const char *key, const char **value);
+INGOT_API ingot_status ingot_gguf_array_length(const ingot_gguf *gguf, const char *key, uint64_t *length);
+INGOT_API ingot_status ingot_gguf_array_integer(const ingot_gguf *gguf, const char *key, uint64_t index, uint64_t *value);
+INGOT_API ingot_status ingot_gguf_array_string(const ingot_gguf *gguf, const char *key, uint64_t index, const char **value);
+/* Gguf::read_range (:361-366): `len` bytes at `offset` inside the tensor. */
+INGOT_API ingot_status ingot_gguf_read_range(ingot_gguf *gguf, const ingot_tensor_info *tensor, uint64_t offset, void *dst,
+                                             uint64_t len);
+/* Gguf::rows (:417-447): rows[i] of the tensor, in caller order (repeats allowed), `n` x stride bytes. */
+INGOT_API ingot_status ingot_gguf_rows(ingot_gguf *gguf, const char *name, const uint64_t *rows, uint64_t n, void *dst);
+/* Gguf::matrix (:448-476): the listed experts of a tensor whose dims equal `shape`. */
+INGOT_API ingot_status ingot_gguf_matrix(ingot_gguf *gguf, const char *name, const uint64_t *shape, uint32_t rank,
+                                         const uint64_t *experts, uint64_t n_experts, void *dst);
+/* Weight::load (src/weights.rs:22-32) + Gpu::load_weight (src/metal.rs:546-582): checks the shape,
+ * reads the tensor through a pinned staging buffer and uploads it (a discrete GPU cannot map the
+ * file in place).  *device is released with ingot_buffer_free. */
+INGOT_API ingot_status ingot_weight_load(ingot_gpu *gpu, ingot_gguf *gguf, const char *name, const uint64_t *shape,
+                                         uint32_t rank, void **device, ingot_tensor_info *info);
+
 /* ---- host-vector conveniences (the reference's public parity hooks) ------ */
 
 /* Gpu::dequant(&Matrix) (src/metal.rs:1581-1601) with validate_matrix

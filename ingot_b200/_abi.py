@@ -63,6 +63,19 @@ SIGNATURES = {
     "ingot_packed_digits_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_digits": [vp, vp, u32, u32, u32, vp],
     "ingot_matvec_static": [vp, u32, u32, u32, u32, u32, vp, vp, vp, i32],
+    "ingot_gguf_open": [C.c_char_p, C.POINTER(vp)],
+    "ingot_gguf_tensor_at": [vp, u64, C.POINTER(C.c_char_p), vp],
+    "ingot_gguf_tensor": [vp, C.c_char_p, vp],
+    "ingot_gguf_integer": [vp, C.c_char_p, C.POINTER(u64)],
+    "ingot_gguf_float": [vp, C.c_char_p, C.POINTER(f32)],
+    "ingot_gguf_string": [vp, C.c_char_p, C.POINTER(C.c_char_p)],
+    "ingot_gguf_array_length": [vp, C.c_char_p, C.POINTER(u64)],
+    "ingot_gguf_array_integer": [vp, C.c_char_p, u64, C.POINTER(u64)],
+    "ingot_gguf_array_string": [vp, C.c_char_p, u64, C.POINTER(C.c_char_p)],
+    "ingot_gguf_read_range": [vp, vp, u64, vp, u64],
+    "ingot_gguf_rows": [vp, C.c_char_p, vp, u64, vp],
+    "ingot_gguf_matrix": [vp, C.c_char_p, vp, u32, vp, u64, vp],
+    "ingot_weight_load": [vp, vp, C.c_char_p, vp, u32, C.POINTER(vp), vp],
     "ingot_chain_begin": [vp],
     "ingot_chain_end": [vp, C.POINTER(vp)],
     "ingot_chain_submit": [vp, vp],
@@ -79,6 +92,11 @@ OTHER = {
     "ingot_last_error": (C.c_char_p, [vp]),
     "ingot_command_destroy": (None, [vp]),
     "ingot_chain_destroy": (None, [vp]),
+    "ingot_gguf_close": (None, [vp]),
+    "ingot_gguf_last_error": (C.c_char_p, []),
+    "ingot_gguf_architecture": (C.c_char_p, [vp]),
+    "ingot_gguf_tensor_count": (u64, [vp]),
+    "ingot_gguf_bytes_read": (u64, [vp]),
     "ingot_matvec_static_error": (C.c_char_p, []),
 }
 

@@ -19,7 +19,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libingot_cuda.so")
 OBJ_DIR = os.path.join(PKG, "build")
 
-SOURCES = ["abi.cu", "gemv.cu", "gemv_mma.cu", "gemv_tc.cu", "misc.cu", "gemm.cu", "noalloc.cu"]
+SOURCES = ["abi.cu", "gemv.cu", "gemv_mma.cu", "gemv_tc.cu", "misc.cu", "gemm.cu", "noalloc.cu", "gguf.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -45,7 +45,7 @@ def _deps_mtime() -> float:
     newest = 0.0
     for root in (CSRC, os.path.join(os.path.dirname(PKG), "include")):
         for name in os.listdir(root):
-            if name.endswith((".cu", ".cuh", ".h")):
+            if name.endswith((".cu", ".cuh", ".h", ".cpp")):
                 newest = max(newest, os.path.getmtime(os.path.join(root, name)))
     return newest
 
@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     extra = ["-Xptxas", "-v"] if verbose else []
 
     def compile_one(src: str) -> tuple[str, str]:
-        obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
+        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
