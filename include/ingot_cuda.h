@@ -251,6 +251,50 @@ INGOT_API ingot_status ingot_gate_up_normed(ingot_gpu *gpu, const void *gate, co
                                             const float *b, const float *norm_w, float *s, float eps, uint32_t add,
                                             uint32_t round_bf16, uint32_t gelu, float *y);
 
+/* ---- the rest of a generic decode step (graph: Generic::hidden, src/generic.rs:664-749) ---- */
+
+/* embedding_batch (kernels/qwen.metal:139): y[t][j] = weight_at(row ids[t] of w, j) for `count`
+ * tokens; w is `rows` (the vocabulary) x width in any type of this path; bit-exact.  A token
+ * id >= rows is reported by ingot_synchronize as INGOT_INVALID (its row is zeros). */
+INGOT_API ingot_status ingot_embedding_batch(ingot_gpu *gpu, const void *w, const uint32_t *ids, uint32_t width,
+                                             uint32_t rows, uint32_t stride, uint32_t kind, uint32_t count, float *y);
+
+/* The integer and float parameters of qk_rope_cache (kernels/generic.metal:405-410: head dim
+ * <= 512, heads, kv heads, rotated dims, position, base, NeoX pairing, frequency factors,
+ * QK norm, eps, unweighted value norm, q scale). */
+typedef struct ingot_rope_params {
+    uint32_t head_dim, heads, kv_heads, rotated, position;
+    float base;
+    uint32_t neox, use_factors, qk_norm;
+    float eps;
+    uint32_t value_norm;
+    float q_scale;
+} ingot_rope_params;
+
+/* qk_rope_cache (kernels/generic.metal:405-438): per head row of `tokens` tokens, optional QK
+ * RMS norm (weights q_norm, k_norm), rotary embedding of the first `rotated` dimensions at
+ * position + t (interleaved pairs, or NeoX halves), q times q_scale to q_out [t][heads][D];
+ * k and v (v optionally RMS-normalised without a weight) into the float32 caches at row
+ * position + t, [row][kv_heads][D]. */
+INGOT_API ingot_status ingot_qk_rope_cache(ingot_gpu *gpu, const float *q, const float *k, const float *v,
+                                           const float *q_norm, const float *k_norm, const float *factors,
+                                           float *q_out, float *k_cache, float *v_cache,
+                                           const ingot_rope_params *params, uint32_t tokens);
+
+/* attention_decode_<D> (kernels/generic.metal:440-474): causal attention of 1..4 query tokens
+ * (the first at `position`) over the float32 caches, softmax scale 1/sqrt(D), grouped-query
+ * heads, sliding window (0: none).  D in {64, 96, 128, 256, 512}, else INGOT_UNSUPPORTED. */
+INGOT_API ingot_status ingot_attention_decode(ingot_gpu *gpu, const float *q, const float *k_cache,
+                                              const float *v_cache, float *out, uint32_t head_dim, uint32_t heads,
+                                              uint32_t kv_heads, uint32_t position, uint32_t window, uint32_t tokens);
+
+/* greedy_select (kernels/qwen.metal:384-410) in its two stages, as Gpu::finish_greedy issues them
+ * (src/metal.rs:1507-1548): out[r] = (token of the largest logit of row r — equal values, signed
+ * zeros included, go to the smaller token id; `mapping` (may be NULL) renames column i —, 1 when
+ * the row holds a non-finite logit).  scratch: rows * ceil(vocab / 1024) * 3 words. */
+INGOT_API ingot_status ingot_greedy_select(ingot_gpu *gpu, const float *logits, const uint32_t *mapping, uint32_t rows,
+                                           uint32_t vocab, uint32_t *scratch, uint32_t *out);
+
 /* expert_layout + expert_pairs (kernels/prefill.metal:7-35): stable
  * expert-major grouping of `pairs` ids.  layout [experts][2] = (count, first),
  * tiles [tile_capacity][4] = (expert, first, n <= 32, mode), packed[pos] =

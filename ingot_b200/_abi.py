@@ -63,6 +63,10 @@ SIGNATURES = {
     "ingot_packed_digits_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_digits": [vp, vp, u32, u32, u32, vp],
     "ingot_matvec_static": [vp, u32, u32, u32, u32, u32, vp, vp, vp, i32],
+    "ingot_embedding_batch": [vp, vp, vp, u32, u32, u32, u32, u32, vp],
+    "ingot_qk_rope_cache": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32],
+    "ingot_attention_decode": [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32],
+    "ingot_greedy_select": [vp, vp, vp, u32, u32, vp, vp],
     "ingot_gguf_open": [C.c_char_p, C.POINTER(vp)],
     "ingot_gguf_tensor_at": [vp, u64, C.POINTER(C.c_char_p), vp],
     "ingot_gguf_tensor": [vp, C.c_char_p, vp],

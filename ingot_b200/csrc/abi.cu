@@ -659,6 +659,54 @@ ingot_status ingot_convert_bf16(ingot_gpu *g, const float *x, uint64_t n, void *
     return after_launch(g, launch_convert_bf16(x, n, y, ctx_of(g)), "convert_bf16");
 }
 
+// ---- the rest of a generic decode step ---------------------------------------------------------
+
+ingot_status ingot_embedding_batch(ingot_gpu *g, const void *w, const uint32_t *ids, uint32_t width, uint32_t rows, uint32_t stride,
+                                   uint32_t kind, uint32_t count, float *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, "embedding_batch: only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
+    if ((st = check_matrix(g, kind, width, rows, stride))) return st;
+    if (!w || !ids || !y) return fail(g, INGOT_INVALID, "null pointer");
+    return after_launch(g, launch_embedding(static_cast<const uint8_t *>(w), ids, width, stride, kind, count, rows, y, ctx_of(g)), "embedding_batch");
+}
+
+ingot_status ingot_qk_rope_cache(ingot_gpu *g, const float *q, const float *k, const float *v, const float *q_norm, const float *k_norm,
+                                 const float *factors, float *q_out, float *k_cache, float *v_cache, const ingot_rope_params *p,
+                                 uint32_t tokens) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, "qk_rope_cache: only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
+    if (!p || !q || !k || !v || !q_out || !k_cache || !v_cache) return fail(g, INGOT_INVALID, "null pointer");
+    if (p->head_dim == 0 || p->head_dim > 512 || p->heads == 0 || p->kv_heads == 0 || p->rotated > p->head_dim || (p->rotated & 1u) ||
+        (p->qk_norm && (!q_norm || !k_norm)) || (p->use_factors && !factors))
+        return fail(g, INGOT_INVALID, "qk_rope_cache: bad geometry");
+    RopeParams rp = {p->head_dim, p->heads, p->kv_heads, p->rotated, p->position, p->base, p->neox, p->use_factors, p->qk_norm, p->eps,
+                     p->value_norm, p->q_scale};
+    return after_launch(g, launch_rope_cache(q, k, v, q_norm, k_norm, factors, q_out, k_cache, v_cache, rp, tokens, ctx_of(g)), "qk_rope_cache");
+}
+
+ingot_status ingot_attention_decode(ingot_gpu *g, const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t head_dim,
+                                    uint32_t heads, uint32_t kv_heads, uint32_t position, uint32_t window, uint32_t tokens) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, "attention_decode: only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
+    if (!q || !k_cache || !v_cache || !out) return fail(g, INGOT_INVALID, "null pointer");
+    if (heads == 0 || kv_heads == 0 || heads % kv_heads || tokens > 4) return fail(g, INGOT_INVALID, "attention_decode: bad geometry (one to four query tokens)");
+    cudaError_t e = launch_attention_decode(q, k_cache, v_cache, out, head_dim, heads, kv_heads, position, window, tokens, ctx_of(g));
+    if (e == cudaErrorNotSupported) { cudaGetLastError(); return fail(g, INGOT_UNSUPPORTED, "attention_decode: head dimension must be 64, 96, 128, 256 or 512"); }
+    return after_launch(g, e, "attention_decode");
+}
+
+ingot_status ingot_greedy_select(ingot_gpu *g, const float *logits, const uint32_t *mapping, uint32_t rows, uint32_t vocab, uint32_t *scratch,
+                                 uint32_t *out) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, "greedy_select: only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
+    if (!logits || !scratch || !out || vocab == 0) return fail(g, INGOT_INVALID, "greedy_select: bad arguments");
+    return after_launch(g, launch_greedy(logits, mapping, rows, vocab, scratch, out, ctx_of(g)), "greedy_select");
+}
+
 ingot_status ingot_packed_x_bytes(uint32_t cols, uint64_t *bytes) {
     if (!bytes || cols == 0 || cols % 64u) return INGOT_INVALID;
     *bytes = packed_x_bytes(cols);

@@ -135,4 +135,23 @@ cudaError_t launch_ep_localize(const uint32_t *ids, const float *w, uint32_t pai
                                uint32_t *ids_out, float *w_out, const LaunchCtx &ctx);
 cudaError_t launch_convert_bf16(const float *x, uint64_t n, void *y_bf16, const LaunchCtx &ctx);
 
+// The rest of a generic decode step (decode_ops.cu).
+struct RopeParams {
+    uint32_t head_dim, heads, kv_heads, rotated, position;
+    float base;
+    uint32_t neox, use_factors, qk_norm;
+    float eps;
+    uint32_t value_norm;
+    float q_scale;
+};
+cudaError_t launch_embedding(const uint8_t *w, const uint32_t *ids, uint32_t width, uint32_t stride, uint32_t kind, uint32_t count,
+                             uint32_t vocab, float *y, const LaunchCtx &ctx);
+cudaError_t launch_rope_cache(const float *q, const float *k, const float *v, const float *qn, const float *kn, const float *factors,
+                              float *qo, float *kc, float *vc, const RopeParams &p, uint32_t tokens, const LaunchCtx &ctx);
+cudaError_t launch_attention_decode(const float *q, const float *k, const float *v, float *out, uint32_t head_dim, uint32_t heads,
+                                    uint32_t kv_heads, uint32_t position, uint32_t window, uint32_t tokens, const LaunchCtx &ctx);
+// partial: rows * ceil(vocab / 1024) * 3 words of scratch; out: rows * 2 words (token, non-finite flag).
+cudaError_t launch_greedy(const float *logits, const uint32_t *mapping, uint32_t rows, uint32_t vocab, uint32_t *partial, uint32_t *out,
+                          const LaunchCtx &ctx);
+
 }  // namespace ingot

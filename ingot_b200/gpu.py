@@ -137,6 +137,12 @@ class Graph:
             pass
 
 
+class _RopeParams(C.Structure):
+    _fields_ = [("head_dim", C.c_uint32), ("heads", C.c_uint32), ("kv_heads", C.c_uint32), ("rotated", C.c_uint32),
+                ("position", C.c_uint32), ("base", C.c_float), ("neox", C.c_uint32), ("use_factors", C.c_uint32),
+                ("qk_norm", C.c_uint32), ("eps", C.c_float), ("value_norm", C.c_uint32), ("q_scale", C.c_float)]
+
+
 class Chain:
     """A recorded sequence of fused-norm projections that runs as one persistent kernel."""
 
@@ -465,6 +471,48 @@ class Gpu:
         p = out or self.empty_bytes(rows * self.packed_digits_bytes(cols))
         self._check(self._lib.ingot_pack_digits(self._h, x.ptr, x_kind, rows, cols, p.ptr))
         return p
+
+    # ---- the rest of a generic decode step ----
+    def embedding_batch(self, cmd, w: Weight, ids: Buffer, count: int) -> Buffer:
+        """Rows ids[t] of the embedding matrix as float32 (embedding_batch, kernels/qwen.metal:139)."""
+        t = w.t
+        y = self.output(t.dims[0] * count)
+        self._check(self._lib.ingot_embedding_batch(self._h, w.buffer.ptr, ids.ptr, t.dims[0], t.dims[1], t.stride, t.kind, count, y.ptr))
+        return y
+
+    def qk_rope_cache(self, cmd, q: Buffer, k: Buffer, v: Buffer, q_out: Buffer, k_cache: Buffer, v_cache: Buffer, *, head_dim: int,
+                      heads: int, kv_heads: int, rotated: int, position: int, base: float, tokens: int, neox: bool = False,
+                      factors: Buffer | None = None, q_norm: Buffer | None = None, k_norm: Buffer | None = None, eps: float = 1e-6,
+                      value_norm: bool = False, q_scale: float = 1.0) -> None:
+        """qk_rope_cache (kernels/generic.metal:405-438)."""
+        p = _RopeParams(head_dim, heads, kv_heads, rotated, position, base, int(neox), int(factors is not None),
+                        int(q_norm is not None), eps, int(value_norm), q_scale)
+        ptr = lambda b: b.ptr if b is not None else None
+        self._check(self._lib.ingot_qk_rope_cache(self._h, q.ptr, k.ptr, v.ptr, ptr(q_norm), ptr(k_norm), ptr(factors), q_out.ptr,
+                                                  k_cache.ptr, v_cache.ptr, C.byref(p), tokens))
+
+    def attention_decode(self, cmd, q: Buffer, k_cache: Buffer, v_cache: Buffer, head_dim: int, heads: int, kv_heads: int,
+                         position: int, tokens: int, window: int = 0):
+        """attention_decode_<D> (kernels/generic.metal:440-474); None when there is no kernel for the head dimension."""
+        out = self.output(tokens * heads * head_dim)
+        st = self._lib.ingot_attention_decode(self._h, q.ptr, k_cache.ptr, v_cache.ptr, out.ptr, head_dim, heads, kv_heads, position,
+                                              window, tokens)
+        if st == _abi.UNSUPPORTED:
+            return None
+        self._check(st)
+        return out
+
+    def finish_greedy(self, cmd, logits: Buffer, rows: int, vocabulary: int, mapping: Buffer | None = None) -> list[int]:
+        """Gpu::finish_greedy (src/metal.rs:1507-1548): the greedy token of every row; non-finite logits are an error."""
+        chunks = (vocabulary + 1023) // 1024
+        partial, result = self.empty_bytes(4 * rows * chunks * 3), self.empty_bytes(4 * rows * 2)
+        self._check(self._lib.ingot_greedy_select(self._h, logits.ptr, mapping.ptr if mapping else None, rows, vocabulary, partial.ptr,
+                                                  result.ptr))
+        self.complete(cmd)
+        out = self.read_u32(result, rows * 2).reshape(rows, 2)
+        if out[:, 1].any():
+            raise InvalidData("non-finite logits")
+        return [int(v) for v in out[:, 0]]
 
     def route_topk(self, logits: Buffer, experts: int, top: int, tokens: int):
         ids = self.empty_bytes(4 * top * tokens)

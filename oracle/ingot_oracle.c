@@ -448,3 +448,109 @@ ORACLE_API void oracle_add_rms(const float *a, const float *b, const float *w, u
         y[j] = s * scale * (w ? w[j] : 1.0f);
     }
 }
+
+/* ------------------------------------------------------------------------
+ * The rest of a generic decode step.
+ * ------------------------------------------------------------------------ */
+
+/* embedding_batch (kernels/qwen.metal:139): y[t][j] = weight_at(row ids[t], j). */
+ORACLE_API int oracle_embedding(const uint8_t *w, const uint32_t *ids, uint64_t width, uint64_t rows, uint64_t stride,
+                                uint32_t kind, uint64_t count, float *y) {
+    for (uint64_t t = 0; t < count; ++t) {
+        if (ids[t] >= rows) return -1;
+        if (oracle_dequant_rows(w + (uint64_t)ids[t] * stride, width, 1, stride, kind, y + t * width)) return -2;
+    }
+    return 0;
+}
+
+/* qk_rope_cache (kernels/generic.metal:405-438), one head row at a time, float arithmetic as written there. */
+ORACLE_API void oracle_qk_rope_cache(const float *q, const float *k, const float *v, const float *qn, const float *kn,
+                                     const float *factors, float *qo, float *kc, float *vc, uint32_t D, uint32_t H,
+                                     uint32_t KV, uint32_t rot, uint32_t position, float base, int neox, int use_factors,
+                                     int qk_norm, float eps, int value_norm, float q_scale, uint32_t tokens) {
+    float row[512];
+    for (uint32_t t = 0; t < tokens; ++t)
+        for (uint32_t r = 0; r < H + 2 * KV; ++r) {
+            if (r >= H + KV) {
+                uint32_t h = r - H - KV;
+                const float *src = v + ((uint64_t)t * KV + h) * D;
+                float *dst = vc + ((uint64_t)(position + t) * KV + h) * D;
+                float inv = 1.0f;
+                if (value_norm) {
+                    double s = 0.0;
+                    for (uint32_t j = 0; j < D; ++j) s += (double)src[j] * src[j];
+                    inv = (float)(1.0 / sqrt(s / D + eps));
+                }
+                for (uint32_t j = 0; j < D; ++j) dst[j] = value_norm ? src[j] * inv : src[j];
+                continue;
+            }
+            int isq = r < H;
+            uint32_t h = isq ? r : r - H;
+            const float *src = isq ? q + ((uint64_t)t * H + h) * D : k + ((uint64_t)t * KV + h) * D;
+            float *dst = isq ? qo + ((uint64_t)t * H + h) * D : kc + ((uint64_t)(position + t) * KV + h) * D;
+            const float *w = isq ? qn : kn;
+            float inv = 1.0f;
+            if (qk_norm) {
+                double s = 0.0;
+                for (uint32_t j = 0; j < D; ++j) s += (double)src[j] * src[j];
+                inv = (float)(1.0 / sqrt(s / D + eps));
+            }
+            for (uint32_t j = 0; j < D; ++j) row[j] = qk_norm ? src[j] * inv * w[j] : src[j];
+            float qs = isq ? q_scale : 1.0f;
+            for (uint32_t j = 0; j < D; ++j) {
+                if (j >= rot) { dst[j] = row[j] * qs; continue; }
+                uint32_t f = neox ? j % (rot / 2) : j / 2, a = neox ? f : (j & ~1u), b = neox ? a + rot / 2 : a + 1;
+                double theta = (double)(position + t) * pow((double)base, -2.0 * (double)f / (double)rot);
+                if (use_factors) theta /= factors[f];
+                double c = cos(theta), s = sin(theta);
+                int first = neox ? j < rot / 2 : (j & 1u) == 0;
+                double y = first ? row[a] * c - row[b] * s : row[a] * s + row[b] * c;
+                dst[j] = (float)(y * qs);
+            }
+        }
+}
+
+/* attention_decode (kernels/generic.metal:440-474) as plain softmax attention in double. */
+ORACLE_API void oracle_attention_decode(const float *q, const float *k, const float *v, float *out, uint32_t D, uint32_t H,
+                                        uint32_t KV, uint32_t position, uint32_t window, uint32_t tokens) {
+    double *score = (double *)malloc(sizeof(double) * (position + tokens + 1));
+    for (uint32_t t = 0; t < tokens; ++t)
+        for (uint32_t h = 0; h < H; ++h) {
+            uint32_t kh = h / (H / KV), stride = KV * D, length = position + t + 1;
+            uint32_t start = window && length > window ? length - window : 0;
+            const float *qr = q + ((uint64_t)t * H + h) * D;
+            double m = -INFINITY;
+            for (uint32_t pos = start; pos < length; ++pos) {
+                const float *kr = k + (uint64_t)pos * stride + kh * D;
+                double s = 0.0;
+                for (uint32_t j = 0; j < D; ++j) s += (double)qr[j] * kr[j];
+                score[pos] = s / sqrt((double)D);
+                if (score[pos] > m) m = score[pos];
+            }
+            double l = 0.0;
+            for (uint32_t pos = start; pos < length; ++pos) { score[pos] = exp(score[pos] - m); l += score[pos]; }
+            for (uint32_t j = 0; j < D; ++j) {
+                double acc = 0.0;
+                for (uint32_t pos = start; pos < length; ++pos) acc += score[pos] * v[(uint64_t)pos * stride + kh * D + j];
+                out[((uint64_t)t * H + h) * D + j] = (float)(acc / l);
+            }
+        }
+    free(score);
+}
+
+/* greedy_select (kernels/qwen.metal:384-410): largest value, ties (signed zeros included) to the smaller
+ * token id; bad = a non-finite value was seen. */
+ORACLE_API void oracle_greedy(const float *logits, const uint32_t *mapping, uint64_t rows, uint64_t vocab, uint32_t *out) {
+    for (uint64_t r = 0; r < rows; ++r) {
+        float best = -INFINITY;
+        uint32_t id = 0xffffffffu, bad = 0;
+        for (uint64_t i = 0; i < vocab; ++i) {
+            float value = logits[r * vocab + i];
+            uint32_t token = mapping ? mapping[i] : (uint32_t)i;
+            bad |= !isfinite(value);
+            if (value > best || (value == best && token < id)) { best = value; id = token; }
+        }
+        out[2 * r] = id;
+        out[2 * r + 1] = bad;
+    }
+}

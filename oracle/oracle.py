@@ -75,6 +75,15 @@ def _load():
     lib.oracle_add_rms.restype = None
     lib.oracle_add_rms.argtypes = [_f32p, _f32p, _f32p, C.c_uint64, C.c_float, C.c_int, _f32p,
                                    _f32p]
+    lib.oracle_embedding.restype = C.c_int
+    lib.oracle_embedding.argtypes = [_u8p, _u32p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, _f32p]
+    lib.oracle_qk_rope_cache.restype = None
+    lib.oracle_qk_rope_cache.argtypes = [_f32p] * 9 + [C.c_uint32] * 5 + [C.c_float, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int,
+                                                                            C.c_float, C.c_uint32]
+    lib.oracle_attention_decode.restype = None
+    lib.oracle_attention_decode.argtypes = [_f32p] * 4 + [C.c_uint32] * 6
+    lib.oracle_greedy.restype = None
+    lib.oracle_greedy.argtypes = [_f32p, _u32p, C.c_uint64, C.c_uint64, _u32p]
     return lib
 
 
@@ -290,4 +299,45 @@ def ref_dequant(data, cols: int, rows: int, kind: int) -> np.ndarray:
         o = np.empty(cols, np.float32)
         r.ref_dequant_row(_p(row, _u8p), kind, cols, _p(o, _f32p))
         out[i] = o
+    return out
+
+
+# ---- the rest of a generic decode step ----
+
+def embedding(data, ids, width: int, rows: int, kind: int) -> np.ndarray:
+    raw = _bytes(data)
+    i = np.ascontiguousarray(np.asarray(ids, dtype=np.uint32).reshape(-1))
+    y = np.empty((i.size, width), dtype=np.float32)
+    if lib().oracle_embedding(_p(raw, _u8p), _p(i, _u32p), width, rows, stride_of(kind, width), kind, i.size, _p(y, _f32p)):
+        raise ValueError("token outside vocabulary")
+    return y
+
+
+def qk_rope_cache(q, k, v, kc, vc, *, head_dim, heads, kv_heads, rotated, position, base, tokens, neox=False, factors=None,
+                  q_norm=None, k_norm=None, eps=1e-6, value_norm=False, q_scale=1.0):
+    """Returns q_out [tokens, heads, D]; kc and vc (float32 [rows, kv_heads, D]) are updated in place."""
+    qf, kf, vf = _f32(q).reshape(-1), _f32(k).reshape(-1), _f32(v).reshape(-1)
+    qo = np.empty(tokens * heads * head_dim, np.float32)
+    ptr = lambda a: None if a is None else _p(_f32(a).reshape(-1), _f32p)
+    lib().oracle_qk_rope_cache(_p(qf, _f32p), _p(kf, _f32p), _p(vf, _f32p), ptr(q_norm), ptr(k_norm), ptr(factors), _p(qo, _f32p),
+                               _p(kc, _f32p), _p(vc, _f32p), head_dim, heads, kv_heads, rotated, position, base, int(neox),
+                               int(factors is not None), int(q_norm is not None), eps, int(value_norm), q_scale,
+                               tokens)
+    return qo.reshape(tokens, heads, head_dim)
+
+
+def attention_decode(q, kc, vc, head_dim, heads, kv_heads, position, tokens, window=0) -> np.ndarray:
+    qf = _f32(q).reshape(-1)
+    out = np.empty(tokens * heads * head_dim, np.float32)
+    lib().oracle_attention_decode(_p(qf, _f32p), _p(kc, _f32p), _p(vc, _f32p), _p(out, _f32p), head_dim, heads, kv_heads, position,
+                                  window, tokens)
+    return out.reshape(tokens, heads, head_dim)
+
+
+def greedy(logits, vocab: int, mapping=None) -> np.ndarray:
+    """uint32 [rows, 2]: (token, non-finite flag)."""
+    l = _f32(logits).reshape(-1, vocab)
+    m = None if mapping is None else np.ascontiguousarray(np.asarray(mapping, dtype=np.uint32))
+    out = np.empty((l.shape[0], 2), np.uint32)
+    lib().oracle_greedy(_p(l, _f32p), None if m is None else _p(m, _u32p), l.shape[0], vocab, _p(out, _u32p))
     return out
