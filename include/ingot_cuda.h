@@ -303,6 +303,23 @@ INGOT_API ingot_status ingot_expert_layout(ingot_gpu *gpu, const uint32_t *ids, 
                                            uint32_t experts, uint32_t tile_capacity, uint32_t *layout,
                                            uint32_t *tiles, uint32_t *packed, uint32_t *inverse);
 
+/* The per-expert projections of the packed MoE path (Generic::moe_packed, src/generic.rs:578-660):
+ * quant_expert_gather / quant_expert_packed (kernels/qwen.metal:953-999) and quant_expert_gate_up
+ * (:1002-1081).  `tiles` and `pairs` are the tables of ingot_expert_layout; every tile's expert is
+ * streamed once per four of its pairs.  x holds float32 rows: with gather, packed position q reads
+ * row pairs[q] / top (the token's activations); without, row q (activations already in packed order,
+ * the down projection).  y_packed[q][rows] is in packed order; ingot_combine_packed brings it back.
+ * INGOT_UNSUPPORTED when the weight type or alignment has no grouped kernel (project pair by pair
+ * with ingot_routed / ingot_routed_gate_up instead). */
+INGOT_API ingot_status ingot_expert_project(ingot_gpu *gpu, const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
+                                            uint32_t kind, uint32_t experts, const float *x, const uint32_t *tiles,
+                                            const uint32_t *pairs, uint32_t tile_capacity, uint32_t top, uint32_t n_pairs,
+                                            uint32_t gather, float *y_packed);
+INGOT_API ingot_status ingot_expert_gate_up(ingot_gpu *gpu, const void *gate, const void *up, uint32_t cols, uint32_t rows,
+                                            uint32_t stride, uint32_t kind, uint32_t experts, const float *x,
+                                            const uint32_t *tiles, const uint32_t *pairs, uint32_t tile_capacity,
+                                            uint32_t top, uint32_t n_pairs, float *y_packed);
+
 /* combine_packed without the shared expert (kernels/prefill.metal:39). */
 INGOT_API ingot_status ingot_combine_packed(ingot_gpu *gpu, const float *routed, const float *weights,
                                             const uint32_t *inverse, uint32_t width, uint32_t top,

@@ -63,6 +63,8 @@ SIGNATURES = {
     "ingot_packed_digits_bytes": [u32, C.POINTER(u64)],
     "ingot_pack_digits": [vp, vp, u32, u32, u32, vp],
     "ingot_matvec_static": [vp, u32, u32, u32, u32, u32, vp, vp, vp, i32],
+    "ingot_expert_project": [vp, vp, u32, u32, u32, u32, u32, vp, vp, vp, u32, u32, u32, u32, vp],
+    "ingot_expert_gate_up": [vp, vp, vp, u32, u32, u32, u32, u32, vp, vp, vp, u32, u32, u32, vp],
     "ingot_embedding_batch": [vp, vp, vp, u32, u32, u32, u32, u32, vp],
     "ingot_qk_rope_cache": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32],
     "ingot_attention_decode": [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32],

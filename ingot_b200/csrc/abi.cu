@@ -576,6 +576,42 @@ ingot_status ingot_routed_gate_up(ingot_gpu *g, const void *gate, const void *up
     return gemv_common(g, c, x_kind, "routed_gate_up");
 }
 
+// Per-expert projections over the expert grouping (Generic::moe_packed, src/generic.rs:578-660).
+static ingot_status expert_tiles_common(ingot_gpu *g, GemvCall &c, const uint32_t *tiles, const uint32_t *pairs, uint32_t tile_capacity,
+                                        bool gather, const char *what) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, std::string(what) + ": only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
+    if ((st = check_matrix(g, c.kind, c.cols, c.rows, c.stride))) return st;
+    if (!c.w[0] || (c.nmat == 2 && !c.w[1]) || !c.x || !c.y || !tiles || !pairs || c.top == 0 || c.n_experts == 0 || tile_capacity == 0)
+        return fail(g, INGOT_INVALID, std::string(what) + ": bad arguments");
+    cudaError_t e = cudaSuccess;
+    if (g->no_mma || g->force_plain || !try_launch_gemv_tiles(c, tiles, pairs, tile_capacity, gather, ctx_of(g), e))
+        return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": no grouped kernel for this weight type or alignment; project pair by pair");
+    return after_launch(g, e, what);
+}
+
+ingot_status ingot_expert_project(ingot_gpu *g, const void *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind,
+                                  uint32_t experts, const float *x, const uint32_t *tiles, const uint32_t *pairs, uint32_t tile_capacity,
+                                  uint32_t top, uint32_t n_pairs, uint32_t gather, float *y_packed) {
+    GemvCall c = {};
+    c.w[0] = static_cast<const uint8_t *>(w);
+    c.x = x; c.y = y_packed; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
+    c.pairs = n_pairs; c.top = top; c.n_experts = experts; c.nmat = 1;
+    return expert_tiles_common(g, c, tiles, pairs, tile_capacity, gather != 0, "expert_project");
+}
+
+ingot_status ingot_expert_gate_up(ingot_gpu *g, const void *gate, const void *up, uint32_t cols, uint32_t rows, uint32_t stride,
+                                  uint32_t kind, uint32_t experts, const float *x, const uint32_t *tiles, const uint32_t *pairs,
+                                  uint32_t tile_capacity, uint32_t top, uint32_t n_pairs, float *y_packed) {
+    GemvCall c = {};
+    c.w[0] = static_cast<const uint8_t *>(gate);
+    c.w[1] = static_cast<const uint8_t *>(up);
+    c.x = x; c.y = y_packed; c.cols = cols; c.rows = rows; c.stride = stride; c.kind = kind;
+    c.pairs = n_pairs; c.top = top; c.n_experts = experts; c.nmat = 2; c.glu = 1;
+    return expert_tiles_common(g, c, tiles, pairs, tile_capacity, true, "expert_gate_up");
+}
+
 ingot_status ingot_route_topk(ingot_gpu *g, const float *logits, uint32_t experts, uint32_t top, uint32_t tokens,
                               uint32_t *ids, float *weights) {
     ingot_status st = enter(g);

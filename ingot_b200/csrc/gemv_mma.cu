@@ -76,6 +76,7 @@ struct MmaPlan {
     uint32_t ctas;
     uint32_t red_slots;      // ring of partial-sum buffers, > stages
     uint32_t xm;             // form of the activation row in shared memory (XM_*)
+    uint32_t x_row_stride;   // bytes between activation rows when several are held (tiles of one expert)
 };
 
 // Activation row forms.  The binary16 forms are what ingot_pack_x / ingot_pack_x_hi write; the
@@ -133,9 +134,10 @@ struct MmaFixed {
     uint32_t x_bytes, slot_bytes, slots;
     uint32_t warps;          // consumer warps of the kernel (8 or 16)
 };
+static constexpr uint32_t MMA_TILE_TOKENS = 4;      // pairs of one expert multiplied per pass over its rows
 
 static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t nmat, uint32_t max_ctas,
-                     uint32_t budget, uint32_t xm, MmaPlan &p, const MmaFixed *common = nullptr) {
+                     uint32_t budget, uint32_t xm, MmaPlan &p, const MmaFixed *common = nullptr, uint32_t tokens = 1) {
     if (!mma_kind(kind)) return false;
     uint32_t block, bytes;
     geometry(kind, block, bytes);
@@ -150,12 +152,13 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     p.row_tiles = (uint32_t)MMA_WARPS >> kw;
     const uint32_t per_warp = p.nsteps >> kw;                 // steps each warp owns per row
     p.xm = xm;
-    p.x_bytes = common ? common->x_bytes : x_row_bytes(xm, cols);
+    p.x_row_stride = (x_row_bytes(xm, cols) + 15u) & ~15u;
+    p.x_bytes = common ? common->x_bytes : tokens > 1 ? tokens * p.x_row_stride : x_row_bytes(xm, cols);
     if (common && x_row_bytes(xm, cols) > common->x_bytes) return false;
     // the int8 steps of the K-quants read 8 bytes per lane
     const uint32_t lead = (xm >= XM_FX2 && (kind == KIND_Q4_K || kind == KIND_Q6_K)) ? 32u : 16u;
-    p.red_slots = budget <= MMA_SMEM_SMALL ? 4u : MMA_RED_SLOTS;
-    p.red_bytes = p.red_slots * MMA_WARPS * 2u * 16u * 4u + MMA_ZERO_BYTES;   // [slot][warp][mat][row] + zeros
+    p.red_slots = (budget <= MMA_SMEM_SMALL || tokens > 1) ? 4u : MMA_RED_SLOTS;
+    p.red_bytes = p.red_slots * MMA_WARPS * tokens * 2u * 16u * 4u + MMA_ZERO_BYTES;   // [slot][warp][token][mat][row] + zeros
     const uint32_t fixed = MMA_BAR_BYTES + ((p.x_bytes + 127u) & ~127u) + p.red_bytes;
     if (fixed >= budget) return false;
     // chunk = the most steps per warp whose stage stays near the target, leaves at least
@@ -753,13 +756,24 @@ struct MmaRun {
     unsigned long long *trace = nullptr;    // debugging: where thread 0 stores the time at which the activation row was ready
 };
 
+// A group of up to TK routed pairs that share one expert (one pass over a tile of the expert grouping):
+// the expert's rows are streamed once and multiplied with each pair's activation row.
+struct MmaTile {
+    uint32_t expert;         // the tile's expert
+    uint32_t first;          // packed position of the pass's first pair
+    uint32_t nt;             // pairs in this pass (1..TK)
+    uint32_t gather;         // the activation row of packed position q is row pairs[q] / top of x (else row q)
+    const uint32_t *pairs;   // packed position -> pair index
+};
+
 // The whole CTA's work on one projection: CTA `cta` of `nctas` (its share of the rows), pair `pair`.
 // False when a bounded wait ran out (the status word says which).
 // CW consumer warps in groups of eight: a group splits the columns of a tile among its warps and takes
 // every (CW / 8)-th tile, so with sixteen warps two stages of the ring are in work at once.
-template <uint32_t KIND, int NMAT, int XM, int CW = MMA_WARPS>
+// TK > 1: `tile` names up to TK pairs of one expert; their rows sit TK deep in shared memory (p.x_row_stride apart).
+template <uint32_t KIND, int NMAT, int XM, int CW = MMA_WARPS, int TK = 1>
 __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, const uint32_t cta, const uint32_t nctas, const uint32_t pair,
-                                              const bool whole_tiles, MmaRun &run) {
+                                              const bool whole_tiles, MmaRun &run, const MmaTile *tile = nullptr) {
     const MmaPlan &p = a.plan;
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MMA_MAX_STAGES;
@@ -813,8 +827,8 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         // ---- producer warp: weights first (they do not depend on the previous kernel),
         // then, once the ring is primed, wait for the previous kernel and fetch the
         // packed activations ----
-        uint32_t expert = a.expert, x_row = 0;
-        if (a.ids) {                                   // routing comes from the previous kernel
+        uint32_t expert = tile ? tile->expert : a.expert, x_row = 0;
+        if (a.ids && !tile) {                          // routing comes from the previous kernel
             ptx::pdl_wait();
             expert = a.ids[pair];
             if (expert >= a.n_experts) return true;    // skipped pair, or out of range: consumers handle it
@@ -889,7 +903,9 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     }
 
     // ---- consumer warps ----
-    if (a.ids) {
+    const uint32_t ntok = tile ? tile->nt : 1u;        // activation rows in work
+    const uint32_t xrs = TK > 1 ? p.x_row_stride : 0u;
+    if (a.ids && !tile) {
         ptx::pdl_wait();
         const uint32_t e = a.ids[pair];
         if (e >= a.n_experts) {
@@ -906,7 +922,10 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         // kernels/generic.metal:390-404): the 256 consumer threads of every CTA build the packed row ----
         ptx::pdl_wait();
         const uint32_t tid = threadIdx.x, n4 = p.cols >> 2;
-        const uint32_t in_row = a.ids ? (a.per_pair ? pair : pair / a.top) : 0u;
+       for (uint32_t ti = 0; ti < ntok; ++ti) {
+        const uint32_t in_row = tile ? (tile->gather ? tile->pairs[tile->first + ti] / a.top : tile->first + ti)
+                                     : a.ids ? (a.per_pair ? pair : pair / a.top) : 0u;
+        uint8_t *const xrow_t = xrow + (size_t)ti * xrs;
         const float4 *a4 = reinterpret_cast<const float4 *>(a.na) + (size_t)in_row * n4, *b4 = reinterpret_cast<const float4 *>(a.nb);
         float *scratch = red;                          // the partial-sum area is idle until the first tile ends
         auto load = [&](uint32_t j) {
@@ -971,7 +990,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             for (uint32_t i = 0; i < NV; ++i) {
                 if (i * NT >= n4) break;                               // uniform: the shuffles of a sub-block keep all its lanes
                 const uint32_t j = tid + i * NT;
-                fx_norm_store<ND>(xrow, p.cols, j, v[i], inv, a.nw, a.nround_bf16, j < n4);
+                fx_norm_store<ND>(xrow_t, p.cols, j, v[i], inv, a.nw, a.nround_bf16, j < n4);
             }
         };
         if (n4 <= 4u * NT) in_registers(std::integral_constant<uint32_t, 4>{});            // up to 4096 columns
@@ -987,9 +1006,10 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             for (uint32_t j0 = 0; j0 < n4; j0 += NT) {                 // uniform trip count: the shuffles of a sub-block keep all its lanes
                 const uint32_t j = j0 + tid;
                 const bool live = j < n4;
-                fx_norm_store<ND>(xrow, p.cols, j, live ? load(j) : make_float4(0.f, 0.f, 0.f, 0.f), inv, a.nw, a.nround_bf16, live);
+                fx_norm_store<ND>(xrow_t, p.cols, j, live ? load(j) : make_float4(0.f, 0.f, 0.f, 0.f), inv, a.nw, a.nround_bf16, live);
             }
         }
+       }
         ptx::named_bar_sync(1, MMA_WARPS * 32);
       }
       // (the first eight warps build the row, so its arithmetic does not depend on CW; the others wait here)
@@ -1026,7 +1046,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                               : xrow + (HI ? t : (g & 1u) * 4u + t) * 8u;
     const uint8_t *zlane = FX ? zeros + lane * 8u : zeros + ((g & 1u) * 4u + t) * 8u;
     const float nibf = (t & 1u) ? 0.0625f : 1.0f;                  // Q4_K int8 steps: odd sub-blocks keep their nibbles in place (16 q)
-    float *y = a.y + (a.ids ? (size_t)pair * p.rows : 0);
+    float *y = a.y + (tile ? (size_t)tile->first * p.rows : a.ids ? (size_t)pair * p.rows : 0);       // row of the first activation row in work
     const uint32_t kmask = (1u << p.kw_log2) - 1u;
 
     // Sum of a finished tile's partials over the K warps -> y.  The warp that sums rotates with
@@ -1037,7 +1057,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         const uint32_t ring = tile_base + tile;
         if (((ring ^ kw) & kmask) != 0u) return true;                  // another warp's turn
         const uint32_t slot_id = ring % p.red_slots;
-        const float *slot = red + (size_t)slot_id * MMA_WARPS * 2u * 16u;
+        const float *slot = red + (size_t)slot_id * MMA_WARPS * TK * 2u * 16u;
         if (!ptx::mbar_wait_sleep<20>(&tbar[slot_id], (ring / p.red_slots) & 1u)) {
             if (lane == 0) set_status_word(a.status, KERNEL_ERR_CONSUMER_TIMEOUT);
             return false;
@@ -1047,12 +1067,16 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         const uint32_t lrow = rt * 16u + (lane & 15u), first = rt << p.kw_log2;
         // NMAT == 2: lanes 0..15 sum matrix 0 and lanes 16..31 matrix 1, then exchange
         const uint32_t m = NMAT == 2 ? (lane >> 4) : 0u;
-        float sum = 0.f;
-        if (lrow < nrows && (NMAT == 2 || lane < 16u))
-            for (uint32_t k = 0; k <= kmask; ++k) sum = add_rn(sum, slot[((first + k) * 2u + m) * 16u + (lane & 15u)]);
-        sum = mul_rn(sum, unscale);
-        const float other = NMAT == 2 ? __shfl_xor_sync(0xffffffffu, sum, 16) : 0.f;
-        if (lrow < nrows && lane < 16u) y[row0 + lrow] = NMAT == 2 ? glu_f(sum, other, a.glu == 2) : sum;
+#pragma unroll
+        for (uint32_t ti = 0; ti < (uint32_t)TK; ++ti) {
+            if (ti >= ntok) break;
+            float sum = 0.f;
+            if (lrow < nrows && (NMAT == 2 || lane < 16u))
+                for (uint32_t k = 0; k <= kmask; ++k) sum = add_rn(sum, slot[(((first + k) * TK + ti) * 2u + m) * 16u + (lane & 15u)]);
+            sum = mul_rn(sum, unscale);
+            const float other = NMAT == 2 ? __shfl_xor_sync(0xffffffffu, sum, 16) : 0.f;
+            if (lrow < nrows && lane < 16u) y[(size_t)ti * p.rows + row0 + lrow] = NMAT == 2 ? glu_f(sum, other, a.glu == 2) : sum;
+        }
         return true;
     };
 
@@ -1064,9 +1088,11 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         const uint32_t lr0 = rt * 16u + g, lr1 = lr0 + 8u;             // rows of this lane inside the stage
         const uint32_t ur0 = lr0 < nrows ? lr0 : rt * 16u;              // rows past the end read the tile's first row
         const uint32_t ur1 = lr1 < nrows ? lr1 : rt * 16u;
-        float acc[NMAT][2];
+        float acc[TK][NMAT][2];
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m) acc[m][0] = acc[m][1] = 0.f;
+        for (int ti = 0; ti < TK; ++ti)
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) acc[ti][m][0] = acc[ti][m][1] = 0.f;
         for (uint32_t c = 0; c < p.chunks; ++c) {
             const uint32_t gs0 = c * (p.spw << p.kw_log2) + kw;                // first step inside the row
 #pragma unroll
@@ -1078,10 +1104,13 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 }
                 const uint8_t *st = stages + (size_t)s * p.stage_bytes;
                 if (rt * 16u < nrows) {
+#pragma unroll
+                  for (uint32_t ti = 0; ti < (uint32_t)TK; ++ti) {
+                    if (ti >= ntok) break;
                     const uint8_t *b0 = st + (size_t)ur0 * p.row_pitch + kw * STEP_BYTES;
                     const uint8_t *b1 = st + (size_t)ur1 * p.row_pitch + kw * STEP_BYTES;
-                    const uint8_t *xs = xlane + (size_t)gs0 * MMAS * XS;
-                    const float *ss = sx + gs0 * MMAS * (FX ? 2u : 1u);
+                    const uint8_t *xs = xlane + (size_t)ti * xrs + (size_t)gs0 * MMAS * XS;
+                    const float *ss = reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(sx) + (size_t)ti * xrs) + gs0 * MMAS * (FX ? 2u : 1u);
                     for (uint32_t i = 0; i < p.spw; ++i) {
                         if constexpr (FX) {
                             // chain position p of this lane: its own digits at the sub-block of that position, zeros elsewhere
@@ -1090,7 +1119,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                                                           own == 3 ? xs + 3u * PS : zlane};
                             // rows start on 16-byte boundaries in the stage: a Q6_K block (210 bytes) starts 2 (block mod 4)
                             // bytes past an 8-byte boundary (warp-uniform; the other formats ignore it)
-                            ImmaStep<KIND>::template run<ND>(b0, b1, xb, reinterpret_cast<const uint8_t *>(ss), t, nibf, acc[m][0], acc[m][1],
+                            ImmaStep<KIND>::template run<ND>(b0, b1, xb, reinterpret_cast<const uint8_t *>(ss), t, nibf, acc[ti][m][0], acc[ti][m][1],
                                                              (kw + (i << p.kw_log2)) & 3u);
                         } else {
                             const uint8_t *const xb[4] = {own == 0 ? xs : zlane, own == 1 ? xs : zlane, own == 2 ? xs : zlane,
@@ -1098,13 +1127,14 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                             // rows start on 16-byte boundaries in the stage: an odd Q6_K block (210 bytes) starts
                             // 2 bytes past a 4-byte boundary (warp-uniform; the other formats ignore it)
                             if (KIND == KIND_Q6_K && (((kw + (i << p.kw_log2)) & 1u) != 0u))
-                                MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1], true);
+                                MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[ti][m][0], acc[ti][m][1], true);
                             else
-                                MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[m][0], acc[m][1], false);
+                                MmaStep<KIND>::template run<XS>(b0, b1, xb, ss, t, acc[ti][m][0], acc[ti][m][1], false);
                         }
                         b0 += step_stride; b1 += step_stride;
                         xs += x_stride; ss += s_stride * (FX ? 2u : 1u);
                     }
+                  }
                 }
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&empty[s]);
@@ -1112,16 +1142,18 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         }
         // quad reduce (the four lanes hold different scale groups), then across the K warps
         const uint32_t slot_id = (tile_base + tile) % p.red_slots;
-        float *slot = red + (size_t)slot_id * MMA_WARPS * 2u * 16u;
+        float *slot = red + (size_t)slot_id * MMA_WARPS * TK * 2u * 16u;
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m)
+        for (int ti = 0; ti < TK; ++ti)
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float v = acc[m][h];
-                v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
-                v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
-                if (t == 0) slot[(wg * 2u + m) * 16u + g + 8u * h] = v;
-            }
+            for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float v = acc[ti][m][h];
+                    v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+                    v = add_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+                    if (t == 0) slot[((wg * TK + ti) * 2u + m) * 16u + g + 8u * h] = v;
+                }
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&tbar[slot_id]);
         if (tile >= GROUPS && !sum_tile(tile - GROUPS)) return false;
@@ -1140,6 +1172,95 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
     extern __shared__ __align__(128) uint8_t smem[];
     MmaRun run;
     gemv_mma_body<KIND, NMAT, XM>(a, smem, blockIdx.x, gridDim.x, blockIdx.y, false, run);
+}
+
+// Routed projections grouped by expert (the reference's packed MoE path for more than four tokens:
+// Generic::moe_packed, src/generic.rs:578-660, with quant_expert_gather / quant_expert_packed /
+// quant_expert_gate_up, kernels/qwen.metal:953-1081): grid.y walks the tiles of the expert grouping
+// (expert, first packed position, up to 32 pairs); the CTAs of a tile stream the expert's rows ONCE per
+// pass and multiply them with up to MMA_TILE_TOKENS activation rows held side by side in shared memory,
+// instead of once per pair.  Activation rows are gathered through pairs[] (gate/up: row pair / top of x)
+// or taken in packed order (down); results go to packed rows.
+struct MmaTileArgs {
+    MmaArgs a;
+    const uint32_t *tiles;       // [capacity][4] = expert, first, pairs, mode
+    const uint32_t *pairs;       // packed position -> pair index
+    uint32_t gather;
+};
+
+template <uint32_t KIND, int NMAT>
+__global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_tiles_kernel(const __grid_constant__ MmaTileArgs ta) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    ptx::pdl_wait();                                   // the grouping tables come from the kernels before
+    const uint32_t *tl = ta.tiles + 4u * blockIdx.y;
+    const uint32_t expert = tl[0], first = tl[1], n = tl[2];
+    if (n == 0) return;                                // unused tile
+    if (expert >= ta.a.n_experts) {
+        if (threadIdx.x == 0) set_status_word(ta.a.status, KERNEL_ERR_EXPERT_RANGE);
+        return;
+    }
+    MmaRun run;
+    for (uint32_t tok0 = 0; tok0 < n; tok0 += MMA_TILE_TOKENS) {
+        // the rows of the pass before are rebuilt: every consumer warp must be through with them
+        if (tok0 && threadIdx.x < MMA_WARPS * 32) ptx::named_bar_sync(5, MMA_WARPS * 32);
+        MmaTile tile = {expert, first + tok0, n - tok0 < MMA_TILE_TOKENS ? n - tok0 : MMA_TILE_TOKENS, ta.gather, ta.pairs};
+        if (!gemv_mma_body<KIND, NMAT, XM_FX4, MMA_WARPS, (int)MMA_TILE_TOKENS>(ta.a, smem, blockIdx.x, gridDim.x, blockIdx.y, false, run, &tile)) return;
+    }
+}
+
+template <uint32_t KIND, int NMAT>
+static cudaError_t launch_tiles_t(const MmaTileArgs &ta, dim3 grid, cudaStream_t stream, bool pdl) {
+    auto kernel = gemv_mma_tiles_kernel<KIND, NMAT>;
+    static DeviceOnce once;
+    {
+        const cudaError_t e = once.smem(kernel, (int)MMA_SMEM_MAX);
+        if (e != cudaSuccess) return e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(MMA_THREADS);
+    cfg.dynamicSmemBytes = ta.a.plan.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, ta);
+}
+
+// y_packed[pos][rows] = W[expert of pos] . x[row of pos] (nmat == 2: glu(gate . x, up . x)) for the packed positions
+// of every tile.  False when the call is not one this kernel handles (the caller then projects pair by pair).
+bool try_launch_gemv_tiles(const GemvCall &c, const uint32_t *tiles, const uint32_t *pairs, uint32_t tile_capacity, bool gather,
+                           const LaunchCtx &ctx, cudaError_t &err) {
+    if (!mma_kind(c.kind) || c.cols % 64u || c.x_packed || c.x_bf16 || ((uintptr_t)c.x % 16u) || !tiles || !pairs || tile_capacity == 0) return false;
+    if (((uintptr_t)c.w[0] % 16u) || (c.nmat == 2 && ((uintptr_t)c.w[1] % 16u)) || ((size_t)c.rows * c.stride) % 16u) return false;
+    MmaPlan plan;
+    if (!plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, 1u, MMA_SMEM_BUDGET, XM_FX4, plan, nullptr, MMA_TILE_TOKENS) &&
+        !plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, 1u, MMA_SMEM_MAX, XM_FX4, plan, nullptr, MMA_TILE_TOKENS))
+        return false;
+    // CTAs per tile: about as many live tiles as there are experts touched (at most min(pairs, experts)); two waves of CTAs at most
+    const uint32_t live = c.pairs < c.n_experts ? (c.pairs ? c.pairs : 1u) : c.n_experts;
+    uint32_t ctas = (2u * ctx.sm_count + live - 1) / live;
+    const uint32_t row_tiles = (c.rows + 16u * plan.row_tiles - 1) / (16u * plan.row_tiles);
+    if (ctas > row_tiles) ctas = row_tiles;
+    if (ctas < 1) ctas = 1;
+    plan.ctas = ctas;
+    MmaTileArgs ta = {};
+    MmaArgs &a = ta.a;
+    a.plan = plan;
+    a.w[0] = c.w[0]; a.w[1] = c.w[1]; a.y = c.y;
+    a.n_experts = c.n_experts; a.top = c.top ? c.top : 1u; a.glu = c.glu; a.status = ctx.status;
+    a.na = static_cast<const float *>(c.x); a.npack = 1u;
+    ta.tiles = tiles; ta.pairs = pairs; ta.gather = gather ? 1u : 0u;
+    const dim3 grid(ctas, tile_capacity);
+    switch (c.kind) {
+    case KIND_Q4_K: err = c.nmat == 2 ? launch_tiles_t<KIND_Q4_K, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q4_K, 1>(ta, grid, ctx.stream, ctx.pdl); break;
+    case KIND_Q6_K: err = c.nmat == 2 ? launch_tiles_t<KIND_Q6_K, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q6_K, 1>(ta, grid, ctx.stream, ctx.pdl); break;
+    case KIND_Q4_0: err = c.nmat == 2 ? launch_tiles_t<KIND_Q4_0, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q4_0, 1>(ta, grid, ctx.stream, ctx.pdl); break;
+    default: err = c.nmat == 2 ? launch_tiles_t<KIND_Q8_0, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q8_0, 1>(ta, grid, ctx.stream, ctx.pdl); break;
+    }
+    return true;
 }
 
 // Several independent one-token projections in one launch (what the reference's
@@ -1795,11 +1916,10 @@ bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCt
 
 static constexpr uint32_t CHAIN_NO_WAIT = 0xffffffffu;
 
-struct ChainOp {
+struct alignas(16) ChainOp {
     MmaArgs a;
     uint32_t wait_op;        // the projection whose completion (by every CTA) this one waits for, or CHAIN_NO_WAIT
     uint32_t reuse_x;        // the activation row of the previous projection is this one's as well
-    uint32_t pad[2];
 };
 static_assert(sizeof(ChainOp) % 16 == 0, "copied as 16-byte words");
 

@@ -94,6 +94,10 @@ bool chain_call_eligible(const GemvCall &c);
 cudaError_t chain_build(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx, ChainLaunch &out, const char *&why);
 cudaError_t chain_launch(const ChainLaunch &c, const LaunchCtx &ctx);
 void chain_free(ChainLaunch &c);
+// Routed projections grouped by expert: the tiles and pairs tables of launch_expert_layout; x float32 rows; results in
+// packed positions.  False when the call is not one the kernel handles.
+bool try_launch_gemv_tiles(const GemvCall &c, const uint32_t *tiles, const uint32_t *pairs, uint32_t tile_capacity, bool gather,
+                           const LaunchCtx &ctx, cudaError_t &err);
 // The tcgen05 int8 GEMV (one token, Q4_K); false when the call is not one it handles.
 bool try_launch_gemv_tc(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
 // Packs `rows` activation rows (f32 or bf16) as base-256 digits for it.

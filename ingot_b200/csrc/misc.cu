@@ -602,9 +602,14 @@ cudaError_t launch_ep_localize(const uint32_t *ids, const float *w, uint32_t pai
 }
 
 // ---------------------------------------------------------------------------
-// Expert grouping for packed prefill MoE (reference expert_layout /
-// expert_pairs: kernels/prefill.metal:7-35): experts ascending, pair indices
-// ascending inside an expert, tiles of at most 32 pairs.
+// Expert grouping for the packed MoE path.  The tables are the reference's (expert_layout /
+// expert_pairs: kernels/prefill.metal:7-35): experts ascending, pair indices ascending inside an
+// expert, tiles of at most 32 pairs, mode 1 for tiles of two or more.  They are built by ONE
+// CTA in one launch: a shared-memory histogram, a block-wide exclusive scan over the experts
+// (warp shuffles, then the warp totals), and a stable placement of the pairs in which the
+// sixteen warps take turns in pair order — inside a warp, match_any gives every lane its rank
+// among the earlier lanes with the same expert, and the group's first lane advances that
+// expert's running position.
 // ---------------------------------------------------------------------------
 
 struct LayoutArgs {
@@ -614,82 +619,74 @@ struct LayoutArgs {
     int *status;
 };
 
-__global__ void __launch_bounds__(256) expert_layout_kernel(const __grid_constant__ LayoutArgs a) {
+static constexpr uint32_t GROUP_THREADS = 512;      // one expert per thread in the scan: at most 512 experts
+
+__global__ void __launch_bounds__(GROUP_THREADS) expert_group_kernel(const __grid_constant__ LayoutArgs a) {
     pdl_prologue();
-    extern __shared__ uint32_t sh[];          // counts[experts], first[experts], tile0[experts + 1]
-    uint32_t *counts = sh, *first = sh + a.experts, *tile0 = first + a.experts;
-    const uint32_t tid = threadIdx.x;
-    for (uint32_t e = tid; e < a.experts; e += 256) counts[e] = 0;
+    __shared__ uint32_t counts[GROUP_THREADS], next_pos[GROUP_THREADS], warp_pairs[GROUP_THREADS / 32], warp_tiles[GROUP_THREADS / 32];
+    __shared__ uint32_t total_tiles;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    counts[tid] = 0;
     __syncthreads();
-    for (uint32_t i = tid; i < a.n_pairs; i += 256) {
+    for (uint32_t i = tid; i < a.n_pairs; i += GROUP_THREADS) {
         const uint32_t e = a.ids[i];
         if (e < a.experts) atomicAdd(&counts[e], 1u);
         else atomicCAS(a.status, 0, KERNEL_ERR_EXPERT_RANGE);
     }
     __syncthreads();
-    if (tid == 0) {
-        uint32_t at = 0, tile = 0;
-        for (uint32_t e = 0; e < a.experts; ++e) {
-            first[e] = at; tile0[e] = tile;
-            at += counts[e]; tile += (counts[e] + 31u) / 32u;
-        }
-        tile0[a.experts] = tile;
+    // exclusive scan over the experts of (pairs, tiles): inclusive inside the warp, then the warps' totals
+    const uint32_t n = tid < a.experts ? counts[tid] : 0u, nt = (n + 31u) / 32u;
+    uint32_t sp = n, st = nt;
+    for (uint32_t off = 1; off < 32; off <<= 1) {
+        const uint32_t op = __shfl_up_sync(0xffffffffu, sp, off), ot = __shfl_up_sync(0xffffffffu, st, off);
+        if (lane >= off) { sp += op; st += ot; }
     }
+    if (lane == 31) { warp_pairs[warp] = sp; warp_tiles[warp] = st; }
     __syncthreads();
-    for (uint32_t e = tid; e < a.experts; e += 256) {
-        const uint32_t n = counts[e];
-        a.layout[2 * e] = n; a.layout[2 * e + 1] = first[e];
-        for (uint32_t k = 0; 32u * k < n; ++k) {
-            const uint32_t t = tile0[e] + k;
+    uint32_t base_p = 0, base_t = 0;
+    for (uint32_t w = 0; w < warp; ++w) { base_p += warp_pairs[w]; base_t += warp_tiles[w]; }
+    const uint32_t first = base_p + sp - n, tile0 = base_t + st - nt;
+    if (tid == GROUP_THREADS - 1) total_tiles = base_t + st;
+    next_pos[tid] = first;
+    if (tid < a.experts) {
+        a.layout[2 * tid] = n;
+        a.layout[2 * tid + 1] = first;
+        for (uint32_t k = 0; k < nt; ++k) {
+            const uint32_t t = tile0 + k;
             if (t >= a.tile_capacity) { atomicCAS(a.status, 0, KERNEL_ERR_EXPERT_RANGE); break; }
-            const uint32_t nt = n - 32u * k < 32u ? n - 32u * k : 32u;
-            a.tiles[4 * t] = e; a.tiles[4 * t + 1] = first[e] + 32u * k;
-            a.tiles[4 * t + 2] = nt; a.tiles[4 * t + 3] = nt >= 2u ? 1u : 0u;
+            const uint32_t m = n - 32u * k < 32u ? n - 32u * k : 32u;
+            a.tiles[4 * t] = tid; a.tiles[4 * t + 1] = first + 32u * k; a.tiles[4 * t + 2] = m; a.tiles[4 * t + 3] = m >= 2u ? 1u : 0u;
         }
     }
-    for (uint32_t t = tile0[a.experts] + tid; t < a.tile_capacity; t += 256)
+    __syncthreads();
+    for (uint32_t t = total_tiles + tid; t < a.tile_capacity; t += GROUP_THREADS)
         a.tiles[4 * t] = a.tiles[4 * t + 1] = a.tiles[4 * t + 2] = a.tiles[4 * t + 3] = 0;
-}
-
-// One block per expert: threads own consecutive slices of the pair list, count
-// their matches, and write them after an exclusive scan, which keeps the pair
-// order ascending inside the expert.
-__global__ void __launch_bounds__(256) expert_pairs_kernel(const __grid_constant__ LayoutArgs a) {
-    pdl_prologue();
-    __shared__ uint32_t before[256];
-    const uint32_t e = blockIdx.x, tid = threadIdx.x;
-    if (a.layout[2 * e] == 0) return;
-    const uint32_t slice = (a.n_pairs + 255u) / 256u;
-    const uint32_t start = min(a.n_pairs, tid * slice), end = min(a.n_pairs, start + slice);
-    uint32_t mine = 0;
-    for (uint32_t i = start; i < end; ++i) mine += a.ids[i] == e;
-    before[tid] = mine;
-    __syncthreads();
-    if (tid == 0) {
-        uint32_t run = 0;
-        for (uint32_t k = 0; k < 256; ++k) { const uint32_t v = before[k]; before[k] = run; run += v; }
+    // stable placement: chunks of 512 pairs in order, the warps of a chunk one after the other
+    for (uint32_t i0 = 0; i0 < a.n_pairs; i0 += GROUP_THREADS) {
+        const uint32_t i = i0 + tid;
+        const uint32_t e = i < a.n_pairs ? a.ids[i] : 0xffffffffu;
+        const bool live = e < a.experts;
+        const uint32_t same = __match_any_sync(0xffffffffu, e);
+        const uint32_t rank = __popc(same & ((1u << lane) - 1u));
+        for (uint32_t w = 0; w < GROUP_THREADS / 32; ++w) {
+            if (warp == w && live) {
+                const uint32_t at = next_pos[e] + rank;
+                a.inverse[i] = at;
+                a.pairs[at] = i;
+            }
+            __syncwarp();
+            if (warp == w && live && rank == 0) next_pos[e] += __popc(same);
+            __syncthreads();
+        }
     }
-    __syncthreads();
-    uint32_t at = a.layout[2 * e + 1] + before[tid];
-    for (uint32_t i = start; i < end; ++i)
-        if (a.ids[i] == e) { a.inverse[i] = at; a.pairs[at++] = i; }
 }
 
 cudaError_t launch_expert_layout(const uint32_t *ids, uint32_t n_pairs, uint32_t experts, uint32_t tile_capacity,
                                  uint32_t *layout, uint32_t *tiles, uint32_t *pairs, uint32_t *inverse,
                                  const LaunchCtx &ctx) {
-    if (experts == 0 || experts > 4096) return cudaErrorInvalidValue;
+    if (experts == 0 || experts > GROUP_THREADS) return cudaErrorInvalidValue;
     LayoutArgs a = {ids, layout, tiles, pairs, inverse, n_pairs, experts, tile_capacity, ctx.status};
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1);
-    cfg.blockDim = dim3(256);
-    cfg.dynamicSmemBytes = (3 * experts + 1) * sizeof(uint32_t);
-    cfg.stream = ctx.stream;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, expert_layout_kernel, a);
-    if (e != cudaSuccess) return e;
-    LaunchCtx plain = ctx;
-    plain.pdl = false;
-    return launch(expert_pairs_kernel, dim3(experts), dim3(256), plain, a);
+    return launch(expert_group_kernel, dim3(1), dim3(GROUP_THREADS), ctx, a);
 }
 
 }  // namespace ingot

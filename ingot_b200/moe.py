@@ -88,6 +88,13 @@ class MoeChain:
         self.act = gpu.zeros(pairs * s.ffn)
         self.out = gpu.zeros(pairs * s.hidden)
         self.y = gpu.zeros(tokens * s.hidden)
+        # the expert grouping of the packed path (more than four tokens; Generic::moe_packed, src/generic.rs:578-660)
+        self.blocks = (pairs + 31) // 32 + s.experts
+        self.layout = gpu.empty_bytes(4 * 2 * s.experts)
+        self.tiles = gpu.empty_bytes(4 * 4 * self.blocks)
+        self.packed = gpu.empty_bytes(4 * pairs)
+        self.inverse = gpu.empty_bytes(4 * pairs)
+        self.grouped = True           # tokens > 4 take the grouped path on one device; False: pair by pair (comparison)
         self.launches_per_step = 0
 
     def layer(self, i: int) -> None:
@@ -104,6 +111,18 @@ class MoeChain:
             ids, w = self.ids_l, self.w_l
             n += 1
         tg, td = ws["gate"].t, ws["down"].t
+        if self.tokens > 4 and self.world == 1 and self.grouped:
+            # every expert touched is streamed once per four of its pairs, not once per pair
+            blocks = (pairs + 31) // 32 + s.experts
+            g._check(lib.ingot_expert_layout(h, ids.ptr, pairs, s.experts, blocks, self.layout.ptr, self.tiles.ptr, self.packed.ptr,
+                                             self.inverse.ptr))
+            g._check(lib.ingot_expert_gate_up(h, ws["gate"].buffer.ptr, ws["up"].buffer.ptr, tg.dims[0], tg.dims[1], tg.stride, tg.kind,
+                                              self.local, self.x.ptr, self.tiles.ptr, self.packed.ptr, blocks, s.top, pairs, self.act.ptr))
+            g._check(lib.ingot_expert_project(h, ws["down"].buffer.ptr, td.dims[0], td.dims[1], td.stride, td.kind, self.local,
+                                              self.act.ptr, self.tiles.ptr, self.packed.ptr, blocks, s.top, pairs, 0, self.out.ptr))
+            g._check(lib.ingot_combine_packed(h, self.out.ptr, w.ptr, self.inverse.ptr, s.hidden, s.top, self.tokens, self.y.ptr))
+            self.launches_per_step += 5
+            return
         g._check(lib.ingot_routed_gate_up(h, ws["gate"].buffer.ptr, ws["up"].buffer.ptr, tg.dims[0], tg.dims[1], tg.stride,
                                           tg.kind, self.local, self.x.ptr, F32, ids.ptr, s.top, pairs, self.act.ptr))
         g._check(lib.ingot_routed(h, ws["down"].buffer.ptr, td.dims[0], td.dims[1], td.stride, td.kind, self.local,

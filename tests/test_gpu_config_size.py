@@ -135,19 +135,27 @@ def test_moe_layer_at_128_experts(gpu, tokens):
     ids = gpu.read_u32(c.ids, tokens * s.top)
     wts = gpu.read_f32(c.w, tokens * s.top)
     ws = c.weights[0]
+    # more than four tokens take the grouped path: act and out are then in packed (expert-major) order
+    grouped = tokens > 4
+    place = gpu.read_u32(c.inverse, tokens * s.top) if grouped else np.arange(tokens * s.top)
+    if grouped:
+        layout, tiles, packed, inverse, n_tiles = O.expert_layout(ids, s.experts, c.blocks)
+        assert np.array_equal(place, inverse) and np.array_equal(gpu.read_u32(c.packed, tokens * s.top), packed)
+        assert np.array_equal(gpu.read_u32(c.tiles, 4 * c.blocks).reshape(-1, 4), tiles)
+        assert np.array_equal(gpu.read_u32(c.layout, 2 * s.experts).reshape(-1, 2), layout)
     for t in range(tokens):
         e_ids, e_w = O.route(logits[t], s.top)
         assert ids[t * s.top:(t + 1) * s.top].tolist() == e_ids.tolist()
         assert np.abs(wts[t * s.top:(t + 1) * s.top] - e_w).max() < 2e-6
         for j, k in enumerate(e_ids):
-            p = t * s.top + j
+            p = int(place[t * s.top + j])
             eg = O.matvec_f64(ws["gate_host"], s.hidden, s.ffn, Q4_K, x[t], expert=int(k))[0]
             eu = O.matvec_f64(ws["up_host"], s.hidden, s.ffn, Q4_K, x[t], expert=int(k))[0]
             ea = O.glu(eg.astype(np.float32), eu.astype(np.float32)).astype(np.float64)
             assert (np.abs(act[p] - ea) <= tol_contract(ea)).all(), (t, j)
             ed = O.matvec_f64(ws["down_host"], s.ffn, s.hidden, Q4_K, act[p], expert=int(k))[0]      # the input the GPU's down projection read
             assert (np.abs(out[p] - ed) <= tol_ref_scaled(ed)).all(), (t, j)
-        e_y = O.moe_sum(out[t * s.top:(t + 1) * s.top], wts[t * s.top:(t + 1) * s.top], s.hidden, s.top)[0]
+        e_y = O.moe_sum(out[place[t * s.top:(t + 1) * s.top]], wts[t * s.top:(t + 1) * s.top], s.hidden, s.top)[0]
         assert np.abs(y[t] - e_y).max() <= 1e-6 * max(1.0, float(np.abs(e_y).max()))
 
 
@@ -180,3 +188,38 @@ def test_gemm_at_config_size_on_sampled_rows(gpu, kind, cols, rows, tokens):
     scale = float(np.sqrt(np.mean(np.square(one))))
     assert np.abs(y[0] - one).max() <= 2e-3 * scale
     w.release()
+
+
+def test_expert_projection_tile_tails(gpu):
+    # the reference's tile fixture (src/metal/tests.rs:923-925, 2755-2776): tiles [expert, first, n, mode] =
+    # [1,3,7,0] [0,10,16,1] [1,26,9,1] [0,35,1,1] [0,36,32,1] [1,68,19,1] over packed rows, pairs in reversed order;
+    # packed rows outside the tiles stay as they were (zero), the others meet the f64 dot
+    cols, rows, experts, top = 512, 65, 2, 2
+    tiles = np.array([[1, 3, 7, 0], [0, 10, 16, 1], [1, 26, 9, 1], [0, 35, 1, 1], [0, 36, 32, 1], [1, 68, 19, 1], [0, 0, 0, 0]], np.uint32)
+    total = 87
+    pairs = np.arange(total, dtype=np.uint32)[::-1].copy()            # packed position q holds pair total - 1 - q
+    raw = synth.random_matrix(Q4_K, cols, rows, experts, seed=60)
+    w = gpu.bytes(raw)
+    stride = synth.stride_of(Q4_K, cols)
+    for gather in (1, 0):
+        n_rows = (total + top - 1) // top if gather else total
+        x = (synth.activations(n_rows, cols, seed=61 + gather) * np.float32(0.05)).astype(np.float32)
+        y, xb, tb, pb = gpu.zeros(total * rows), gpu.floats(x), gpu.bytes(tiles), gpu.bytes(pairs)       # kept alive until the launch has run
+        gpu._check(gpu._lib.ingot_expert_project(gpu._h, w.ptr, cols, rows, stride, Q4_K, experts, xb.ptr, tb.ptr, pb.ptr, len(tiles), top,
+                                                 total, gather, y.ptr))
+        got = gpu.finish(None, y).reshape(total, rows)
+        covered = np.zeros(total, bool)
+        for e, first, n, _ in tiles:
+            for q in range(first, first + n):
+                covered[q] = True
+                src = int(pairs[q]) // top if gather else q
+                want = O.matvec_f64(raw, cols, rows, Q4_K, x[src], expert=int(e))[0]
+                assert (np.abs(got[q] - want) <= tol_ref_scaled(want)).all(), (gather, q)
+        assert not got[~covered].any()
+    # an expert id beyond the matrix is an error code, not a fault
+    bad = np.array([[2, 0, 1, 0]], np.uint32)
+    xb, tb, pb, yb = gpu.zeros(cols), gpu.bytes(bad), gpu.bytes(pairs), gpu.zeros(total * rows)
+    gpu._check(gpu._lib.ingot_expert_project(gpu._h, w.ptr, cols, rows, stride, Q4_K, experts, xb.ptr, tb.ptr, pb.ptr, 1, top, total, 0, yb.ptr))
+    from ingot_b200 import InvalidData
+    with pytest.raises(InvalidData):
+        gpu.complete()
