@@ -215,6 +215,9 @@ def main():
     ap.add_argument("--fused-norm", type=int, default=1, help="0: add_rms as separate launches (comparison)")
     ap.add_argument("--chain", type=int, default=0,
                     help="1: the one-token step of a single GPU runs as one persistent kernel (ingot_chain_*); 0: one launch per projection, replayed as a CUDA graph")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: peer = the projections store their row shards as tagged words into every rank's window "
+                         "(ingot_group_*); nccl = one NCCL all-gather after each projection (comparison)")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of layer 0 and the logits after the timed region")
     ap.add_argument("--group-scope", type=int, default=1,
                     help="0: the projections of an independent scope on their own streams instead of one grid (comparison)")
@@ -279,7 +282,18 @@ def main():
         dst = _tensor_view(torch, full.ptr, n * world, local)
         dist.all_gather_into_tensor(dst, src)
 
-    chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, rank=rank, world=world,
+    group = None
+    if world > 1 and args.exchange == "peer" and args.fused_norm and args.batch == 1:
+        from ingot_b200.gpu import Group
+        n_layers = shape.layers if args.layers is None else args.layers
+        window = 4 * args.batch * (shape.q + 2 * shape.hidden + shape.ffn + shape.vocab) + 8 * 256
+        group = Group(gpu, rank, world, window, DecodeChain.exchange_slots(n_layers))
+        mine = torch.frombuffer(bytearray(group.handle), dtype=torch.uint8).to(f"cuda:{local}")
+        everyone = torch.empty(64 * world, dtype=torch.uint8, device=f"cuda:{local}")
+        dist.all_gather_into_tensor(everyone, mine)               # the IPC handles travel over the process group; nothing else does
+        group.connect(bytes(everyone.cpu().numpy()))
+        dist.barrier()
+    chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, rank=rank, world=world, group=group,
                         all_gather=all_gather if world > 1 else None, layers=args.layers, packed=not args.no_mma, fused_norm=bool(args.fused_norm),
                         keep_host=1 if (rank == 0 and world == 1 and not (args.no_cpu and args.no_parity)) else 0)
     h0 = np.random.default_rng(1).normal(0, 1, (args.batch, shape.hidden)).astype(np.float32)
@@ -295,6 +309,12 @@ def main():
         fused = chain.record_chain()
         graph = None
     elif world == 1:
+        graph = chain.record() if args.graph else None
+    elif group is not None:
+        # no collective inside the step: the library records it itself.  One eager step first, all ranks in step.
+        chain.step()
+        gpu.complete()
+        dist.barrier()
         graph = chain.record() if args.graph else None
     else:
         # the step contains NCCL all-gathers: let torch record it (its NCCL bindings join the
@@ -407,7 +427,9 @@ def main():
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(shape, args.batch, chain.n_layers, world, total_bytes, args.activations),
             "launch_mode": ("one persistent kernel per step (chain of %(projections)d projections, %(waits)d grid-wide waits, %(stages)d stages of %(stage_bytes)d bytes per SM)" % fused.info())
-                                 if fused is not None else "one recorded command (CUDA graph) per step" + (" incl. NCCL all-gathers" if world > 1 else ""),
+                                 if fused is not None else "one recorded command (CUDA graph) per step" + (
+                                 " incl. NCCL all-gathers" if world > 1 and group is None else
+                                 "; row shards exchanged by the projections themselves (tagged 8-byte words stored into every rank's window, polled by the next projection)" if world > 1 else ""),
             "hbm_gbs_effective": total_bytes / world / (ms_per_step * 1e-3) / 1e9,
             "hbm_frac_of_peak_chain": total_bytes / world / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "e2e": {"value": args.batch * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,

@@ -403,6 +403,49 @@ INGOT_API ingot_status ingot_command_end(ingot_gpu *gpu, ingot_graph **out);
 INGOT_API ingot_status ingot_command_submit(ingot_gpu *gpu, ingot_graph *graph);
 INGOT_API void ingot_command_destroy(ingot_graph *graph);
 
+/* ---- tensor-parallel groups: output rows sharded over the GPUs of one node -------------
+ * No counterpart in the reference, whose Gpu owns one device (src/metal.rs:193-208).  Rank r of
+ * `world` owns rows [r N / world, (r + 1) N / world) of every matrix (block quantisation runs
+ * along K, so a row split keeps the GGUF layout).  Every rank has a WINDOW of device memory that
+ * the other ranks can write: the activation vectors that have to be whole on every rank live
+ * there, at the same offset on every rank, and each has a TAGGED TWIN behind the window: one
+ * 8-byte word {value, tag} per element, the tag naming the step and the slot.  A fused-norm
+ * projection marked with ingot_tp_signal_next stores its rows as plain floats where it was told
+ * AND as tagged words, each with one 8-byte store, into the twin of every rank (over NVLink for
+ * the peers).  A projection marked with ingot_tp_wait_next reads the awaited inputs from their
+ * twins and polls each word until it carries this step's tag — with a time limit, reported as
+ * INGOT_TIMEOUT by ingot_synchronize.  A word arrives whole or not at all, so the exchange needs
+ * no fence, flag or counter, and no collective launch sits between two projections: it is the
+ * epilogue of one kernel and the prologue of the next.  Every slot is signalled by exactly one
+ * projection per step; ingot_group_step (once per step, first) advances the step counter.  The
+ * plain copy of an exchanged vector holds only the own rows until ingot_group_wait fills it.
+ *
+ * One process per GPU: ingot_group_create returns 64 bytes (a CUDA IPC handle); gather the
+ * handles of all ranks by any means (MPI, torch.distributed, a file) and pass the world x 64
+ * bytes to ingot_group_connect.  One process driving several GPUs: create the groups, then
+ * ingot_group_connect_local(groups, world).  A rank's kernels never wait for kernels of the
+ * same GPU: do not put two ranks of a group on one device. */
+typedef struct ingot_group ingot_group;
+INGOT_API ingot_status ingot_group_create(ingot_gpu *gpu, uint32_t rank, uint32_t world, size_t window_bytes,
+                                          uint32_t slots, ingot_group **out, void *handle64);
+INGOT_API ingot_status ingot_group_connect(ingot_group *group, const void *handles);
+INGOT_API ingot_status ingot_group_connect_local(ingot_group **groups, uint32_t world);
+/* Base address of rank `rank`'s window as this process sees it (the own window: a device pointer
+ * to allocate the shared activation vectors in; window_bytes of it are the caller's). */
+INGOT_API ingot_status ingot_group_window(const ingot_group *group, uint32_t rank, void **base);
+INGOT_API ingot_status ingot_group_step(ingot_group *group);
+/* Enqueues a kernel that waits (time-limited) for every rank's rows of `slot` in this step and
+ * copies them out of the twin into the plain vector `whole` (n floats, inside the own window):
+ * what a reader outside the fused projections (attention, the sampler, the host) needs. */
+INGOT_API ingot_status ingot_group_wait(ingot_group *group, uint32_t slot, float *whole, uint32_t n);
+/* The next ingot_matmul_normed / ingot_gate_up_normed on the group's handle: its output (which
+ * must lie inside the own window) also goes, tagged with `slot`, to the twin on every rank. */
+INGOT_API ingot_status ingot_tp_signal_next(ingot_group *group, uint32_t slot);
+/* The next fused-norm projection reads the vectors of slot_a and, unless 0xffffffff, slot_b from
+ * their twins; each must be one of its two normalised inputs (the whole vector, in the window). */
+INGOT_API ingot_status ingot_tp_wait_next(ingot_group *group, uint32_t slot_a, uint32_t slot_b);
+INGOT_API void ingot_group_destroy(ingot_group *group);
+
 /* ---- chains: a whole decode step as ONE kernel -----------------------------
  * The reference encodes a token's operators into one command buffer
  * (src/generic.rs:701-704) and Metal runs them back to back.  On B200 a chain of short,

@@ -82,6 +82,14 @@ SIGNATURES = {
     "ingot_gguf_rows": [vp, C.c_char_p, vp, u64, vp],
     "ingot_gguf_matrix": [vp, C.c_char_p, vp, u32, vp, u64, vp],
     "ingot_weight_load": [vp, vp, C.c_char_p, vp, u32, C.POINTER(vp), vp],
+    "ingot_group_create": [vp, u32, u32, sz, u32, C.POINTER(vp), vp],
+    "ingot_group_connect": [vp, vp],
+    "ingot_group_connect_local": [C.POINTER(vp), u32],
+    "ingot_group_window": [vp, u32, C.POINTER(vp)],
+    "ingot_group_step": [vp],
+    "ingot_group_wait": [vp, u32, vp, u32],
+    "ingot_tp_signal_next": [vp, u32],
+    "ingot_tp_wait_next": [vp, u32, u32],
     "ingot_chain_begin": [vp],
     "ingot_chain_end": [vp, C.POINTER(vp)],
     "ingot_chain_submit": [vp, vp],
@@ -98,6 +106,7 @@ OTHER = {
     "ingot_last_error": (C.c_char_p, [vp]),
     "ingot_command_destroy": (None, [vp]),
     "ingot_chain_destroy": (None, [vp]),
+    "ingot_group_destroy": (None, [vp]),
     "ingot_gguf_close": (None, [vp]),
     "ingot_gguf_last_error": (C.c_char_p, []),
     "ingot_gguf_architecture": (C.c_char_p, [vp]),

@@ -52,6 +52,8 @@ class FusedOp:
     shard_only: bool = False      # row shards: nobody reads the whole vector, the shard stays at the front of y
     gather_late: bool = False     # row shards: gathered after the operator's scope has closed
     gelu: bool = False
+    signal: int | None = None     # row shards with a group: the exchange slot this operator's rows raise on every rank
+    waits: tuple = ()             # ... and the slots of the assembled inputs it waits for
 
 
 QWEN3_8B = DenseShape("qwen3-8b-q4_k_m", 36, 4096, 4096, 1024, 12288, 151936,
@@ -97,9 +99,12 @@ class DecodeChain:
 
     def __init__(self, gpu: Gpu, shape: DenseShape, batch: int = 1, x_kind: int = BF16, seed: int = 0,
                  rank: int = 0, world: int = 1, all_gather=None, layers: int | None = None,
-                 keep_host: int = 0, packed: bool = True, independent_qkv: bool = True, fused_norm: bool = True):
+                 keep_host: int = 0, packed: bool = True, independent_qkv: bool = True, fused_norm: bool = True, group=None):
         self.gpu, self.shape, self.batch, self.x_kind = gpu, shape, batch, x_kind
         self.rank, self.world, self.all_gather = rank, world, all_gather
+        # a tensor-parallel group (gpu.Group): the projections exchange their row shards themselves (peer stores and
+        # arrival counters) instead of an all-gather after each of them
+        self.group = group if world > 1 else None
         self.n_layers = shape.layers if layers is None else layers
         self.host = {}                 # (layer, role) -> (bytes, cols, rows, kind) kept for checks/baselines
         self.weights: list[dict[str, Weight]] = []
@@ -116,13 +121,14 @@ class DecodeChain:
         self.h_in = gpu.zeros(b * h)                  # the step's input hidden state (float32)
         self.h = gpu.zeros(b * h)                     # residual stream
         self.xn = gpu.empty_bytes(b * h * xb)
-        self.q, self.k, self.v = gpu.zeros(b * shape.q), gpu.zeros(b * shape.kv), gpu.zeros(b * shape.kv)
+        shared = self.group.alloc if self.group else gpu.zeros        # vectors every rank needs whole live in the group's window
+        self.q, self.k, self.v = shared(b * shape.q), gpu.zeros(b * shape.kv), gpu.zeros(b * shape.kv)
         self.a = gpu.empty_bytes(b * shape.q * xb)
-        self.o = gpu.zeros(b * h)
-        self.act = gpu.zeros(b * shape.ffn)
+        self.o = shared(b * h)
+        self.act = shared(b * shape.ffn)
         self.actn = gpu.empty_bytes(b * shape.ffn * xb)
-        self.d = gpu.zeros(b * h)
-        self.logits = gpu.zeros(b * shape.vocab)
+        self.d = shared(b * h)
+        self.logits = shared(b * shape.vocab)
         # per-rank partial outputs when sharded
         self.part = gpu.zeros(b * max(shape.ffn, shape.vocab) // world + b * 8) if world > 1 else None
         # activations packed once per distinct GEMV input (one token: the tensor-core GEMV)
@@ -231,13 +237,36 @@ class DecodeChain:
             ops.append(FusedOp("down", li, ws["down"], None, self.act, None, None, self.d))
             delta = self.d
         ops.append(FusedOp("head", self.n_layers, self.head, None, cur, delta, None, self.logits))
+        if self.group:
+            # one exchange slot per operator whose rows every rank needs; an operator waits for the slots of the
+            # vectors among its inputs that were assembled that way (the latest writer of each)
+            slot_of: dict[int, int] = {}
+            n = 0
+            for op in ops:
+                op.waits = tuple(slot_of[x.ptr] for x in (op.a, op.b) if x is not None and x.ptr in slot_of)
+                if not op.shard_only:
+                    op.signal, n = n, n + 1
+                    slot_of[op.y.ptr] = op.signal
         return ops
+
+    @staticmethod
+    def exchange_slots(layers: int) -> int:
+        """Slots a group needs for this chain: q, o, gate/up and down of every layer, and the head."""
+        return 4 * layers + 1
 
     def issue(self, op: "FusedOp") -> None:
         """Issues one fused operator (and, on a row shard, the gather of its result)."""
         g, t = self.gpu, op.w.t
         sharded = self.world > 1 and not op.shard_only
         dst = self.part if sharded else op.y           # every rank norms the whole input itself
+        if self.group:
+            # the rows go straight to their place in the whole vector, here and on every peer
+            r0, _ = shard_rows(self._full_rows(op), self.rank, self.world)
+            dst = op.y if op.shard_only else op.y.view_f32(r0, t.dims[1])
+            if op.signal is not None:
+                self.group.signal_next(op.signal)
+            if op.waits:
+                self.group.wait_next(*op.waits)
         a, b, sm = op.a.ptr, op.b.ptr if op.b else None, op.s.ptr if op.s else None
         rb = int(self.x_kind == BF16)
         if op.w2 is None:
@@ -247,12 +276,20 @@ class DecodeChain:
             g._check(g._lib.ingot_gate_up_normed(g._h, op.w.buffer.ptr, op.w2.buffer.ptr, t.dims[0], t.dims[1], t.stride,
                                                  t.kind, a, b, None, sm, 1e-6, 1 if op.b else 0, rb, int(op.gelu), dst.ptr))
         self.launches_per_step += 1
-        if sharded and not op.gather_late:
+        if sharded and not op.gather_late and not self.group:
             self.all_gather(dst, op.y, self.batch, t.dims[1])
+
+    def _full_rows(self, op: "FusedOp") -> int:
+        """Rows of the operator's whole (unsharded) output."""
+        s = self.shape
+        return {"q": s.q, "k": s.kv, "v": s.kv, "o": s.hidden, "gate_up": s.ffn, "down": s.hidden, "head": s.vocab}[op.name]
 
     def _step_fused(self) -> None:
         g = self.gpu
         self.launches_per_step = 0
+        if self.group:
+            self.group.step()
+            self.launches_per_step += 1
         ops = self.fused_ops()
         i = 0
         while i < len(ops):
@@ -264,11 +301,14 @@ class DecodeChain:
                 for op in ops[i:j]:
                     self.issue(op)
             for op in ops[i:j]:
-                if self.world > 1 and op.gather_late and not op.shard_only:
+                if self.world > 1 and op.gather_late and not op.shard_only and not self.group:
                     self.all_gather(self.part, op.y, self.batch, op.w.t.dims[1])
             if j - i > 1:
                 self.launches_per_step -= j - i - 1      # the scope issues its projections as one grid
             i = j
+        if self.group:
+            self.group.wait(ops[-1].signal, ops[-1].y)   # the logits of every rank, for whoever reads them after the step
+            self.launches_per_step += 1
 
     def step(self) -> None:
         """Issues one token step on the handle's stream (asynchronous)."""

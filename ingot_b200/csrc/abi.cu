@@ -42,10 +42,29 @@ struct ingot_gpu {
     int scope_next = 0;               // stream of the next launch inside the scope: 0 = main, i > 0 = side[i - 1]
     int scope_used = 0;               // side streams touched in this scope (bit mask)
     std::vector<GemvCall> pending;    // one-token tensor-core projections of the open scope: they share one launch at its end
+    // links of the next fused-norm projection to a tensor-parallel group (ingot_tp_signal_next / ingot_tp_wait_next)
+    ingot_group *tp_signal_group = nullptr, *tp_wait_group = nullptr;
+    uint32_t tp_signal_slot = 0, tp_wait_slot[2] = {0, 0};
     bool chain_recording = false;     // fused-norm projections are being collected for one persistent kernel
     std::vector<GemvCall> chain_calls;
     std::string error;
 };
+
+// A tensor-parallel group as one rank sees it: its window (the activations other ranks write into, then a
+// control area: the step counter and one arrival counter per exchange slot) and the other ranks' windows.
+struct ingot_group {
+    ingot_gpu *gpu = nullptr;
+    uint32_t rank = 0, world = 1, slots = 0;
+    // the allocation: the window of plain vectors | the tagged twins (8 bytes per float of the window) | the step counter
+    size_t window_bytes = 0, twin_off = 0, ctrl_off = 0, total_bytes = 0;
+    uint8_t *peer[TP_MAX_RANKS] = {};                 // base of every rank's window; peer[rank] is the own one
+    bool opened[TP_MAX_RANKS] = {};                   // mapped through an IPC handle (closed again on destroy)
+    struct Shard { size_t off = 0; uint32_t rows = 0; };
+    std::vector<Shard> shard;                         // per slot: where this rank's rows of the slot's vector lie (known once its projection was issued)
+    uint32_t *step_counter() const { return reinterpret_cast<uint32_t *>(peer[rank] + ctrl_off); }
+    uint64_t *twin(uint32_t r, size_t off) const { return reinterpret_cast<uint64_t *>(peer[r] + twin_off + 2u * off); }
+};
+static constexpr uint32_t TP_NO_SLOT = 0xffffffffu;
 
 struct ingot_chain {
     ChainLaunch launch;
@@ -260,6 +279,7 @@ ingot_status ingot_synchronize(ingot_gpu *g) {
     case KERNEL_ERR_CONSUMER_TIMEOUT: return fail(g, INGOT_TIMEOUT, "GEMV consumer wait ran out");
     case KERNEL_ERR_GEMM_TIMEOUT: return fail(g, INGOT_TIMEOUT, "GEMM pipeline wait ran out");
     case KERNEL_ERR_CHAIN_TIMEOUT: return fail(g, INGOT_TIMEOUT, "chain kernel: a projection never saw the one it depends on finish");
+    case KERNEL_ERR_PEER_TIMEOUT: return fail(g, INGOT_TIMEOUT, "row-sharded projection: a rank's shard of the input never arrived");
     default: return fail(g, INGOT_DEVICE, "unknown device status " + std::to_string(code));
     }
 }
@@ -507,6 +527,52 @@ ingot_status ingot_gate_up(ingot_gpu *g, const void *gate, const void *up, uint3
     return gemv_common(g, c, x_kind, "gate_up");
 }
 
+// Consumes the links ingot_tp_signal_next / ingot_tp_wait_next set for this projection.
+static ingot_status apply_tp_links(ingot_gpu *g, GemvCall &c, const float *a, const float *b, const char *what) {
+    ingot_group *sg = g->tp_signal_group, *wg = g->tp_wait_group;
+    g->tp_signal_group = g->tp_wait_group = nullptr;
+    if (sg) {
+        const uint8_t *base = sg->peer[sg->rank];
+        const uint8_t *y = reinterpret_cast<const uint8_t *>(c.y);
+        if (y < base || y + (size_t)c.rows * 4u > base + sg->window_bytes || ((size_t)(y - base) % 4u))
+            return fail(g, INGOT_INVALID, std::string(what) + ": the output of a signalling projection must lie inside the group's window");
+        const size_t off = (size_t)(y - base);
+        for (uint32_t r = 0; r < sg->world; ++r) {
+            if (!sg->peer[r]) return fail(g, INGOT_INVALID, std::string(what) + ": the group is not connected");
+            c.tp.out[r] = sg->twin(r, off);
+        }
+        c.tp.n_out = sg->world;
+        c.tp.out_tag = g->tp_signal_slot + 1u;
+        c.tp.tag_mul = sg->slots + 1u;
+        c.tp.step = sg->step_counter();
+        sg->shard[g->tp_signal_slot] = {off, c.rows};
+    }
+    if (wg) {
+        const uint8_t *base = wg->peer[wg->rank];
+        const float *in[2] = {a, b};
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t slot = g->tp_wait_slot[i];
+            if (slot == TP_NO_SLOT) continue;
+            const ingot_group::Shard &sh = wg->shard[slot];
+            if (sh.rows == 0) return fail(g, INGOT_INVALID, std::string(what) + ": waits for a slot no projection has signalled yet");
+            // which of the two normalised inputs the slot's vector is: the one that contains this rank's rows of it
+            int k = -1;
+            for (int v = 0; v < 2 && k < 0; ++v) {
+                const uint8_t *x = reinterpret_cast<const uint8_t *>(in[v]);
+                if (x && x >= base && x + (size_t)c.cols * 4u <= base + wg->window_bytes && (size_t)(x - base) <= sh.off &&
+                    sh.off + (size_t)sh.rows * 4u <= (size_t)(x - base) + (size_t)c.cols * 4u && !c.tp.in[v])
+                    k = v;
+            }
+            if (k < 0) return fail(g, INGOT_INVALID, std::string(what) + ": the awaited slot's vector is not one of this projection's inputs");
+            c.tp.in[k] = wg->twin(wg->rank, (size_t)(reinterpret_cast<const uint8_t *>(in[k]) - base));
+            c.tp.in_tag[k] = slot + 1u;
+        }
+        c.tp.tag_mul = wg->slots + 1u;
+        c.tp.step = wg->step_counter();
+    }
+    return INGOT_OK;
+}
+
 // add_rms fused into the projection that consumes it (one token, tensor-core GEMV only).
 static ingot_status normed_common(ingot_gpu *g, GemvCall &c, const float *a, const float *b, const float *norm_w, float *s,
                                   float eps, uint32_t add, uint32_t round_bf16, const char *what) {
@@ -520,7 +586,9 @@ static ingot_status normed_common(ingot_gpu *g, GemvCall &c, const float *a, con
     c.norm_a = a; c.norm_b = add ? b : nullptr; c.norm_w = norm_w; c.norm_s = add ? s : nullptr;
     c.norm_eps = eps; c.norm_round_bf16 = round_bf16;
     c.count = 1;
+    if ((st = apply_tp_links(g, c, a, add ? b : nullptr, what))) return st;
     if (g->chain_recording) {
+        if (c.tp.n_out || c.tp.in[0] || c.tp.in[1]) return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": tensor-parallel links cannot be recorded into a chain");
         if (g->no_mma || g->force_plain || !chain_call_eligible(c))
             return fail(g, INGOT_UNSUPPORTED, std::string(what) + ": this projection cannot be part of a chain (weight type, alignment or shape)");
         g->chain_calls.push_back(c);
@@ -819,6 +887,135 @@ ingot_status ingot_independent_end(ingot_gpu *g) {
         if (e != cudaSuccess) return cuda_fail(g, e, "independent scope join");
     }
     return st;
+}
+
+// ---- tensor-parallel groups: row shards over several GPUs, exchanged by the projections themselves ----
+
+ingot_status ingot_group_create(ingot_gpu *g, uint32_t rank, uint32_t world, size_t window_bytes, uint32_t slots, ingot_group **out,
+                                void *handle64) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!out || world == 0 || world > TP_MAX_RANKS || rank >= world || slots == 0) return fail(g, INGOT_INVALID, "group_create: bad arguments");
+    *out = nullptr;
+    ingot_group *gr = new (std::nothrow) ingot_group();
+    if (!gr) return fail(g, INGOT_DEVICE, "out of host memory");
+    gr->gpu = g; gr->rank = rank; gr->world = world; gr->slots = slots;
+    gr->window_bytes = window_bytes;
+    gr->twin_off = (window_bytes + 255u) & ~(size_t)255u;
+    gr->ctrl_off = gr->twin_off + 2u * gr->twin_off;
+    gr->total_bytes = gr->ctrl_off + 256u;
+    gr->shard.assign(slots, {});
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, gr->total_bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, gr->total_bytes);
+    if (e == cudaSuccess && handle64) {
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+        e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle64), p);
+    }
+    if (e != cudaSuccess) {
+        if (p) cudaFree(p);
+        delete gr;
+        if (e == cudaErrorMemoryAllocation) { cudaGetLastError(); return fail(g, INGOT_INVALID, "out of device memory"); }
+        return cuda_fail(g, e, "group_create");
+    }
+    gr->peer[rank] = static_cast<uint8_t *>(p);
+    *out = gr;
+    return INGOT_OK;
+}
+
+ingot_status ingot_group_connect(ingot_group *gr, const void *handles) {
+    if (!gr || !handles) return INGOT_INVALID;
+    ingot_gpu *g = gr->gpu;
+    ingot_status st = enter(g);
+    if (st) return st;
+    for (uint32_t r = 0; r < gr->world; ++r) {
+        if (r == gr->rank || gr->peer[r]) continue;
+        void *p = nullptr;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const uint8_t *>(handles) + 64u * r, 64);
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) { cudaGetLastError(); return fail(g, INGOT_DEVICE, std::string("group_connect: cannot map the window of rank ") + std::to_string(r) + ": " + cudaGetErrorString(e)); }
+        gr->peer[r] = static_cast<uint8_t *>(p);
+        gr->opened[r] = true;
+    }
+    return INGOT_OK;
+}
+
+ingot_status ingot_group_connect_local(ingot_group **groups, uint32_t world) {
+    if (!groups || world == 0 || world > TP_MAX_RANKS) return INGOT_INVALID;
+    for (uint32_t a = 0; a < world; ++a) {
+        ingot_group *ga = groups[a];
+        if (!ga || ga->world != world || ga->rank != a) return INGOT_INVALID;
+        if (cudaSetDevice(ga->gpu->device) != cudaSuccess) return INGOT_DEVICE;
+        for (uint32_t b = 0; b < world; ++b) {
+            if (a == b) continue;
+            if (groups[b]->gpu->device != ga->gpu->device) {
+                cudaError_t e = cudaDeviceEnablePeerAccess(groups[b]->gpu->device, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+                else if (e != cudaSuccess) { cudaGetLastError(); return fail(ga->gpu, INGOT_DEVICE, std::string("group_connect_local: ") + cudaGetErrorString(e)); }
+            }
+            ga->peer[b] = groups[b]->peer[b];
+        }
+    }
+    return INGOT_OK;
+}
+
+ingot_status ingot_group_window(const ingot_group *gr, uint32_t rank, void **base) {
+    if (!gr || !base || rank >= gr->world || !gr->peer[rank]) return INGOT_INVALID;
+    *base = gr->peer[rank];
+    return INGOT_OK;
+}
+
+ingot_status ingot_group_step(ingot_group *gr) {
+    if (!gr) return INGOT_INVALID;
+    ingot_gpu *g = gr->gpu;
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->in_scope || g->chain_recording) return fail(g, INGOT_INVALID, "group_step: not inside an independent scope or a chain recording");
+    return after_launch(g, launch_increment(gr->step_counter(), ctx_on(g, g->stream)), "group_step");
+}
+
+ingot_status ingot_group_wait(ingot_group *gr, uint32_t slot, float *whole, uint32_t n) {
+    if (!gr || slot >= gr->slots) return INGOT_INVALID;
+    ingot_gpu *g = gr->gpu;
+    ingot_status st = enter(g);
+    if (st) return st;
+    const ingot_group::Shard &sh = gr->shard[slot];
+    if (sh.rows == 0) return fail(g, INGOT_INVALID, "group_wait: no projection has signalled this slot yet");
+    const uint8_t *base = gr->peer[gr->rank], *x = reinterpret_cast<const uint8_t *>(whole);
+    if (!whole || x < base || x + (size_t)n * 4u > base + gr->window_bytes || (size_t)(x - base) > sh.off ||
+        sh.off + (size_t)sh.rows * 4u > (size_t)(x - base) + (size_t)n * 4u)
+        return fail(g, INGOT_INVALID, "group_wait: the vector must lie inside the window and contain this rank's rows of the slot");
+    return after_launch(g, launch_collect_tagged(gr->twin(gr->rank, (size_t)(x - base)), whole, n, gr->step_counter(), gr->slots + 1u, slot + 1u,
+                                                 ctx_on(g, g->stream)),
+                        "group_wait");
+}
+
+ingot_status ingot_tp_signal_next(ingot_group *gr, uint32_t slot) {
+    if (!gr || slot >= gr->slots) return INGOT_INVALID;
+    gr->gpu->tp_signal_group = gr;
+    gr->gpu->tp_signal_slot = slot;
+    return INGOT_OK;
+}
+
+ingot_status ingot_tp_wait_next(ingot_group *gr, uint32_t slot_a, uint32_t slot_b) {
+    if (!gr || slot_a >= gr->slots || (slot_b != TP_NO_SLOT && slot_b >= gr->slots)) return INGOT_INVALID;
+    gr->gpu->tp_wait_group = gr;
+    gr->gpu->tp_wait_slot[0] = slot_a;
+    gr->gpu->tp_wait_slot[1] = slot_b;
+    return INGOT_OK;
+}
+
+void ingot_group_destroy(ingot_group *gr) {
+    if (!gr) return;
+    cudaSetDevice(gr->gpu->device);
+    cudaStreamSynchronize(gr->gpu->stream);
+    for (uint32_t r = 0; r < gr->world; ++r)
+        if (gr->opened[r]) cudaIpcCloseMemHandle(gr->peer[r]);
+    if (gr->peer[gr->rank]) cudaFree(gr->peer[gr->rank]);
+    if (gr->gpu->tp_signal_group == gr) gr->gpu->tp_signal_group = nullptr;
+    if (gr->gpu->tp_wait_group == gr) gr->gpu->tp_wait_group = nullptr;
+    delete gr;
 }
 
 // ---- chains: a sequence of fused-norm projections as one persistent kernel ------------

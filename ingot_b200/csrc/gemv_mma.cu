@@ -111,6 +111,10 @@ struct MmaArgs {
     // optional tensor maps (device memory) of the matrices as rows of 8-byte elements, in boxes of
     // (row_pitch / 8) x (16 row_tiles): a stage then arrives by one tiled copy instead of one copy per row
     const void *tmap[2];
+    // row shards over several GPUs (tensor parallel): the results are also stored into the same place of
+    // every peer's window, then every CTA raises a counter on every rank; a projection whose inputs are
+    // assembled that way waits, with a time limit, until its own counters have reached step x arrivals
+    TpLink tp;
 };
 
 static bool mma_kind(uint32_t kind) { return kind == KIND_Q4_K || kind == KIND_Q6_K || kind == KIND_Q4_0 || kind == KIND_Q8_0; }
@@ -746,6 +750,16 @@ template <> struct ImmaStep<KIND_Q8_0> {
 // kernel
 // ---------------------------------------------------------------------------
 
+// Four elements of a tagged vector: two 16-byte loads of two {value, tag} words each (every 8-byte word is read
+// whole).  False unless all four carry the tag.
+__device__ __forceinline__ bool tagged_load4(const uint64_t *tagged, uint32_t j, uint32_t tag, float4 &v) {
+    uint64_t w0, w1, w2, w3;
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(tagged + 4u * (size_t)j) : "memory");
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w2), "=l"(w3) : "l"(tagged + 4u * (size_t)j + 2u) : "memory");
+    v = make_float4(__uint_as_float((uint32_t)w0), __uint_as_float((uint32_t)w1), __uint_as_float((uint32_t)w2), __uint_as_float((uint32_t)w3));
+    return (uint32_t)(w0 >> 32) == tag && (uint32_t)(w1 >> 32) == tag && (uint32_t)(w2 >> 32) == tag && (uint32_t)(w3 >> 32) == tag;
+}
+
 // What a thread carries from one projection to the next when a kernel runs several of them
 // back to back over the same ring (the one-projection kernels use a fresh one).
 struct MmaRun {
@@ -922,6 +936,26 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         // kernels/generic.metal:390-404): the 256 consumer threads of every CTA build the packed row ----
         ptx::pdl_wait();
         const uint32_t tid = threadIdx.x, n4 = p.cols >> 2;
+        // inputs assembled from every rank's rows are read from their tagged twins, polling until each word carries
+        // this step's tag (bounded; on a time-out the step goes on with what is there and the status word tells)
+        const uint64_t *const ta = a.tp.in[0], *const tb = a.tp.in[1];
+        uint32_t tag_a = 0, tag_b = 0;
+        if (ta || tb) {
+            const uint32_t step = *reinterpret_cast<const volatile uint32_t *>(a.tp.step);
+            tag_a = step * a.tp.tag_mul + a.tp.in_tag[0];
+            tag_b = step * a.tp.tag_mul + a.tp.in_tag[1];
+        }
+        // (a wait that ran out earlier in the step has set the status word: do not wait again)
+        bool gave_up = (ta || tb) && a.status && *reinterpret_cast<const volatile int *>(a.status) != 0;
+        auto poll = [&](auto pass) {                   // pass() issues a batch of loads and says whether all were this step's
+            uint64_t t0 = 0;
+            for (uint32_t spins = 1; !pass() && !gave_up; ++spins) {
+                if ((spins & 63u) != 0u) continue;
+                const uint64_t now = ptx::global_timer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > ptx::WAIT_LIMIT_NS) { set_status_word(a.status, KERNEL_ERR_PEER_TIMEOUT); gave_up = true; }
+            }
+        };
        for (uint32_t ti = 0; ti < ntok; ++ti) {
         const uint32_t in_row = tile ? (tile->gather ? tile->pairs[tile->first + ti] / a.top : tile->first + ti)
                                      : a.ids ? (a.per_pair ? pair : pair / a.top) : 0u;
@@ -930,8 +964,14 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         float *scratch = red;                          // the partial-sum area is idle until the first tile ends
         auto load = [&](uint32_t j) {
             // (read through L2: in a kernel that runs several projections the vectors come from other CTAs)
-            float4 v = __ldcg(a4 + j);
-            if (b4) { const float4 o = __ldcg(b4 + j); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+            float4 v, o;
+            if (ta) poll([&] { return tagged_load4(ta, j, tag_a, v); });
+            else v = __ldcg(a4 + j);
+            if (b4) {
+                if (tb) poll([&] { return tagged_load4(tb, j, tag_b, o); });
+                else o = __ldcg(b4 + j);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+            }
             return v;
         };
         auto reduce = [&](float v, bool is_max) {
@@ -956,19 +996,45 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             float sum = 0.f;
             // all loads of the row first, nothing that depends on one of them in between: one trip to L2 for the
             // whole row (a store of the residual sum after each load would make every load wait for the one before)
+            if (ta) {
+                poll([&] {
+                    bool all = true;
 #pragma unroll
-            for (uint32_t i = 0; i < NV; ++i) {
-                const uint32_t j = tid + i * NT;
-                v[i] = j < n4 ? __ldcg(a4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (uint32_t i = 0; i < NV; ++i) {
+                        const uint32_t j = tid + i * NT;
+                        if (j < n4) all &= tagged_load4(ta, j, tag_a, v[i]);
+                        else v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    return all;
+                });
+            } else {
+#pragma unroll
+                for (uint32_t i = 0; i < NV; ++i) {
+                    const uint32_t j = tid + i * NT;
+                    v[i] = j < n4 ? __ldcg(a4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
             if (b4) {                                  // (four at a time: the second vector's loads are in flight together with the first's)
 #pragma unroll
                 for (uint32_t i0 = 0; i0 < NV; i0 += 4u) {
                     float4 o[4];
+                    if (tb) {
+                        poll([&] {
+                            bool all = true;
 #pragma unroll
-                    for (uint32_t k = 0; k < 4u; ++k) {
-                        const uint32_t j = tid + (i0 + k) * NT;
-                        o[k] = (i0 + k < NV && j < n4) ? __ldcg(b4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            for (uint32_t k = 0; k < 4u; ++k) {
+                                const uint32_t j = tid + (i0 + k) * NT;
+                                if (i0 + k < NV && j < n4) all &= tagged_load4(tb, j, tag_b, o[k]);
+                                else o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                            return all;
+                        });
+                    } else {
+#pragma unroll
+                        for (uint32_t k = 0; k < 4u; ++k) {
+                            const uint32_t j = tid + (i0 + k) * NT;
+                            o[k] = (i0 + k < NV && j < n4) ? __ldcg(b4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
                     }
 #pragma unroll
                     for (uint32_t k = 0; k < 4u; ++k)
@@ -1053,6 +1119,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     // the tile, and it sums tile T only after its own work on tile T + 1, when the partials are
     // long complete: no warp falls behind the others at a tile boundary.
     const uint32_t tile_base = run.tiles;          // position of this projection's first tile in the partial-sum ring
+    const uint32_t out_tag = a.tp.n_out ? *reinterpret_cast<const volatile uint32_t *>(a.tp.step) * a.tp.tag_mul + a.tp.out_tag : 0u;
     auto sum_tile = [&](uint32_t tile) -> bool {
         const uint32_t ring = tile_base + tile;
         if (((ring ^ kw) & kmask) != 0u) return true;                  // another warp's turn
@@ -1075,7 +1142,15 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
                 for (uint32_t k = 0; k <= kmask; ++k) sum = add_rn(sum, slot[(((first + k) * TK + ti) * 2u + m) * 16u + (lane & 15u)]);
             sum = mul_rn(sum, unscale);
             const float other = NMAT == 2 ? __shfl_xor_sync(0xffffffffu, sum, 16) : 0.f;
-            if (lrow < nrows && lane < 16u) y[(size_t)ti * p.rows + row0 + lrow] = NMAT == 2 ? glu_f(sum, other, a.glu == 2) : sum;
+            if (lrow < nrows && lane < 16u) {
+                const float out = NMAT == 2 ? glu_f(sum, other, a.glu == 2) : sum;
+                y[(size_t)ti * p.rows + row0 + lrow] = out;
+                if (a.tp.n_out) {                      // the row's tagged word, whole, into every rank's twin (NVLink stores)
+                    const uint64_t word = ((uint64_t)out_tag << 32) | __float_as_uint(out);
+                    for (uint32_t pr = 0; pr < a.tp.n_out; ++pr)
+                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.tp.out[pr] + (size_t)ti * p.rows + row0 + lrow), "l"(word) : "memory");
+                }
+            }
         }
         return true;
     };
@@ -1797,6 +1872,8 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     a.per_pair = c.per_pair; a.top = c.top ? c.top : 1u; a.glu = c.glu;
     a.status = ctx.status;
     a.na = c.norm_a; a.nb = c.norm_b; a.nw = c.norm_w; a.ns = c.norm_s; a.neps = c.norm_eps; a.nround_bf16 = c.norm_round_bf16;
+    a.tp = c.tp;
+    if ((a.tp.n_out || a.tp.in[0] || a.tp.in[1]) && !a.na) return false;      // the exchange is built into the fused-norm form only
     if (pack_inside) { a.na = static_cast<const float *>(c.x); a.npack = 1u; }
     const dim3 grid(plan.ctas, gy);
     switch (c.kind) {
@@ -1887,6 +1964,7 @@ bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCt
         a.ids = nullptr; a.expert = c.expert; a.n_experts = c.n_experts; a.per_pair = 0; a.top = 1; a.glu = 0;
         a.status = ctx.status;
         a.na = c.norm_a; a.nb = c.norm_b; a.nw = c.norm_w; a.ns = c.norm_s; a.neps = c.norm_eps; a.nround_bf16 = c.norm_round_bf16;
+        a.tp = c.tp;
         ga.first[k + 1] = ga.first[k] + ctas;
         if (plan.smem_bytes > smem_bytes) smem_bytes = plan.smem_bytes;
     }

@@ -33,7 +33,23 @@ enum : int {
     KERNEL_ERR_EXPERT_RANGE = 3,       // routed id >= number of experts
     KERNEL_ERR_ROUTER_INPUT = 4,       // non-finite router logit
     KERNEL_ERR_GEMM_TIMEOUT = 5,       // prefill GEMM pipeline wait ran out
-    KERNEL_ERR_CHAIN_TIMEOUT = 6       // a projection of a chain kernel never saw the one it depends on finish
+    KERNEL_ERR_CHAIN_TIMEOUT = 6,      // a projection of a chain kernel never saw the one it depends on finish
+    KERNEL_ERR_PEER_TIMEOUT = 7        // a row-sharded projection never saw every rank's shard of its input arrive
+};
+
+// Tensor-parallel links of one projection (all null / zero on a single GPU).
+static constexpr uint32_t TP_MAX_RANKS = 8;
+struct TpLink {
+    // A vector that is assembled from every rank's rows has a tagged twin in each rank's window: one 8-byte word
+    // {value, tag} per element, stored whole (so a reader sees either the old word or the new one), the tag naming the
+    // step and the projection that wrote it.  A reader polls the words themselves: no fence, flag or arrival count.
+    uint64_t *out[TP_MAX_RANKS];            // this output's tagged twin on every rank, the own one included
+    uint32_t n_out;
+    uint32_t out_tag;                       // this step's tag of the output = step * tag_mul + out_tag
+    const uint64_t *in[2];                  // tagged twins of the two normalised inputs (null: a plain vector)
+    uint32_t in_tag[2];
+    uint32_t tag_mul;
+    const uint32_t *step;                   // own step counter (1 in the first step)
 };
 
 struct LaunchCtx {
@@ -72,6 +88,7 @@ struct GemvCall {
     float *norm_s;
     float norm_eps;
     uint32_t norm_round_bf16;
+    TpLink tp;
 };
 cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);
 // The tensor-core-assisted streaming GEMV; false when the call is not one it handles.
@@ -138,6 +155,10 @@ cudaError_t launch_gemm_dequant(const uint8_t *w, uint32_t cols, uint32_t rows, 
 cudaError_t launch_ep_localize(const uint32_t *ids, const float *w, uint32_t pairs, uint32_t first, uint32_t count,
                                uint32_t *ids_out, float *w_out, const LaunchCtx &ctx);
 cudaError_t launch_convert_bf16(const float *x, uint64_t n, void *y_bf16, const LaunchCtx &ctx);
+// *counter += 1 by one thread (the step counter of a tensor-parallel group).
+cudaError_t launch_increment(uint32_t *counter, const LaunchCtx &ctx);
+// One thread waits, with the time limit, until *counter has reached *step x arrivals (counters raised by other GPUs).
+cudaError_t launch_collect_tagged(const uint64_t *tagged, float *plain, uint32_t n, const uint32_t *step, uint32_t tag_mul, uint32_t tag_add, const LaunchCtx &ctx);
 
 // The rest of a generic decode step (decode_ops.cu).
 struct RopeParams {

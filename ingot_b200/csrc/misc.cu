@@ -569,6 +569,55 @@ cudaError_t launch_convert_bf16(const float *x, uint64_t n, void *y_bf16, const 
     return launch(convert_bf16_kernel, dim3((uint32_t)blocks), dim3(256), ctx, a);
 }
 
+__global__ void increment_kernel(uint32_t *counter) {
+    pdl_prologue();
+    *counter += 1u;
+}
+
+struct CollectArgs {
+    const uint64_t *tagged;
+    float *plain;
+    uint32_t n;
+    const uint32_t *step;
+    uint32_t tag_mul, tag_add;
+    int *status;
+};
+
+// Copies a vector out of its tagged twin once every word carries this step's tag (bounded wait): after it the plain
+// vector holds the rows of every rank.
+__global__ void __launch_bounds__(256) collect_tagged_kernel(const __grid_constant__ CollectArgs a) {
+    pdl_prologue();
+    const uint32_t tag = *reinterpret_cast<const volatile uint32_t *>(a.step) * a.tag_mul + a.tag_add;
+    if (a.status && *reinterpret_cast<const volatile int *>(a.status) != 0) return;      // a wait already ran out in this step
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += gridDim.x * blockDim.x) {
+        uint64_t t0 = 0;
+        for (;;) {
+            bool done = false;
+            for (int k = 0; k < 256 && !done; ++k) {
+                uint64_t w;
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(a.tagged + i) : "memory");
+                if ((uint32_t)(w >> 32) == tag) { a.plain[i] = __uint_as_float((uint32_t)w); done = true; }
+            }
+            if (done) break;
+            const uint64_t now = ptx::global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > ptx::WAIT_LIMIT_NS) { set_status_word(a.status, KERNEL_ERR_PEER_TIMEOUT); return; }
+        }
+    }
+}
+
+cudaError_t launch_collect_tagged(const uint64_t *tagged, float *plain, uint32_t n, const uint32_t *step, uint32_t tag_mul, uint32_t tag_add,
+                                  const LaunchCtx &ctx) {
+    CollectArgs a = {tagged, plain, n, step, tag_mul, tag_add, ctx.status};
+    uint32_t blocks = (n + 255u) / 256u;
+    if (blocks > ctx.sm_count * 2u) blocks = ctx.sm_count * 2u;
+    return launch(collect_tagged_kernel, dim3(blocks ? blocks : 1u), dim3(256), ctx, a);
+}
+
+cudaError_t launch_increment(uint32_t *counter, const LaunchCtx &ctx) {
+    return launch(increment_kernel, dim3(1), dim3(1), ctx, counter);
+}
+
 // ---------------------------------------------------------------------------
 // Expert-parallel sharding: keep the pairs whose expert lies in [first, first + count)
 // (ids become local), mark the others ROUTE_SKIP with weight 0.  The routed GEMVs

@@ -143,6 +143,69 @@ class _RopeParams(C.Structure):
                 ("qk_norm", C.c_uint32), ("eps", C.c_float), ("value_norm", C.c_uint32), ("q_scale", C.c_float)]
 
 
+class Group:
+    """One rank's end of a tensor-parallel group (ingot_group_*): a window of device memory the other ranks
+    write into, and the exchange slots the projections signal and wait for."""
+    NO_SLOT = 0xFFFFFFFF
+
+    def __init__(self, gpu: "Gpu", rank: int, world: int, window_bytes: int, slots: int):
+        self.gpu, self.rank, self.world, self.window_bytes = gpu, rank, world, window_bytes
+        h, handle = C.c_void_p(), (C.c_uint8 * 64)()
+        gpu._check(gpu._lib.ingot_group_create(gpu._h, rank, world, window_bytes, slots, C.byref(h), handle))
+        self._g, self.handle, self._used = h.value, bytes(handle), 0
+
+    def connect(self, handles: bytes) -> None:
+        """`handles`: the 64-byte handles of all ranks, in rank order (one process per GPU)."""
+        buf = (C.c_uint8 * len(handles)).from_buffer_copy(handles)
+        self.gpu._check(self.gpu._lib.ingot_group_connect(self._g, buf))
+
+    @staticmethod
+    def connect_local(groups: "list[Group]") -> None:
+        """All ranks live in this process (one handle per device)."""
+        arr = (C.c_void_p * len(groups))(*[g._g for g in groups])
+        st = groups[0].gpu._lib.ingot_group_connect_local(arr, len(groups))
+        if st != _abi.OK:
+            raise DeviceError("cannot connect the group's windows (peer access between the devices)")
+
+    def window(self, rank: int | None = None) -> int:
+        p = C.c_void_p()
+        self.gpu._check(self.gpu._lib.ingot_group_window(self._g, self.rank if rank is None else rank, C.byref(p)))
+        return p.value
+
+    def alloc(self, n_f32: int) -> "Buffer":
+        """float32 vector inside the own window; every rank allocates in the same order, so offsets agree."""
+        off = (self._used + 255) & ~255
+        if off + 4 * n_f32 > self.window_bytes:
+            raise InvalidData("group window exhausted")
+        self._used = off + 4 * n_f32
+        holder = Buffer(self.gpu, 0, 0)
+        return Buffer(self.gpu, self.window() + off, 4 * n_f32, holder)       # a view: the window owns the memory
+
+    def step(self) -> None:
+        self.gpu._check(self.gpu._lib.ingot_group_step(self._g))
+
+    def wait(self, slot: int, whole: "Buffer") -> None:
+        """Enqueues the collection of every rank's rows of `slot` in this step into the plain vector `whole`."""
+        self.gpu._check(self.gpu._lib.ingot_group_wait(self._g, slot, whole.ptr, whole.nbytes // 4))
+
+    def signal_next(self, slot: int) -> None:
+        self.gpu._check(self.gpu._lib.ingot_tp_signal_next(self._g, slot))
+
+    def wait_next(self, slot_a: int, slot_b: int | None = None) -> None:
+        self.gpu._check(self.gpu._lib.ingot_tp_wait_next(self._g, slot_a, self.NO_SLOT if slot_b is None else slot_b))
+
+    def close(self) -> None:
+        if self._g:
+            self.gpu._lib.ingot_group_destroy(self._g)
+            self._g = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class Chain:
     """A recorded sequence of fused-norm projections that runs as one persistent kernel."""
 
