@@ -284,15 +284,9 @@ def main():
 
     group = None
     if world > 1 and args.exchange == "peer" and args.fused_norm and args.batch == 1:
-        from ingot_b200.gpu import Group
         n_layers = shape.layers if args.layers is None else args.layers
         window = 4 * args.batch * (shape.q + 2 * shape.hidden + shape.ffn + shape.vocab) + 8 * 256
-        group = Group(gpu, rank, world, window, DecodeChain.exchange_slots(n_layers))
-        mine = torch.frombuffer(bytearray(group.handle), dtype=torch.uint8).to(f"cuda:{local}")
-        everyone = torch.empty(64 * world, dtype=torch.uint8, device=f"cuda:{local}")
-        dist.all_gather_into_tensor(everyone, mine)               # the IPC handles travel over the process group; nothing else does
-        group.connect(bytes(everyone.cpu().numpy()))
-        dist.barrier()
+        group = connect_group(torch, dist, gpu, rank, world, local, window, DecodeChain.exchange_slots(n_layers))
     chain = DecodeChain(gpu, shape, batch=args.batch, x_kind=x_kind, seed=0, rank=rank, world=world, group=group,
                         all_gather=all_gather if world > 1 else None, layers=args.layers, packed=not args.no_mma, fused_norm=bool(args.fused_norm),
                         keep_host=1 if (rank == 0 and world == 1 and not (args.no_cpu and args.no_parity)) else 0)
@@ -452,12 +446,26 @@ def main():
 
 # ---- helpers ------------------------------------------------------------------------
 
+def connect_group(torch, dist, gpu, rank, world, local, window_bytes, slots):
+    """One rank's end of an ingot_group_* group; the 64-byte IPC handles travel over the process group, nothing else does."""
+    from ingot_b200.gpu import Group
+    group = Group(gpu, rank, world, window_bytes, slots)
+    mine = torch.frombuffer(bytearray(group.handle), dtype=torch.uint8).to(f"cuda:{local}")
+    everyone = torch.empty(64 * world, dtype=torch.uint8, device=f"cuda:{local}")
+    dist.all_gather_into_tensor(everyone, mine)
+    group.connect(bytes(everyone.cpu().numpy()))
+    dist.barrier()
+    return group
+
+
 def run_moe(torch, gpu, stream, args, rank, world, local):
     """Qwen3-30B-A3B-shaped expert-routed FFN chain: 48 layers of route_topk -> routed gate/up + SiLU ->
     routed down -> moe_sum, Q4_K experts, synthetic N(0,1) router logits, for each token count.
-    With N > 1 ranks the 128 experts are split expert-parallel (rank r owns experts [r*128/N, ...)),
-    every rank sees the same tokens and routing, and one NCCL all-reduce per layer completes the
-    output: weak scaling is not meaningful here, the same step runs on more GPUs (strong)."""
+    With N > 1 ranks the 128 experts are split expert-parallel (rank r owns experts [r*128/N, ...)) and the SAME
+    total step runs on more GPUs (strong scaling).  --exchange peer (default): the tokens are split over the ranks
+    too, every rank routes its own and the rows travel to the experts' owners and back (token all-to-all,
+    ingot_ep_*; a count that does not divide leaves the last ranks with fewer tokens).  --exchange nccl: every rank
+    sees all tokens, runs its experts' pairs, and one NCCL all-reduce per layer completes the output (comparison)."""
     from ingot_b200.moe import QWEN3_30B_A3B, MoeChain, expert_bytes
     from ingot_b200.gpu import Buffer
     dist = None
@@ -470,18 +478,45 @@ def run_moe(torch, gpu, stream, args, rank, world, local):
     s = QWEN3_30B_A3B
     peaks, peak_src = measured_peaks()
     results = []
-    chain = MoeChain(gpu, s, tokens=max(args.tokens), seed=0, rank=rank, world=world, all_reduce=all_reduce if world > 1 else None,
-                     layers=args.layers, local_weights_only=True)
+    a2a = world > 1 and args.exchange == "peer"
+
+    def own(tokens: int) -> tuple[int, int]:
+        """This rank's span of the step's tokens (token all-to-all), else all of them."""
+        if not a2a:
+            return 0, tokens
+        per = -(-tokens // world)
+        return min(rank * per, tokens), min((rank + 1) * per, tokens)
+
+    most = max(-(-t // world) if a2a else t for t in args.tokens)
+    group = None
+    if a2a:
+        from ingot_b200.gpu import EpExchange
+        n_layers = args.layers or s.layers
+        group = connect_group(torch, dist, gpu, rank, world, local, EpExchange.window_bytes(world, most * s.top, s.hidden),
+                              MoeChain.exchange_slots(n_layers))
+    chain = MoeChain(gpu, s, tokens=most, seed=0, rank=rank, world=world, all_reduce=all_reduce if world > 1 else None,
+                     layers=args.layers, local_weights_only=True, group=group)
     for tokens in args.tokens:
-        chain.tokens = tokens               # the buffers are sized for the largest count
+        t0, t1 = own(tokens)
+        chain.tokens = t1 - t0              # the buffers are sized for the largest count
+        if a2a:
+            chain.set_capacity(-(-tokens // world) * s.top)       # places per region: the most pairs a rank has in this step
         rng = np.random.default_rng(100 + tokens)
-        logits = rng.normal(0, 1, (tokens, s.experts)).astype(np.float32)
-        x = rng.normal(0, 1, (tokens, s.hidden)).astype(np.float32)
-        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.logits.ptr, logits.ctypes.data, logits.nbytes))
-        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.x.ptr, x.ctypes.data, x.nbytes))
+        logits = rng.normal(0, 1, (tokens, s.experts)).astype(np.float32)[t0:t1].copy()
+        x = rng.normal(0, 1, (tokens, s.hidden)).astype(np.float32)[t0:t1].copy()
+        if t1 > t0:
+            gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.logits.ptr, logits.ctypes.data, logits.nbytes))
+            gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, chain.x.ptr, x.ctypes.data, x.nbytes))
         gpu.complete()
         graph, tgraph = None, None
-        if world == 1:
+        if a2a:
+            torch.cuda.synchronize()
+            dist.barrier()                  # every rank's inputs are in place before anybody's rows arrive
+            chain.step()
+            gpu.complete()
+            dist.barrier()
+            graph = chain.record()
+        elif world == 1:
             chain.step()
             gpu.complete()
             graph = chain.record()
@@ -516,8 +551,15 @@ def run_moe(torch, gpu, stream, args, rank, world, local):
             t = torch.tensor([ms], device=f"cuda:{local}")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        ids = gpu.read_bytes(chain.ids).view(np.uint32)[:tokens * s.top]
-        unique = int(len(np.unique(ids)))
+        ids = gpu.read_bytes(chain.ids).view(np.uint32)[:(t1 - t0) * s.top]
+        if a2a:                             # the step's experts: the union over the ranks' own tokens
+            seen = torch.zeros(s.experts, dtype=torch.int32, device=f"cuda:{local}")
+            if len(ids):
+                seen[torch.from_numpy(np.unique(ids).astype(np.int64)).to(seen.device)] = 1
+            dist.all_reduce(seen, op=dist.ReduceOp.MAX)
+            unique = int(seen.sum().item())
+        else:
+            unique = int(len(np.unique(ids)))
         algo = chain.n_layers * unique * expert_bytes(s)        # every layer routes the same synthetic logits
         results.append({"tokens": tokens, "ms_per_step": ms, "tok_per_s": tokens * 1000.0 / ms, "unique_experts": unique,
                         "expert_bytes_per_step": algo, "gbs": algo / (ms * 1e-3) / 1e9,
@@ -532,7 +574,8 @@ def run_moe(torch, gpu, stream, args, rank, world, local):
                           "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                           "config": {"workload": "qwen3-30b-a3b expert-routed FFN chain (configs[3]), tokens %s" % args.tokens,
                                      "layers": args.layers or s.layers, "experts": s.experts, "top": s.top,
-                                     "parallelism": "ep%d" % world if world > 1 else "single GPU",
+                                     "parallelism": ("ep%d, token all-to-all inside the library (peer stores, tagged words)" % world if a2a else
+                                                     "ep%d, tokens replicated, one NCCL all-reduce per layer" % world) if world > 1 else "single GPU",
                                      "peak_source": peak_src},
                           "by_tokens": results}), flush=True)
     if world > 1:

@@ -444,6 +444,44 @@ INGOT_API ingot_status ingot_tp_signal_next(ingot_group *group, uint32_t slot);
 /* The next fused-norm projection reads the vectors of slot_a and, unless 0xffffffff, slot_b from
  * their twins; each must be one of its two normalised inputs (the whole vector, in the window). */
 INGOT_API ingot_status ingot_tp_wait_next(ingot_group *group, uint32_t slot_a, uint32_t slot_b);
+
+/* ---- expert-parallel token exchange (a group whose ranks each own experts / world experts) ----
+ * No counterpart in the reference, which keeps every expert on its one device
+ * (src/weights.rs:55-58; dataflow of the layer: Generic::moe, src/generic.rs:508-574).  Every
+ * rank routes its OWN tokens (ingot_route_topk); then, per layer:
+ *   ingot_ep_dispatch  each pair's activation row and {local expert id, pair index} go into region
+ *                      `rank` of the owner's receive area (plain stores over NVLink), unused places
+ *                      of the region are marked skipped, one tagged word per owner closes the region
+ *   ingot_ep_receive   waits (time-limited) for the regions of all ranks and writes ids_out[world x
+ *                      cap] (local expert id or 0xffffffff) for ingot_routed_gate_up / ingot_routed
+ *                      over the world x cap places (x = rx_rows, one row per place, top = 1)
+ *   ingot_ep_return    each live place's output row (row `place` of `rows`, or row inverse[place] when
+ *                      the places ran through the expert grouping: ingot_expert_layout accepts the
+ *                      skipped places of ids_out and gives them no position) goes to the home rank's
+ *                      ret_rows at the pair's index, one tagged word per home rank closes it
+ *   ingot_ep_combine   waits (time-limited) for all owners, then y[t] = sum_k w[t][k] ret_rows[t top + k]
+ *                      in route order — what ingot_moe_sum computes on one device, bit for bit.
+ * The five areas lie inside the own window at the same offsets on every rank: rx_rows
+ * [world][cap][hidden] floats, rx_meta [world][cap] words, rx_ready [world] 8-byte words, ret_rows
+ * [cap][hidden] floats, ret_ready [world] 8-byte words; cap >= tokens x top of every rank, at
+ * most 4096.  `slot` names the exchange within the step (two per layer: dispatch, return); a
+ * wait that runs out is INGOT_TIMEOUT at the next ingot_synchronize. */
+typedef struct ingot_ep_buffers {
+    float *rx_rows;
+    uint32_t *rx_meta;
+    uint64_t *rx_ready;
+    float *ret_rows;
+    uint64_t *ret_ready;
+} ingot_ep_buffers;
+INGOT_API ingot_status ingot_ep_dispatch(ingot_group *group, uint32_t slot, const ingot_ep_buffers *bufs, const float *x,
+                                         const uint32_t *ids, uint32_t tokens, uint32_t top, uint32_t hidden, uint32_t cap,
+                                         uint32_t experts_per_rank);
+INGOT_API ingot_status ingot_ep_receive(ingot_group *group, uint32_t slot, const ingot_ep_buffers *bufs, uint32_t hidden, uint32_t cap,
+                                        uint32_t *ids_out);
+INGOT_API ingot_status ingot_ep_return(ingot_group *group, uint32_t slot, const ingot_ep_buffers *bufs, const float *rows,
+                                       const uint32_t *inverse, uint32_t hidden, uint32_t cap);
+INGOT_API ingot_status ingot_ep_combine(ingot_group *group, uint32_t slot, const ingot_ep_buffers *bufs, const float *weights,
+                                        uint32_t hidden, uint32_t top, uint32_t tokens, uint32_t cap, float *y);
 INGOT_API void ingot_group_destroy(ingot_group *group);
 
 /* ---- chains: a whole decode step as ONE kernel -----------------------------

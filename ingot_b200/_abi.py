@@ -90,6 +90,10 @@ SIGNATURES = {
     "ingot_group_wait": [vp, u32, vp, u32],
     "ingot_tp_signal_next": [vp, u32],
     "ingot_tp_wait_next": [vp, u32, u32],
+    "ingot_ep_dispatch": [vp, u32, vp, vp, vp, u32, u32, u32, u32, u32],
+    "ingot_ep_receive": [vp, u32, vp, u32, u32, vp],
+    "ingot_ep_return": [vp, u32, vp, vp, vp, u32, u32],
+    "ingot_ep_combine": [vp, u32, vp, vp, u32, u32, u32, u32, vp],
     "ingot_chain_begin": [vp],
     "ingot_chain_end": [vp, C.POINTER(vp)],
     "ingot_chain_submit": [vp, vp],

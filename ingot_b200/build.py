@@ -19,7 +19,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libingot_cuda.so")
 OBJ_DIR = os.path.join(PKG, "build")
 
-SOURCES = ["abi.cu", "gemv.cu", "gemv_mma.cu", "gemv_tc.cu", "misc.cu", "gemm.cu", "noalloc.cu", "decode_ops.cu", "gguf.cpp"]
+SOURCES = ["abi.cu", "gemv.cu", "gemv_mma.cu", "gemv_tc.cu", "misc.cu", "gemm.cu", "noalloc.cu", "decode_ops.cu", "ep_exchange.cu", "gguf.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1006,6 +1006,97 @@ ingot_status ingot_tp_wait_next(ingot_group *gr, uint32_t slot_a, uint32_t slot_
     return INGOT_OK;
 }
 
+// ---- expert-parallel token exchange --------------------------------------------------------------
+
+// The exchange areas (all inside the own window) as every rank sees them.
+static ingot_status ep_link(ingot_group *gr, uint32_t slot, const ingot_ep_buffers *b, uint32_t cap, uint32_t hidden, uint32_t counter,
+                            EpLink &l, const char *what) {
+    ingot_gpu *g = gr->gpu;
+    if (!b || !b->rx_rows || !b->rx_meta || !b->rx_ready || !b->ret_rows || !b->ret_ready || cap == 0 || hidden == 0)
+        return fail(g, INGOT_INVALID, std::string(what) + ": bad arguments");
+    const uint8_t *base = gr->peer[gr->rank];
+    auto inside = [&](const void *p, size_t bytes, size_t align) {
+        const uint8_t *x = static_cast<const uint8_t *>(p);
+        return x >= base && x + bytes <= base + gr->window_bytes && ((uintptr_t)x % align) == 0;
+    };
+    const size_t places = (size_t)gr->world * cap;
+    if (!inside(b->rx_rows, places * hidden * 4u, 16) || !inside(b->rx_meta, places * 4u, 4) || !inside(b->rx_ready, gr->world * 8u, 8) ||
+        !inside(b->ret_rows, (size_t)cap * hidden * 4u, 16) || !inside(b->ret_ready, gr->world * 8u, 8))
+        return fail(g, INGOT_INVALID, std::string(what) + ": the exchange areas must lie inside the group's window (rows 16-byte aligned)");
+    l = {};
+    for (uint32_t r = 0; r < gr->world; ++r) {
+        if (!gr->peer[r]) return fail(g, INGOT_INVALID, std::string(what) + ": the group is not connected");
+        auto at = [&](const void *p) { return gr->peer[r] + (static_cast<const uint8_t *>(p) - base); };
+        l.rx_rows[r] = reinterpret_cast<float *>(at(b->rx_rows));
+        l.rx_meta[r] = reinterpret_cast<uint32_t *>(at(b->rx_meta));
+        l.rx_ready[r] = reinterpret_cast<uint64_t *>(at(b->rx_ready));
+        l.ret_rows[r] = reinterpret_cast<float *>(at(b->ret_rows));
+        l.ret_ready[r] = reinterpret_cast<uint64_t *>(at(b->ret_ready));
+    }
+    l.launch_count = reinterpret_cast<uint32_t *>(gr->peer[gr->rank] + gr->ctrl_off + 64u * (1u + counter));
+    l.step = gr->step_counter();
+    l.tag_mul = gr->slots + 1u;
+    l.tag_add = slot + 1u;
+    l.world = gr->world;
+    l.rank = gr->rank;
+    return INGOT_OK;
+}
+
+static ingot_status ep_enter(ingot_group *gr, uint32_t slot, const char *what) {
+    if (!gr || slot >= gr->slots) return INGOT_INVALID;
+    ingot_gpu *g = gr->gpu;
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->in_scope || g->chain_recording) return fail(g, INGOT_INVALID, std::string(what) + ": not inside an independent scope or a chain recording");
+    return INGOT_OK;
+}
+
+ingot_status ingot_ep_dispatch(ingot_group *gr, uint32_t slot, const ingot_ep_buffers *bufs, const float *x, const uint32_t *ids,
+                               uint32_t tokens, uint32_t top, uint32_t hidden, uint32_t cap, uint32_t experts_per_rank) {
+    ingot_status st = ep_enter(gr, slot, "ep_dispatch");
+    if (st) return st;
+    ingot_gpu *g = gr->gpu;
+    EpLink l;
+    if ((st = ep_link(gr, slot, bufs, cap, hidden, 0, l, "ep_dispatch"))) return st;
+    const uint64_t pairs = (uint64_t)tokens * top;
+    if (!x || !ids || top == 0 || pairs > cap || pairs > EP_MAX_PAIRS || hidden % 4u || experts_per_rank == 0 || ((uintptr_t)x % 16u))
+        return fail(g, INGOT_INVALID, "ep_dispatch: tokens x top must fit the capacity (at most 4096 pairs per rank); rows of 4 n floats, 16-byte aligned");
+    return after_launch(g, launch_ep_dispatch(l, x, ids, (uint32_t)pairs, top, hidden, cap, experts_per_rank, ctx_on(g, g->stream)), "ep_dispatch");
+}
+
+ingot_status ingot_ep_receive(ingot_group *gr, uint32_t slot, const ingot_ep_buffers *bufs, uint32_t hidden, uint32_t cap, uint32_t *ids_out) {
+    ingot_status st = ep_enter(gr, slot, "ep_receive");
+    if (st) return st;
+    ingot_gpu *g = gr->gpu;
+    EpLink l;
+    if ((st = ep_link(gr, slot, bufs, cap, hidden, 0, l, "ep_receive"))) return st;
+    if (!ids_out) return fail(g, INGOT_INVALID, "ep_receive: null pointer");
+    return after_launch(g, launch_ep_receive(l, cap, ids_out, ctx_on(g, g->stream)), "ep_receive");
+}
+
+ingot_status ingot_ep_return(ingot_group *gr, uint32_t slot, const ingot_ep_buffers *bufs, const float *rows, const uint32_t *inverse,
+                             uint32_t hidden, uint32_t cap) {
+    ingot_status st = ep_enter(gr, slot, "ep_return");
+    if (st) return st;
+    ingot_gpu *g = gr->gpu;
+    EpLink l;
+    if ((st = ep_link(gr, slot, bufs, cap, hidden, 1, l, "ep_return"))) return st;
+    if (!rows || hidden % 4u || ((uintptr_t)rows % 16u)) return fail(g, INGOT_INVALID, "ep_return: rows of 4 n floats, 16-byte aligned");
+    return after_launch(g, launch_ep_return(l, rows, inverse, cap, hidden, ctx_on(g, g->stream)), "ep_return");
+}
+
+ingot_status ingot_ep_combine(ingot_group *gr, uint32_t slot, const ingot_ep_buffers *bufs, const float *weights, uint32_t hidden,
+                              uint32_t top, uint32_t tokens, uint32_t cap, float *y) {
+    ingot_status st = ep_enter(gr, slot, "ep_combine");
+    if (st) return st;
+    ingot_gpu *g = gr->gpu;
+    EpLink l;
+    if ((st = ep_link(gr, slot, bufs, cap, hidden, 1, l, "ep_combine"))) return st;
+    if (!weights || !y || hidden % 4u || (uint64_t)tokens * top > cap || ((uintptr_t)y % 16u))
+        return fail(g, INGOT_INVALID, "ep_combine: bad arguments");
+    return after_launch(g, launch_ep_combine(l, weights, hidden, top, tokens, y, ctx_on(g, g->stream)), "ep_combine");
+}
+
 void ingot_group_destroy(ingot_group *gr) {
     if (!gr) return;
     cudaSetDevice(gr->gpu->device);

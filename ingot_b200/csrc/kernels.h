@@ -52,6 +52,19 @@ struct TpLink {
     const uint32_t *step;                   // own step counter (1 in the first step)
 };
 
+// Expert-parallel exchange areas of one rank's window as every rank sees them (index = rank).
+static constexpr uint32_t EP_MAX_PAIRS = 4096;
+struct EpLink {
+    float *rx_rows[TP_MAX_RANKS];           // [world][cap][hidden]: region s holds the rows rank s sent
+    uint32_t *rx_meta[TP_MAX_RANKS];        // [world][cap]: local expert id | pair index << 16, or ROUTE_SKIP
+    uint64_t *rx_ready[TP_MAX_RANKS];       // [world] tagged: region s is complete (low half: its live places)
+    float *ret_rows[TP_MAX_RANKS];          // [cap][hidden]: the outputs of the rank's own pairs, by pair index
+    uint64_t *ret_ready[TP_MAX_RANKS];      // [world] tagged: owner s has returned everything it had
+    uint32_t *launch_count;                 // own device: CTAs of this kind of launch so far (the last one of a launch signals)
+    const uint32_t *step;
+    uint32_t tag_mul, tag_add, world, rank;
+};
+
 struct LaunchCtx {
     cudaStream_t stream;
     int *status;          // device status word
@@ -157,6 +170,14 @@ cudaError_t launch_ep_localize(const uint32_t *ids, const float *w, uint32_t pai
 cudaError_t launch_convert_bf16(const float *x, uint64_t n, void *y_bf16, const LaunchCtx &ctx);
 // *counter += 1 by one thread (the step counter of a tensor-parallel group).
 cudaError_t launch_increment(uint32_t *counter, const LaunchCtx &ctx);
+// Expert-parallel token exchange (dispatch to the experts' owners, receive, return, weighted sum at home).
+cudaError_t launch_ep_dispatch(const EpLink &link, const float *x, const uint32_t *ids, uint32_t pairs, uint32_t top, uint32_t hidden,
+                               uint32_t cap, uint32_t experts_per_rank, const LaunchCtx &ctx);
+cudaError_t launch_ep_receive(const EpLink &link, uint32_t cap, uint32_t *ids_out, const LaunchCtx &ctx);
+cudaError_t launch_ep_return(const EpLink &link, const float *rows, const uint32_t *inverse, uint32_t cap, uint32_t hidden,
+                             const LaunchCtx &ctx);
+cudaError_t launch_ep_combine(const EpLink &link, const float *w, uint32_t hidden, uint32_t top, uint32_t tokens, float *y,
+                              const LaunchCtx &ctx);
 // One thread waits, with the time limit, until *counter has reached *step x arrivals (counters raised by other GPUs).
 cudaError_t launch_collect_tagged(const uint64_t *tagged, float *plain, uint32_t n, const uint32_t *step, uint32_t tag_mul, uint32_t tag_add, const LaunchCtx &ctx);
 

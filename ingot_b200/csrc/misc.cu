@@ -680,7 +680,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) expert_group_kernel(const __gri
     for (uint32_t i = tid; i < a.n_pairs; i += GROUP_THREADS) {
         const uint32_t e = a.ids[i];
         if (e < a.experts) atomicAdd(&counts[e], 1u);
-        else atomicCAS(a.status, 0, KERNEL_ERR_EXPERT_RANGE);
+        else if (e != ROUTE_SKIP) atomicCAS(a.status, 0, KERNEL_ERR_EXPERT_RANGE);       // (a skipped pair takes no place)
     }
     __syncthreads();
     // exclusive scan over the experts of (pairs, tiles): inclusive inside the warp, then the warps' totals
@@ -715,6 +715,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) expert_group_kernel(const __gri
         const uint32_t i = i0 + tid;
         const uint32_t e = i < a.n_pairs ? a.ids[i] : 0xffffffffu;
         const bool live = e < a.experts;
+        if (i < a.n_pairs && !live) a.inverse[i] = ROUTE_SKIP;
         const uint32_t same = __match_any_sync(0xffffffffu, e);
         const uint32_t rank = __popc(same & ((1u << lane) - 1u));
         for (uint32_t w = 0; w < GROUP_THREADS / 32; ++w) {

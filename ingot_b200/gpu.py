@@ -143,6 +143,48 @@ class _RopeParams(C.Structure):
                 ("qk_norm", C.c_uint32), ("eps", C.c_float), ("value_norm", C.c_uint32), ("q_scale", C.c_float)]
 
 
+class _EpBuffers(C.Structure):
+    _fields_ = [("rx_rows", C.c_void_p), ("rx_meta", C.c_void_p), ("rx_ready", C.c_void_p), ("ret_rows", C.c_void_p),
+                ("ret_ready", C.c_void_p)]
+
+
+class EpExchange:
+    """The areas of one rank's window that the expert-parallel token exchange uses (ingot_ep_*): `cap` places
+    per sending rank, rows of `hidden` floats."""
+
+    def __init__(self, group: "Group", cap: int, hidden: int):
+        self.group, self.cap, self.hidden = group, cap, hidden
+        w = group.world
+        self.rx_rows = group.alloc(w * cap * hidden)
+        self.rx_meta = group.alloc(w * cap)
+        self.rx_ready = group.alloc(2 * w)
+        self.ret_rows = group.alloc(cap * hidden)
+        self.ret_ready = group.alloc(2 * w)
+        self._c = _EpBuffers(self.rx_rows.ptr, self.rx_meta.ptr, self.rx_ready.ptr, self.ret_rows.ptr, self.ret_ready.ptr)
+
+    @staticmethod
+    def window_bytes(world: int, cap: int, hidden: int) -> int:
+        return 4 * (world * cap * hidden + world * cap + 4 * world + cap * hidden) + 5 * 256
+
+    def dispatch(self, slot: int, x: "Buffer", ids: "Buffer", tokens: int, top: int, experts_per_rank: int) -> None:
+        g = self.group.gpu
+        g._check(g._lib.ingot_ep_dispatch(self.group._g, slot, C.byref(self._c), x.ptr, ids.ptr, tokens, top, self.hidden, self.cap,
+                                          experts_per_rank))
+
+    def receive(self, slot: int, ids_out: "Buffer") -> None:
+        g = self.group.gpu
+        g._check(g._lib.ingot_ep_receive(self.group._g, slot, C.byref(self._c), self.hidden, self.cap, ids_out.ptr))
+
+    def give_back(self, slot: int, rows: "Buffer", inverse: "Buffer | None" = None) -> None:
+        g = self.group.gpu
+        g._check(g._lib.ingot_ep_return(self.group._g, slot, C.byref(self._c), rows.ptr, inverse.ptr if inverse else None, self.hidden,
+                                        self.cap))
+
+    def combine(self, slot: int, weights: "Buffer", top: int, tokens: int, y: "Buffer") -> None:
+        g = self.group.gpu
+        g._check(g._lib.ingot_ep_combine(self.group._g, slot, C.byref(self._c), weights.ptr, self.hidden, top, tokens, self.cap, y.ptr))
+
+
 class Group:
     """One rank's end of a tensor-parallel group (ingot_group_*): a window of device memory the other ranks
     write into, and the exchange slots the projections signal and wait for."""

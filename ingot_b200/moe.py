@@ -51,9 +51,14 @@ class MoeChain:
     decode step for `tokens` tokens."""
 
     def __init__(self, gpu: Gpu, shape: MoeShape, tokens: int = 1, seed: int = 0, rank: int = 0, world: int = 1,
-                 all_reduce=None, layers: int | None = None, keep_host: bool = False, local_weights_only: bool = False):
+                 all_reduce=None, layers: int | None = None, keep_host: bool = False, local_weights_only: bool = False,
+                 group=None):
+        """world > 1 without `group`: every rank holds all `tokens` tokens, runs its experts' pairs and the partial
+        sums are all-reduced.  With `group` (gpu.Group): `tokens` are this rank's OWN tokens; rows travel to the
+        experts' owners and back (token all-to-all, ingot_ep_*)."""
         self.gpu, self.shape, self.tokens = gpu, shape, tokens
         self.rank, self.world, self.all_reduce = rank, world, all_reduce
+        self.group = group if world > 1 else None
         self.n_layers = shape.layers if layers is None else layers
         gpu.set_option(5, world)                  # INGOT_OPT_EP_WORLD: routed launches expect pairs / world live pairs
         self.first, end = expert_range(shape.experts, rank, world)
@@ -95,7 +100,33 @@ class MoeChain:
         self.packed = gpu.empty_bytes(4 * pairs)
         self.inverse = gpu.empty_bytes(4 * pairs)
         self.grouped = True           # tokens > 4 take the grouped path on one device; False: pair by pair (comparison)
+        # token all-to-all: the received places run pair by pair unless this is set (with a few places per expert and
+        # rank the grouped kernel measured slower on two GPUs: 13.4 against 11.8 ms per 32-token step)
+        self.grouped_places = False
         self.launches_per_step = 0
+        if self.group:
+            from .gpu import EpExchange
+            self.cap = pairs                                  # places per sending rank: all its pairs may choose one owner
+            self.ep = EpExchange(self.group, self.cap, s.hidden)
+            places = world * self.cap
+            self.ids_rx = gpu.empty_bytes(4 * places)
+            self.act_rx = gpu.zeros(places * s.ffn)
+            self.out_rx = gpu.zeros(places * s.hidden)
+            self.tiles_rx = gpu.empty_bytes(4 * 4 * ((places + 31) // 32 + self.local))
+            self.packed_rx = gpu.empty_bytes(4 * places)
+            self.inverse_rx = gpu.empty_bytes(4 * places)
+
+    def set_capacity(self, cap: int) -> None:
+        """Places per sending rank for the next steps (the same on every rank, at most what the areas were sized
+        for): the routed projections run over world x cap places, so a tight capacity keeps their grids small."""
+        if cap * self.shape.hidden > self.ep.ret_rows.nbytes // 4:
+            raise ValueError("capacity beyond the exchange areas")
+        self.cap = self.ep.cap = cap
+
+    @staticmethod
+    def exchange_slots(layers: int) -> int:
+        """Slots a group needs for the token all-to-all: dispatch and return of every layer."""
+        return 2 * layers
 
     def layer(self, i: int) -> None:
         """One MoE FFN layer on the handle's stream: y = sum_k w_k * down_k(silu(gate_k x) * up_k x)."""
@@ -105,6 +136,35 @@ class MoeChain:
         g._check(lib.ingot_route_topk(h, self.logits.ptr, s.experts, s.top, self.tokens, self.ids.ptr, self.w.ptr))
         ids, w = self.ids, self.w
         n = 1
+        if self.group:
+            # token all-to-all: this rank's pairs go to the experts' owners; the places received from all ranks are
+            # run pair by pair (one activation row per place), their rows go home and are summed there
+            ep, places = self.ep, self.world * self.cap
+            ep.dispatch(2 * i, self.x, self.ids, self.tokens, s.top, self.local)
+            ep.receive(2 * i, self.ids_rx)
+            tg, td = ws["gate"].t, ws["down"].t
+            if self.grouped_places and places > 4:
+                # the places of one expert share its rows: grouped by expert, four at a time (skipped places take no position)
+                blocks = (places + 31) // 32 + self.local
+                g._check(lib.ingot_expert_layout(h, self.ids_rx.ptr, places, self.local, blocks, self.layout.ptr, self.tiles_rx.ptr,
+                                                 self.packed_rx.ptr, self.inverse_rx.ptr))
+                g._check(lib.ingot_expert_gate_up(h, ws["gate"].buffer.ptr, ws["up"].buffer.ptr, tg.dims[0], tg.dims[1], tg.stride, tg.kind,
+                                                  self.local, ep.rx_rows.ptr, self.tiles_rx.ptr, self.packed_rx.ptr, blocks, 1, places,
+                                                  self.act_rx.ptr))
+                g._check(lib.ingot_expert_project(h, ws["down"].buffer.ptr, td.dims[0], td.dims[1], td.stride, td.kind, self.local,
+                                                  self.act_rx.ptr, self.tiles_rx.ptr, self.packed_rx.ptr, blocks, 1, places, 0, self.out_rx.ptr))
+                ep.give_back(2 * i + 1, self.out_rx, self.inverse_rx)
+                ep.combine(2 * i + 1, self.w, s.top, self.tokens, self.y)
+                self.launches_per_step += 8
+                return
+            g._check(lib.ingot_routed_gate_up(h, ws["gate"].buffer.ptr, ws["up"].buffer.ptr, tg.dims[0], tg.dims[1], tg.stride,
+                                              tg.kind, self.local, ep.rx_rows.ptr, F32, self.ids_rx.ptr, 1, places, self.act_rx.ptr))
+            g._check(lib.ingot_routed(h, ws["down"].buffer.ptr, td.dims[0], td.dims[1], td.stride, td.kind, self.local,
+                                      self.act_rx.ptr, F32, self.ids_rx.ptr, 1, 1, places, self.out_rx.ptr))
+            ep.give_back(2 * i + 1, self.out_rx)
+            ep.combine(2 * i + 1, self.w, s.top, self.tokens, self.y)
+            self.launches_per_step += 7
+            return
         if self.world > 1:
             g._check(lib.ingot_ep_localize(h, self.ids.ptr, self.w.ptr, pairs, self.first, self.local, self.ids_l.ptr,
                                            self.w_l.ptr))
@@ -134,6 +194,9 @@ class MoeChain:
 
     def step(self) -> None:
         self.launches_per_step = 0
+        if self.group:
+            self.group.step()
+            self.launches_per_step += 1
         for i in range(self.n_layers):
             self.layer(i)
 

@@ -83,3 +83,63 @@ def test_a_wait_nobody_answers_runs_out_and_reports_a_timeout():
     assert g.zeros(4).nbytes == 16           # the handle is usable after the time-out
     g.complete()
     del chain
+
+
+@pytest.mark.skipif(_device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("grouped", [False, True], ids=["pair-by-pair", "grouped"])
+@pytest.mark.parametrize("own_tokens", [1, 4, 16])
+def test_token_all_to_all_equals_the_single_device_layers(own_tokens, grouped):
+    """Two ranks, each with its own tokens and half of the experts: after two MoE layers with the token
+    all-to-all every token's result is bit-identical to the layers run on one device that holds all experts,
+    the received words are the ones the oracle's bookkeeping gives, and a second step repeats the first."""
+    from ingot_b200 import Q4_K, Gpu
+    from ingot_b200.gpu import EpExchange, Group
+    from ingot_b200.moe import MoeChain, MoeShape
+    from oracle import ep_exchange as X
+    shape = MoeShape("test", 2, 512, 16, 4, 256, Q4_K)
+    world, layers = 2, 2
+    rng = np.random.default_rng(7)
+    logits = rng.normal(0, 1, (world, own_tokens, shape.experts)).astype(np.float32)
+    xs = (rng.normal(0, 1, (world, own_tokens, shape.hidden)) * 0.05).astype(np.float32)
+
+    def load(c, r):
+        g = c.gpu
+        g._check(g._lib.ingot_buffer_upload(g._h, c.logits.ptr, logits[r].ctypes.data, logits[r].nbytes))
+        g._check(g._lib.ingot_buffer_upload(g._h, c.x.ptr, xs[r].ctypes.data, xs[r].nbytes))
+        g.complete()
+
+    g0 = Gpu(0)
+    want = []
+    for r in range(world):                   # one device, all experts, the tokens of rank r, pair by pair
+        ref = MoeChain(g0, shape, tokens=own_tokens, seed=3, layers=layers)
+        ref.grouped = grouped
+        load(ref, r)
+        ref.step()
+        g0.complete()
+        want.append(g0.read_f32(ref.y).copy())
+        del ref
+    gpus = [g0, Gpu(1)]
+    cap = own_tokens * shape.top
+    window = EpExchange.window_bytes(world, cap, shape.hidden)
+    groups = [Group(g, r, world, window, MoeChain.exchange_slots(layers)) for r, g in enumerate(gpus)]
+    Group.connect_local(groups)
+    chains = [MoeChain(g, shape, tokens=own_tokens, seed=3, layers=layers, rank=r, world=world, group=groups[r])
+              for r, g in enumerate(gpus)]
+    for r, c in enumerate(chains):
+        c.grouped_places = grouped
+        load(c, r)
+    for _ in range(2):
+        for c in chains:                     # both ranks are issued before either is waited for
+            c.step()
+        for r, (c, g) in enumerate(zip(chains, gpus)):
+            g.complete()
+            got = g.read_f32(c.y)
+            assert np.array_equal(got.view(np.uint32), want[r].view(np.uint32))
+    # the words of the last layer's receive areas against the oracle's plan (every layer routes the same logits)
+    ids = [g.read_bytes(c.ids).view(np.uint32)[:cap] for c, g in zip(chains, gpus)]
+    plans = [X.dispatch_plan(i, world, shape.experts // world, cap)[2] for i in ids]
+    for r, (c, g) in enumerate(zip(chains, gpus)):
+        region, ids_rx = X.receive_regions(plans, r)
+        assert np.array_equal(g.read_bytes(c.ep.rx_meta).view(np.uint32)[:world * cap], region)
+        assert np.array_equal(g.read_bytes(c.ids_rx).view(np.uint32), ids_rx)
+    del chains
