@@ -261,7 +261,14 @@ def main():
     x_kind = BF16 if args.activations == "bf16" else F32
     if args.workload == "gemm":
         args.tokens = args.tokens or [512, 2048, 8192]
-        print(json.dumps(run_gemm(torch, gpu, stream, args)), flush=True)
+        out = run_gemm(torch, gpu, stream, args, rank, world, local)
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier()
+            sys.stdout.flush()
+            os._exit(0)
         gpu.close()
         return
     if args.workload == "moe":
@@ -586,41 +593,85 @@ def run_moe(torch, gpu, stream, args, rank, world, local):
     gpu.close()
 
 
-def run_gemm(torch, gpu, stream, args):
+def run_gemm(torch, gpu, stream, args, rank=0, world=1, local=0):
     """The batched prefill dequant-GEMM: Q4_K 4096 -> 12288 and Q6_K 12288 -> 4096 against bf16
     activations of `--tokens` rows, timed alone with CUDA events; TFLOP/s against the measured
-    dense bf16 peak (burst figure: each shape is timed in isolation)."""
+    dense bf16 peak (burst figure: each shape is timed in isolation).  With N > 1 ranks the weight rows are
+    split (rank r multiplies rows [r R / N, (r + 1) R / N): block quantisation runs along K, so the GGUF
+    layout is kept), the activations are replicated, and an NCCL all-gather assembles Y on every rank as
+    [rank][token][rows / N]; both the multiplication alone and multiplication + all-gather are timed (max over
+    ranks), the same total work on more GPUs (strong scaling)."""
     from ingot_b200 import BF16, synth
+    from ingot_b200.chain import shard_rows
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
     peaks, peak_src = measured_peaks()
     rows_out = []
     launches = 0
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) * 1e-3 / args.steps
+        if world > 1:
+            t = torch.tensor([sec], device=f"cuda:{local}")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        return sec
+
     for kind, name, cols, rows in ((synth.Q4_K, "q4_k", 4096, 12288), (synth.Q6_K, "q6_k", 12288, 4096)):
-        raw = synth.random_matrix(kind, cols, rows, seed=5)
+        r0, r1 = shard_rows(rows, rank, world)
+        mine = r1 - r0
+        raw = synth.random_matrix(kind, cols, mine, seed=5 + 1000 * rank)
         w = gpu.bytes(raw)
         stride = synth.stride_of(kind, cols)
         for m in args.tokens:
             x = np.random.default_rng(m).normal(0, 1, (m, cols)).astype(np.float32)
             xb = gpu.bf16(x)
-            y = gpu.zeros(m * rows)
-            for _ in range(args.warmup):
-                gpu.gemm(None, w, cols, rows, stride, kind, 0, xb, m, BF16, out=y)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(args.steps):
-                gpu.gemm(None, w, cols, rows, stride, kind, 0, xb, m, BF16, out=y)
-            e1.record(stream)
-            torch.cuda.synchronize()
-            sec = e0.elapsed_time(e1) * 1e-3 / args.steps
+            y = gpu.zeros(m * mine)
+            whole = gpu.zeros(m * mine * world) if world > 1 else None
+
+            def multiply():
+                gpu.gemm(None, w, cols, mine, stride, kind, 0, xb, m, BF16, out=y)
+
+            def multiply_and_gather():
+                multiply()
+                dist.all_gather_into_tensor(_tensor_view(torch, whole.ptr, m * mine * world, local), _tensor_view(torch, y.ptr, m * mine, local))
+
+            sec = timed(multiply)
             launches += 2 * args.steps
             flops = 2.0 * m * cols * rows
-            rows_out.append({"kind": name, "cols": cols, "rows": rows, "tokens": m, "us": sec * 1e6,
-                             "tflops": flops / sec / 1e12, "frac": flops / sec / 1e12 / peaks["bf16_tflops"],
-                             "tok_per_s": m / sec})
-            for b in (xb, y):
-                b.release()
+            row = {"kind": name, "cols": cols, "rows": rows, "tokens": m, "us": sec * 1e6,
+                   "tflops": flops / sec / 1e12, "frac": flops / sec / 1e12 / (peaks["bf16_tflops"] * world),
+                   "tok_per_s": m / sec}
+            if world > 1:
+                sec_g = timed(multiply_and_gather)
+                row.update({"us_with_all_gather": sec_g * 1e6, "tok_per_s_with_all_gather": m / sec_g,
+                            "all_gather_bytes_per_rank": 4 * m * mine * (world - 1)})
+            rows_out.append(row)
+            for b in (xb, y, whole):
+                if b is not None:
+                    b.release()
         w.release()
-    return {"workload": "prefill dequant-GEMM (configs[4])", "unit": "TFLOP/s", "peak": peaks["bf16_tflops"],
+    head = max((r for r in rows_out if r["kind"] == "q4_k"), key=lambda r: r["tokens"])
+    return {"metric": "prefill tok/s, Q4_K 4096 -> 12288 dequant-GEMM at %d tokens" % head["tokens"],
+            "value": head["tok_per_s"], "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": head["us"] * 1e-3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 x dequantised bf16 weights, f32 accumulation", "data": "synthetic",
+            "config": {"workload": "prefill dequant-GEMM (configs[4])",
+                       "parallelism": "weight rows split over %d ranks, activations replicated" % world if world > 1 else "single GPU",
+                       "peak_source": peak_src},
+            "workload": "prefill dequant-GEMM (configs[4])", "unit_roofline": "TFLOP/s", "peak": peaks["bf16_tflops"],
             "peak_source": peak_src, "bound": "tensor", "gpu_launches": launches, "shapes": rows_out}
 
 

@@ -133,6 +133,21 @@ INGOT_API ingot_status ingot_synchronize(ingot_gpu *gpu);
 
 INGOT_API ingot_status ingot_buffer_alloc(ingot_gpu *gpu, size_t bytes, void **device_ptr);
 INGOT_API ingot_status ingot_buffer_free(ingot_gpu *gpu, void *device_ptr);
+
+/* Gpu::output and Gpu::configure_workspace (src/metal.rs:1278-1337): float32 output buffers from a
+ * size-keyed pool.  With no budget set (0, the default) ingot_output_alloc is a plain allocation.
+ * With a budget, a released buffer waits on the idle list of its exact length and the next
+ * request of that length takes it (a reuse); a request of a new length allocates, charged in
+ * 16 KiB pages, after giving up only as much idle capacity as it needs, largest buffers first;
+ * INGOT_INVALID "workspace live allocation exceeds budget" when leased buffers alone exceed it.
+ * A released buffer may still be read by work already enqueued on the handle's stream: its next
+ * holder's work is enqueued behind that.  ingot_workspace_statistics = workspace_statistics
+ * (src/metal.rs:1338-1342): cumulative allocations, reuses, managed bytes now, peak. */
+INGOT_API ingot_status ingot_gpu_configure_workspace(ingot_gpu *gpu, size_t limit_bytes);
+INGOT_API ingot_status ingot_output_alloc(ingot_gpu *gpu, size_t count_f32, float **device_ptr);
+INGOT_API ingot_status ingot_output_release(ingot_gpu *gpu, float *device_ptr);
+INGOT_API ingot_status ingot_workspace_statistics(const ingot_gpu *gpu, uint64_t *allocations, uint64_t *reuses,
+                                                  size_t *managed_bytes, size_t *peak_bytes);
 /* host -> device, asynchronous on the handle's stream when `host` is pinned */
 INGOT_API ingot_status ingot_buffer_upload(ingot_gpu *gpu, void *device_ptr, const void *host, size_t bytes);
 /* device -> host; returns after the copy has completed */
@@ -571,6 +586,30 @@ INGOT_API ingot_status ingot_weight_load(ingot_gpu *gpu, ingot_gguf *gguf, const
 INGOT_API ingot_status ingot_dequant_host(ingot_gpu *gpu, const void *data, size_t data_bytes, uint64_t cols,
                                           uint64_t rows, uint64_t count, uint32_t kind, uint64_t stride,
                                           float *out);
+
+/* Gpu::ffn (src/metal.rs:1634-1661) on device buffers: `count` stacked experts' SwiGLU FFN of the same
+ * input x[width]: gate and up are [count][inner][width], down is [count][width][inner], all of
+ * `kind`; scratch holds 3 x inner x count floats; expert_ids = 0 .. count - 1 on the device;
+ * out[count][width]. */
+INGOT_API ingot_status ingot_ffn(ingot_gpu *gpu, const void *gate, const void *up, const void *down, uint32_t width,
+                                 uint32_t inner, uint32_t count, uint32_t kind, const float *x, float *scratch,
+                                 const uint32_t *expert_ids, float *out);
+
+/* Gpu::moe(&[Matrix; 3], &[Matrix; 3], &Matrix, &[f32], &[f32]) (src/metal.rs:1663-1713) with host
+ * vectors: routed = the selected experts' gate, up, down stacked (count = weights), shared = the
+ * shared expert's three (count 1), shared_gate [1][width];
+ * out[j] = sum_e weights[e] routed_e[j] + sigmoid(shared_gate . x) shared[j].  Shape and
+ * finiteness errors are INGOT_INVALID with the reference's messages. */
+typedef struct ingot_host_matrix {
+    const void *data;
+    size_t bytes;
+    uint64_t cols, rows, count;
+    uint32_t kind;
+    uint64_t stride;
+} ingot_host_matrix;
+INGOT_API ingot_status ingot_moe_host(ingot_gpu *gpu, const ingot_host_matrix routed[3], const ingot_host_matrix shared[3],
+                                      const ingot_host_matrix *shared_gate, const float *input, size_t width,
+                                      const float *weights, size_t n_weights, float *out);
 
 /* Gpu::project(&Matrix, &[f32]) (src/metal.rs:1622-1632): count must be 1,
  * input finite and of length cols. */

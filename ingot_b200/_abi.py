@@ -101,6 +101,12 @@ SIGNATURES = {
     "ingot_command_begin": [vp],
     "ingot_command_end": [vp, C.POINTER(vp)],
     "ingot_command_submit": [vp, vp],
+    "ingot_gpu_configure_workspace": [vp, sz],
+    "ingot_output_alloc": [vp, sz, C.POINTER(vp)],
+    "ingot_output_release": [vp, vp],
+    "ingot_workspace_statistics": [vp, C.POINTER(u64), C.POINTER(u64), C.POINTER(sz), C.POINTER(sz)],
+    "ingot_ffn": [vp, vp, vp, vp, u32, u32, u32, u32, vp, vp, vp, vp],
+    "ingot_moe_host": [vp, vp, vp, vp, vp, sz, vp, sz, vp],
     "ingot_dequant_host": [vp, vp, sz, u64, u64, u64, u32, u64, vp],
     "ingot_project_host": [vp, vp, sz, u64, u64, u64, u32, u64, vp, sz, vp],
 }

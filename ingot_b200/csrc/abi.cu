@@ -6,8 +6,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <map>
 #include <new>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "gemv_core.cuh"
@@ -42,6 +44,11 @@ struct ingot_gpu {
     int scope_next = 0;               // stream of the next launch inside the scope: 0 = main, i > 0 = side[i - 1]
     int scope_used = 0;               // side streams touched in this scope (bit mask)
     std::vector<GemvCall> pending;    // one-token tensor-core projections of the open scope: they share one launch at its end
+    // the size-keyed pool of output buffers (the reference's Workspace: src/metal.rs:1278-1337)
+    size_t pool_limit = 0, pool_managed = 0, pool_peak = 0;
+    uint64_t pool_allocations = 0, pool_reuses = 0;
+    std::map<size_t, std::vector<void *>> pool_free;      // idle buffers by length
+    std::unordered_map<void *, size_t> pool_lengths;      // every buffer the pool manages, idle or leased
     // links of the next fused-norm projection to a tensor-parallel group (ingot_tp_signal_next / ingot_tp_wait_next)
     ingot_group *tp_signal_group = nullptr, *tp_wait_group = nullptr;
     uint32_t tp_signal_slot = 0, tp_wait_slot[2] = {0, 0};
@@ -232,6 +239,8 @@ void ingot_gpu_destroy(ingot_gpu *g) {
     if (g->status) cudaFree(g->status);
     if (g->workspace) cudaFree(g->workspace);
     for (void *p : g->retired) cudaFree(p);
+    for (auto &kv : g->pool_free)
+        for (void *p : kv.second) cudaFree(p);            // (leased output buffers belong to their holders)
     if (g->tc_scratch) cudaFree(g->tc_scratch);
     if (g->status_host) cudaFreeHost(g->status_host);
     delete g;
@@ -303,6 +312,76 @@ ingot_status ingot_buffer_free(ingot_gpu *g, void *p) {
     cudaSetDevice(g->device);
     cudaError_t e = cudaFree(p);
     if (e != cudaSuccess && !g->failed) return cuda_fail(g, e, "cudaFree");
+    return INGOT_OK;
+}
+
+// ---- output buffers from a size-keyed pool (Gpu::output / configure_workspace: src/metal.rs:1278-1337) ----
+
+static size_t allocation_charge(size_t length) { return (length + 16383u) / 16384u * 16384u; }      // charged by 16 KiB pages
+
+ingot_status ingot_gpu_configure_workspace(ingot_gpu *g, size_t limit_bytes) {
+    if (!g) return INGOT_INVALID;
+    g->pool_limit = limit_bytes;
+    return INGOT_OK;
+}
+
+ingot_status ingot_output_alloc(ingot_gpu *g, size_t count_f32, float **out) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!out) return fail(g, INGOT_INVALID, "null output pointer");
+    *out = nullptr;
+    if (count_f32 == 0 || count_f32 > (size_t)-1 / 4u) return fail(g, INGOT_INVALID, "output size overflow");
+    const size_t bytes = count_f32 * 4u;
+    if (g->pool_limit == 0) return ingot_buffer_alloc(g, bytes, reinterpret_cast<void **>(out));      // no budget: a plain allocation
+    auto idle = g->pool_free.find(bytes);
+    if (idle != g->pool_free.end() && !idle->second.empty()) {
+        *out = static_cast<float *>(idle->second.back());
+        idle->second.pop_back();
+        g->pool_reuses += 1;
+        return INGOT_OK;
+    }
+    const size_t charge = allocation_charge(bytes);
+    // give up only as much idle capacity as this allocation needs, largest buffers first
+    while (g->pool_managed + charge > g->pool_limit) {
+        auto largest = g->pool_free.end();
+        for (auto it = g->pool_free.begin(); it != g->pool_free.end(); ++it)
+            if (!it->second.empty()) largest = it;                     // (ordered by length: the last non-empty one)
+        if (largest == g->pool_free.end()) break;
+        void *victim = largest->second.back();
+        largest->second.pop_back();
+        g->pool_managed -= allocation_charge(largest->first);
+        g->pool_lengths.erase(victim);
+        cudaFree(victim);                                              // (waits for the device: nothing enqueued still uses it)
+    }
+    if (g->pool_managed + charge > g->pool_limit)
+        return fail(g, INGOT_INVALID, "workspace live allocation exceeds budget: " + std::to_string(g->pool_managed) + " + " +
+                                          std::to_string(charge) + " > " + std::to_string(g->pool_limit));
+    void *p = nullptr;
+    if ((st = ingot_buffer_alloc(g, bytes, &p))) return st;
+    g->pool_managed += charge;
+    if (g->pool_managed > g->pool_peak) g->pool_peak = g->pool_managed;
+    g->pool_allocations += 1;
+    g->pool_lengths[p] = bytes;
+    *out = static_cast<float *>(p);
+    return INGOT_OK;
+}
+
+ingot_status ingot_output_release(ingot_gpu *g, float *p) {
+    if (!g) return INGOT_INVALID;
+    if (!p) return INGOT_OK;
+    auto it = g->pool_lengths.find(p);
+    if (it == g->pool_lengths.end()) return ingot_buffer_free(g, p);   // allocated while no budget was set
+    // back on the idle list of its length; work already enqueued on the handle's stream runs before any later user's
+    g->pool_free[it->second].push_back(p);
+    return INGOT_OK;
+}
+
+ingot_status ingot_workspace_statistics(const ingot_gpu *g, uint64_t *allocations, uint64_t *reuses, size_t *managed, size_t *peak) {
+    if (!g) return INGOT_INVALID;
+    if (allocations) *allocations = g->pool_allocations;
+    if (reuses) *reuses = g->pool_reuses;
+    if (managed) *managed = g->pool_managed;
+    if (peak) *peak = g->pool_peak;
     return INGOT_OK;
 }
 
@@ -452,7 +531,7 @@ ingot_status ingot_matmul(ingot_gpu *g, const void *w, uint32_t cols, uint32_t r
     // (inside an independent scope the projections run concurrently and the GEMM's scratch is the handle's
     // one workspace: such calls take the GEMV in groups of four tokens, as the reference's project() does
     // for any count inside independent_projections, src/qwen.rs:822)
-    if (g && !g->no_mma && !g->force_plain && !g->in_scope && count > 4 && (kind == INGOT_KIND_Q4_K || kind == INGOT_KIND_Q6_K) && cols % 256u == 0 &&
+    if (g && !g->no_mma && !g->force_plain && !g->in_scope && count > 4 && (kind == INGOT_KIND_Q4_K || kind == INGOT_KIND_Q6_K || kind == INGOT_KIND_Q4_0) && cols % 256u == 0 &&
         ((uintptr_t)w % 16u) == 0 && (x_kind == INGOT_KIND_F32 || x_kind == INGOT_KIND_BF16))
         return ingot_gemm(g, w, cols, rows, stride, kind, expert, x, x_kind, count, y);
     return gemv_common(g, c, x_kind, "matmul");
@@ -485,7 +564,7 @@ ingot_status ingot_gemm(ingot_gpu *g, const void *w, uint32_t cols, uint32_t row
     if ((st = check_matrix(g, kind, cols, rows, stride))) return st;
     if (x_kind != INGOT_KIND_F32 && x_kind != INGOT_KIND_BF16) return fail(g, INGOT_UNSUPPORTED, "gemm: activations must be F32 or BF16");
     if (!w || !x || !y || count == 0) return fail(g, INGOT_INVALID, "gemm: bad arguments");
-    if ((kind != INGOT_KIND_Q4_K && kind != INGOT_KIND_Q6_K) || cols % 256u || ((uintptr_t)w % 16u))
+    if ((kind != INGOT_KIND_Q4_K && kind != INGOT_KIND_Q6_K && kind != INGOT_KIND_Q4_0) || cols % 256u || ((uintptr_t)w % 16u))
         return fail(g, INGOT_UNSUPPORTED, "gemm: no tensor-core kernel for this type or shape");
     if ((st = ensure_workspace(g, gemm_scratch_bytes(cols, rows, count, g->sm_count)))) return st;
     cudaError_t e = launch_gemm_dequant(static_cast<const uint8_t *>(w), cols, rows, stride, kind, expert, x,
@@ -504,7 +583,7 @@ ingot_status ingot_gate_up(ingot_gpu *g, const void *gate, const void *up, uint3
     c.count = count; c.nmat = 2; c.glu = gelu ? 2 : 1;
     // more than four tokens: two tensor-core GEMMs and the activation, as the reference's generic_gate_up
     // falls back to separate projections + glu for wide batches (src/metal_generic.rs:231-261)
-    if (g && !g->no_mma && !g->force_plain && !g->in_scope && count > 4 && (kind == INGOT_KIND_Q4_K || kind == INGOT_KIND_Q6_K) &&
+    if (g && !g->no_mma && !g->force_plain && !g->in_scope && count > 4 && (kind == INGOT_KIND_Q4_K || kind == INGOT_KIND_Q6_K || kind == INGOT_KIND_Q4_0) &&
         cols % 256u == 0 && ((uintptr_t)gate % 16u) == 0 && ((uintptr_t)up % 16u) == 0 &&
         (x_kind == INGOT_KIND_F32 || x_kind == INGOT_KIND_BF16) && gate && up && x && y) {
         ingot_status st = enter(g);
@@ -1277,6 +1356,84 @@ ingot_status ingot_project_host(ingot_gpu *g, const void *data, size_t data_byte
     cudaFree(y);
     if (!st)
         for (uint64_t i = 0; i < rows; ++i)
+            if (!isfinite(out[i])) return fail(g, INGOT_INVALID, "output contains non-finite values");
+    return st;
+}
+
+// Gpu::ffn (src/metal.rs:1634-1661) on device buffers: every stacked expert's SwiGLU FFN of the same input.
+ingot_status ingot_ffn(ingot_gpu *g, const void *gate, const void *up, const void *down, uint32_t width, uint32_t inner,
+                       uint32_t count, uint32_t kind, const float *x, float *scratch, const uint32_t *expert_ids, float *out) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!gate || !up || !down || !x || !scratch || !expert_ids || !out || count == 0)
+        return fail(g, INGOT_INVALID, "ffn: null pointer");
+    uint32_t block, bytes;
+    if (!geometry(kind, block, bytes)) return fail(g, INGOT_UNSUPPORTED, "GGML type " + std::to_string(kind) + " is unsupported");
+    if (width % block || inner % block || (uint64_t)inner * count > 0xffffffffull) return fail(g, INGOT_INVALID, "FFN matrix shapes do not match");
+    const uint32_t in_stride = width / block * bytes, down_stride = inner / block * bytes, n = inner * count;
+    // gate and up of the stacked experts are one tall matrix each over the same input
+    float *gv = scratch, *uv = scratch + n, *act = scratch + 2u * (size_t)n;
+    if ((st = ingot_matmul(g, gate, width, n, in_stride, kind, 0, x, INGOT_KIND_F32, 1, gv))) return st;
+    if ((st = ingot_matmul(g, up, width, n, in_stride, kind, 0, x, INGOT_KIND_F32, 1, uv))) return st;
+    if ((st = ingot_activation(g, gv, uv, n, 0, act))) return st;
+    // down: expert e multiplies its own slice of the activation (one input row per expert)
+    return ingot_routed(g, down, inner, width, down_stride, kind, count, act, INGOT_KIND_F32, expert_ids, 1, 1, count, out);
+}
+
+// Gpu::moe (src/metal.rs:1663-1713) with host vectors: the FFNs of the selected experts (stacked in `routed`, one
+// weight each) and of the shared expert, merged as sum_e w_e routed_e + sigmoid(shared_gate . x) shared.
+ingot_status ingot_moe_host(ingot_gpu *g, const ingot_host_matrix routed[3], const ingot_host_matrix shared[3],
+                            const ingot_host_matrix *shared_gate, const float *input, size_t width, const float *weights,
+                            size_t n_weights, float *out) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!routed || !shared || !shared_gate || !input || !weights || !out) return fail(g, INGOT_INVALID, "null pointer");
+    const ingot_host_matrix *all[7] = {&routed[0], &routed[1], &routed[2], &shared[0], &shared[1], &shared[2], shared_gate};
+    for (const ingot_host_matrix *m : all) {
+        if (!m->data) return fail(g, INGOT_INVALID, "null pointer");
+        if ((st = check_host_matrix(g, m->bytes, m->cols, m->rows, m->count, m->kind, m->stride))) return st;
+    }
+    bool finite = true;
+    for (size_t i = 0; i < width; ++i) finite = finite && isfinite(input[i]);
+    for (size_t i = 0; i < n_weights; ++i) finite = finite && isfinite(weights[i]);
+    if (!finite || routed[0].cols != width || shared[0].cols != width || shared[0].count != 1 || routed[0].count != n_weights ||
+        shared_gate->cols != width || shared_gate->rows != 1 || shared_gate->count != 1)
+        return fail(g, INGOT_INVALID, "MoE input shape mismatch");
+    for (const ingot_host_matrix *f : {routed, shared}) {
+        if (f[1].cols != f[0].cols || f[1].rows != f[0].rows || f[1].count != f[0].count || f[1].kind != f[0].kind ||
+            f[2].cols != f[0].rows || f[2].rows != f[0].cols || f[2].count != f[0].count || f[2].kind != f[0].kind)
+            return fail(g, INGOT_INVALID, "FFN matrix shapes do not match");
+    }
+    const uint32_t top = (uint32_t)n_weights, w32 = (uint32_t)width;
+    std::vector<void *> owned;
+    auto dev = [&](size_t bytes, const void *host) -> void * {
+        void *p = nullptr;
+        if (st) return p;
+        if ((st = ingot_buffer_alloc(g, bytes, &p))) return nullptr;
+        owned.push_back(p);
+        if (host) st = ingot_buffer_upload(g, p, host, bytes);
+        return p;
+    };
+    void *wdev[7];
+    for (int i = 0; i < 7; ++i) wdev[i] = dev(all[i]->bytes, all[i]->data);
+    float *x = static_cast<float *>(dev(width * 4u, input));
+    float *wts = static_cast<float *>(dev(n_weights * 4u, weights));
+    std::vector<uint32_t> iota(top > 1u ? top : 1u);
+    for (uint32_t i = 0; i < iota.size(); ++i) iota[i] = i;
+    uint32_t *ids = static_cast<uint32_t *>(dev(iota.size() * 4u, iota.data()));
+    const size_t n_r = (size_t)routed[0].rows * routed[0].count, n_s = (size_t)shared[0].rows;
+    float *scr_r = static_cast<float *>(dev(3u * n_r * 4u, nullptr)), *scr_s = static_cast<float *>(dev(3u * n_s * 4u, nullptr));
+    float *out_r = static_cast<float *>(dev((size_t)top * width * 4u, nullptr)), *out_s = static_cast<float *>(dev(width * 4u, nullptr));
+    float *logit = static_cast<float *>(dev(4u, nullptr)), *y = static_cast<float *>(dev(width * 4u, nullptr));
+    if (!st) st = ingot_ffn(g, wdev[0], wdev[1], wdev[2], w32, (uint32_t)routed[0].rows, top, routed[0].kind, x, scr_r, ids, out_r);
+    if (!st) st = ingot_ffn(g, wdev[3], wdev[4], wdev[5], w32, (uint32_t)shared[0].rows, 1, shared[0].kind, x, scr_s, ids, out_s);
+    if (!st) st = ingot_matmul(g, wdev[6], w32, 1, (uint32_t)shared_gate->stride, shared_gate->kind, 0, x, INGOT_KIND_F32, 1, logit);
+    if (!st) st = ingot_merge(g, out_r, out_s, wts, logit, w32, top, y);
+    if (!st) st = ingot_buffer_read(g, out, y, width * 4u);
+    if (!st) st = ingot_synchronize(g);
+    for (void *p : owned) cudaFree(p);
+    if (!st)
+        for (size_t i = 0; i < width; ++i)
             if (!isfinite(out[i])) return fail(g, INGOT_INVALID, "output contains non-finite values");
     return st;
 }

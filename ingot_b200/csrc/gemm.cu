@@ -197,6 +197,32 @@ __device__ __forceinline__ uint32_t ldg32_u2(const uint8_t *p) {
     return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
 }
 
+// Q4_0 (the reference's gemm_q4_0: generic_gemm instantiated at kernels/generic.metal:387): a thread's 32 columns
+// are one 18-byte block (binary16 d, then 16 bytes whose low nibbles are elements 0..15 and whose high nibbles are
+// elements 16..31; w = d (q - 8)).  Blocks are only 2-byte aligned.  Raw: d, then the four words of quants.
+__device__ __forceinline__ void load32_q40(const uint8_t *row, uint32_t ks, uint32_t half, GemmRaw &raw) {
+    const uint8_t *b = row + (size_t)(2u * ks + half) * 18u;
+    raw.w[0] = *reinterpret_cast<const unsigned short *>(b);
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) raw.w[1 + i] = ldg32_u2(b + 2u + 4u * i);
+}
+__device__ __forceinline__ void emit32_q40(const GemmRaw &raw, uint32_t half, uint8_t *dst_row_base, uint32_t r) {
+    const float d = __half2float(__ushort_as_half((unsigned short)raw.w[0]));
+#pragma unroll
+    for (uint32_t ch = 0; ch < 4; ++ch) {           // 8 columns: bytes 8 (ch % 2) .. + 7, low nibbles for ch < 2, high for the rest
+        uint32_t out[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 2; ++i) {
+            const uint32_t wq = (raw.w[1 + 2 * (ch & 1u) + i] >> (4u * (ch >> 1))) & 0x0f0f0f0fu;
+            const float p0 = __fmul_rn(d, (float)(int)(wq & 0xffu) - 8.0f), p1 = __fmul_rn(d, (float)(int)((wq >> 8) & 0xffu) - 8.0f);
+            const float p2 = __fmul_rn(d, (float)(int)((wq >> 16) & 0xffu) - 8.0f), p3 = __fmul_rn(d, (float)(int)(wq >> 24) - 8.0f);
+            out[2 * i] = pack_h2(p0, p1);
+            out[2 * i + 1] = pack_h2(p2, p3);
+        }
+        *reinterpret_cast<uint4 *>(dst_row_base + swz_off(r, 4u * half + ch)) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
 // 32 bytes at p, where p is CLS bytes (0, 2, 4 or 6) past an 8-byte boundary: four or five 64-bit loads and,
 // for the odd classes, funnel shifts.  The decode of Q6_K is bound by the number of its global loads.
 template <uint32_t CLS>
@@ -330,20 +356,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_dequant_tcgen05_kernel(c
         const uint32_t grp = threadIdx.x >> 8;
         const bool live = n0 + r < a.rows;
         const uint8_t *row = a.w + (size_t)(live ? n0 + r : 0) * a.stride;
-        const bool q4k = a.kind == KIND_Q4_K;
+        const bool q4k = a.kind == KIND_Q4_K, q40 = a.kind == KIND_Q4_0;
         const bool rows4 = (a.stride % 4u) == 0u, rows8 = (a.stride % 8u) == 0u;           // the weight base is 16-byte aligned
         GemmRaw cur = {}, nxt = {};
-        if (live && grp < ksteps) { if (q4k) load32_q4k(row, ks0 + grp, cur); else load32_q6k(row, ks0 + grp, half, rows4, rows8, cur); }
+        auto load = [&](uint32_t ks, GemmRaw &raw) {
+            if (q4k) load32_q4k(row, ks, raw);
+            else if (q40) load32_q40(row, ks, half, raw);
+            else load32_q6k(row, ks, half, rows4, rows8, raw);
+        };
+        if (live && grp < ksteps) load(ks0 + grp, cur);
         for (uint32_t ks = grp; ks < ksteps && !failed; ks += GEMM_DECODE_GROUPS) {
             const uint32_t s = ks % A_STAGES, ph = (ks / A_STAGES) & 1u;
-            if (live && ks + GEMM_DECODE_GROUPS < ksteps) {
-                if (q4k) load32_q4k(row, ks0 + ks + GEMM_DECODE_GROUPS, nxt);
-                else load32_q6k(row, ks0 + ks + GEMM_DECODE_GROUPS, half, rows4, rows8, nxt);
-            }
+            if (live && ks + GEMM_DECODE_GROUPS < ksteps) load(ks0 + ks + GEMM_DECODE_GROUPS, nxt);
             if (!ptx::mbar_wait_sleep<20>(&empty_a[s], ph ^ 1u)) { failed = true; break; }
             uint8_t *dst = tiles_a + (size_t)s * GEMM_A_BYTES;
             if (live) {
                 if (q4k) emit32_q4k(cur, ks0 + ks, half, dst, r);
+                else if (q40) emit32_q40(cur, half, dst, r);
                 else emit32_q6k(cur, ks0 + ks, half, dst, r);
             } else {
 #pragma unroll
@@ -480,7 +509,7 @@ size_t gemm_scratch_bytes(uint32_t cols, uint32_t rows, uint32_t tokens, uint32_
 cudaError_t launch_gemm_dequant(const uint8_t *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind, uint32_t expert,
                                 const void *x, uint32_t x_bf16, uint32_t tokens, float *y, void *x_half_scratch,
                                 const LaunchCtx &ctx) {
-    if (kind != KIND_Q4_K && kind != KIND_Q6_K) return cudaErrorNotSupported;
+    if (kind != KIND_Q4_K && kind != KIND_Q6_K && kind != KIND_Q4_0) return cudaErrorNotSupported;
     if (cols % 256u || tokens == 0 || rows == 0) return cudaErrorInvalidValue;
     if (((uintptr_t)w % 16u) || (stride % 2u) || (kind == KIND_Q4_K && stride % 16u)) return cudaErrorNotSupported;
     ToHalfArgs h = {x, static_cast<__half *>(x_half_scratch), (uint64_t)tokens * cols, x_bf16};

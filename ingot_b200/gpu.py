@@ -89,6 +89,7 @@ class Buffer:
     def __init__(self, gpu: "Gpu", ptr: int, nbytes: int, owner: "Buffer | None" = None):
         self.gpu, self.ptr, self.nbytes, self._owner = gpu, ptr, nbytes, owner
         self._owned = owner is None
+        self._pooled = False          # an output buffer: goes back to the handle's size-keyed pool
 
     def view_f32(self, offset: int, count: int) -> "Buffer":
         if offset < 0 or count < 0 or (offset + count) * 4 > self.nbytes:
@@ -102,7 +103,10 @@ class Buffer:
 
     def release(self) -> None:
         if self._owned and self.ptr and self.gpu._h:
-            self.gpu._lib.ingot_buffer_free(self.gpu._h, self.ptr)
+            if self._pooled:
+                self.gpu._lib.ingot_output_release(self.gpu._h, self.ptr)
+            else:
+                self.gpu._lib.ingot_buffer_free(self.gpu._h, self.ptr)
         self.ptr = 0
 
     def __del__(self):
@@ -135,6 +139,11 @@ class Graph:
                 self._g = 0
         except Exception:
             pass
+
+
+class _HostMatrix(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("bytes", C.c_size_t), ("cols", C.c_uint64), ("rows", C.c_uint64), ("count", C.c_uint64),
+                ("kind", C.c_uint32), ("stride", C.c_uint64)]
 
 
 class _RopeParams(C.Structure):
@@ -367,7 +376,23 @@ class Gpu:
         return b
 
     def output(self, n_f32: int) -> Buffer:
-        return self.empty_bytes(4 * n_f32)
+        """Gpu::output (src/metal.rs:1278-1333): a float32 buffer from the size-keyed pool (a plain allocation while
+        no workspace budget is set)."""
+        p = C.c_void_p()
+        self._check(self._lib.ingot_output_alloc(self._h, n_f32, C.byref(p)))
+        b = Buffer(self, p.value, 4 * n_f32)
+        b._pooled = True
+        return b
+
+    def configure_workspace(self, limit: int) -> None:
+        """Gpu::configure_workspace (src/metal.rs:1335-1337)."""
+        self._check(self._lib.ingot_gpu_configure_workspace(self._h, limit))
+
+    def workspace_statistics(self) -> tuple[int, int, int, int]:
+        """Cumulative new allocations, reuse count, current managed bytes and peak bytes (src/metal.rs:1338-1342)."""
+        a, r, m, pk = C.c_uint64(), C.c_uint64(), C.c_size_t(), C.c_size_t()
+        self._check(self._lib.ingot_workspace_statistics(self._h, C.byref(a), C.byref(r), C.byref(m), C.byref(pk)))
+        return a.value, r.value, m.value, pk.value
 
     def load_weight(self, data, t: Tensor) -> Buffer:
         raw = _as_u8(data)
@@ -654,44 +679,42 @@ class Gpu:
                                                  m.kind, m.stride, out.ctypes.data))
         return out[: m.cols * m.rows * m.count]
 
-    def _ffn(self, matrices, x: Buffer) -> Buffer:
+    def ffn(self, matrices, x: Buffer) -> Buffer:
         """Gpu::ffn (src/metal.rs:1634-1661): every stacked expert's SwiGLU FFN of the same input;
-        returns `count` rows of `down.rows` values."""
+        returns `count` rows of `down.rows` values (ingot_ffn on device buffers)."""
         gate, up, down = matrices
-        if (gate.cols, gate.rows, gate.count) != (up.cols, up.rows, up.count) or \
-                (down.cols, down.rows, down.count) != (gate.rows, gate.cols, gate.count):
+        if (gate.cols, gate.rows, gate.count, gate.kind) != (up.cols, up.rows, up.count, up.kind) or \
+                (down.cols, down.rows, down.count, down.kind) != (gate.rows, gate.cols, gate.count, gate.kind):
             raise InvalidData("FFN matrix shapes do not match")
-        n = gate.rows * gate.count
         bufs = [self.bytes(_as_u8(m.data)) for m in matrices]
-        # the stacked experts of gate and up are one tall matrix over the same input
-        g = self.matmul(None, bufs[0], gate.cols, n, gate.stride, gate.kind, 0, x, 1)
-        u = self.matmul(None, bufs[1], up.cols, n, up.stride, up.kind, 0, x, 1)
-        act = self.activation(None, g, u, n)
-        # down: expert e multiplies its own slice of the activation (one input row per pair)
+        scratch = self.empty_bytes(4 * 3 * gate.rows * gate.count)
         ids = self.bytes(np.arange(gate.count, dtype=np.uint32).view(np.uint8))
         out = self.output(down.rows * down.count)
-        self._check(self._lib.ingot_routed(self._h, bufs[2].ptr, down.cols, down.rows, down.stride, down.kind, down.count,
-                                           act.ptr, F32, ids.ptr, 1, 1, down.count, out.ptr))
+        self._check(self._lib.ingot_ffn(self._h, bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, gate.cols, gate.rows, gate.count, gate.kind,
+                                        x.ptr, scratch.ptr, ids.ptr, out.ptr))
+        self._check(self._lib.ingot_synchronize(self._h))          # the temporaries above are released on return
         return out
 
     def moe(self, routed, shared, shared_gate: Matrix, x, weights) -> np.ndarray:
         """Gpu::moe (src/metal.rs:1663-1713): the FFNs of the selected experts (stacked in `routed`, one
-        weight each) and of the shared expert, merged as sum_e w_e * routed_e + sigmoid(shared_gate . x) * shared."""
+        weight each) and of the shared expert, merged as sum_e w_e * routed_e + sigmoid(shared_gate . x) * shared
+        (ingot_moe_host does the checks and the work)."""
         xv = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
         wv = np.ascontiguousarray(weights, dtype=np.float32).reshape(-1)
-        for m in list(routed) + list(shared) + [shared_gate]:
-            self._validate(m)
-        width = xv.size
-        if not (np.isfinite(xv).all() and np.isfinite(wv).all()) or routed[0].cols != width or shared[0].cols != width \
-                or shared[0].count != 1 or routed[0].count != wv.size \
-                or (shared_gate.cols, shared_gate.rows, shared_gate.count) != (width, 1, 1):
-            raise InvalidData("MoE input shape mismatch")
-        xb = self.floats(xv)
-        routed_out = self._ffn(routed, xb)
-        shared_out = self._ffn(shared, xb)
-        logit = self.matmul(None, self.bytes(_as_u8(shared_gate.data)), width, 1, shared_gate.stride, shared_gate.kind, 0, xb, 1)
-        y = self.merge(None, routed_out, shared_out, self.floats(wv), logit, width, routed[0].count)
-        return self.finish(None, y)
+        keep = []
+
+        def host(m: Matrix) -> _HostMatrix:
+            raw = _as_u8(m.data)
+            keep.append(raw)
+            return _HostMatrix(raw.ctypes.data, raw.size, m.cols, m.rows, m.count, m.kind, m.stride)
+
+        r3 = (_HostMatrix * 3)(*[host(m) for m in routed])
+        s3 = (_HostMatrix * 3)(*[host(m) for m in shared])
+        sg = host(shared_gate)
+        out = np.empty(max(xv.size, 1), dtype=np.float32)
+        self._check(self._lib.ingot_moe_host(self._h, r3, s3, C.byref(sg), xv.ctypes.data, xv.size, wv.ctypes.data, wv.size,
+                                             out.ctypes.data))
+        return out[:xv.size]
 
     def _validate(self, m: Matrix) -> None:
         """validate_matrix (src/metal.rs:1602-1621) through the library's own layout check."""

@@ -6,8 +6,13 @@
 #   kernels/quant_tables.metal  (whole file, minus its two include lines)
 #   kernels/iq3_mix.metal:6-36  (mix_half .. mix_weight_at)
 #   kernels/moe.metal:6-89      (half_at, weight_at)
+# usage: build_ref.sh <path of the reference tree>   (or INGOT_REFERENCE in the environment)
 set -e
-REF="${1:-/root/reference}"
+REF="${1:-$INGOT_REFERENCE}"
+if [ -z "$REF" ] || [ ! -d "$REF/kernels" ]; then
+  echo "usage: $0 <path of the reference tree>" >&2
+  exit 2
+fi
 HERE="$(cd "$(dirname "$0")" && pwd)"
 mkdir -p "$HERE/_ref"
 {

@@ -65,3 +65,24 @@ def test_missing_library_is_a_loud_error(monkeypatch):
     monkeypatch.setattr(_abi, "LIB_PATH", "/nonexistent/libingot_cuda.so")
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         _abi.load()
+
+
+def test_rust_sys_bindings_name_every_declared_function():
+    """include/rust/ingot-cuda-sys/src/lib.rs is generated from the header: regenerating it changes nothing, and
+    it declares every INGOT_API function."""
+    import importlib.util
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rs_path = os.path.join(root, "include", "rust", "ingot-cuda-sys", "src", "lib.rs")
+    committed = open(rs_path).read()
+    header = open(os.path.join(root, "include", "ingot_cuda.h")).read()
+    header = re.sub(r"/\*.*?\*/", " ", header, flags=re.S)
+    declared = set(re.findall(r"INGOT_API\s+[^;{]*?\b(ingot_\w+)\s*\(", header))
+    bound = set(re.findall(r"pub fn (ingot_\w+)\(", committed))
+    assert declared and declared == bound, sorted(declared ^ bound)
+    spec = importlib.util.spec_from_file_location("gen_sys", os.path.join(root, "include", "rust", "gen_sys.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    gen.main()
+    assert open(rs_path).read() == committed, "run python include/rust/gen_sys.py"

@@ -472,7 +472,7 @@ def test_moe_layer_matches_oracle_and_expert_shards_sum_to_it(gpu):
 
 # ---- prefill GEMM on the tensor cores ------------------------------------------------------
 
-@pytest.mark.parametrize("kind", [Q4_K, Q6_K])
+@pytest.mark.parametrize("kind", [Q4_K, Q6_K, Q4_0])
 @pytest.mark.parametrize("cols,rows,tokens", [(256, 128, 16), (512, 200, 70), (1024, 128, 256), (2560, 37, 32), (4096, 300, 513),
                                               (512, 128, 300), (768, 140, 600)])
 def test_gemm_matches_f16_staged_expectation(gpu, kind, cols, rows, tokens):
@@ -502,10 +502,10 @@ def test_gemm_random_activations_and_unsupported_shapes(gpu):
     exact = O.matvec_f64(raw, cols, rows, Q4_K, x)
     assert np.abs(y - exact).max() <= 2e-3 * np.abs(exact).max()                       # F16 staging: ~1e-3 of full precision
     with pytest.raises(InvalidData):
-        gpu.gemm(None, w, cols, rows, synth.stride_of(Q4_K, cols), Q4_0, 0, xb, tokens)          # layout mismatch
-    w0 = gpu.bytes(synth.random_matrix(Q4_0, 256, 8, seed=1))
+        gpu.gemm(None, w, cols, rows, synth.stride_of(Q4_K, cols), Q6_K, 0, xb, tokens)          # layout mismatch
+    w0 = gpu.bytes(synth.random_matrix(Q8_0, 256, 8, seed=1))
     with pytest.raises(InvalidData):
-        gpu.gemm(None, w0, 256, 8, synth.stride_of(Q4_0, 256), Q4_0, 0, xb, 8)                   # no tensor-core kernel
+        gpu.gemm(None, w0, 256, 8, synth.stride_of(Q8_0, 256), Q8_0, 0, xb, 8)                   # no tensor-core kernel
 
 
 # ---- one-token GEMV on the tcgen05 int8 tensor cores -----------------------------------------
