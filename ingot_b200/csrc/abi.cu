@@ -998,6 +998,11 @@ ingot_status ingot_group_create(ingot_gpu *g, uint32_t rank, uint32_t world, siz
         return cuda_fail(g, e, "group_create");
     }
     gr->peer[rank] = static_cast<uint8_t *>(p);
+    if ((e = preload_exchange_kernels()) != cudaSuccess) {      // a first step must not spend a peer's bounded wait loading modules
+        cudaFree(p);
+        delete gr;
+        return cuda_fail(g, e, "group_create");
+    }
     *out = gr;
     return INGOT_OK;
 }

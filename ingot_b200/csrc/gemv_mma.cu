@@ -785,7 +785,14 @@ struct MmaTile {
 // CW consumer warps in groups of eight: a group splits the columns of a tile among its warps and takes
 // every (CW / 8)-th tile, so with sixteen warps two stages of the ring are in work at once.
 // TK > 1: `tile` names up to TK pairs of one expert; their rows sit TK deep in shared memory (p.x_row_stride apart).
-template <uint32_t KIND, int NMAT, int XM, int CW = MMA_WARPS, int TK = 1>
+// (LINK: the kernel exchanges row shards with other GPUs — tagged words out, tagged inputs in.  It is a template
+// parameter because the polling loads would otherwise sit in every launch's prologue, whose time is
+// instruction fetch: with them the single-GPU step ran 2.79 ms instead of 2.28 ms.  For the same reason which
+// of the two normalised inputs is tagged is known at compile time in the common cases, so a prologue holds
+// one form of each input's loads: LINK_OUT = plain inputs, LINK_A / LINK_B = that input tagged, LINK_ANY =
+// decided at run time.)
+enum { LINK_NONE = 0, LINK_OUT = 1, LINK_A = 2, LINK_B = 3, LINK_ANY = 4 };
+template <uint32_t KIND, int NMAT, int XM, int CW = MMA_WARPS, int TK = 1, int LINK = LINK_NONE>
 __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, const uint32_t cta, const uint32_t nctas, const uint32_t pair,
                                               const bool whole_tiles, MmaRun &run, const MmaTile *tile = nullptr) {
     const MmaPlan &p = a.plan;
@@ -938,15 +945,17 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         const uint32_t tid = threadIdx.x, n4 = p.cols >> 2;
         // inputs assembled from every rank's rows are read from their tagged twins, polling until each word carries
         // this step's tag (bounded; on a time-out the step goes on with what is there and the status word tells)
-        const uint64_t *const ta = a.tp.in[0], *const tb = a.tp.in[1];
+        const uint64_t *const ta = (LINK == LINK_A || LINK == LINK_ANY) ? a.tp.in[0] : nullptr;
+        const uint64_t *const tb = (LINK == LINK_B || LINK == LINK_ANY) ? a.tp.in[1] : nullptr;
+        const bool use_ta = LINK == LINK_A || (LINK == LINK_ANY && ta), use_tb = LINK == LINK_B || (LINK == LINK_ANY && tb);
         uint32_t tag_a = 0, tag_b = 0;
-        if (ta || tb) {
+        if (use_ta || use_tb) {
             const uint32_t step = *reinterpret_cast<const volatile uint32_t *>(a.tp.step);
             tag_a = step * a.tp.tag_mul + a.tp.in_tag[0];
             tag_b = step * a.tp.tag_mul + a.tp.in_tag[1];
         }
         // (a wait that ran out earlier in the step has set the status word: do not wait again)
-        bool gave_up = (ta || tb) && a.status && *reinterpret_cast<const volatile int *>(a.status) != 0;
+        bool gave_up = (use_ta || use_tb) && a.status && *reinterpret_cast<const volatile int *>(a.status) != 0;
         auto poll = [&](auto pass) {                   // pass() issues a batch of loads and says whether all were this step's
             uint64_t t0 = 0;
             for (uint32_t spins = 1; !pass() && !gave_up; ++spins) {
@@ -965,10 +974,10 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
         auto load = [&](uint32_t j) {
             // (read through L2: in a kernel that runs several projections the vectors come from other CTAs)
             float4 v, o;
-            if (ta) poll([&] { return tagged_load4(ta, j, tag_a, v); });
+            if (use_ta) poll([&] { return tagged_load4(ta, j, tag_a, v); });
             else v = __ldcg(a4 + j);
             if (b4) {
-                if (tb) poll([&] { return tagged_load4(tb, j, tag_b, o); });
+                if (use_tb) poll([&] { return tagged_load4(tb, j, tag_b, o); });
                 else o = __ldcg(b4 + j);
                 v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
             }
@@ -996,7 +1005,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             float sum = 0.f;
             // all loads of the row first, nothing that depends on one of them in between: one trip to L2 for the
             // whole row (a store of the residual sum after each load would make every load wait for the one before)
-            if (ta) {
+            if (use_ta) {
                 poll([&] {
                     bool all = true;
 #pragma unroll
@@ -1018,7 +1027,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
 #pragma unroll
                 for (uint32_t i0 = 0; i0 < NV; i0 += 4u) {
                     float4 o[4];
-                    if (tb) {
+                    if (use_tb) {
                         poll([&] {
                             bool all = true;
 #pragma unroll
@@ -1119,7 +1128,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     // the tile, and it sums tile T only after its own work on tile T + 1, when the partials are
     // long complete: no warp falls behind the others at a tile boundary.
     const uint32_t tile_base = run.tiles;          // position of this projection's first tile in the partial-sum ring
-    const uint32_t out_tag = a.tp.n_out ? *reinterpret_cast<const volatile uint32_t *>(a.tp.step) * a.tp.tag_mul + a.tp.out_tag : 0u;
+    const uint32_t out_tag = LINK && a.tp.n_out ? *reinterpret_cast<const volatile uint32_t *>(a.tp.step) * a.tp.tag_mul + a.tp.out_tag : 0u;
     auto sum_tile = [&](uint32_t tile) -> bool {
         const uint32_t ring = tile_base + tile;
         if (((ring ^ kw) & kmask) != 0u) return true;                  // another warp's turn
@@ -1145,7 +1154,7 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
             if (lrow < nrows && lane < 16u) {
                 const float out = NMAT == 2 ? glu_f(sum, other, a.glu == 2) : sum;
                 y[(size_t)ti * p.rows + row0 + lrow] = out;
-                if (a.tp.n_out) {                      // the row's tagged word, whole, into every rank's twin (NVLink stores)
+                if (LINK && a.tp.n_out) {              // the row's tagged word, whole, into every rank's twin (NVLink stores)
                     const uint64_t word = ((uint64_t)out_tag << 32) | __float_as_uint(out);
                     for (uint32_t pr = 0; pr < a.tp.n_out; ++pr)
                         asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.tp.out[pr] + (size_t)ti * p.rows + row0 + lrow), "l"(word) : "memory");
@@ -1242,11 +1251,11 @@ __device__ __forceinline__ bool gemv_mma_body(const MmaArgs &a, uint8_t *smem, c
     return true;
 }
 
-template <uint32_t KIND, int NMAT, int OCC, int XM>
+template <uint32_t KIND, int NMAT, int OCC, int XM, int LINK = LINK_NONE>
 __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     MmaRun run;
-    gemv_mma_body<KIND, NMAT, XM>(a, smem, blockIdx.x, gridDim.x, blockIdx.y, false, run);
+    gemv_mma_body<KIND, NMAT, XM, MMA_WARPS, 1, LINK>(a, smem, blockIdx.x, gridDim.x, blockIdx.y, false, run);
 }
 
 // Routed projections grouped by expert (the reference's packed MoE path for more than four tokens:
@@ -1351,7 +1360,7 @@ struct MmaGroupArgs {
 
 // Two CTAs per SM: the Q6_K step needs the registers, and a three-per-SM form without it (smaller
 // rings, a few spills) measured slower on an all-Q4_0 group (11.2 us against 6.7 us).
-template <int XM>
+template <int XM, int LINK = LINK_NONE>
 __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_group_kernel(const __grid_constant__ MmaGroupArgs ga) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint32_t i = 0;
@@ -1360,10 +1369,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_group_kernel(const __
     const uint32_t cta = blockIdx.x - ga.first[i], nctas = ga.first[i + 1] - ga.first[i];
     MmaRun run;
     switch (a.plan.kind) {
-    case KIND_Q4_K: gemv_mma_body<KIND_Q4_K, 1, XM>(a, smem, cta, nctas, 0u, true, run); break;
-    case KIND_Q6_K: gemv_mma_body<KIND_Q6_K, 1, XM>(a, smem, cta, nctas, 0u, true, run); break;
-    case KIND_Q4_0: gemv_mma_body<KIND_Q4_0, 1, XM>(a, smem, cta, nctas, 0u, true, run); break;
-    default: gemv_mma_body<KIND_Q8_0, 1, XM>(a, smem, cta, nctas, 0u, true, run); break;
+    case KIND_Q4_K: gemv_mma_body<KIND_Q4_K, 1, XM, MMA_WARPS, 1, LINK>(a, smem, cta, nctas, 0u, true, run); break;
+    case KIND_Q6_K: gemv_mma_body<KIND_Q6_K, 1, XM, MMA_WARPS, 1, LINK>(a, smem, cta, nctas, 0u, true, run); break;
+    case KIND_Q4_0: gemv_mma_body<KIND_Q4_0, 1, XM, MMA_WARPS, 1, LINK>(a, smem, cta, nctas, 0u, true, run); break;
+    default: gemv_mma_body<KIND_Q8_0, 1, XM, MMA_WARPS, 1, LINK>(a, smem, cta, nctas, 0u, true, run); break;
     }
 }
 
@@ -1759,9 +1768,9 @@ bool try_launch_gemv_mt(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &er
 // launch
 // ---------------------------------------------------------------------------
 
-template <uint32_t KIND, int NMAT, int OCC, int XM>
+template <uint32_t KIND, int NMAT, int OCC, int XM, int LINK = LINK_NONE>
 static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl) {
-    auto kernel = gemv_mma_kernel<KIND, NMAT, OCC, XM>;
+    auto kernel = gemv_mma_kernel<KIND, NMAT, OCC, XM, LINK>;
     static DeviceOnce once;
     {
         const cudaError_t e = once.smem(kernel, (int)(OCC == 3 ? MMA_SMEM_SMALL : MMA_SMEM_MAX));
@@ -1780,14 +1789,33 @@ static cudaError_t launch_mma_t(const MmaArgs &a, dim3 grid, cudaStream_t stream
     return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
-template <uint32_t KIND, int XM>
+template <uint32_t KIND, int XM, int LINK = LINK_NONE>
 static cudaError_t launch_mma_h(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl, int occ) {
     if (occ == 3)
-        return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 3, XM>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 3, XM>(a, grid, stream, pdl);
-    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 2, XM>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 2, XM>(a, grid, stream, pdl);
+        return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 3, XM, LINK>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 3, XM, LINK>(a, grid, stream, pdl);
+    return a.plan.nmat == 2 ? launch_mma_t<KIND, 2, 2, XM, LINK>(a, grid, stream, pdl) : launch_mma_t<KIND, 1, 2, XM, LINK>(a, grid, stream, pdl);
+}
+// Which form of the exchange a projection needs (the specialised forms exist for the K-quant matrices with
+// bfloat16-rounded rows, what a sharded decode step runs; everything else takes the run-time form).
+static int link_of(const MmaArgs &a) {
+    if (!a.tp.n_out && !a.tp.in[0] && !a.tp.in[1]) return LINK_NONE;
+    if (a.plan.xm != XM_FX2 || (a.plan.kind != KIND_Q4_K && a.plan.kind != KIND_Q6_K)) return LINK_ANY;
+    if (a.tp.in[0] && a.tp.in[1]) return LINK_ANY;
+    return a.tp.in[0] ? LINK_A : a.tp.in[1] ? LINK_B : LINK_OUT;
 }
 template <uint32_t KIND>
 static cudaError_t launch_mma_k(const MmaArgs &a, dim3 grid, cudaStream_t stream, bool pdl, int occ) {
+    const int link = link_of(a);
+    if (link != LINK_NONE) {              // the exchange lives in the fused-norm (fixed-point row) forms only
+        if constexpr (KIND == KIND_Q4_K || KIND == KIND_Q6_K) {
+            if (link == LINK_OUT) return launch_mma_h<KIND, XM_FX2, LINK_OUT>(a, grid, stream, pdl, occ);
+            if (link == LINK_A) return launch_mma_h<KIND, XM_FX2, LINK_A>(a, grid, stream, pdl, occ);
+            if (link == LINK_B) return launch_mma_h<KIND, XM_FX2, LINK_B>(a, grid, stream, pdl, occ);
+        }
+        if (a.plan.xm == XM_FX2) return launch_mma_h<KIND, XM_FX2, LINK_ANY>(a, grid, stream, pdl, occ);
+        if (a.plan.xm == XM_FX4) return launch_mma_h<KIND, XM_FX4, LINK_ANY>(a, grid, stream, pdl, occ);
+        return cudaErrorInvalidValue;
+    }
     switch (a.plan.xm) {
     case XM_F16: return launch_mma_h<KIND, XM_F16>(a, grid, stream, pdl, occ);
     case XM_F16_HI: return launch_mma_h<KIND, XM_F16_HI>(a, grid, stream, pdl, occ);
@@ -1894,9 +1922,9 @@ bool gemv_mma_group_eligible(const GemvCall &c, const LaunchCtx &ctx) {
     return plan_mma(c.kind, c.cols, c.rows, c.stride, 1, 2u * ctx.sm_count, MMA_SMEM_BUDGET, x_mode_of(c, false), plan);
 }
 
-template <int XM>
+template <int XM, int LINK = LINK_NONE>
 static cudaError_t launch_mma_group_t(const MmaGroupArgs &ga, uint32_t smem_bytes, cudaStream_t stream, bool pdl) {
-    auto kernel = gemv_mma_group_kernel<XM>;
+    auto kernel = gemv_mma_group_kernel<XM, LINK>;
     static DeviceOnce once;
     {
         const cudaError_t e = once.smem(kernel, (int)MMA_SMEM_BUDGET);
@@ -1913,6 +1941,35 @@ static cudaError_t launch_mma_group_t(const MmaGroupArgs &ga, uint32_t smem_byte
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, ga);
+}
+
+// Loads the exchange forms of the kernels onto the current device.  A module is otherwise loaded at a kernel's
+// first launch, which can take longer than a peer's bounded wait for this rank's rows in the very first step.
+template <uint32_t KIND, int XM, int LINK>
+static cudaError_t preload_link_kind() {
+    cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<KIND, 1, 3, XM, LINK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_SMALL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<KIND, 2, 3, XM, LINK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_SMALL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<KIND, 1, 2, XM, LINK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_MAX);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<KIND, 2, 2, XM, LINK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_MAX);
+    return e;
+}
+cudaError_t preload_exchange_kernels() {
+    cudaError_t e = preload_link_kind<KIND_Q4_K, XM_FX2, LINK_OUT>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q4_K, XM_FX2, LINK_A>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q4_K, XM_FX2, LINK_B>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q6_K, XM_FX2, LINK_OUT>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q6_K, XM_FX2, LINK_A>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q6_K, XM_FX2, LINK_B>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q4_K, XM_FX2, LINK_ANY>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q6_K, XM_FX2, LINK_ANY>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q4_K, XM_FX4, LINK_ANY>();
+    if (e == cudaSuccess) e = preload_link_kind<KIND_Q6_K, XM_FX4, LINK_ANY>();
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_group_kernel<XM_FX2, LINK_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_BUDGET);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_group_kernel<XM_FX2, LINK_A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_BUDGET);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_group_kernel<XM_FX2, LINK_B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_BUDGET);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_group_kernel<XM_FX2, LINK_ANY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_BUDGET);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_group_kernel<XM_FX4, LINK_ANY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM_BUDGET);
+    return e;
 }
 
 // Launches 2..MMA_GROUP_MAX eligible calls as one grid.  False (nothing launched) when they
@@ -1967,6 +2024,26 @@ bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCt
         a.tp = c.tp;
         ga.first[k + 1] = ga.first[k] + ctas;
         if (plan.smem_bytes > smem_bytes) smem_bytes = plan.smem_bytes;
+    }
+    // the parts of a scope read the same inputs (q, k, v of a layer): one form of the exchange when every part has
+    // the same input tagged, else the run-time form (a part without an output side just has n_out = 0)
+    bool linked = false, any_a = false, any_b = false, all_a = true, all_b = true;
+    for (uint32_t i = 0; i < ga.n; ++i) {
+        const TpLink &t = ga.part[i].tp;
+        linked = linked || t.n_out || t.in[0] || t.in[1];
+        any_a = any_a || t.in[0]; all_a = all_a && t.in[0];
+        any_b = any_b || t.in[1]; all_b = all_b && t.in[1];
+    }
+    const int link = !linked ? LINK_NONE : (any_a && any_b) ? LINK_ANY : any_a ? (all_a ? LINK_A : LINK_ANY)
+                                         : any_b ? (all_b ? LINK_B : LINK_ANY) : LINK_OUT;
+    if (link != LINK_NONE) {
+        if (xm0 == XM_FX2 && link == LINK_OUT) err = launch_mma_group_t<XM_FX2, LINK_OUT>(ga, smem_bytes, ctx.stream, ctx.pdl);
+        else if (xm0 == XM_FX2 && link == LINK_A) err = launch_mma_group_t<XM_FX2, LINK_A>(ga, smem_bytes, ctx.stream, ctx.pdl);
+        else if (xm0 == XM_FX2 && link == LINK_B) err = launch_mma_group_t<XM_FX2, LINK_B>(ga, smem_bytes, ctx.stream, ctx.pdl);
+        else if (xm0 == XM_FX2) err = launch_mma_group_t<XM_FX2, LINK_ANY>(ga, smem_bytes, ctx.stream, ctx.pdl);
+        else if (xm0 == XM_FX4) err = launch_mma_group_t<XM_FX4, LINK_ANY>(ga, smem_bytes, ctx.stream, ctx.pdl);
+        else err = cudaErrorInvalidValue;
+        return true;
     }
     switch (xm0) {
     case XM_F16: err = launch_mma_group_t<XM_F16>(ga, smem_bytes, ctx.stream, ctx.pdl); break;

@@ -108,6 +108,8 @@ cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);
 bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
 // Several independent one-token projections as one grid (2..4 calls that gemv_mma_group_eligible accepts).
 bool gemv_mma_group_eligible(const GemvCall &c, const LaunchCtx &ctx);
+// Loads the kernels a tensor-parallel group's projections use onto the current device (before the first step).
+cudaError_t preload_exchange_kernels();
 bool try_launch_gemv_mma_group(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx, cudaError_t &err);
 // A recorded sequence of one-token fused-norm projections run by one persistent kernel: built once
 // (device copies of the projection list and its completion counters), launched any number of times.
