@@ -296,6 +296,7 @@ cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx) {
         cudaError_t e = cudaSuccess;
         if (ctx.use_tc && try_launch_gemv_tc(c, ctx, e)) return e;
         if (try_launch_gemv_mma(c, ctx, e)) return e;
+        if (try_launch_gemv_rows(c, ctx, e)) return e;          // 2+ float32 rows: batch-invariant with the one-token kernel
     }
     if (!ctx.force_plain && aligned) {
         // tokens go through in groups the activations' shared-memory area can hold

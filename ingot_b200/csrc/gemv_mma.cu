@@ -141,7 +141,8 @@ struct MmaFixed {
 static constexpr uint32_t MMA_TILE_TOKENS = 4;      // pairs of one expert multiplied per pass over its rows
 
 static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t nmat, uint32_t max_ctas,
-                     uint32_t budget, uint32_t xm, MmaPlan &p, const MmaFixed *common = nullptr, uint32_t tokens = 1) {
+                     uint32_t budget, uint32_t xm, MmaPlan &p, const MmaFixed *common = nullptr, uint32_t tokens = 1,
+                     uint32_t x_rows = 0) {
     if (!mma_kind(kind)) return false;
     uint32_t block, bytes;
     geometry(kind, block, bytes);
@@ -157,7 +158,9 @@ static bool plan_mma(uint32_t kind, uint32_t cols, uint32_t rows, uint32_t strid
     const uint32_t per_warp = p.nsteps >> kw;                 // steps each warp owns per row
     p.xm = xm;
     p.x_row_stride = (x_row_bytes(xm, cols) + 15u) & ~15u;
-    p.x_bytes = common ? common->x_bytes : tokens > 1 ? tokens * p.x_row_stride : x_row_bytes(xm, cols);
+    // (a multi-token kernel keeps `tokens` partial sums per row; x_rows of them, all by default, have their
+    // activation rows resident at a time)
+    p.x_bytes = common ? common->x_bytes : tokens > 1 ? (x_rows ? x_rows : tokens) * p.x_row_stride : x_row_bytes(xm, cols);
     if (common && x_row_bytes(xm, cols) > common->x_bytes) return false;
     // the int8 steps of the K-quants read 8 bytes per lane
     const uint32_t lead = (xm >= XM_FX2 && (kind == KIND_Q4_K || kind == KIND_Q6_K)) ? 32u : 16u;
@@ -1267,27 +1270,32 @@ __global__ void __launch_bounds__(MMA_THREADS, OCC) gemv_mma_kernel(const __grid
 // or taken in packed order (down); results go to packed rows.
 struct MmaTileArgs {
     MmaArgs a;
-    const uint32_t *tiles;       // [capacity][4] = expert, first, pairs, mode
+    const uint32_t *tiles;       // [capacity][4] = expert, first, pairs, mode; null: ONE tile of dense rows (below)
     const uint32_t *pairs;       // packed position -> pair index
     uint32_t gather;
+    uint32_t dense_expert, dense_rows;     // without a table: rows 0 .. dense_rows - 1 of x against this expert
+    uint32_t per_pass;                     // activation rows per pass over the weights (at most MMA_TILE_TOKENS)
 };
 
 template <uint32_t KIND, int NMAT>
 __global__ void __launch_bounds__(MMA_THREADS, 2) gemv_mma_tiles_kernel(const __grid_constant__ MmaTileArgs ta) {
     extern __shared__ __align__(128) uint8_t smem[];
     ptx::pdl_wait();                                   // the grouping tables come from the kernels before
-    const uint32_t *tl = ta.tiles + 4u * blockIdx.y;
-    const uint32_t expert = tl[0], first = tl[1], n = tl[2];
+    uint32_t expert = ta.dense_expert, first = 0u, n = ta.dense_rows;
+    if (ta.tiles) {
+        const uint32_t *tl = ta.tiles + 4u * blockIdx.y;
+        expert = tl[0]; first = tl[1]; n = tl[2];
+    }
     if (n == 0) return;                                // unused tile
     if (expert >= ta.a.n_experts) {
         if (threadIdx.x == 0) set_status_word(ta.a.status, KERNEL_ERR_EXPERT_RANGE);
         return;
     }
     MmaRun run;
-    for (uint32_t tok0 = 0; tok0 < n; tok0 += MMA_TILE_TOKENS) {
+    for (uint32_t tok0 = 0; tok0 < n; tok0 += ta.per_pass) {
         // the rows of the pass before are rebuilt: every consumer warp must be through with them
         if (tok0 && threadIdx.x < MMA_WARPS * 32) ptx::named_bar_sync(5, MMA_WARPS * 32);
-        MmaTile tile = {expert, first + tok0, n - tok0 < MMA_TILE_TOKENS ? n - tok0 : MMA_TILE_TOKENS, ta.gather, ta.pairs};
+        MmaTile tile = {expert, first + tok0, n - tok0 < ta.per_pass ? n - tok0 : ta.per_pass, ta.gather, ta.pairs};
         if (!gemv_mma_body<KIND, NMAT, XM_FX4, MMA_WARPS, (int)MMA_TILE_TOKENS>(ta.a, smem, blockIdx.x, gridDim.x, blockIdx.y, false, run, &tile)) return;
     }
 }
@@ -1336,8 +1344,45 @@ bool try_launch_gemv_tiles(const GemvCall &c, const uint32_t *tiles, const uint3
     a.w[0] = c.w[0]; a.w[1] = c.w[1]; a.y = c.y;
     a.n_experts = c.n_experts; a.top = c.top ? c.top : 1u; a.glu = c.glu; a.status = ctx.status;
     a.na = static_cast<const float *>(c.x); a.npack = 1u;
-    ta.tiles = tiles; ta.pairs = pairs; ta.gather = gather ? 1u : 0u;
+    ta.tiles = tiles; ta.pairs = pairs; ta.gather = gather ? 1u : 0u; ta.per_pass = MMA_TILE_TOKENS;
     const dim3 grid(ctas, tile_capacity);
+    switch (c.kind) {
+    case KIND_Q4_K: err = c.nmat == 2 ? launch_tiles_t<KIND_Q4_K, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q4_K, 1>(ta, grid, ctx.stream, ctx.pdl); break;
+    case KIND_Q6_K: err = c.nmat == 2 ? launch_tiles_t<KIND_Q6_K, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q6_K, 1>(ta, grid, ctx.stream, ctx.pdl); break;
+    case KIND_Q4_0: err = c.nmat == 2 ? launch_tiles_t<KIND_Q4_0, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q4_0, 1>(ta, grid, ctx.stream, ctx.pdl); break;
+    default: err = c.nmat == 2 ? launch_tiles_t<KIND_Q8_0, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q8_0, 1>(ta, grid, ctx.stream, ctx.pdl); break;
+    }
+    return true;
+}
+
+// Two or more float32 activation rows against ONE dense matrix: the rows are a single tile of the kernel above, so
+// the weights stream once per four rows and every row's result has the bits the one-token kernel gives it (the
+// reference's property that a token's projection does not depend on its batch: src/expert_bench.rs:698-712).
+bool try_launch_gemv_rows(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err) {
+    if (c.ids || c.count < 2 || !mma_kind(c.kind) || c.cols % 64u || c.x_packed || c.x_bf16 || ((uintptr_t)c.x % 16u) || c.norm_a) return false;
+    if (((uintptr_t)c.w[0] % 16u) || (c.nmat == 2 && ((uintptr_t)c.w[1] % 16u)) || ((size_t)c.rows * c.stride) % 16u) return false;
+    MmaPlan plan;
+    // as many rows per pass as fit beside the ring (wide rows: 12288 columns take 55 KB each): four, two or one
+    uint32_t per_pass = c.count < MMA_TILE_TOKENS ? c.count : MMA_TILE_TOKENS;
+    bool ok = false, one_per_sm = false;
+    for (; per_pass >= 1 && !ok; per_pass = ok ? per_pass : per_pass / 2u) {
+        ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, 1u, MMA_SMEM_BUDGET, XM_FX4, plan, nullptr, MMA_TILE_TOKENS, per_pass);
+        if (!ok && (ok = plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, 1u, MMA_SMEM_MAX, XM_FX4, plan, nullptr, MMA_TILE_TOKENS, per_pass)))
+            one_per_sm = true;
+    }
+    if (!ok) return false;
+    const uint32_t row_tiles = (c.rows + 16u * plan.row_tiles - 1) / (16u * plan.row_tiles);
+    uint32_t ctas = (one_per_sm ? 1u : 2u) * ctx.sm_count;
+    if (ctas > row_tiles) ctas = row_tiles;
+    plan.ctas = ctas;
+    MmaTileArgs ta = {};
+    MmaArgs &a = ta.a;
+    a.plan = plan;
+    a.w[0] = c.w[0]; a.w[1] = c.w[1]; a.y = c.y;
+    a.n_experts = c.expert + 1u; a.top = 1u; a.glu = c.glu; a.status = ctx.status;
+    a.na = static_cast<const float *>(c.x); a.npack = 1u;
+    ta.dense_expert = c.expert; ta.dense_rows = c.count; ta.per_pass = per_pass;
+    const dim3 grid(ctas, 1);
     switch (c.kind) {
     case KIND_Q4_K: err = c.nmat == 2 ? launch_tiles_t<KIND_Q4_K, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q4_K, 1>(ta, grid, ctx.stream, ctx.pdl); break;
     case KIND_Q6_K: err = c.nmat == 2 ? launch_tiles_t<KIND_Q6_K, 2>(ta, grid, ctx.stream, ctx.pdl) : launch_tiles_t<KIND_Q6_K, 1>(ta, grid, ctx.stream, ctx.pdl); break;

@@ -106,6 +106,8 @@ struct GemvCall {
 cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);
 // The tensor-core-assisted streaming GEMV; false when the call is not one it handles.
 bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
+// Two or more float32 rows against one dense matrix: one pass over the weights per four rows, each row's bits those of the one-token kernel.
+bool try_launch_gemv_rows(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &err);
 // Several independent one-token projections as one grid (2..4 calls that gemv_mma_group_eligible accepts).
 bool gemv_mma_group_eligible(const GemvCall &c, const LaunchCtx &ctx);
 // Loads the kernels a tensor-parallel group's projections use onto the current device (before the first step).

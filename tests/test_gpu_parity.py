@@ -148,16 +148,18 @@ def test_f32_matmul_tails_and_expert_offsets(gpu):
             assert np.abs(y - exp).max() < 2e-5
 
 
+@pytest.mark.parametrize("mma", [False, True], ids=["fp32 kernels", "default path"])
 @pytest.mark.parametrize("kind,cols", [(Q4_K, 2560), (Q6_K, 4096), (Q4_0, 2560), (Q8_0, 1024), (Q4_K, 12288)])
-def test_token_counts_agree_bitwise_and_with_oracle(gpu, kind, cols):
-    # counts 2..8 bitwise equal to count 1 (src/expert_bench.rs:698-712) and tails of tokens
+def test_token_counts_agree_bitwise_and_with_oracle(gpu, kind, cols, mma):
+    # counts 2..8 bitwise equal to count 1 (src/expert_bench.rs:698-712) and tails of tokens: within the fp32
+    # streaming kernels, and on the default path (one token: the int8 tensor-core kernel; 2..4: the same kernel
+    # over a tile of rows; more than four tokens take the tensor-core GEMM there, as in the reference)
     rows = 37
     raw = synth.random_matrix(kind, cols, rows, seed=4)
     x = synth.activations(8, cols, seed=5)
-    # one kernel family at a time: the fp32 streaming kernel here
-    singles = np.concatenate([gemv(gpu, raw, cols, rows, kind, x[t], mma=False) for t in range(8)])
-    for n in (2, 3, 4, 5, 7, 8):
-        y = gemv(gpu, raw, cols, rows, kind, x[:n], mma=False)
+    singles = np.concatenate([gemv(gpu, raw, cols, rows, kind, x[t], mma=mma) for t in range(8)])
+    for n in ((2, 3, 4) if mma else (2, 3, 4, 5, 7, 8)):
+        y = gemv(gpu, raw, cols, rows, kind, x[:n], mma=mma)
         assert np.array_equal(y.view(np.uint32), singles[:n].view(np.uint32)), (kind, n)
     e = O.matvec_f64(raw, cols, rows, kind, x)
     assert (np.abs(singles - e) <= tol_ref(e)).all()
@@ -616,13 +618,14 @@ def test_normed_projection_matches_add_rms_then_matmul(gpu, kind, cols, rows, ad
     s_s, packed = gpu.output(cols), gpu.empty_bytes(gpu.packed_x_bytes(cols))
     gpu._check(gpu._lib.ingot_add_rms_packed(gpu._h, ab.ptr, bb.ptr, None, s_s.ptr, None, None, packed.ptr, bf16, cols, 1, 1e-6, add))
     sep = gpu.finish(None, gpu.matmul(None, w, cols, rows, stride, kind, 0, packed, 1, X_PACKED))
-    e_s, e_x = O.add_rms(a, b, None, 1e-6, add=bool(add))
-    if bf16:
-        e_x = synth.from_bf16_bits(synth.to_bf16_bits(e_x.astype(np.float32)))
-    e = O.matvec_f64(raw, cols, rows, kind, e_x.astype(np.float32).reshape(1, cols))[0]
-    # the two differ only by the order of the sum of squares (256 against 512 threads)
-    assert (np.abs(fused - sep) <= 4 * tol_ref_scaled(e)).all(), float(np.abs(fused - sep).max())
-    assert (np.abs(fused - e) <= 8 * tol_ref_scaled(e)).all(), float(np.abs(fused - e).max())
+    # the reference's bound against an f64 dot of the normalised (and bfloat16-rounded) row, plus, with bfloat16
+    # rounding, what the columns whose rounding hangs on the last float32 bits of the norm can move (one bfloat16
+    # step each: oracle/chain_check.py).  The separate path differs from the fused one by the order of the sum of
+    # squares and by its activation row form (binary16 parts against fixed point): each meets the bound by itself.
+    from oracle.chain_check import expect_projection
+    _, e, tol = expect_projection(raw, cols, rows, kind, a[0], b[0] if add else None, bool(bf16))
+    assert (np.abs(fused - e) <= tol).all(), float((np.abs(fused - e) / tol).max())
+    assert (np.abs(sep - e) <= tol).all(), float((np.abs(sep - e) / tol).max())
     if add:
         assert np.array_equal(gpu.read_f32(s_f).view(np.uint32), gpu.read_f32(s_s).view(np.uint32))
         with pytest.raises(InvalidData):        # the sum cannot go over an input
@@ -723,7 +726,9 @@ def test_moe_host_wrapper_matches_oracle(gpu):
     shared_e = expert_ffn(shared, 0).astype(np.float32)
     logit = float(np.dot(gate.data.view(np.float32).astype(np.float64), x.astype(np.float64)))
     e = O.combine(routed_e, shared_e, weights, logit, width).astype(np.float64)
-    assert (np.abs(y - e) <= 4 * tol_ref_scaled(e)).all(), float(np.abs(y - e).max())
+    # three chained projections: the bound of the last one plus the first two's carried through it would be the
+    # principled figure; the layer's outputs are O(1e-3) here, so the reference's plain bound is checked instead
+    assert (np.abs(y - e) <= tol_ref(e)).all(), float(np.abs(y - e).max())
     with pytest.raises(InvalidData):
         gpu.moe(routed, shared, gate, x, weights[:3])
 
@@ -737,7 +742,12 @@ def test_gate_up_wide_batch_takes_the_gemm(gpu):
     y = gpu.finish(None, gpu.generic_gate_up(None, [wg, wu], gpu.floats(x), tokens, False)).reshape(tokens, rows)
     eg, eu = O.gemm_f16_f64(g_raw, cols, rows, Q4_K, x), O.gemm_f16_f64(u_raw, cols, rows, Q4_K, x)
     e = O.glu(eg.astype(np.float32), eu.astype(np.float32)).reshape(tokens, rows).astype(np.float64)
-    assert (np.abs(y - e) <= 4 * tol_contract(e)).all(), float(np.abs(y - e).max())
+    # act = silu(g) u: the two GEMM bounds carried through the activation (|d act| <= 1.13 |u| dg + |silu(g)| du)
+    tg, tu = tol_ref_scaled(eg.reshape(tokens, rows)), tol_ref_scaled(eu.reshape(tokens, rows))
+    eg2, eu2 = eg.reshape(tokens, rows), eu.reshape(tokens, rows)
+    silu = np.abs(eg2 / (1.0 + np.exp(-eg2)))
+    tol = 1.13 * np.abs(eu2) * tg + (silu + 1.13 * tg) * tu + 4e-6 * np.abs(e) + 1e-30
+    assert (np.abs(y - e) <= tol).all(), float((np.abs(y - e) / tol).max())
 
 
 # ---- several tokens per pass over the weights (high-part rows) ---------------------------------
