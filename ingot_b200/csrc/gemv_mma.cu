@@ -1896,10 +1896,15 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     MmaPlan plan;
     int occ = 3;
     uint32_t max_ctas = (3u * ctx.sm_count + gy_live - 1) / gy_live;
-    // a matrix whose 16-row tiles all fit in one wave of two CTAs per SM takes that form: its
-    // deeper ring holds a CTA's whole share, so the copies of one launch run under the tail of
-    // the launch before it (4096 x 4096 Q4_K: 6.3 us against 7.6 us back to back)
-    bool ok = !(gy_live == 1 && (c.rows + 15u) / 16u <= 2u * ctx.sm_count) &&
+    // two CTAs per SM have deeper rings: a short matrix's CTA holds its whole share, so the copies of one
+    // launch run under the tail of the launch before it (4096 x 4096 Q4_K: 6.3 us against 7.6 us back to back)
+    // three CTAs per SM pay only in the steady state of a long stream (the 151936-row head: 93 us against 100 us
+    // with two); with a few tiles per CTA (gate/up: 3.5) two CTAs with deeper rings give the same launch time
+    // and a shorter token step (2.25 against 2.30 ms: the next launch's CTAs find room earlier)
+    // (the 18- and 34-byte block formats issue more instructions per byte and keep three: Gemma's Q4_0 step
+    // measured 1.97 ms with two against 1.79 ms)
+    const bool long_stream = (uint64_t)((c.rows + 15u) / 16u) * c.nmat >= 24ull * ctx.sm_count || c.kind == KIND_Q4_0 || c.kind == KIND_Q8_0;
+    bool ok = !(gy_live == 1 && !long_stream) &&
               plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, xmode, plan);
     if (!ok) {
         occ = 2;
