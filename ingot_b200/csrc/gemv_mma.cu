@@ -1899,6 +1899,9 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     MmaPlan plan;
     int occ = 3;
     uint32_t max_ctas = (3u * ctx.sm_count + gy_live - 1) / gy_live;
+    // (many live pairs: two waves of shorter CTAs, for the same reason as in the expert-grouped kernel; 128 live
+    // pairs per device 10.8 -> 10.0 ms per step, 32 live pairs 4.4 -> 4.1 ms; with a handful of pairs it costs time)
+    if (routed && gy_live >= 16u) max_ctas = (6u * ctx.sm_count + gy_live - 1) / gy_live;
     // two CTAs per SM have deeper rings: a short matrix's CTA holds its whole share, so the copies of one
     // launch run under the tail of the launch before it (4096 x 4096 Q4_K: 6.3 us against 7.6 us back to back)
     // three CTAs per SM pay only in the steady state of a long stream (the 151936-row head: 93 us against 100 us
