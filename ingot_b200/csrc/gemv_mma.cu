@@ -1900,16 +1900,23 @@ bool try_launch_gemv_mma(const GemvCall &c, const LaunchCtx &ctx, cudaError_t &e
     int occ = 3;
     uint32_t max_ctas = (3u * ctx.sm_count + gy_live - 1) / gy_live;
     // (many live pairs: two waves of shorter CTAs, for the same reason as in the expert-grouped kernel; 128 live
-    // pairs per device 10.8 -> 10.0 ms per step, 32 live pairs 4.4 -> 4.1 ms; with a handful of pairs it costs time)
-    if (routed && gy_live >= 16u) max_ctas = (6u * ctx.sm_count + gy_live - 1) / gy_live;
-    // two CTAs per SM have deeper rings: a short matrix's CTA holds its whole share, so the copies of one
-    // launch run under the tail of the launch before it (4096 x 4096 Q4_K: 6.3 us against 7.6 us back to back)
-    // three CTAs per SM pay only in the steady state of a long stream (the 151936-row head: 93 us against 100 us
-    // with two); with a few tiles per CTA (gate/up: 3.5) two CTAs with deeper rings give the same launch time
-    // and a shorter token step (2.25 against 2.30 ms: the next launch's CTAs find room earlier)
-    // (the 18- and 34-byte block formats issue more instructions per byte and keep three: Gemma's Q4_0 step
-    // measured 1.97 ms with two against 1.79 ms)
-    const bool long_stream = (uint64_t)((c.rows + 15u) / 16u) * c.nmat >= 24ull * ctx.sm_count || c.kind == KIND_Q4_0 || c.kind == KIND_Q8_0;
+    // pairs per device 10.8 -> 10.0 ms per step, 32 live pairs 4.4 -> 4.1 ms; with a handful of pairs it costs time,
+    // and so it does when most of the grid is pairs of other devices, whose CTAs only leave: 32 live pairs of 256
+    // on eight devices 6.1 -> 6.9 ms)
+    if (routed && gy_live >= 16u && gy <= 2u * gy_live) max_ctas = (6u * ctx.sm_count + gy_live - 1) / gy_live;
+    // Two or three CTAs per SM (dense launches).  Two have deeper rings: a matrix whose 16-row tiles all fit in one
+    // wave of two holds a CTA's whole share in its ring, so the copies of one launch run under the tail of the launch
+    // before it (4096 x 4096 Q4_K: 6.3 us against 7.6 us back to back).  Three pay only in the steady state of a
+    // long stream (the 151936-row head: 93 us against 100 us with two); with a few tiles per CTA (gate/up: 3.5) two
+    // give the same launch time and a shorter token step (2.25 against 2.30 ms: the next launch's CTAs find room
+    // earlier).  Measured exceptions that keep three: the 18- and 34-byte block formats, which issue more
+    // instructions per byte (Gemma's Q4_0 step 1.97 ms with two against 1.79 ms), and projections that exchange
+    // their rows with other GPUs (two-GPU step 2.30 ms with two against 2.23 ms).
+    const uint64_t tiles16 = (c.rows + 15u) / 16u;
+    const bool exchanges = c.tp.n_out || c.tp.in[0] || c.tp.in[1];
+    const bool k_quant = c.kind == KIND_Q4_K || c.kind == KIND_Q6_K;
+    const bool prefers_two = tiles16 <= 2ull * ctx.sm_count || (k_quant && !exchanges && tiles16 * c.nmat < 24ull * ctx.sm_count);
+    const bool long_stream = !prefers_two;
     bool ok = !(gy_live == 1 && !long_stream) &&
               plan_mma(c.kind, c.cols, c.rows, c.stride, c.nmat, max_ctas, MMA_SMEM_SMALL, xmode, plan);
     if (!ok) {
