@@ -48,7 +48,8 @@ struct ingot_gpu {
     size_t pool_limit = 0, pool_managed = 0, pool_peak = 0;
     uint64_t pool_allocations = 0, pool_reuses = 0;
     std::map<size_t, std::vector<void *>> pool_free;      // idle buffers by length
-    std::unordered_map<void *, size_t> pool_lengths;      // every buffer the pool manages, idle or leased
+    struct PoolEntry { size_t length; bool leased; };
+    std::unordered_map<void *, PoolEntry> pool_lengths;   // every buffer the pool manages, idle or leased
     // links of the next fused-norm projection to a tensor-parallel group (ingot_tp_signal_next / ingot_tp_wait_next)
     ingot_group *tp_signal_group = nullptr, *tp_wait_group = nullptr;
     uint32_t tp_signal_slot = 0, tp_wait_slot[2] = {0, 0};
@@ -337,6 +338,7 @@ ingot_status ingot_output_alloc(ingot_gpu *g, size_t count_f32, float **out) {
     if (idle != g->pool_free.end() && !idle->second.empty()) {
         *out = static_cast<float *>(idle->second.back());
         idle->second.pop_back();
+        g->pool_lengths[*out].leased = true;
         g->pool_reuses += 1;
         return INGOT_OK;
     }
@@ -361,7 +363,7 @@ ingot_status ingot_output_alloc(ingot_gpu *g, size_t count_f32, float **out) {
     g->pool_managed += charge;
     if (g->pool_managed > g->pool_peak) g->pool_peak = g->pool_managed;
     g->pool_allocations += 1;
-    g->pool_lengths[p] = bytes;
+    g->pool_lengths[p] = {bytes, true};
     *out = static_cast<float *>(p);
     return INGOT_OK;
 }
@@ -371,8 +373,10 @@ ingot_status ingot_output_release(ingot_gpu *g, float *p) {
     if (!p) return INGOT_OK;
     auto it = g->pool_lengths.find(p);
     if (it == g->pool_lengths.end()) return ingot_buffer_free(g, p);   // allocated while no budget was set
+    if (!it->second.leased) return fail(g, INGOT_INVALID, "output_release: this buffer is already back in the pool");
     // back on the idle list of its length; work already enqueued on the handle's stream runs before any later user's
-    g->pool_free[it->second].push_back(p);
+    it->second.leased = false;
+    g->pool_free[it->second.length].push_back(p);
     return INGOT_OK;
 }
 

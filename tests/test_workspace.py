@@ -66,6 +66,18 @@ def test_released_buffers_are_reused_in_stream_order(gpu):
     assert gpu.workspace_statistics()[0] == before
 
 
+def test_a_buffer_goes_back_to_the_pool_once(gpu):
+    gpu.configure_workspace(4 * PAGE)
+    b = gpu.output(16)
+    ptr = b.ptr
+    b.release()
+    assert gpu._lib.ingot_output_release(gpu._h, ptr) != 0          # a second release is refused, not queued twice
+    c, d = gpu.output(16), gpu.output(16)
+    assert c.ptr == ptr and d.ptr != ptr
+    c.release()
+    d.release()
+
+
 def test_without_a_budget_outputs_are_plain_allocations(gpu):
     x = gpu.output(1000)
     assert gpu.workspace_statistics() == (0, 0, 0, 0)
