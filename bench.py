@@ -204,6 +204,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="debug: fewer layers (invalid as a benchmark)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the prefill GEMM and MoE tables that the default single-GPU line carries under \"gemm\" and \"moe\"")
     ap.add_argument("--profile-kernel", default=None,
                     help="run only this GEMV (gate_up_q4k, down_q6k, q_q4k, k_q4k, v_q6k, head_q6k) over --layers "
                          "layers, a small case for ncu; prints its timing and exits")
@@ -420,6 +422,25 @@ def main():
                "sample": "measured on layer 0 (%.1f ms) and the head (%.1f ms) of the same weights; the step is %d such layers and the head"
                          % (t_layer * 1e3, t_head * 1e3, chain.n_layers)}
 
+    extra = {}
+    if rank == 0 and world == 1 and args.workload == "chain" and args.batch == 1 and args.layers is None and not args.no_extra \
+            and not args.profile_kernel:
+        # the other two measured configurations, each with a clock record of its own (they are not part of `value`):
+        # the prefill dequant-GEMM table (configs[4]) and the expert-routed FFN chain (configs[3])
+        other = argparse.Namespace(**vars(args))
+        other.steps, other.warmup, other.layers = 10, 3, None
+        s2 = ClockSampler(local)
+        s2.start()
+        other.tokens = [512, 2048, 8192]
+        g = run_gemm(torch, gpu, stream, other)
+        extra["gemm"] = {"workload": g["workload"], "unit": "TFLOP/s", "bound": "tensor", "peak": g["peak"], "peak_source": g["peak_source"],
+                         "steps": other.steps, "warmup": other.warmup, "shapes": g["shapes"], "clocks": s2.stop()}
+        s3 = ClockSampler(local)
+        s3.start()
+        other.tokens = [1, 8, 32]
+        rows = run_moe(torch, gpu, stream, other, rank, world, local, table_only=True)
+        extra["moe"] = {"workload": "qwen3-30b-a3b expert-routed FFN chain (configs[3]), 48 layers, one GPU", "unit": "tok/s",
+                        "steps": other.steps, "warmup": other.warmup, "by_tokens": rows, "clocks": s3.stop()}
     if rank == 0:
         total_bytes = weight_bytes_per_token(shape) if args.layers is None else chain.bytes_streamed
         line = {
@@ -440,6 +461,7 @@ def main():
         }
         if parity:
             line.update(parity)
+        line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
         # leave without tearing the communicator down: the recorded step holds NCCL work, and
@@ -465,7 +487,7 @@ def connect_group(torch, dist, gpu, rank, world, local, window_bytes, slots):
     return group
 
 
-def run_moe(torch, gpu, stream, args, rank, world, local):
+def run_moe(torch, gpu, stream, args, rank, world, local, table_only=False):
     """Qwen3-30B-A3B-shaped expert-routed FFN chain: 48 layers of route_topk -> routed gate/up + SiLU ->
     routed down -> moe_sum, Q4_K experts, synthetic N(0,1) router logits, for each token count.
     With N > 1 ranks the 128 experts are split expert-parallel (rank r owns experts [r*128/N, ...)) and the SAME
@@ -573,6 +595,9 @@ def run_moe(torch, gpu, stream, args, rank, world, local):
                         "frac_of_hbm_peak": algo / (ms * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world),
                         "launches_per_step": chain.launches_per_step})
         del graph, tgraph
+    if table_only:                      # the caller's own line carries the table (single GPU)
+        del chain
+        return results
     if rank == 0:
         head = results[0]
         print(json.dumps({"metric": "decode tok/s, Qwen3-30B-A3B shape (expert-routed Q4_K GEMV chain)", "value": head["tok_per_s"],
