@@ -303,6 +303,17 @@ INGOT_API ingot_status ingot_attention_decode(ingot_gpu *gpu, const float *q, co
                                               const float *v_cache, float *out, uint32_t head_dim, uint32_t heads,
                                               uint32_t kv_heads, uint32_t position, uint32_t window, uint32_t tokens);
 
+/* flash_prefill_<D> (kernels/generic.metal:19-136, driven by Generic::flash, src/generic.rs:421-470):
+ * causal attention of `rows` query rows — the first at `position`, position + rows <= length —
+ * over the float32 caches, same scale, grouped-query heads and sliding window as above; what the
+ * reference runs for more than four tokens.  Here one CTA per (row, head) with an online softmax
+ * (the decode kernel over more rows): the same result, without the reference kernel's tiling of
+ * eight query rows per threadgroup. */
+INGOT_API ingot_status ingot_attention_prefill(ingot_gpu *gpu, const float *q, const float *k_cache,
+                                               const float *v_cache, float *out, uint32_t head_dim,
+                                               uint32_t heads, uint32_t kv_heads, uint32_t length,
+                                               uint32_t position, uint32_t rows, uint32_t window);
+
 /* greedy_select (kernels/qwen.metal:384-410) in its two stages, as Gpu::finish_greedy issues them
  * (src/metal.rs:1507-1548): out[r] = (token of the largest logit of row r — equal values, signed
  * zeros included, go to the smaller token id; `mapping` (may be NULL) renames column i —, 1 when

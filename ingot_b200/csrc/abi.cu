@@ -885,6 +885,21 @@ ingot_status ingot_attention_decode(ingot_gpu *g, const float *q, const float *k
     return after_launch(g, e, "attention_decode");
 }
 
+// flash_prefill_<D> (kernels/generic.metal:19-136; Generic::flash, src/generic.rs:421-470): causal attention of `rows` query rows,
+// the first at `position`, over the first `length` rows of the float32 caches.
+ingot_status ingot_attention_prefill(ingot_gpu *g, const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t head_dim,
+                                     uint32_t heads, uint32_t kv_heads, uint32_t length, uint32_t position, uint32_t rows, uint32_t window) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, "attention_prefill: only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
+    if (!q || !k_cache || !v_cache || !out) return fail(g, INGOT_INVALID, "null pointer");
+    if (heads == 0 || kv_heads == 0 || heads % kv_heads || rows > 65535u || (uint64_t)position + rows > length)
+        return fail(g, INGOT_INVALID, "attention_prefill: bad geometry (position + rows must lie within length; at most 65535 rows)");
+    cudaError_t e = launch_attention_decode(q, k_cache, v_cache, out, head_dim, heads, kv_heads, position, window, rows, ctx_of(g));
+    if (e == cudaErrorNotSupported) { cudaGetLastError(); return fail(g, INGOT_UNSUPPORTED, "attention_prefill: head dimension must be 64, 96, 128, 256 or 512"); }
+    return after_launch(g, e, "attention_prefill");
+}
+
 ingot_status ingot_greedy_select(ingot_gpu *g, const float *logits, const uint32_t *mapping, uint32_t rows, uint32_t vocab, uint32_t *scratch,
                                  uint32_t *out) {
     ingot_status st = enter(g);

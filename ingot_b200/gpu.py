@@ -632,6 +632,18 @@ class Gpu:
         self._check(st)
         return out
 
+    def attention_prefill(self, cmd, q: Buffer, k_cache: Buffer, v_cache: Buffer, head_dim: int, heads: int, kv_heads: int,
+                          position: int, rows: int, window: int = 0):
+        """Generic::flash (src/generic.rs:421-470; flash_prefill_<D>, kernels/generic.metal:19-136): causal attention of
+        `rows` query rows from `position` on; None when there is no kernel for the head dimension."""
+        out = self.output(rows * heads * head_dim)
+        st = self._lib.ingot_attention_prefill(self._h, q.ptr, k_cache.ptr, v_cache.ptr, out.ptr, head_dim, heads, kv_heads,
+                                               position + rows, position, rows, window)
+        if st == _abi.UNSUPPORTED:
+            return None
+        self._check(st)
+        return out
+
     def finish_greedy(self, cmd, logits: Buffer, rows: int, vocabulary: int, mapping: Buffer | None = None) -> list[int]:
         """Gpu::finish_greedy (src/metal.rs:1507-1548): the greedy token of every row; non-finite logits are an error."""
         chunks = (vocabulary + 1023) // 1024

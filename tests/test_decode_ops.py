@@ -66,6 +66,23 @@ def test_attention_decode(gpu, D, H, KV, position, tokens, window):
     assert np.abs(got - want).max() <= 2e-5, float(np.abs(got - want).max())
 
 
+@pytest.mark.parametrize("D,H,KV,position,rows,window", [(64, 8, 2, 0, 40, 0), (128, 4, 4, 57, 70, 0), (128, 8, 2, 100, 33, 48),
+                                                        (256, 2, 1, 3, 9, 0), (96, 4, 2, 0, 130, 64)])
+def test_attention_prefill(gpu, D, H, KV, position, rows, window):
+    # what the reference runs for more than four tokens (flash_prefill_<D>): the tails of its 8-row and 64-key tiles
+    # (rows and lengths that are no multiples) are ordinary cases here
+    length = position + rows
+    rng = np.random.default_rng(D + rows)
+    q = rng.normal(0, 1, (rows, H, D)).astype(np.float32)
+    kc, vc = (rng.normal(0, 1, (length, KV, D)).astype(np.float32) for _ in range(2))
+    out = gpu.attention_prefill(None, gpu.floats(q), gpu.floats(kc), gpu.floats(vc), D, H, KV, position, rows, window)
+    got = gpu.finish(None, out).reshape(rows, H, D)
+    want = O.attention_decode(q, kc, vc, D, H, KV, position, rows, window)
+    assert np.abs(got - want).max() <= 2e-5, float(np.abs(got - want).max())
+    with pytest.raises(InvalidData):            # rows beyond the stated length
+        gpu._check(gpu._lib.ingot_attention_prefill(gpu._h, out.ptr, out.ptr, out.ptr, out.ptr, D, H, KV, length - 1, position, rows, window))
+
+
 def test_attention_decode_without_a_kernel_is_unsupported(gpu):
     z = gpu.zeros(4 * 80)
     assert gpu.attention_decode(None, z, z, z, 80, 4, 4, 0, 1) is None
