@@ -227,6 +227,18 @@ INGOT_API ingot_status ingot_moe_sum(ingot_gpu *gpu, const float *routed, const 
 INGOT_API ingot_status ingot_activation(ingot_gpu *gpu, const float *gate, const float *up, uint64_t n,
                                         uint32_t gelu, float *y);
 
+/* Architecture glue of the generic path (kernels/generic_arch.metal:2-17; Gemma and Phi-3 graphs in
+ * src/generic.rs), one element per thread:
+ *   scale_rows     y[i] = x[i] * scale                                  (:2-3)
+ *   softcap_rows   y[i] = cap * tanh(x[i] / cap), final logit soft-cap  (:4-5)
+ *   swiglu_fused   y[t][j] = silu(x[t][j]) * x[t][ff + j] over fused gate|up rows of width 2 ff (:11-15)
+ *   copy_columns   y[r][j] = x[r * stride + offset + j], j < width      (:16-17) */
+INGOT_API ingot_status ingot_scale_rows(ingot_gpu *gpu, const float *x, uint64_t n, float scale, float *y);
+INGOT_API ingot_status ingot_softcap_rows(ingot_gpu *gpu, const float *x, uint64_t n, float cap, float *y);
+INGOT_API ingot_status ingot_swiglu_fused(ingot_gpu *gpu, const float *x, uint32_t tokens, uint32_t ff, float *y);
+INGOT_API ingot_status ingot_copy_columns(ingot_gpu *gpu, const float *x, uint32_t rows, uint32_t width,
+                                          uint32_t offset, uint32_t stride, float *y);
+
 /* Gpu::merge (src/metal.rs:1199-1223; combine kernels/moe.metal:412-422):
  * y[j] = sum_e routed[e][j] * weights[e] + shared[j] * sigmoid(shared_logit[0]). */
 INGOT_API ingot_status ingot_merge(ingot_gpu *gpu, const float *routed, const float *shared,

@@ -68,6 +68,10 @@ SIGNATURES = {
     "ingot_embedding_batch": [vp, vp, vp, u32, u32, u32, u32, u32, vp],
     "ingot_qk_rope_cache": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32],
     "ingot_attention_decode": [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32],
+    "ingot_scale_rows": [vp, vp, u64, f32, vp],
+    "ingot_softcap_rows": [vp, vp, u64, f32, vp],
+    "ingot_swiglu_fused": [vp, vp, u32, u32, vp],
+    "ingot_copy_columns": [vp, vp, u32, u32, u32, u32, vp],
     "ingot_attention_prefill": [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32],
     "ingot_greedy_select": [vp, vp, vp, u32, u32, vp, vp],
     "ingot_gguf_open": [C.c_char_p, C.POINTER(vp)],

@@ -787,6 +787,36 @@ ingot_status ingot_activation(ingot_gpu *g, const float *gate, const float *up, 
     return after_launch(g, launch_activation(gate, up, n, gelu, y, ctx_of(g)), "activation");
 }
 
+// ---- architecture glue of the generic path (kernels/generic_arch.metal:2-17) ----
+
+static ingot_status glue_common(ingot_gpu *g, uint32_t op, const float *x, uint64_t n, uint32_t width, uint32_t offset, uint32_t stride,
+                                float value, float *y, const char *what) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, std::string(what) + ": only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
+    if (!x || !y) return fail(g, INGOT_INVALID, "null pointer");
+    return after_launch(g, launch_glue(op, x, n, width, offset, stride, value, y, ctx_of(g)), what);
+}
+
+ingot_status ingot_scale_rows(ingot_gpu *g, const float *x, uint64_t n, float scale, float *y) {
+    return glue_common(g, 0, x, n, 1, 0, 0, scale, y, "scale_rows");
+}
+
+ingot_status ingot_softcap_rows(ingot_gpu *g, const float *x, uint64_t n, float cap, float *y) {
+    if (g && !(cap != 0.0f)) return fail(g, INGOT_INVALID, "softcap_rows: the cap must not be zero");
+    return glue_common(g, 1, x, n, 1, 0, 0, cap, y, "softcap_rows");
+}
+
+ingot_status ingot_swiglu_fused(ingot_gpu *g, const float *x, uint32_t tokens, uint32_t ff, float *y) {
+    if (g && ff == 0) return fail(g, INGOT_INVALID, "swiglu_fused: zero width");
+    return glue_common(g, 2, x, (uint64_t)tokens * ff, ff, 0, 0, 0.f, y, "swiglu_fused");
+}
+
+ingot_status ingot_copy_columns(ingot_gpu *g, const float *x, uint32_t rows, uint32_t width, uint32_t offset, uint32_t stride, float *y) {
+    if (g && (width == 0 || (uint64_t)offset + width > stride)) return fail(g, INGOT_INVALID, "copy_columns: the columns must lie inside a row");
+    return glue_common(g, 3, x, (uint64_t)rows * width, width, offset, stride, 0.f, y, "copy_columns");
+}
+
 ingot_status ingot_merge(ingot_gpu *g, const float *routed, const float *shared, const float *weights,
                          const float *shared_logit, uint32_t width, uint32_t top, float *y) {
     ingot_status st = enter(g);

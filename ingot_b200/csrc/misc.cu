@@ -323,6 +323,51 @@ cudaError_t launch_activation(const float *gate, const float *up, uint64_t n, ui
 }
 
 // ---------------------------------------------------------------------------
+// Architecture glue of the generic path (kernels/generic_arch.metal:2-17): one element per thread.
+//   scale    y = x * scale
+//   softcap  y = c * tanh(x / c)                       (final logit soft-capping)
+//   swiglu   y[t][j] = silu(x[t][j]) * x[t][ff + j]    (fused gate|up rows of width 2 ff)
+//   columns  y[r][j] = x[r * stride + offset + j]      (columns [offset, offset + width) of rows)
+// ---------------------------------------------------------------------------
+
+struct GlueArgs {
+    const float *x;
+    float *y;
+    uint64_t n;
+    uint32_t op, width, offset, stride;
+    float value;
+};
+
+__global__ void __launch_bounds__(256) glue_kernel(const __grid_constant__ GlueArgs a) {
+    pdl_prologue();
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
+        switch (a.op) {
+        case 0: a.y[i] = __fmul_rn(a.x[i], a.value); break;
+        case 1: a.y[i] = __fmul_rn(a.value, tanhf(__fdiv_rn(a.x[i], a.value))); break;
+        case 2: {
+            const uint64_t t = i / a.width, j = i - t * a.width;
+            const float g = a.x[t * 2u * a.width + j];
+            a.y[i] = __fmul_rn(__fdiv_rn(g, 1.0f + expf(-g)), a.x[t * 2u * a.width + a.width + j]);
+            break;
+        }
+        default: {
+            const uint64_t r = i / a.width, j = i - r * a.width;
+            a.y[i] = a.x[r * a.stride + a.offset + j];
+        }
+        }
+    }
+}
+
+cudaError_t launch_glue(uint32_t op, const float *x, uint64_t n, uint32_t width, uint32_t offset, uint32_t stride, float value, float *y,
+                        const LaunchCtx &ctx) {
+    if (n == 0) return cudaSuccess;
+    GlueArgs a = {x, y, n, op, width, offset, stride, value};
+    uint64_t blocks = (n + 255) / 256, cap = (uint64_t)ctx.sm_count * 8u;
+    if (blocks > cap) blocks = cap;
+    return launch(glue_kernel, dim3((uint32_t)blocks), dim3(256), ctx, a);
+}
+
+// ---------------------------------------------------------------------------
 // Routed sum plus sigmoid-gated shared expert, one token
 // (reference combine: kernels/moe.metal:412-422).
 // ---------------------------------------------------------------------------

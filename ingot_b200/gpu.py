@@ -632,6 +632,27 @@ class Gpu:
         self._check(st)
         return out
 
+    # ---- architecture glue of the generic path (kernels/generic_arch.metal:2-17) ----
+    def scale_rows(self, cmd, x: Buffer, n: int, scale: float) -> Buffer:
+        y = self.output(n)
+        self._check(self._lib.ingot_scale_rows(self._h, x.ptr, n, scale, y.ptr))
+        return y
+
+    def softcap_rows(self, cmd, x: Buffer, n: int, cap: float) -> Buffer:
+        y = self.output(n)
+        self._check(self._lib.ingot_softcap_rows(self._h, x.ptr, n, cap, y.ptr))
+        return y
+
+    def swiglu_fused(self, cmd, x: Buffer, tokens: int, ff: int) -> Buffer:
+        y = self.output(tokens * ff)
+        self._check(self._lib.ingot_swiglu_fused(self._h, x.ptr, tokens, ff, y.ptr))
+        return y
+
+    def copy_columns(self, cmd, x: Buffer, rows: int, width: int, offset: int, stride: int) -> Buffer:
+        y = self.output(rows * width)
+        self._check(self._lib.ingot_copy_columns(self._h, x.ptr, rows, width, offset, stride, y.ptr))
+        return y
+
     def attention_prefill(self, cmd, q: Buffer, k_cache: Buffer, v_cache: Buffer, head_dim: int, heads: int, kv_heads: int,
                           position: int, rows: int, window: int = 0):
         """Generic::flash (src/generic.rs:421-470; flash_prefill_<D>, kernels/generic.metal:19-136): causal attention of

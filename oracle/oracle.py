@@ -341,3 +341,29 @@ def greedy(logits, vocab: int, mapping=None) -> np.ndarray:
     out = np.empty((l.shape[0], 2), np.uint32)
     lib().oracle_greedy(_p(l, _f32p), None if m is None else _p(m, _u32p), l.shape[0], vocab, _p(out, _u32p))
     return out
+
+
+# ---- architecture glue of the generic path (kernels/generic_arch.metal:2-17), restated in numpy ----
+
+def scale_rows(x, scale: float) -> np.ndarray:
+    """y = x * scale in float32 (:2-3)."""
+    return _f32(x) * np.float32(scale)
+
+
+def softcap_rows(x, cap: float) -> np.ndarray:
+    """y = c * tanh(x / c) (:4-5), evaluated in float64 and rounded once."""
+    c = np.float64(np.float32(cap))
+    return (c * np.tanh(_f32(x).astype(np.float64) / c)).astype(np.float32)
+
+
+def swiglu_fused(x, tokens: int, ff: int) -> np.ndarray:
+    """y[t][j] = silu(x[t][j]) * x[t][ff + j] over fused gate|up rows of width 2 ff (:11-15), in float64, rounded once."""
+    rows = _f32(x).reshape(tokens, 2 * ff).astype(np.float64)
+    g, u = rows[:, :ff], rows[:, ff:]
+    return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+
+
+def copy_columns(x, rows: int, width: int, offset: int, stride: int) -> np.ndarray:
+    """Columns [offset, offset + width) of rows of `stride` floats (:16-17)."""
+    return np.ascontiguousarray(_f32(x).reshape(-1)[: rows * stride].reshape(rows, stride)[:, offset:offset + width])
+

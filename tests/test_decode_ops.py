@@ -83,6 +83,26 @@ def test_attention_prefill(gpu, D, H, KV, position, rows, window):
         gpu._check(gpu._lib.ingot_attention_prefill(gpu._h, out.ptr, out.ptr, out.ptr, out.ptr, D, H, KV, length - 1, position, rows, window))
 
 
+def test_architecture_glue(gpu):
+    # kernels/generic_arch.metal:2-17: scale, logit soft-cap, SwiGLU over fused gate|up rows, column copy
+    rng = np.random.default_rng(5)
+    x = rng.normal(0, 4, 3 * 1000).astype(np.float32)
+    xb = gpu.floats(x)
+    got = gpu.finish(None, gpu.scale_rows(None, xb, x.size, 0.0625 * 3))
+    assert np.array_equal(got.view(np.uint32), O.scale_rows(x, 0.0625 * 3).view(np.uint32))
+    got, want = gpu.finish(None, gpu.softcap_rows(None, xb, x.size, 30.0)), O.softcap_rows(x, 30.0)
+    assert np.abs(got - want).max() <= 4e-6 * 30.0
+    got, want = gpu.finish(None, gpu.swiglu_fused(None, xb, 3, 500)).reshape(3, 500), O.swiglu_fused(x, 3, 500)
+    assert (np.abs(got - want) <= 2e-6 * np.abs(want) + 1e-7).all(), float(np.abs(got - want).max())
+    got = gpu.finish(None, gpu.copy_columns(None, xb, 3, 77, 123, 1000)).reshape(3, 77)
+    assert np.array_equal(got.view(np.uint32), O.copy_columns(x, 3, 77, 123, 1000).view(np.uint32))
+    assert gpu.finish(None, gpu.copy_columns(None, xb, 3, 1000, 0, 1000)).size == 3000            # whole rows
+    with pytest.raises(InvalidData):
+        gpu.copy_columns(None, xb, 3, 77, 950, 1000)                                               # columns past the row
+    with pytest.raises(InvalidData):
+        gpu.softcap_rows(None, xb, x.size, 0.0)
+
+
 def test_attention_decode_without_a_kernel_is_unsupported(gpu):
     z = gpu.zeros(4 * 80)
     assert gpu.attention_decode(None, z, z, z, 80, 4, 4, 0, 1) is None
