@@ -333,6 +333,24 @@ INGOT_API ingot_status ingot_attention_prefill(ingot_gpu *gpu, const float *q, c
 INGOT_API ingot_status ingot_greedy_select(ingot_gpu *gpu, const float *logits, const uint32_t *mapping, uint32_t rows,
                                            uint32_t vocab, uint32_t *scratch, uint32_t *out);
 
+/* The packed MoE path at prefill width (Generic::moe_packed, src/generic.rs:578-660, with quant_expert_gemm and
+ * indexed_gate_up, kernels/qwen.metal:895-1081): after ingot_expert_layout, ingot_gather_rows puts the
+ * activation rows into packed order (y[pos] = x[packed[pos] / top]); ingot_expert_gemm_gate_up and
+ * ingot_expert_gemm then run every expert's pairs — a contiguous run of packed rows — through the dense
+ * operators (the tcgen05 GEMM for more than four pairs, the GEMV otherwise), driven by the (count, first)
+ * table, which they read back to the host first (they wait for the stream; not inside a recording);
+ * ingot_combine_packed finishes.  For a few pairs per expert ingot_expert_gate_up / ingot_expert_project
+ * (below) stream each expert once without leaving the device. */
+INGOT_API ingot_status ingot_gather_rows(ingot_gpu *gpu, const float *x, const uint32_t *packed, uint32_t pairs,
+                                         uint32_t top, uint32_t width, float *y);
+INGOT_API ingot_status ingot_expert_gemm(ingot_gpu *gpu, const void *w, uint32_t cols, uint32_t rows, uint32_t stride,
+                                         uint32_t kind, uint32_t experts, const float *x_packed, const uint32_t *layout,
+                                         uint32_t pairs, float *y_packed);
+INGOT_API ingot_status ingot_expert_gemm_gate_up(ingot_gpu *gpu, const void *gate, const void *up, uint32_t cols,
+                                                 uint32_t rows, uint32_t stride, uint32_t kind, uint32_t experts,
+                                                 const float *x_packed, const uint32_t *layout, uint32_t pairs,
+                                                 uint32_t gelu, float *y_packed);
+
 /* expert_layout + expert_pairs (kernels/prefill.metal:7-35): stable
  * expert-major grouping of `pairs` ids.  layout [experts][2] = (count, first),
  * tiles [tile_capacity][4] = (expert, first, n <= 32, mode), packed[pos] =

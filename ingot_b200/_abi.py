@@ -68,6 +68,9 @@ SIGNATURES = {
     "ingot_embedding_batch": [vp, vp, vp, u32, u32, u32, u32, u32, vp],
     "ingot_qk_rope_cache": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32],
     "ingot_attention_decode": [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32],
+    "ingot_gather_rows": [vp, vp, vp, u32, u32, u32, vp],
+    "ingot_expert_gemm": [vp, vp, u32, u32, u32, u32, u32, vp, vp, u32, vp],
+    "ingot_expert_gemm_gate_up": [vp, vp, vp, u32, u32, u32, u32, u32, vp, vp, u32, u32, vp],
     "ingot_scale_rows": [vp, vp, u64, f32, vp],
     "ingot_softcap_rows": [vp, vp, u64, f32, vp],
     "ingot_swiglu_fused": [vp, vp, u32, u32, vp],

@@ -852,6 +852,68 @@ ingot_status ingot_expert_layout(ingot_gpu *g, const uint32_t *ids, uint32_t pai
                         "expert_layout");
 }
 
+// ---- the packed MoE path at prefill width: per-expert tensor-core GEMMs over the grouping's packed rows ----
+
+ingot_status ingot_gather_rows(ingot_gpu *g, const float *x, const uint32_t *packed, uint32_t pairs, uint32_t top, uint32_t width, float *y) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (g->chain_recording) return fail(g, INGOT_INVALID, "gather_rows: only ingot_matmul_normed and ingot_gate_up_normed can be recorded into a chain");
+    if (!x || !packed || !y || top == 0 || width % 4u || ((uintptr_t)x % 16u) || ((uintptr_t)y % 16u))
+        return fail(g, INGOT_INVALID, "gather_rows: rows of 4 n floats, 16-byte aligned");
+    return after_launch(g, launch_gather_rows(x, packed, pairs, top, width, y, ctx_of(g)), "gather_rows");
+}
+
+// The (count, first) table of ingot_expert_layout on the host: the loop over the experts below is driven from here,
+// as the reference's host drives one tiled GEMM per expert tile.  Waits for the stream (not while recording).
+static ingot_status read_layout(ingot_gpu *g, const uint32_t *layout, uint32_t experts, uint32_t pairs, std::vector<uint32_t> &host, const char *what) {
+    if (g->capturing || g->in_scope || g->chain_recording)
+        return fail(g, INGOT_INVALID, std::string(what) + ": reads the grouping back to the host; not inside a recording, a scope or a chain");
+    host.resize(2u * (size_t)experts);
+    ingot_status st = ingot_buffer_read(g, host.data(), layout, host.size() * 4u);
+    if (st) return st;
+    uint64_t total = 0;
+    for (uint32_t e = 0; e < experts; ++e) {
+        if (host[2u * e + 1u] != total) return fail(g, INGOT_INVALID, std::string(what) + ": the layout table is not an expert grouping");
+        total += host[2u * e];
+    }
+    if (total > pairs) return fail(g, INGOT_INVALID, std::string(what) + ": the layout table holds more pairs than given");
+    return INGOT_OK;
+}
+
+ingot_status ingot_expert_gemm(ingot_gpu *g, const void *w, uint32_t cols, uint32_t rows, uint32_t stride, uint32_t kind, uint32_t experts,
+                               const float *x_packed, const uint32_t *layout, uint32_t pairs, float *y_packed) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!w || !x_packed || !layout || !y_packed || experts == 0) return fail(g, INGOT_INVALID, "expert_gemm: bad arguments");
+    if ((st = check_matrix(g, kind, cols, rows, stride))) return st;
+    std::vector<uint32_t> table;
+    if ((st = read_layout(g, layout, experts, pairs, table, "expert_gemm"))) return st;
+    const uint8_t *base = static_cast<const uint8_t *>(w);
+    for (uint32_t e = 0; e < experts && !st; ++e) {
+        const uint32_t n = table[2u * e], first = table[2u * e + 1u];
+        if (n) st = ingot_matmul(g, base, cols, rows, stride, kind, e, x_packed + (size_t)first * cols, INGOT_KIND_F32, n, y_packed + (size_t)first * rows);
+    }
+    return st;
+}
+
+ingot_status ingot_expert_gemm_gate_up(ingot_gpu *g, const void *gate, const void *up, uint32_t cols, uint32_t rows, uint32_t stride,
+                                       uint32_t kind, uint32_t experts, const float *x_packed, const uint32_t *layout, uint32_t pairs,
+                                       uint32_t gelu, float *y_packed) {
+    ingot_status st = enter(g);
+    if (st) return st;
+    if (!gate || !up || !x_packed || !layout || !y_packed || experts == 0) return fail(g, INGOT_INVALID, "expert_gemm_gate_up: bad arguments");
+    if ((st = check_matrix(g, kind, cols, rows, stride))) return st;
+    std::vector<uint32_t> table;
+    if ((st = read_layout(g, layout, experts, pairs, table, "expert_gemm_gate_up"))) return st;
+    const size_t slab = (size_t)rows * stride;
+    for (uint32_t e = 0; e < experts && !st; ++e) {
+        const uint32_t n = table[2u * e], first = table[2u * e + 1u];
+        if (n) st = ingot_gate_up(g, static_cast<const uint8_t *>(gate) + e * slab, static_cast<const uint8_t *>(up) + e * slab, cols, rows, stride,
+                                  kind, x_packed + (size_t)first * cols, INGOT_KIND_F32, n, gelu, y_packed + (size_t)first * rows);
+    }
+    return st;
+}
+
 ingot_status ingot_combine_packed(ingot_gpu *g, const float *routed, const float *weights, const uint32_t *inverse,
                                   uint32_t width, uint32_t top, uint32_t tokens, float *y) {
     ingot_status st = enter(g);

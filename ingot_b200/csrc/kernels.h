@@ -151,6 +151,8 @@ cudaError_t launch_route_topk(const float *logits, uint32_t experts, uint32_t to
                               float *weights, const LaunchCtx &ctx);
 cudaError_t launch_moe_sum(const float *routed, const float *w, uint32_t width, uint32_t top, uint32_t tokens,
                            float *y, const LaunchCtx &ctx);
+// y[pos] = x[pairs[pos] / top]: activation rows in the expert grouping's packed order
+cudaError_t launch_gather_rows(const float *x, const uint32_t *pairs, uint32_t n, uint32_t top, uint32_t width, float *y, const LaunchCtx &ctx);
 // scale (0), soft-cap (1), SwiGLU over fused gate|up rows (2), column copy (3): kernels/generic_arch.metal:2-17
 cudaError_t launch_glue(uint32_t op, const float *x, uint64_t n, uint32_t width, uint32_t offset, uint32_t stride, float value, float *y,
                         const LaunchCtx &ctx);

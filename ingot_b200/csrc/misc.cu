@@ -358,6 +358,33 @@ __global__ void __launch_bounds__(256) glue_kernel(const __grid_constant__ GlueA
     }
 }
 
+struct GatherArgs {
+    const float *x;
+    const uint32_t *pairs;       // packed position -> pair index
+    float *y;
+    uint32_t n, top, width;
+};
+
+// y[pos] = x[pairs[pos] / top]: the activation rows in the expert grouping's packed order (one warp per row).
+__global__ void __launch_bounds__(256) gather_rows_kernel(const __grid_constant__ GatherArgs a) {
+    pdl_prologue();
+    const uint32_t lane = threadIdx.x & 31u, w4 = a.width >> 2;
+    for (uint32_t pos = blockIdx.x * 8u + (threadIdx.x >> 5); pos < a.n; pos += gridDim.x * 8u) {
+        const float4 *src = reinterpret_cast<const float4 *>(a.x + (size_t)(a.pairs[pos] / a.top) * a.width);
+        float4 *dst = reinterpret_cast<float4 *>(a.y + (size_t)pos * a.width);
+        for (uint32_t j = lane; j < w4; j += 32u) dst[j] = src[j];
+    }
+}
+
+cudaError_t launch_gather_rows(const float *x, const uint32_t *pairs, uint32_t n, uint32_t top, uint32_t width, float *y, const LaunchCtx &ctx) {
+    if (n == 0) return cudaSuccess;
+    if (width % 4u || top == 0) return cudaErrorInvalidValue;
+    GatherArgs a = {x, pairs, y, n, top, width};
+    uint32_t blocks = (n + 7u) / 8u;
+    if (blocks > ctx.sm_count * 8u) blocks = ctx.sm_count * 8u;
+    return launch(gather_rows_kernel, dim3(blocks), dim3(256), ctx, a);
+}
+
 cudaError_t launch_glue(uint32_t op, const float *x, uint64_t n, uint32_t width, uint32_t offset, uint32_t stride, float value, float *y,
                         const LaunchCtx &ctx) {
     if (n == 0) return cudaSuccess;

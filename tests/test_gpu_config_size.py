@@ -223,3 +223,38 @@ def test_expert_projection_tile_tails(gpu):
     from ingot_b200 import InvalidData
     with pytest.raises(InvalidData):
         gpu.complete()
+
+
+def test_moe_layer_at_prefill_width_takes_the_per_expert_gemms(gpu):
+    """More than 256 tokens: rows gathered into packed order, every expert's run through the tensor-core GEMM
+    (Generic::moe_packed, src/generic.rs:578-660).  The GEMM stages weights and activations in binary16, as the
+    reference's does, so the layer is compared with the pair-by-pair GEMV result within that staging's noise
+    (three chained projections: 1e-3 of full precision each, src/expert_bench.rs:734-749), and the bookkeeping —
+    every packed row belongs to the expert and the token the tables say — exactly."""
+    from ingot_b200.moe import MoeChain, MoeShape
+    from ingot_b200 import Q4_K
+    shape = MoeShape("test", 1, 512, 16, 4, 256, Q4_K)
+    tokens = 300
+    rng = np.random.default_rng(77)
+    logits = rng.normal(0, 1, (tokens, shape.experts)).astype(np.float32)
+    x = (rng.normal(0, 1, (tokens, shape.hidden)) * 0.05).astype(np.float32)
+    results = []
+    for grouped in (False, True):
+        c = MoeChain(gpu, shape, tokens=tokens, seed=9, layers=1)
+        c.grouped = grouped
+        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, c.logits.ptr, logits.ctypes.data, logits.nbytes))
+        gpu._check(gpu._lib.ingot_buffer_upload(gpu._h, c.x.ptr, x.ctypes.data, x.nbytes))
+        c.layer(0)
+        results.append(gpu.finish(None, c.y).reshape(tokens, shape.hidden).copy())
+        if grouped:
+            pairs = tokens * shape.top
+            ids = gpu.read_u32(c.ids, pairs)
+            packed, layout = gpu.read_u32(c.packed, pairs), gpu.read_u32(c.layout, 2 * shape.experts).reshape(-1, 2)
+            xp = gpu.read_f32(c.x_packed).reshape(pairs, shape.hidden)
+            assert np.array_equal(xp.view(np.uint32), x[packed // shape.top].view(np.uint32))
+            for e, (n, first) in enumerate(layout):
+                assert (ids[packed[first:first + n]] == e).all()
+        del c
+    plain, gemm = results
+    scale = float(np.abs(plain).max())
+    assert np.abs(gemm - plain).max() <= 1e-2 * scale, float(np.abs(gemm - plain).max() / scale)
