@@ -117,9 +117,14 @@ INGOT_API ingot_status ingot_independent_end(ingot_gpu *gpu);
  * number of devices the experts are split over (ingot_ep_localize): routed launches
  * then expect about pairs / value live pairs and give each more CTAs;
  * INGOT_OPT_GROUP_SCOPE (default 1) launches the one-token projections of an
- * independent scope as one grid at the scope's end (0: each on its own stream). */
+ * independent scope as one grid at the scope's end (0: each on its own stream);
+ * INGOT_OPT_WIDE_ROWS (default 0) makes the fused-norm projections build their
+ * activation rows with 30 bits of fixed point per 32 columns even when they round
+ * to bfloat16 (default then: 15 bits, which leave the small neighbours of an
+ * outlier hundreds of times their size fewer bits than bfloat16 carries), at the
+ * price of twice the tensor-core instructions. */
 enum { INGOT_OPT_PDL = 1, INGOT_OPT_FORCE_PLAIN = 2, INGOT_OPT_NO_MMA = 3, INGOT_OPT_TCGEN05_GEMV = 4, INGOT_OPT_EP_WORLD = 5,
-       INGOT_OPT_GROUP_SCOPE = 6 };
+       INGOT_OPT_GROUP_SCOPE = 6, INGOT_OPT_WIDE_ROWS = 7 };
 INGOT_API ingot_status ingot_gpu_set_option(ingot_gpu *gpu, int32_t option, int32_t value);
 
 /* Command::wait / Gpu::complete (src/metal.rs:1224-1235): blocks until the

@@ -12,7 +12,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libingot_cuda.so")
 
 OK, INVALID, UNSUPPORTED, DEVICE, EOF, INTERRUPTED, TIMEOUT = range(7)
-OPT_PDL, OPT_FORCE_PLAIN, OPT_NO_MMA, OPT_TCGEN05_GEMV, OPT_EP_WORLD, OPT_GROUP_SCOPE = 1, 2, 3, 4, 5, 6
+OPT_PDL, OPT_FORCE_PLAIN, OPT_NO_MMA, OPT_TCGEN05_GEMV, OPT_EP_WORLD, OPT_GROUP_SCOPE, OPT_WIDE_ROWS = 1, 2, 3, 4, 5, 6, 7
 X_PACKED = 256
 X_DIGITS = 258
 X_PACKED_HI = 259

@@ -35,6 +35,7 @@ struct ingot_gpu {
     bool force_plain = false;
     bool no_mma = false;
     bool group_scope = true;
+    bool wide_rows = false;           // fused-norm rows with four digits even when rounding to bfloat16
     bool capturing = false;
     // independent-projection scope: launches rotate over the main stream and side streams
     static constexpr int SIDE_STREAMS = 3;
@@ -265,6 +266,7 @@ ingot_status ingot_gpu_set_option(ingot_gpu *g, int32_t option, int32_t value) {
     case INGOT_OPT_TCGEN05_GEMV: g->use_tc = value != 0; return INGOT_OK;
     case INGOT_OPT_EP_WORLD: g->ep_world = value > 1 ? (uint32_t)value : 1u; return INGOT_OK;
     case INGOT_OPT_GROUP_SCOPE: g->group_scope = value != 0; return INGOT_OK;
+    case INGOT_OPT_WIDE_ROWS: g->wide_rows = value != 0; return INGOT_OK;
     default: return fail(g, INGOT_INVALID, "unknown option");
     }
 }
@@ -667,7 +669,7 @@ static ingot_status normed_common(ingot_gpu *g, GemvCall &c, const float *a, con
     if (((uintptr_t)a % 16u) || (b && ((uintptr_t)b % 16u)) || (s && ((uintptr_t)s % 16u)) || (norm_w && ((uintptr_t)norm_w % 16u)))
         return fail(g, INGOT_INVALID, std::string(what) + ": vectors must be 16-byte aligned");
     c.norm_a = a; c.norm_b = add ? b : nullptr; c.norm_w = norm_w; c.norm_s = add ? s : nullptr;
-    c.norm_eps = eps; c.norm_round_bf16 = round_bf16;
+    c.norm_eps = eps; c.norm_round_bf16 = round_bf16; c.norm_wide = g->wide_rows ? 1u : 0u;
     c.count = 1;
     if ((st = apply_tp_links(g, c, a, add ? b : nullptr, what))) return st;
     if (g->chain_recording) {

@@ -1875,7 +1875,7 @@ static cudaError_t launch_mma_k(const MmaArgs &a, dim3 grid, cudaStream_t stream
 // The activation row form of a call: the CTAs build fixed-point rows themselves when they norm or
 // pack the activations; rows packed beforehand are binary16.
 static uint32_t x_mode_of(const GemvCall &c, bool pack_inside) {
-    if (c.norm_a) return c.norm_round_bf16 ? XM_FX2 : XM_FX4;
+    if (c.norm_a) return (c.norm_round_bf16 && !c.norm_wide) ? XM_FX2 : XM_FX4;
     if (pack_inside) return XM_FX4;
     return c.x_packed == 4u ? XM_F16_HI : XM_F16;
 }
@@ -2271,11 +2271,11 @@ cudaError_t chain_build(const GemvCall *calls, uint32_t n, const LaunchCtx &ctx,
     if (n == 0) { why = "no projections were recorded"; return cudaErrorInvalidValue; }
     std::vector<GemvCall> cs(calls, calls + n);
     const bool family1 = cs[0].kind == KIND_Q4_0 || cs[0].kind == KIND_Q8_0;
-    const uint32_t xm = cs[0].norm_round_bf16 ? XM_FX2 : XM_FX4;
+    const uint32_t xm = x_mode_of(cs[0], false);
     for (const GemvCall &c : cs) {
         if (!chain_call_eligible(c)) { why = "a recorded projection has no fused tensor-core form (type, alignment or shape)"; return cudaErrorNotSupported; }
         if ((c.kind == KIND_Q4_0 || c.kind == KIND_Q8_0) != family1) { why = "K-quant and legacy weight types cannot share one chain"; return cudaErrorNotSupported; }
-        if ((c.norm_round_bf16 ? XM_FX2 : XM_FX4) != xm) { why = "all projections of a chain round their activations the same way"; return cudaErrorNotSupported; }
+        if (x_mode_of(c, false) != xm) { why = "all projections of a chain round their activations the same way"; return cudaErrorNotSupported; }
     }
     // projections that read the same normalised input build it once: the first of the group takes the
     // group's residual-sum store

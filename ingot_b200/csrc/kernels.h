@@ -101,6 +101,7 @@ struct GemvCall {
     float *norm_s;
     float norm_eps;
     uint32_t norm_round_bf16;
+    uint32_t norm_wide;    // four-digit rows even when rounding to bfloat16
     TpLink tp;
 };
 cudaError_t launch_gemv(const GemvCall &c, const LaunchCtx &ctx);

@@ -845,3 +845,28 @@ def test_recorded_command_survives_growth_of_the_scratch(gpu):
         gpu._check(gpu._lib.ingot_buffer_zero(gpu._h, y.ptr, y.nbytes))
         graph.submit()
         assert np.array_equal(gpu.finish(None, y).view(np.uint32), first.view(np.uint32))
+
+
+def test_wide_rows_keep_the_neighbours_of_an_outlier(gpu):
+    """Two-digit fixed-point rows (the default when the norm rounds to bfloat16) give the 31 neighbours of an outlier
+    300 times their size about 7 bits; INGOT_OPT_WIDE_ROWS builds four-digit rows instead.  The CPU restatement
+    (tests/test_fixed_point_rows.py) puts the default at up to 1.7 times the reference's bound for this case."""
+    from oracle.chain_check import expect_projection
+    kind, cols, rows = Q4_K, 4096, 64
+    raw = synth.random_matrix(kind, cols, rows, seed=cols + rows)
+    a = synth.activations(1, cols, seed=2)
+    a[0, 7] *= 300.0
+    w, ab = gpu.bytes(raw), gpu.floats(a)
+    stride = synth.stride_of(kind, cols)
+    _, e, tol = expect_projection(raw, cols, rows, kind, a[0], None, True)
+    worst = {}
+    try:
+        for wide in (0, 1):
+            gpu.set_option(_abi.OPT_WIDE_ROWS, wide)
+            y = gpu.output(rows)
+            gpu._check(gpu._lib.ingot_matmul_normed(gpu._h, w.ptr, cols, rows, stride, kind, 0, ab.ptr, None, None, None, 1e-6, 0, 1, y.ptr))
+            worst[wide] = float((np.abs(gpu.finish(None, y) - e) / tol).max())
+    finally:
+        gpu.set_option(_abi.OPT_WIDE_ROWS, 0)
+    assert worst[1] <= 1.0, worst
+    assert worst[0] <= 2.0 and worst[1] < worst[0], worst
