@@ -67,14 +67,17 @@ __device__ __forceinline__ bool poll_tagged(const uint64_t *word, uint32_t tag, 
 
 // All rows of this CTA are stored.  The CTA counts itself on the own device (release at device scope); the
 // launch's last CTA releases at system scope and stores the tagged words: causality order carries every CTA's
-// stores through the counter to whoever acquires a word.
+// stores through the counter to whoever acquires a word.  The last CTA also sets the counter back to zero, so
+// launches of different grid sizes can follow each other (the next launch's CTAs count only after their
+// griddepcontrol.wait, when this launch is complete).
 template <class F>
 __device__ __forceinline__ void signal_when_last(uint32_t *launch_count, F store_words) {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
         const uint32_t before = atomicAdd(launch_count, 1u);
-        if ((before + 1u) % gridDim.x == 0u) {
+        if (before + 1u == gridDim.x) {
+            atomicExch(launch_count, 0u);
             __threadfence_system();
             store_words();
         }

@@ -143,3 +143,52 @@ def test_token_all_to_all_equals_the_single_device_layers(own_tokens, grouped):
         assert np.array_equal(g.read_bytes(c.ep.rx_meta).view(np.uint32)[:world * cap], region)
         assert np.array_equal(g.read_bytes(c.ids_rx).view(np.uint32), ids_rx)
     del chains
+
+
+@pytest.mark.skipif(_device_count() < 2, reason="needs two GPUs")
+@pytest.mark.xfail(strict=False, reason="written after this build's GPU time was spent: not yet run on two GPUs")
+def test_one_group_takes_steps_of_different_token_counts():
+    """Two MoE chains of different token counts on the SAME groups, one after the other: the exchange kernels' launches
+    then differ in grid size from step to step, and the last-CTA counter of a launch must start from zero each time."""
+    from ingot_b200 import Q4_K, Gpu
+    from ingot_b200.gpu import EpExchange, Group
+    from ingot_b200.moe import MoeChain, MoeShape
+    shape = MoeShape("test", 2, 512, 16, 4, 256, Q4_K)
+    world, layers = 2, 2
+    counts = (16, 2, 5)
+    rng = np.random.default_rng(8)
+    logits = rng.normal(0, 1, (world, max(counts), shape.experts)).astype(np.float32)
+    xs = (rng.normal(0, 1, (world, max(counts), shape.hidden)) * 0.05).astype(np.float32)
+
+    def load(c, r, n):
+        g = c.gpu
+        g._check(g._lib.ingot_buffer_upload(g._h, c.logits.ptr, np.ascontiguousarray(logits[r][:n]).ctypes.data, 4 * n * shape.experts))
+        g._check(g._lib.ingot_buffer_upload(g._h, c.x.ptr, np.ascontiguousarray(xs[r][:n]).ctypes.data, 4 * n * shape.hidden))
+        g.complete()
+
+    g0 = Gpu(0)
+    want = []
+    for r in range(world):                   # a token's result does not depend on the other tokens of its step
+        ref = MoeChain(g0, shape, tokens=max(counts), seed=3, layers=layers)
+        ref.grouped = False
+        load(ref, r, max(counts))
+        ref.step()
+        g0.complete()
+        want.append(g0.read_f32(ref.y).reshape(max(counts), shape.hidden).copy())
+        del ref
+    gpus = [g0, Gpu(1)]
+    window = sum(EpExchange.window_bytes(world, n * shape.top, shape.hidden) for n in counts)
+    groups = [Group(g, r, world, window, MoeChain.exchange_slots(layers)) for r, g in enumerate(gpus)]
+    Group.connect_local(groups)
+    for n in counts:
+        chains = [MoeChain(g, shape, tokens=n, seed=3, layers=layers, rank=r, world=world, group=groups[r]) for r, g in enumerate(gpus)]
+        for r, c in enumerate(chains):
+            load(c, r, n)
+        for c in chains:
+            c.step()
+        for r, (c, g) in enumerate(zip(chains, gpus)):
+            g.complete()
+            got = g.read_f32(c.y).reshape(n, shape.hidden)
+            assert np.array_equal(got.view(np.uint32), want[r][:n].view(np.uint32)), n
+        del chains
+
